@@ -1,0 +1,153 @@
+/* llsa_b200 -- C ABI of the B200 (sm_100a) implementation of the LLSA
+ * (log-linear sparse attention) hot path.
+ *
+ * Every entry point replaces one kernel group of the reference
+ * (SingleZombie/LLSA, all Triton/Python); the reference file:line each one
+ * stands in for is given beside it.  A Python caller binds these with ctypes
+ * (llsa_b200/_lib.py); any other host language binds them the same way.
+ *
+ * Rules that hold for every function:
+ *   - the caller owns all memory: inputs, outputs and scratch are device
+ *     pointers passed in; unless stated otherwise nothing is allocated or freed
+ *     here and no state is kept between calls;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) and the call returns without synchronising;
+ *   - the return value is 0 on success or a LLSA_ERR_* code; nothing throws.
+ *     llsa_last_error_string() describes the last failure on this thread;
+ *   - tensors are described by LlsaTensor: up to 4 dims, strides in ELEMENTS.
+ *     Attention tensors are [B,H,N,D] with stride[3]==1 and 16-byte aligned
+ *     rows; any batch/head/token strides are accepted (the model passes
+ *     [B,H,N,D] views of [B,N,H,D] storage).
+ */
+#ifndef LLSA_B200_H_
+#define LLSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum LlsaDtype { LLSA_F32 = 0, LLSA_BF16 = 1, LLSA_I32 = 2, LLSA_I64 = 3 };
+
+enum LlsaStatus {
+  LLSA_OK = 0,
+  LLSA_ERR_NULL = 1,        /* a required pointer is NULL                         */
+  LLSA_ERR_DTYPE = 2,       /* unsupported or mismatching element types           */
+  LLSA_ERR_SHAPE = 3,       /* shapes inconsistent or outside the supported set   */
+  LLSA_ERR_STRIDE = 4,      /* innermost stride != 1, or rows not 16-byte aligned */
+  LLSA_ERR_ARG = 5,         /* bad scalar argument (topk, block size, ...)        */
+  LLSA_ERR_WORKSPACE = 6,   /* scratch buffer missing or too small                */
+  LLSA_ERR_CUDA = 7,        /* a CUDA runtime call or kernel launch failed        */
+  LLSA_ERR_DEVICE_CHECK = 8 /* a kernel recorded an out-of-range index            */
+};
+
+typedef struct LlsaTensor {
+  void* ptr;
+  int32_t dtype; /* LlsaDtype */
+  int32_t ndim;
+  int64_t shape[4];
+  int64_t stride[4]; /* in elements */
+} LlsaTensor;
+
+int llsa_version(void);
+const char* llsa_last_error_string(void);
+
+/* ---- pooling: src/llsa/kernel/triton/mean_pool.py --------------------------
+ * y[b,h,s,:] = (sum_{t<k} x[b,h,s*k+t,:]) / k with the sum accumulated
+ * sequentially in x's dtype (mean_pool.py:26-30).  y is contiguous [B,H,S/k,C].
+ * Replaces mean_pool1d / MeanPool1dFunction_BHSC.forward (mean_pool.py:129-148). */
+int llsa_mean_pool_fwd(const LlsaTensor* x, const LlsaTensor* y, int k, void* stream);
+/* dx[b,h,s*k+t,:] = dy[b,h,s,:] / k.  Replaces MeanPool1dFunction_BHSC.backward
+ * (mean_pool.py:150-165). */
+int llsa_mean_pool_bwd(const LlsaTensor* dy, const LlsaTensor* dx, int k, void* stream);
+/* All pyramid levels of up to 3 tensors (q, k, v) in one pass over HBM:
+ * y1[i] = pool(x[i], bs) and, when y2 != NULL, y2[i] = pool(y1[i], bs).  Replaces
+ * the 3 (llsa_l1) or 6 (llsa_l2) mean_pool1d launches of
+ * torch_op/flash_sparse_attention_res_1.py:42-44 and ..._res_2.py:49-55. */
+int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2,
+                          int block_size, void* stream);
+
+/* ---- RoPE: src/llsa/kernel/triton/rope.py ---------------------------------
+ * Interleaved-pair rotation by a [S,D] table whose even columns are sin and odd
+ * columns cos (rope.py:28-50); y has x's shape, any strides.  Replaces
+ * MyRopeFunction.forward (rope.py:100-124) / .backward (rope.py:126-146). */
+int llsa_rope_fwd(const LlsaTensor* x, const LlsaTensor* freq, const LlsaTensor* y, void* stream);
+int llsa_rope_bwd(const LlsaTensor* dy, const LlsaTensor* freq, const LlsaTensor* dx, void* stream);
+
+/* ---- selection: src/llsa/kernel/triton/topk.py ----------------------------
+ * Coarse: idx[b,h,i,:] = top-`topk` columns of round_dtype(pq[b,h,i,:] . pk[b,h,:,:]^T),
+ * descending, ties -> smallest index.  idx is I32 or I64 [B,H,M,topk].  Replaces
+ * gen_sparse_indices (topk.py:6-9: torch.matmul + torch.topk). */
+int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, const LlsaTensor* idx, int topk, void* stream);
+/* Refine: for level-1 query block i with parent P = i / bs the candidates are
+ * the children p*bs .. p*bs+bs-1 of p in p_idx[b,h,P,:]; fp32 scores, top-`topk`,
+ * descending, ties -> smallest block index.  Replaces compute_topk_indices_sparse
+ * + _topk_indices_lastdim_k8_kernel (topk.py:102-197). */
+int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTensor* p_idx, const LlsaTensor* idx,
+                     int topk, int p_topk, int block_size, void* stream);
+
+/* ---- index transpose: src/llsa/kernel/triton/indices_transpose.py ---------
+ * Query-major lists idx [B,H,M,T] (I32/I64, values in [0,n_kv)) -> KV-major CSR:
+ * offsets [B,H,n_kv+1] (I32 or I64) and flat [B,H,M*T] (I32), each bucket in
+ * ascending query order (a stable counting sort without atomics).  `scratch`
+ * is llsa_transpose_scratch_bytes() bytes of device memory (may be NULL when
+ * that returns 0); `status` is one int32 on the device, set non-zero if an
+ * index is out of range (may be NULL).  Replaces transpose_indices =
+ * _count_k_major + torch.cumsum + _k_major_indices (indices_transpose.py:6-109). */
+size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t T, int64_t n_kv);
+int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
+                           void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+
+/* ---- attention ------------------------------------------------------------ */
+typedef struct LlsaAttnArgs {
+  /* forward operands */
+  const LlsaTensor* q;   /* [B,H,N,D] */
+  const LlsaTensor* k;
+  const LlsaTensor* v;
+  const LlsaTensor* pk;  /* [B,H,N/bs,D] contiguous rows */
+  const LlsaTensor* pv;
+  const LlsaTensor* pk2; /* [B,H,N/bs^2,D]; NULL selects the one-level form   */
+  const LlsaTensor* pv2;
+  const LlsaTensor* indices;   /* I32/I64 [B,H,N/bs,topk]                      */
+  const LlsaTensor* p_indices; /* I32/I64 [B,H,N/bs^2,topk_p]; NULL for one level */
+  const LlsaTensor* o;   /* out (fwd) / in (bwd): q's shape, any strides       */
+  const LlsaTensor* lse; /* F32 [B,H,N] contiguous: out (fwd) / in (bwd)       */
+  int32_t topk, topk_p, block_size;
+  float token_weight, token_weight_2;
+  /* backward only */
+  const LlsaTensor* d_o;       /* upstream gradient, any strides               */
+  const LlsaTensor* dq;        /* outputs, dtype of q                          */
+  const LlsaTensor* dk;
+  const LlsaTensor* dv;
+  const LlsaTensor* offsets;   /* CSR of `indices`   (llsa_transpose_indices)  */
+  const LlsaTensor* flat;
+  const LlsaTensor* delta;     /* F32 [B,H,N] scratch                           */
+  const LlsaTensor* dpk_acc;   /* F32 [B,H,N/bs,D] scratch+output: gradient of pk */
+  const LlsaTensor* dpv_acc;
+  const LlsaTensor* dpk2_acc;  /* F32 [B,H,N/bs^2,D]; NULL for one level        */
+  const LlsaTensor* dpv2_acc;
+  int32_t fold_pool_bwd;       /* 1: dk,dv include the pooling backward of the pooled-key
+                                  gradients (what k.grad holds after llsa_l1/llsa_l2);
+                                  0: dk,dv are the fine-token terms only         */
+  float kv_weight, kv_weight_2;/* weights on the pooled dK/dV side; the reference's
+                                  one-level backward uses 1 here (sparse_attention_res_1.py:389) */
+  int32_t force_generic;       /* 1: use the plain FFMA kernels for any dtype   */
+} LlsaAttnArgs;
+
+/* Forward: o, lse.  One level (pk2 == NULL) replaces sparse_indices_attn_res_fwd
+ * (sparse_attention_res_1.py:9-150); two levels replaces
+ * sparse_indices_attn_res_2_2_fwd (sparse_attention_res_2.py:9-199). */
+int llsa_attn_fwd(const LlsaAttnArgs* args, void* stream);
+/* Backward: dq, dk, dv (+ pooled-key gradients in the *_acc tensors, which this
+ * call zero-fills first).  Replaces sparse_indices_attn_res_scatter_bwd_v2
+ * (sparse_attention_res_1.py:403-471) / ..._scatter_2_2_bwd_v2
+ * (sparse_attention_res_2.py:578-681) and, with fold_pool_bwd, the
+ * MeanPool1dFunction_BHSC.backward calls autograd runs after them. */
+int llsa_attn_bwd(const LlsaAttnArgs* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLSA_B200_H_ */

@@ -1,0 +1,268 @@
+// Mean pooling along the token axis (reference: src/llsa/kernel/triton/mean_pool.py).
+//
+// Arithmetic contract (mean_pool.py:26-30): the k rows are added one after the
+// other into an accumulator of the INPUT element type, then divided by k, so a
+// bf16 tensor is rounded to bf16 after every add.  The kernels below keep the
+// accumulator in fp32 registers but round it to T after each add, which gives
+// the same bits.
+//
+// pool_pyramid_kernel writes every pyramid level of q, k and v in one pass over
+// HBM: one CTA owns one level-2 row (bs level-1 rows x bs tokens), each thread
+// a 16-byte channel group of one level-1 row; the bs loads of a thread are
+// independent 128-bit loads, the level-2 row is reduced through shared memory.
+#include "common.cuh"
+
+namespace llsa {
+
+template <typename T>
+struct Vec16;  // 16 bytes of T
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    float4 x = __ldg(reinterpret_cast<const float4*>(p));
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 x = ldg128(p);
+    v[0] = bf16_lo(x.x); v[1] = bf16_hi(x.x); v[2] = bf16_lo(x.y); v[3] = bf16_hi(x.y);
+    v[4] = bf16_lo(x.z); v[5] = bf16_hi(x.z); v[6] = bf16_lo(x.w); v[7] = bf16_hi(x.w);
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 x;
+    x.x = pack_bf16(v[0], v[1]); x.y = pack_bf16(v[2], v[3]); x.z = pack_bf16(v[4], v[5]); x.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = x;
+  }
+};
+
+template <typename T>
+struct PyramidArgs {
+  View<const T> x[3];
+  T* y1[3];  // contiguous [B,H,n1,C]
+  T* y2[3];  // contiguous [B,H,n2,C] or nullptr
+  int H, C;
+  int64_t n1;  // level-1 rows per (b,h)
+  int bs;
+};
+
+// blockDim.x = ROWS * (C / VEC); ROWS level-1 rows per CTA (== bs when LEVELS == 2).
+template <typename T, int LEVELS>
+__global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t ctas_per_head) {
+  constexpr int VEC = Vec16<T>::N;
+  extern __shared__ float smem[];  // LEVELS==2: [rows][C] level-1 results as fp32 images of T
+  const int ti = blockIdx.y;
+  const int64_t bh = blockIdx.x / ctas_per_head;
+  const int64_t grp = blockIdx.x % ctas_per_head;
+  const int b = (int) (bh / a.H), h = (int) (bh % a.H);
+  const int lanes = a.C / VEC;
+  const int r = threadIdx.x / lanes, c = (threadIdx.x % lanes) * VEC;
+  const int64_t row1 = grp * rows_per_cta + r;  // level-1 row inside (b,h)
+  if (row1 < a.n1) {
+    const T* xp = a.x[ti].row(b, h, row1 * a.bs) + c;
+    const int64_t sn = a.x[ti].sn;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    int t = 0;
+    // 8 independent 128-bit loads in flight per thread, consumed in order
+    for (; t + 8 <= a.bs; t += 8) {
+      float v[8][VEC];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) Vec16<T>::load(xp + (int64_t) (t + u) * sn, v[u]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = round_to<T>(acc[i] + v[u][i]);
+    }
+    for (; t < a.bs; ++t) {
+      float v[VEC];
+      Vec16<T>::load(xp + (int64_t) t * sn, v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = round_to<T>(acc[i] + v[i]);
+    }
+    const float kf = (float) a.bs;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = round_to<T>(__fdiv_rn(acc[i], kf));
+    Vec16<T>::store(a.y1[ti] + (bh * a.n1 + row1) * a.C + c, acc);
+    if (LEVELS == 2) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) smem[r * a.C + c + i] = acc[i];
+    }
+  }
+  if (LEVELS == 2) {
+    __syncthreads();
+    // rows_per_cta == bs: the CTA holds exactly the bs level-1 rows of one level-2 row
+    for (int ch = threadIdx.x; ch < a.C; ch += blockDim.x) {
+      float acc2 = 0.f;
+      for (int rr = 0; rr < a.bs; ++rr) acc2 = round_to<T>(acc2 + smem[rr * a.C + ch]);
+      acc2 = round_to<T>(__fdiv_rn(acc2, (float) a.bs));
+      a.y2[ti][(bh * ctas_per_head + grp) * a.C + ch] = from_f32<T>(acc2);
+    }
+  }
+}
+
+// One output row chunk per thread, any k; VEC = 1 handles channel counts that are not a multiple of 16 bytes.
+template <typename T, int VEC>
+__global__ void mean_pool_fwd_kernel(View<const T> x, T* y, int H, int C, int64_t S_out, int k, int64_t total) {
+  const int lanes = C / VEC;
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
+    const int c = (int) (i % lanes) * VEC;
+    const int64_t row = i / lanes;
+    const int64_t s = row % S_out, bh = row / S_out;
+    const T* xp = x.row(bh / H, bh % H, s * k) + c;
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    for (int t = 0; t < k; ++t) {
+      float v[VEC];
+      if constexpr (VEC == 1) v[0] = to_f32<T>(xp[(int64_t) t * x.sn]);
+      else Vec16<T>::load(xp + (int64_t) t * x.sn, v);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] = round_to<T>(acc[j] + v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) y[row * C + c + j] = from_f32<T>(__fdiv_rn(acc[j], (float) k));
+  }
+}
+
+// dx[s*k + t] = dy[s] / k  (mean_pool.py:54-58)
+template <typename T>
+__global__ void mean_pool_bwd_kernel(View<const T> dy, View<T> dx, int H, int C, int64_t S_out, int k, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < total; i += (int64_t) gridDim.x * blockDim.x) {
+    const int c = (int) (i % C);
+    const int64_t row = i / C;  // output row in [0, B*H*S_out*k)
+    const int64_t sx = row % (S_out * k), bh = row / (S_out * k);
+    const float g = to_f32<T>(dy.row(bh / H, bh % H, sx / k)[c]);
+    dx.row(bh / H, bh % H, sx)[c] = from_f32<T>(__fdiv_rn(g, (float) k));
+  }
+}
+
+static int grid_for(int64_t total, int block) {
+  int64_t g = (total + block - 1) / block;
+  const int64_t cap = 148 * 32;
+  return (int) (g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+template <typename T>
+static int launch_pool_fwd(const LlsaTensor* x, const LlsaTensor* y, int k, cudaStream_t st) {
+  const int64_t B = x->shape[0], H = x->shape[1], S = x->shape[2], C = x->shape[3];
+  const int64_t S_out = S / k;
+  constexpr int VEC = Vec16<T>::N;
+  const bool vec_ok = (C % VEC == 0) && ((uintptr_t) x->ptr % 16 == 0) && (x->stride[0] % VEC == 0) &&
+                      (x->stride[1] % VEC == 0) && (x->stride[2] % VEC == 0);
+  View<const T> xv = make_view<const T>(x);
+  if (vec_ok) {
+    const int64_t total = B * H * S_out * (C / VEC);
+    mean_pool_fwd_kernel<T, VEC><<<grid_for(total, 256), 256, 0, st>>>(xv, (T*) y->ptr, (int) H, (int) C, S_out, k, total);
+  } else {
+    const int64_t total = B * H * S_out * C;
+    mean_pool_fwd_kernel<T, 1><<<grid_for(total, 256), 256, 0, st>>>(xv, (T*) y->ptr, (int) H, (int) C, S_out, k, total);
+  }
+  LLSA_LAUNCH_OK("mean_pool_fwd_kernel");
+  return LLSA_OK;
+}
+
+}  // namespace llsa
+
+using namespace llsa;
+
+extern "C" int llsa_mean_pool_fwd(const LlsaTensor* x, const LlsaTensor* y, int k, void* stream) {
+  LLSA_REQUIRE(x && y && x->ptr && y->ptr, LLSA_ERR_NULL, "mean_pool_fwd: null tensor");
+  LLSA_REQUIRE(x->ndim == 4 && y->ndim == 4, LLSA_ERR_SHAPE, "mean_pool_fwd: tensors must be [B,H,S,C]");
+  LLSA_REQUIRE(is_float_dtype(x->dtype) && x->dtype == y->dtype, LLSA_ERR_DTYPE, "mean_pool_fwd: dtype must be f32 or bf16 and equal");
+  LLSA_REQUIRE(k >= 1 && x->shape[2] % k == 0, LLSA_ERR_ARG, "mean_pool_fwd: S=%lld not divisible by k=%d", (long long) x->shape[2], k);
+  LLSA_REQUIRE(x->stride[3] == 1 || x->shape[3] == 1, LLSA_ERR_STRIDE, "mean_pool_fwd: innermost stride must be 1");
+  const int64_t shp[4] = {x->shape[0], x->shape[1], x->shape[2] / k, x->shape[3]};
+  int rc = check_contig(y, "y", x->dtype, 4, shp);
+  if (rc) return rc;
+  if (x->shape[0] * x->shape[1] * x->shape[2] * x->shape[3] == 0) return LLSA_OK;
+  cudaStream_t st = (cudaStream_t) stream;
+  return x->dtype == LLSA_F32 ? launch_pool_fwd<float>(x, y, k, st) : launch_pool_fwd<__nv_bfloat16>(x, y, k, st);
+}
+
+extern "C" int llsa_mean_pool_bwd(const LlsaTensor* dy, const LlsaTensor* dx, int k, void* stream) {
+  LLSA_REQUIRE(dy && dx && dy->ptr && dx->ptr, LLSA_ERR_NULL, "mean_pool_bwd: null tensor");
+  LLSA_REQUIRE(dy->ndim == 4 && dx->ndim == 4, LLSA_ERR_SHAPE, "mean_pool_bwd: tensors must be [B,H,S,C]");
+  LLSA_REQUIRE(is_float_dtype(dy->dtype) && dx->dtype == dy->dtype, LLSA_ERR_DTYPE, "mean_pool_bwd: dtype must be f32 or bf16 and equal");
+  LLSA_REQUIRE(k >= 1 && dx->shape[0] == dy->shape[0] && dx->shape[1] == dy->shape[1] && dx->shape[2] == dy->shape[2] * k &&
+                   dx->shape[3] == dy->shape[3], LLSA_ERR_SHAPE, "mean_pool_bwd: dx must be [B,H,S*k,C]");
+  LLSA_REQUIRE((dy->stride[3] == 1 || dy->shape[3] == 1) && (dx->stride[3] == 1 || dx->shape[3] == 1), LLSA_ERR_STRIDE,
+               "mean_pool_bwd: innermost stride must be 1");
+  const int64_t total = dx->shape[0] * dx->shape[1] * dx->shape[2] * dx->shape[3];
+  if (total == 0) return LLSA_OK;
+  cudaStream_t st = (cudaStream_t) stream;
+  if (dy->dtype == LLSA_F32)
+    mean_pool_bwd_kernel<float><<<grid_for(total, 256), 256, 0, st>>>(make_view<const float>(dy), make_view<float>(dx),
+                                                                      (int) dx->shape[1], (int) dx->shape[3], dy->shape[2], k, total);
+  else
+    mean_pool_bwd_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>(
+        make_view<const __nv_bfloat16>(dy), make_view<__nv_bfloat16>(dx), (int) dx->shape[1], (int) dx->shape[3], dy->shape[2], k, total);
+  LLSA_LAUNCH_OK("mean_pool_bwd_kernel");
+  return LLSA_OK;
+}
+
+template <typename T>
+static int launch_pyramid(int n, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2, int bs, cudaStream_t st) {
+  constexpr int VEC = Vec16<T>::N;
+  PyramidArgs<T> a;
+  const int64_t B = x[0].shape[0], H = x[0].shape[1], N = x[0].shape[2], C = x[0].shape[3];
+  for (int i = 0; i < 3; ++i) {
+    const int j = i < n ? i : 0;
+    a.x[i] = make_view<const T>(&x[j]);
+    a.y1[i] = (T*) y1[j].ptr;
+    a.y2[i] = y2 ? (T*) y2[j].ptr : nullptr;
+  }
+  a.H = (int) H; a.C = (int) C; a.n1 = N / bs; a.bs = bs;
+  const int lanes = (int) (C / VEC);
+  if (y2) {
+    const int64_t n2 = a.n1 / bs;
+    dim3 grid((unsigned) (B * H * n2), n);
+    pool_pyramid_kernel<T, 2><<<grid, bs * lanes, bs * C * sizeof(float), st>>>(a, bs, n2);
+  } else {
+    const int rows = 16;
+    const int64_t per_head = (a.n1 + rows - 1) / rows;
+    dim3 grid((unsigned) (B * H * per_head), n);
+    pool_pyramid_kernel<T, 1><<<grid, rows * lanes, 0, st>>>(a, rows, per_head);
+  }
+  LLSA_LAUNCH_OK("pool_pyramid_kernel");
+  return LLSA_OK;
+}
+
+extern "C" int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2,
+                                     int block_size, void* stream) {
+  LLSA_REQUIRE(x && y1, LLSA_ERR_NULL, "pool_pyramid: null tensor list");
+  LLSA_REQUIRE(n_tensors >= 1 && n_tensors <= 3, LLSA_ERR_ARG, "pool_pyramid: n_tensors must be 1..3");
+  const int bs = block_size;
+  LLSA_REQUIRE(bs >= 1, LLSA_ERR_ARG, "pool_pyramid: bad block size");
+  const int dt = x[0].dtype;
+  LLSA_REQUIRE(is_float_dtype(dt), LLSA_ERR_DTYPE, "pool_pyramid: dtype must be f32 or bf16");
+  const int64_t B = x[0].shape[0], H = x[0].shape[1], N = x[0].shape[2], C = x[0].shape[3];
+  const int vec = dt == LLSA_F32 ? 4 : 8;
+  LLSA_REQUIRE(C % vec == 0 && (int64_t) bs * (C / vec) <= 1024 && 16 * (C / vec) <= 1024, LLSA_ERR_SHAPE,
+               "pool_pyramid: channels=%lld unsupported", (long long) C);
+  LLSA_REQUIRE(N % bs == 0 && (!y2 || N % ((int64_t) bs * bs) == 0), LLSA_ERR_SHAPE,
+               "pool_pyramid: N=%lld not divisible by the pooling factor", (long long) N);
+  for (int i = 0; i < n_tensors; ++i) {
+    int rc = check_bhnd(&x[i], "x", dt, B, H, N, C);
+    if (rc) return rc;
+    const int64_t s1[4] = {B, H, N / bs, C};
+    rc = check_contig(&y1[i], "y1", dt, 4, s1);
+    if (rc) return rc;
+    if (y2) {
+      const int64_t s2[4] = {B, H, N / bs / bs, C};
+      rc = check_contig(&y2[i], "y2", dt, 4, s2);
+      if (rc) return rc;
+    }
+  }
+  if (B * H * N * C == 0) return LLSA_OK;
+  cudaStream_t st = (cudaStream_t) stream;
+  return dt == LLSA_F32 ? launch_pyramid<float>(n_tensors, x, y1, y2, bs, st)
+                        : launch_pyramid<__nv_bfloat16>(n_tensors, x, y1, y2, bs, st);
+}

@@ -1,0 +1,250 @@
+// Coarse-to-fine top-k block selection (reference: src/llsa/kernel/triton/topk.py).
+//
+// coarse_topk_kernel  = gen_sparse_indices (topk.py:6-9): scores pq.pk^T rounded to
+//   the input dtype (torch.matmul writes its result in the input dtype), then the
+//   top-k columns per row, descending.  The score matrix never leaves the SM: a CTA
+//   owns ROWS query rows, streams the keys in chunks through shared memory and
+//   carries the running top-k list from chunk to chunk.
+// refine_topk_kernel  = compute_topk_indices_sparse (topk.py:102-197): one CTA per
+//   level-2 query block scores its bs query rows against the bs*p_topk children of
+//   the selected parents in fp32 (not rounded, topk.py:141-143).
+// Both pick winners by repeated arg-max with ties going to the smallest index, the
+// rule the reference's own kernels use (topk.py:60-62, :159-161).
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace llsa {
+
+constexpr int kMaxTopk = 64;
+
+struct Cand {
+  float v;
+  int64_t i;
+};
+
+__device__ __forceinline__ bool better(float v2, int64_t i2, float v, int64_t i) { return v2 > v || (v2 == v && i2 < i); }
+
+__device__ __forceinline__ Cand warp_argmax(Cand c) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v2 = __shfl_xor_sync(0xffffffffu, c.v, o);
+    const int64_t i2 = __shfl_xor_sync(0xffffffffu, c.i, o);
+    if (better(v2, i2, c.v, c.i)) { c.v = v2; c.i = i2; }
+  }
+  return c;
+}
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int D) {
+  float acc = 0.f;
+  if constexpr (sizeof(T) == 2) {
+    for (int d = 0; d < D; d += 8) {
+      uint4 x = ldg128(k + d);
+      acc = fmaf(q[d], bf16_lo(x.x), acc); acc = fmaf(q[d + 1], bf16_hi(x.x), acc);
+      acc = fmaf(q[d + 2], bf16_lo(x.y), acc); acc = fmaf(q[d + 3], bf16_hi(x.y), acc);
+      acc = fmaf(q[d + 4], bf16_lo(x.z), acc); acc = fmaf(q[d + 5], bf16_hi(x.z), acc);
+      acc = fmaf(q[d + 6], bf16_lo(x.w), acc); acc = fmaf(q[d + 7], bf16_hi(x.w), acc);
+    }
+  } else {
+    for (int d = 0; d < D; d += 4) {
+      float4 x = __ldg(reinterpret_cast<const float4*>(k + d));
+      acc = fmaf(q[d], x.x, acc); acc = fmaf(q[d + 1], x.y, acc); acc = fmaf(q[d + 2], x.z, acc); acc = fmaf(q[d + 3], x.w, acc);
+    }
+  }
+  return acc;
+}
+
+constexpr int kCoarseRows = 8;
+constexpr int kCoarseChunk = 1024;
+constexpr int kCoarseThreads = 128;
+
+// pq, pk: contiguous [B*H, M|n, D].  idx out: [B*H, M, topk] int32 or int64.
+template <typename T>
+__global__ void __launch_bounds__(kCoarseThreads)
+coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __restrict__ idx_out, int idx64, int64_t M, int64_t n, int D,
+                   int topk) {
+  extern __shared__ float sm[];
+  float* qs = sm;                                   // [ROWS][D]
+  float* sc = qs + kCoarseRows * D;                 // [ROWS][CHUNK]
+  float* cv = sc + kCoarseRows * kCoarseChunk;      // [ROWS][kMaxTopk] carried values
+  int64_t* ci = reinterpret_cast<int64_t*>(cv + kCoarseRows * kMaxTopk);  // carried indices
+  float* nv = reinterpret_cast<float*>(ci + kCoarseRows * kMaxTopk);      // [ROWS][kMaxTopk] next list
+  int64_t* ni = reinterpret_cast<int64_t*>(nv + kCoarseRows * kMaxTopk);
+
+  const int64_t bh = blockIdx.y;
+  const int64_t row0 = (int64_t) blockIdx.x * kCoarseRows;
+  const int nrows = (int) min((int64_t) kCoarseRows, M - row0);
+  const T* q0 = pq + (bh * M + row0) * D;
+  const T* k0 = pk + bh * n * D;
+  for (int i = threadIdx.x; i < kCoarseRows * D; i += blockDim.x) qs[i] = (i / D) < nrows ? to_f32<T>(q0[i]) : 0.f;
+  for (int i = threadIdx.x; i < kCoarseRows * kMaxTopk; i += blockDim.x) { cv[i] = -CUDART_INF_F; ci[i] = INT64_MAX; }
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int64_t base = 0; base < n; base += kCoarseChunk) {
+    const int cn = (int) min((int64_t) kCoarseChunk, n - base);
+    for (int j = threadIdx.x; j < cn; j += blockDim.x) {
+      const T* kr = k0 + (base + j) * D;
+#pragma unroll
+      for (int r = 0; r < kCoarseRows; ++r) sc[r * kCoarseChunk + j] = round_to<T>(dot_row<T>(qs + r * D, kr, D));
+    }
+    __syncthreads();
+    for (int r = warp; r < nrows; r += nwarps) {
+      float* s = sc + r * kCoarseChunk;
+      for (int t = 0; t < topk; ++t) {
+        Cand best{-CUDART_INF_F, INT64_MAX};
+        for (int j = lane; j < cn; j += 32) {
+          const float v = s[j];
+          if (better(v, base + j, best.v, best.i)) { best.v = v; best.i = base + j; }
+        }
+        if (lane < topk) {
+          const float v = cv[r * kMaxTopk + lane];
+          const int64_t i = ci[r * kMaxTopk + lane];
+          if (better(v, i, best.v, best.i)) { best.v = v; best.i = i; }
+        }
+        if (topk > 32 && lane + 32 < topk) {
+          const float v = cv[r * kMaxTopk + lane + 32];
+          const int64_t i = ci[r * kMaxTopk + lane + 32];
+          if (better(v, i, best.v, best.i)) { best.v = v; best.i = i; }
+        }
+        best = warp_argmax(best);
+        if (lane == 0) { nv[r * kMaxTopk + t] = best.v; ni[r * kMaxTopk + t] = best.i; }
+        // retire the winner from whichever set holds it
+        if (best.i >= base && best.i < base + cn) {
+          if (lane == 0) s[best.i - base] = -CUDART_INF_F;
+        } else {
+          for (int u = lane; u < topk; u += 32)
+            if (ci[r * kMaxTopk + u] == best.i) cv[r * kMaxTopk + u] = -CUDART_INF_F;
+        }
+        __syncwarp();
+      }
+      for (int u = lane; u < topk; u += 32) { cv[r * kMaxTopk + u] = nv[r * kMaxTopk + u]; ci[r * kMaxTopk + u] = ni[r * kMaxTopk + u]; }
+      __syncwarp();
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < nrows * topk; i += blockDim.x) {
+    const int r = i / topk, t = i % topk;
+    const int64_t o = (bh * M + row0 + r) * topk + t;
+    const int64_t v = ci[r * kMaxTopk + t];
+    if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = v;
+    else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) v;
+  }
+}
+
+// pq1, pk1: contiguous [B*H, M, D]; p_idx [B*H, M/bs, p_topk]; out [B*H, M, topk].
+template <typename T>
+__global__ void __launch_bounds__(128)
+refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
+                   int D, int topk, int p_topk, int bs) {
+  extern __shared__ float sm[];
+  const int C = p_topk * bs;
+  float* qs = sm;                 // [bs][D]
+  float* sc = qs + bs * D;        // [bs][C]
+  int* cand = reinterpret_cast<int*>(sc + bs * C);  // [C] block index of each candidate
+  const int64_t bh = blockIdx.y, P = blockIdx.x, n2 = M / bs;
+  const T* q0 = pq1 + (bh * M + P * bs) * D;
+  const T* k0 = pk1 + bh * M * D;
+  for (int i = threadIdx.x; i < bs * D; i += blockDim.x) qs[i] = to_f32<T>(q0[i]);
+  for (int j = threadIdx.x; j < C; j += blockDim.x) {
+    int64_t p = p_idx.at((bh * n2 + P) * p_topk + j / bs);
+    p = p < 0 ? 0 : (p >= n2 ? n2 - 1 : p);      // never read outside the tensor
+    cand[j] = (int) (p * bs + j % bs);
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < C; j += blockDim.x) {
+    const T* kr = k0 + (int64_t) cand[j] * D;
+    for (int r = 0; r < bs; ++r) sc[r * C + j] = dot_row<T>(qs + r * D, kr, D);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int r = warp; r < bs; r += nwarps) {
+    float* s = sc + r * C;
+    for (int t = 0; t < topk; ++t) {
+      Cand best{-CUDART_INF_F, INT64_MAX};
+      int bj = -1;
+      for (int j = lane; j < C; j += 32) {
+        const float v = s[j];
+        if (better(v, cand[j], best.v, best.i)) { best.v = v; best.i = cand[j]; bj = j; }
+      }
+      const Cand w = warp_argmax(best);
+      if (bj >= 0 && w.i == best.i && w.v == best.v) s[bj] = -CUDART_INF_F;  // candidates are distinct blocks: one owner
+      if (lane == 0) {
+        const int64_t o = (bh * M + P * bs + r) * topk + t;
+        if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = w.i;
+        else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) w.i;
+      }
+      __syncwarp();
+    }
+  }
+}
+
+}  // namespace llsa
+
+using namespace llsa;
+
+extern "C" int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, const LlsaTensor* idx, int topk, void* stream) {
+  LLSA_REQUIRE(pq && pk && idx && pq->ptr && pk->ptr && idx->ptr, LLSA_ERR_NULL, "coarse_topk: null tensor");
+  LLSA_REQUIRE(pq->ndim == 4 && pk->ndim == 4, LLSA_ERR_SHAPE, "coarse_topk: pq, pk must be [B,H,M,D]");
+  const int64_t B = pq->shape[0], H = pq->shape[1], M = pq->shape[2], D = pq->shape[3], n = pk->shape[2];
+  LLSA_REQUIRE(is_float_dtype(pq->dtype) && pk->dtype == pq->dtype, LLSA_ERR_DTYPE, "coarse_topk: pq/pk must both be f32 or bf16");
+  LLSA_REQUIRE(is_index_dtype(idx->dtype), LLSA_ERR_DTYPE, "coarse_topk: idx must be i32 or i64");
+  LLSA_REQUIRE(topk >= 1 && topk <= kMaxTopk && topk <= n, LLSA_ERR_ARG, "coarse_topk: topk=%d must be in 1..min(%d, n=%lld)", topk, kMaxTopk, (long long) n);
+  LLSA_REQUIRE(D % 8 == 0 && D <= 512, LLSA_ERR_SHAPE, "coarse_topk: D=%lld must be a multiple of 8, at most 512", (long long) D);
+  const int64_t sq[4] = {B, H, M, D}, sk[4] = {B, H, n, D}, si[4] = {B, H, M, topk};
+  int rc;
+  if ((rc = check_contig(pq, "pq", pq->dtype, 4, sq))) return rc;
+  if ((rc = check_contig(pk, "pk", pq->dtype, 4, sk))) return rc;
+  if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
+  if (B * H * M == 0) return LLSA_OK;
+  const size_t smem = (size_t) kCoarseRows * (D + kCoarseChunk) * 4 + (size_t) kCoarseRows * kMaxTopk * (4 + 8) * 2;
+  dim3 grid((unsigned) ((M + kCoarseRows - 1) / kCoarseRows), (unsigned) (B * H));
+  cudaStream_t st = (cudaStream_t) stream;
+  if (pq->dtype == LLSA_F32) {
+    LLSA_CUDA_OK(cudaFuncSetAttribute(coarse_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    coarse_topk_kernel<float><<<grid, kCoarseThreads, smem, st>>>((const float*) pq->ptr, (const float*) pk->ptr, idx->ptr,
+                                                                   idx->dtype == LLSA_I64, M, n, (int) D, topk);
+  } else {
+    LLSA_CUDA_OK(cudaFuncSetAttribute(coarse_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    coarse_topk_kernel<__nv_bfloat16><<<grid, kCoarseThreads, smem, st>>>((const __nv_bfloat16*) pq->ptr, (const __nv_bfloat16*) pk->ptr,
+                                                                           idx->ptr, idx->dtype == LLSA_I64, M, n, (int) D, topk);
+  }
+  LLSA_LAUNCH_OK("coarse_topk_kernel");
+  return LLSA_OK;
+}
+
+extern "C" int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTensor* p_idx, const LlsaTensor* idx, int topk,
+                                int p_topk, int block_size, void* stream) {
+  LLSA_REQUIRE(pq1 && pk1 && p_idx && idx && pq1->ptr && pk1->ptr && p_idx->ptr && idx->ptr, LLSA_ERR_NULL, "refine_topk: null tensor");
+  LLSA_REQUIRE(pq1->ndim == 4, LLSA_ERR_SHAPE, "refine_topk: pq1 must be [B,H,M,D]");
+  const int64_t B = pq1->shape[0], H = pq1->shape[1], M = pq1->shape[2], D = pq1->shape[3];
+  const int bs = block_size;
+  LLSA_REQUIRE(is_float_dtype(pq1->dtype) && pk1->dtype == pq1->dtype, LLSA_ERR_DTYPE, "refine_topk: pq1/pk1 must both be f32 or bf16");
+  LLSA_REQUIRE(is_index_dtype(idx->dtype) && is_index_dtype(p_idx->dtype), LLSA_ERR_DTYPE, "refine_topk: index tensors must be i32 or i64");
+  LLSA_REQUIRE(bs >= 1 && M % bs == 0, LLSA_ERR_ARG, "refine_topk: M=%lld not divisible by block size %d", (long long) M, bs);
+  LLSA_REQUIRE(p_topk >= 1 && topk >= 1 && topk <= p_topk * bs && p_topk <= M / bs, LLSA_ERR_ARG, "refine_topk: bad topk=%d / p_topk=%d", topk, p_topk);
+  LLSA_REQUIRE(D % 8 == 0, LLSA_ERR_SHAPE, "refine_topk: D=%lld must be a multiple of 8", (long long) D);
+  const size_t smem = ((size_t) bs * D + (size_t) bs * p_topk * bs + (size_t) p_topk * bs) * 4;
+  LLSA_REQUIRE(smem <= 200 * 1024, LLSA_ERR_ARG, "refine_topk: bs*p_topk too large");
+  const int64_t sq[4] = {B, H, M, D}, sp[4] = {B, H, M / bs, p_topk}, si[4] = {B, H, M, topk};
+  int rc;
+  if ((rc = check_contig(pq1, "pq1", pq1->dtype, 4, sq))) return rc;
+  if ((rc = check_contig(pk1, "pk1", pq1->dtype, 4, sq))) return rc;
+  if ((rc = check_contig(p_idx, "p_idx", p_idx->dtype, 4, sp))) return rc;
+  if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
+  if (B * H * M == 0) return LLSA_OK;
+  dim3 grid((unsigned) (M / bs), (unsigned) (B * H));
+  cudaStream_t st = (cudaStream_t) stream;
+  if (pq1->dtype == LLSA_F32) {
+    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    refine_topk_kernel<float><<<grid, 128, smem, st>>>((const float*) pq1->ptr, (const float*) pk1->ptr, make_idx(p_idx), idx->ptr,
+                                                       idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+  } else {
+    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    refine_topk_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
+                                                               make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+  }
+  LLSA_LAUNCH_OK("refine_topk_kernel");
+  return LLSA_OK;
+}

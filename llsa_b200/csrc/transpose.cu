@@ -1,0 +1,214 @@
+// KV-block -> query-block index transpose used by the backward pass
+// (reference: src/llsa/kernel/triton/indices_transpose.py).
+//
+// The reference builds the CSR with a global-atomic histogram, a cumsum and a
+// second pass that claims slots with atomics, which leaves the order inside a
+// bucket to chance (indices_transpose.py:23-27, :70-78).  Here one CTA per (b,h)
+// runs a stable counting sort WITHOUT atomics:
+//   1. the E = M*T entries are cut into W contiguous segments, one per warp; a
+//      warp walks its segment 32 entries at a time, groups equal keys with
+//      __match_any_sync and lets the lowest lane of each group add the group size
+//      to the warp's own row of a [W][n_kv] count table;
+//   2. every key's column of the table is turned into exclusive prefixes over the
+//      segments and the column totals are scanned across keys -> offsets;
+//   3. the warps walk their segments again; an entry lands at
+//      offsets[key] + (count in earlier segments) + (count earlier in this segment)
+//      + (rank inside its match group).
+// Entries keep their original relative order, so every bucket lists its query
+// blocks in ascending order and the output is bit-reproducible.
+#include "common.cuh"
+
+namespace llsa {
+
+struct TransposeArgs {
+  IdxView idx;      // [BH, M*T]
+  void* offsets;    // [BH, n_kv+1]
+  int off64;
+  int32_t* flat;    // [BH, M*T]
+  int64_t E;        // entries per head
+  int T;
+  int64_t n_kv;
+  uint16_t* gtab;   // global table [BH][W][n_kv] or nullptr (shared memory)
+  int32_t* status;
+};
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& block_total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int s = lane < nw ? warp_sums[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
+    }
+    warp_sums[lane] = s;  // inclusive over warps
+  }
+  __syncthreads();
+  const int before = warp > 0 ? warp_sums[warp - 1] : 0;
+  block_total = warp_sums[nw - 1];
+  const int excl = before + inc - v;
+  __syncthreads();  // warp_sums is reused by the next call
+  return excl;
+}
+
+__global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
+  extern __shared__ unsigned char smraw[];
+  __shared__ int warp_sums[32];
+  const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t bh = blockIdx.x, n = a.n_kv, E = a.E;
+  int* base = reinterpret_cast<int*>(smraw);                                        // [n_kv]
+  uint16_t* tab = a.gtab ? a.gtab + bh * W * n : reinterpret_cast<uint16_t*>(base + n);  // [W][n_kv]
+
+  for (int64_t i = threadIdx.x; i < (int64_t) W * n; i += blockDim.x) tab[i] = 0;
+  __syncthreads();
+
+  int64_t L = (E + W - 1) / W;
+  L = (L + 31) / 32 * 32;
+  const int64_t seg0 = min(E, warp * L), seg1 = min(E, seg0 + L);
+  uint16_t* mytab = tab + (int64_t) warp * n;
+  const unsigned lt_mask = (1u << lane) - 1u;
+
+  // ---- 1: per-segment histograms
+  for (int64_t e0 = seg0; e0 < seg1; e0 += 32) {
+    const int64_t e = e0 + lane;
+    bool valid = e < seg1;
+    int64_t key = valid ? a.idx.at(bh * E + e) : -1;
+    if (valid && (key < 0 || key >= n)) {
+      if (a.status) *a.status = 1;
+      valid = false;
+    }
+    const unsigned act = __ballot_sync(0xffffffffu, valid);
+    if (valid) {
+      const unsigned peers = __match_any_sync(act, (int) key);
+      if ((peers & lt_mask) == 0) mytab[key] = (uint16_t) (mytab[key] + __popc(peers));
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+
+  // ---- 2: per-key prefix over segments, then scan of the totals over keys
+  int carry = 0;
+  for (int64_t j0 = 0; j0 < n; j0 += blockDim.x) {
+    const int64_t j = j0 + threadIdx.x;
+    int run = 0;
+    if (j < n) {
+      for (int s = 0; s < W; ++s) {
+        const int c = tab[(int64_t) s * n + j];
+        tab[(int64_t) s * n + j] = (uint16_t) run;
+        run += c;
+      }
+    }
+    int total;
+    const int excl = block_exclusive_scan(run, warp_sums, total);
+    if (j < n) {
+      base[j] = carry + excl;
+      if (a.off64) reinterpret_cast<int64_t*>(a.offsets)[bh * (n + 1) + j] = carry + excl;
+      else reinterpret_cast<int32_t*>(a.offsets)[bh * (n + 1) + j] = carry + excl;
+    }
+    carry += total;
+  }
+  if (threadIdx.x == 0) {
+    if (a.off64) reinterpret_cast<int64_t*>(a.offsets)[bh * (n + 1) + n] = carry;
+    else reinterpret_cast<int32_t*>(a.offsets)[bh * (n + 1) + n] = carry;
+  }
+  __syncthreads();
+
+  // ---- 3: stable fill
+  for (int64_t e0 = seg0; e0 < seg1; e0 += 32) {
+    const int64_t e = e0 + lane;
+    bool valid = e < seg1;
+    int64_t key = valid ? a.idx.at(bh * E + e) : -1;
+    if (valid && (key < 0 || key >= n)) valid = false;
+    const unsigned act = __ballot_sync(0xffffffffu, valid);
+    unsigned peers = 0;
+    int seen = 0;
+    if (valid) {
+      peers = __match_any_sync(act, (int) key);
+      seen = mytab[key];
+      const int pos = base[key] + seen + __popc(peers & lt_mask);
+      a.flat[bh * E + pos] = (int32_t) (e / a.T);
+    }
+    __syncwarp();
+    if (valid && (peers & lt_mask) == 0) mytab[key] = (uint16_t) (seen + __popc(peers));
+    __syncwarp();
+  }
+}
+
+// Chooses the warp count W and where the [W][n_kv] count table lives.  Returns
+// W (8, 16 or 32); *global is set when the table does not fit in shared memory
+// or the segments would overflow the 16-bit counters with fewer warps.
+static int plan_transpose(int64_t n_kv, int64_t E, size_t* smem, bool* global) {
+  const size_t limit = 200 * 1024;
+  for (int W = 32; W >= 8; W >>= 1) {
+    const size_t need = (size_t) n_kv * 4 + (size_t) W * n_kv * 2;
+    if (need <= limit && (E + W - 1) / W + 32 <= 65535) {
+      *smem = need;
+      *global = false;
+      return W;
+    }
+  }
+  *smem = (size_t) n_kv * 4;
+  *global = true;
+  return 32;
+}
+
+}  // namespace llsa
+
+using namespace llsa;
+
+extern "C" size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t T, int64_t n_kv) {
+  size_t smem;
+  bool global;
+  plan_transpose(n_kv, M * T, &smem, &global);
+  return global ? (size_t) B * H * 32 * n_kv * 2 : 0;
+}
+
+extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
+                                      void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+  LLSA_REQUIRE(idx && offsets && flat && idx->ptr && offsets->ptr && flat->ptr, LLSA_ERR_NULL, "transpose_indices: null tensor");
+  LLSA_REQUIRE(idx->ndim == 4, LLSA_ERR_SHAPE, "transpose_indices: idx must be [B,H,M,T]");
+  const int64_t B = idx->shape[0], H = idx->shape[1], M = idx->shape[2], T = idx->shape[3];
+  LLSA_REQUIRE(is_index_dtype(idx->dtype) && is_index_dtype(offsets->dtype) && flat->dtype == LLSA_I32, LLSA_ERR_DTYPE,
+               "transpose_indices: idx/offsets must be i32 or i64, flat i32");
+  LLSA_REQUIRE(n_kv >= 1 && n_kv < (1ll << 31) && T >= 1, LLSA_ERR_ARG, "transpose_indices: bad n_kv=%lld", (long long) n_kv);
+  const int64_t E = M * T;
+  LLSA_REQUIRE(E <= 32ll * 65504, LLSA_ERR_SHAPE, "transpose_indices: M*T=%lld exceeds the supported %lld", (long long) E, 32ll * 65504);
+  const int64_t si[4] = {B, H, M, T}, so[3] = {B, H, n_kv + 1}, sf[3] = {B, H, E};
+  int rc;
+  if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
+  if ((rc = check_contig(offsets, "offsets", offsets->dtype, 3, so))) return rc;
+  if ((rc = check_contig(flat, "flat", LLSA_I32, 3, sf))) return rc;
+  if (B * H == 0) return LLSA_OK;
+  size_t smem;
+  bool global;
+  const int W = plan_transpose(n_kv, E, &smem, &global);
+  LLSA_REQUIRE(smem <= 200 * 1024, LLSA_ERR_SHAPE, "transpose_indices: n_kv=%lld too large", (long long) n_kv);
+  TransposeArgs a;
+  a.idx = make_idx(idx);
+  a.offsets = offsets->ptr;
+  a.off64 = offsets->dtype == LLSA_I64;
+  a.flat = (int32_t*) flat->ptr;
+  a.E = E;
+  a.T = (int) T;
+  a.n_kv = n_kv;
+  a.gtab = nullptr;
+  a.status = status;
+  if (global) {
+    const size_t need = (size_t) B * H * 32 * n_kv * 2;
+    LLSA_REQUIRE(scratch && scratch_bytes >= need, LLSA_ERR_WORKSPACE, "transpose_indices: needs %zu bytes of scratch", need);
+    a.gtab = (uint16_t*) scratch;
+  }
+  // a segment holds at most 65535 entries, so the 16-bit counters cannot overflow
+  LLSA_CUDA_OK(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  transpose_kernel<<<(unsigned) (B * H), W * 32, smem, (cudaStream_t) stream>>>(a);
+  LLSA_LAUNCH_OK("transpose_kernel");
+  return LLSA_OK;
+}
