@@ -134,6 +134,10 @@ typedef struct LlsaAttnArgs {
   float kv_weight, kv_weight_2;/* weights on the pooled dK/dV side; the reference's
                                   one-level backward uses 1 here (sparse_attention_res_1.py:389) */
   int32_t force_generic;       /* 1: use the plain FFMA kernels for any dtype   */
+  int32_t stage_mask;          /* backward only; 0 = everything.  Otherwise a bit set of
+                                  1: zero the *_acc tensors + delta + dq,  2: pooled-key
+                                  gradients,  4: dk, dv -- to be issued in this order
+                                  (lets a caller time the three kernels separately) */
 } LlsaAttnArgs;
 
 /* Forward: o, lse.  One level (pk2 == NULL) replaces sparse_indices_attn_res_fwd

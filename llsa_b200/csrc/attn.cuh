@@ -1,0 +1,133 @@
+// Parameters shared by the attention kernels (forward, dQ side, dK/dV side).
+//
+// Key sets a query row attends to (reference: sparse_attention_res_1.py:54-106,
+// sparse_attention_res_2.py:60-149); all sets come in blocks of 16 keys:
+//   fine    : the topk selected 16-token blocks of the row's query block, weight 1
+//   pooled-1: one level  -> ALL level-1 pooled keys;
+//             two levels -> the 16 children of each of the topk_p level-2 blocks
+//             selected by the row's PARENT query block; weight token_weight
+//   pooled-2: two levels only -> ALL level-2 pooled keys; weight token_weight_2
+// A pooled stage with fewer than 64 keys is skipped, as the reference's forward
+// loops do (res_1.py:85, res_2.py:127).
+#pragma once
+#include "common.cuh"
+
+namespace llsa {
+
+constexpr int kBS = 16;   // tokens per block
+constexpr int kD = 64;    // head dim
+
+template <typename T>
+struct AttnP {
+  View<const T> q, k, v, d_o, o_in;
+  View<T> o, dq, dk, dv;
+  const T* pk;   // contiguous [BH, n1, D]
+  const T* pv;
+  const T* pk2;  // contiguous [BH, n2, D] or nullptr
+  const T* pv2;
+  IdxView idx, pidx;
+  float* lse;    // [BH, N]
+  float* delta;  // [BH, N]
+  float* dpk;    // fp32 accumulators [BH, n1, D]
+  float* dpv;
+  float* dpk2;   // [BH, n2, D]
+  float* dpv2;
+  const void* offsets;  // CSR of idx: [BH, n1+1]
+  int off64;
+  const int32_t* flat;  // [BH, n1*topk]
+  int H;
+  int64_t N, n1, n2;
+  int topk, topk_p;
+  int two_level;
+  int p1_blocks;   // pooled-1 key blocks per query row (0 when the stage is skipped)
+  int p2_blocks;   // pooled-2 key blocks per query row
+  float w1, w2;    // token weights (forward and dQ side)
+  float kvw1, kvw2;  // weights on the pooled dK/dV side
+  float scale;     // 1/sqrt(D)
+  int fold;        // fold the pooling backward into dk/dv
+};
+
+// Block index (in units of 16 keys) of pooled-1 block `i` (0 <= i < p1_blocks)
+// for query block `qb` of head `bh`.
+template <typename T>
+__device__ __forceinline__ int64_t p1_block(const AttnP<T>& a, int64_t bh, int64_t qb, int i) {
+  if (!a.two_level) return i;
+  int64_t p = a.pidx.at((bh * a.n2 + qb / kBS) * a.topk_p + i);
+  return p < 0 ? 0 : (p >= a.n2 ? a.n2 - 1 : p);
+}
+
+template <typename T>
+__device__ __forceinline__ int64_t fine_block(const AttnP<T>& a, int64_t bh, int64_t qb, int i) {
+  int64_t j = a.idx.at((bh * a.n1 + qb) * a.topk + i);
+  return j < 0 ? 0 : (j >= a.n1 ? a.n1 - 1 : j);
+}
+
+int build_attn_params_check(const LlsaAttnArgs* g, bool bwd);
+
+template <typename T>
+AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd);
+
+int launch_attn_fwd_generic(const LlsaAttnArgs* g, cudaStream_t st);
+int launch_attn_bwd_generic(const LlsaAttnArgs* g, cudaStream_t st);
+int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st);
+int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st);
+
+template <typename T>
+inline AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd) {
+  AttnP<T> a;
+  memset(&a, 0, sizeof(a));
+  a.q = make_view<const T>(g->q);
+  a.k = make_view<const T>(g->k);
+  a.v = make_view<const T>(g->v);
+  a.pk = (const T*) g->pk->ptr;
+  a.pv = (const T*) g->pv->ptr;
+  a.two_level = g->pk2 != nullptr;
+  if (a.two_level) {
+    a.pk2 = (const T*) g->pk2->ptr;
+    a.pv2 = (const T*) g->pv2->ptr;
+    a.pidx = make_idx(g->p_indices);
+  }
+  a.idx = make_idx(g->indices);
+  a.lse = (float*) g->lse->ptr;
+  a.H = (int) g->q->shape[1];
+  a.N = g->q->shape[2];
+  a.n1 = a.N / kBS;
+  a.n2 = a.n1 / kBS;
+  a.topk = g->topk;
+  a.topk_p = g->topk_p;
+  a.w1 = g->token_weight;
+  a.w2 = g->token_weight_2;
+  a.scale = 0.125f;
+  if (a.two_level) {
+    a.p1_blocks = a.topk_p;
+    a.p2_blocks = a.n2 >= 64 ? (int) (a.n2 / kBS) : 0;
+  } else {
+    a.p1_blocks = a.n1 >= 64 ? (int) (a.n1 / kBS) : 0;
+    a.p2_blocks = 0;
+  }
+  if (!bwd) {
+    a.o = make_view<T>(g->o);
+  } else {
+    a.o_in = make_view<const T>(g->o);
+    a.d_o = make_view<const T>(g->d_o);
+    a.dq = make_view<T>(g->dq);
+    a.dk = make_view<T>(g->dk);
+    a.dv = make_view<T>(g->dv);
+    a.delta = (float*) g->delta->ptr;
+    a.dpk = (float*) g->dpk_acc->ptr;
+    a.dpv = (float*) g->dpv_acc->ptr;
+    if (a.two_level) {
+      a.dpk2 = (float*) g->dpk2_acc->ptr;
+      a.dpv2 = (float*) g->dpv2_acc->ptr;
+    }
+    a.offsets = g->offsets->ptr;
+    a.off64 = g->offsets->dtype == LLSA_I64;
+    a.flat = (const int32_t*) g->flat->ptr;
+    a.kvw1 = g->kv_weight;
+    a.kvw2 = g->kv_weight_2;
+    a.fold = g->fold_pool_bwd;
+  }
+  return a;
+}
+
+}  // namespace llsa

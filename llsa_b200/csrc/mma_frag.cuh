@@ -1,0 +1,115 @@
+// Register-direct operand fragments for mma.sync.m16n8k16 (bf16 in, fp32 out).
+//
+// Every tile the attention kernels multiply is 16 rows x 64 channels of bf16 with
+// 128-byte rows.  Instead of staging tiles in shared memory and reading them back
+// with ldmatrix, each lane loads its mma operand registers straight from global
+// memory (L1/L2) with 128-bit loads, using the freedom to PERMUTE the contraction
+// index: an m16n8k16 product only needs A and B to agree on which physical
+// element sits at which logical k.
+//
+// Lane numbering: g = lane / 4 (0..7), t = lane % 4.
+//
+// * RowFrag -- "channel-contraction" layout, for products that sum over the 64
+//   channels (S = Q.K^T, dP = dO.V^T).  Lane (g,t) holds, for row g of the tile,
+//   channels [8t, 8t+8) and [32+8t, 32+8t+8): two 128-bit loads; the four lanes
+//   of a quad cover one 64-byte half row each time.  k-step s (0..3) uses
+//   registers r[2s] (logical k = 2t,2t+1) and r[2s+1] (logical k = 2t+8,2t+9).
+//   The same struct is the A operand (rows g and g+8 -> two RowFrags) and the B
+//   operand (key n = g -> one RowFrag per 8 keys).
+//
+// * ColFrag -- "row-contraction" layout, for products that sum over the 16 rows
+//   of the tile (O += P.V, dQ += dS.K, dV += P^T.dO, dK += dS^T.Q).  Lane (g,t)
+//   loads channels [8g, 8g+8) of rows 2t, 2t+1, 2t+8, 2t+9 (four 128-bit loads,
+//   eight lanes cover a whole 128-byte row) and builds the B registers of output
+//   n-tile j with two byte permutes: n = g of tile j is channel 8g + j.
+//   Consequently accumulator tile j holds channels 16t + j (c0/c2) and
+//   16t + 8 + j (c1/c3): after the 8 tiles a lane owns the 16 CONSECUTIVE
+//   channels [16t, 16t+16) of rows g and g+8, which it stores with 128-bit stores.
+#pragma once
+#include "common.cuh"
+
+namespace llsa {
+
+using bf16 = __nv_bfloat16;
+
+struct RowFrag {
+  uint32_t r[8];
+};
+
+__device__ __forceinline__ void load_rowfrag(RowFrag& f, const bf16* row, int t) {
+  const uint4 a = ldg128(row + 8 * t), b = ldg128(row + 32 + 8 * t);
+  f.r[0] = a.x; f.r[1] = a.y; f.r[2] = a.z; f.r[3] = a.w;
+  f.r[4] = b.x; f.r[5] = b.y; f.r[6] = b.z; f.r[7] = b.w;
+}
+
+struct ColFrag {
+  uint4 row[4];  // rows 2t, 2t+1, 2t+8, 2t+9; channels 8g..8g+7
+};
+
+__device__ __forceinline__ void load_colfrag(ColFrag& f, const bf16* tile, int64_t stride, int g, int t) {
+  const bf16* p = tile + 8 * g;
+  f.row[0] = ldg128(p + (int64_t) (2 * t) * stride);
+  f.row[1] = ldg128(p + (int64_t) (2 * t + 1) * stride);
+  f.row[2] = ldg128(p + (int64_t) (2 * t + 8) * stride);
+  f.row[3] = ldg128(p + (int64_t) (2 * t + 9) * stride);
+}
+
+__device__ __forceinline__ uint32_t u4_get(const uint4& v, int m) { return m == 0 ? v.x : (m == 1 ? v.y : (m == 2 ? v.z : v.w)); }
+
+// B registers of output tile j (compile-time j under full unrolling)
+__device__ __forceinline__ void colfrag_b(const ColFrag& f, int j, uint32_t& b0, uint32_t& b1) {
+  const int m = j >> 1;
+  const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+  b0 = __byte_perm(u4_get(f.row[0], m), u4_get(f.row[1], m), sel);
+  b1 = __byte_perm(u4_get(f.row[2], m), u4_get(f.row[3], m), sel);
+}
+
+// acc[0..1] (16 x 16 keys, two n-tiles) += A(rows g / g+8) . B(keys)^T over the 64 channels
+__device__ __forceinline__ void mma_rows_x_keys(float (&s0)[4], float (&s1)[4], const RowFrag& alo, const RowFrag& ahi, const RowFrag& k0,
+                                                const RowFrag& k1) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    mma_bf16_16816(s0, alo.r[2 * s], ahi.r[2 * s], alo.r[2 * s + 1], ahi.r[2 * s + 1], k0.r[2 * s], k0.r[2 * s + 1]);
+    mma_bf16_16816(s1, alo.r[2 * s], ahi.r[2 * s], alo.r[2 * s + 1], ahi.r[2 * s + 1], k1.r[2 * s], k1.r[2 * s + 1]);
+  }
+}
+
+// acc (16 x 64, eight n-tiles) += A(16 x 16, given as the four A registers) . tile(16 rows x 64 channels)
+__device__ __forceinline__ void mma_x_cols(float (&acc)[8][4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const ColFrag& f) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t b0, b1;
+    colfrag_b(f, j, b0, b1);
+    mma_bf16_16816(acc[j], a0, a1, a2, a3, b0, b1);
+  }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// Stores the 16 consecutive channels [16t, 16t+16) a lane owns for one row (ROW 0: c0/c1, ROW 1: c2/c3)
+template <int ROW>
+__device__ __forceinline__ void store_acc_row(bf16* row, const float (&acc)[8][4], int t, float mul) {
+  constexpr int lo = ROW * 2, hi = ROW * 2 + 1;
+  uint4 x, y;
+  x.x = pack_bf16(acc[0][lo] * mul, acc[1][lo] * mul); x.y = pack_bf16(acc[2][lo] * mul, acc[3][lo] * mul);
+  x.z = pack_bf16(acc[4][lo] * mul, acc[5][lo] * mul); x.w = pack_bf16(acc[6][lo] * mul, acc[7][lo] * mul);
+  y.x = pack_bf16(acc[0][hi] * mul, acc[1][hi] * mul); y.y = pack_bf16(acc[2][hi] * mul, acc[3][hi] * mul);
+  y.z = pack_bf16(acc[4][hi] * mul, acc[5][hi] * mul); y.w = pack_bf16(acc[6][hi] * mul, acc[7][hi] * mul);
+  *reinterpret_cast<uint4*>(row + 16 * t) = x;
+  *reinterpret_cast<uint4*>(row + 16 * t + 8) = y;
+}
+
+}  // namespace llsa

@@ -1,0 +1,565 @@
+"""Host side of the LLSA operators: the reference's Python API over the C ABI.
+
+Function names, argument order and return values mirror the reference
+(SingleZombie/LLSA, src/llsa/kernel/...), so callers written against it run
+unchanged:
+
+    mean_pool1d, my_rope_fn                    triton/mean_pool.py:209, triton/rope.py:148
+    gen_sparse_indices, compute_topk_indices_sparse   triton/topk.py:6, :172
+    transpose_indices                          triton/indices_transpose.py:104
+    sparse_indices_attn_res_fwd / ..._scatter_bwd_v2          triton/sparse_attention_res_1.py:123, :403
+    sparse_indices_attn_res_2_2_fwd / ..._scatter_2_2_bwd_v2  triton/sparse_attention_res_2.py:166, :578
+    flash_sparse_residual_attention_l1_op / _l2_op            torch_op/flash_sparse_attention_res_{1,2}.py:38, :45
+    llsa_l1, llsa_l2                           torch_op/flash_sparse_attention_res_1.py:41, _res_2.py:48
+
+Every function enqueues CUDA work on the current stream through
+libllsa_b200.so; tensors must live on a CUDA device.  The differentiable
+entry points are torch.library custom ops with registered autograd.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import desc, ptr, ref
+
+__all__ = [
+    "mean_pool1d", "my_rope_fn", "gen_sparse_indices", "compute_topk_indices_sparse", "transpose_indices",
+    "sparse_indices_attn_res_fwd", "sparse_indices_attn_res_scatter_bwd_v2",
+    "sparse_indices_attn_res_2_2_fwd", "sparse_indices_attn_res_scatter_2_2_bwd_v2",
+    "flash_sparse_residual_attention_l1_op", "flash_sparse_residual_attention_l2_op",
+    "llsa_l1", "llsa_l2", "pool_pyramid", "set_exact_pooled_grad",
+]
+
+_FLOAT = (torch.float32, torch.bfloat16)
+_force_generic = os.environ.get("LLSA_B200_FORCE_GENERIC", "0") == "1"
+# The reference's one-level backward drops the token weight from the pooled-key
+# gradients (sparse_attention_res_1.py:389).  False reproduces that; True gives
+# the exact gradient.
+_exact_pooled_grad = os.environ.get("LLSA_B200_EXACT_POOLED_GRAD", "0") == "1"
+
+
+_stage_hook = None
+
+
+def set_stage_hook(fn) -> None:
+    """fn(name) is called right before each kernel group is enqueued (and with
+    "end" after the last one of an operator); None disables it.  Used by the
+    benchmark to bracket kernels with CUDA events."""
+    global _stage_hook
+    _stage_hook = fn
+
+
+def _mark(name: str) -> None:
+    if _stage_hook is not None:
+        _stage_hook(name)
+
+
+def set_exact_pooled_grad(flag: bool) -> None:
+    """Choose between the reference-compatible (False, default) and the
+    mathematically exact (True) pooled-key gradient of llsa_l1."""
+    global _exact_pooled_grad
+    _exact_pooled_grad = bool(flag)
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("llsa_b200 runs on CUDA tensors only (got a %s tensor); there is no CPU path" % t.device.type)
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    per16 = 16 // t.element_size()
+    if t.stride(-1) != 1 or t.data_ptr() % 16:
+        return False
+    return all(t.shape[i] == 1 or t.stride(i) % per16 == 0 for i in range(t.dim() - 1))
+
+
+def _prep(t: torch.Tensor) -> torch.Tensor:
+    """Kernels take any batch/head/token strides but need unit channel stride and 16-byte aligned rows."""
+    return t if _rows_ok(t) else t.contiguous()
+
+
+def _check_float(*ts: torch.Tensor) -> None:
+    dt = ts[0].dtype
+    if dt not in _FLOAT:
+        raise TypeError("llsa_b200 supports float32 and bfloat16 tensors, got %s" % dt)
+    for t in ts:
+        if t.dtype != dt:
+            raise TypeError("llsa_b200: all floating-point operands must share one dtype")
+
+
+def _stream(t: torch.Tensor):
+    return _lib.stream_ptr(t.device)
+
+
+# ----------------------------------------------------------------------------- pooling
+def _pool_fwd_impl(x: torch.Tensor, k: int) -> torch.Tensor:
+    _need_cuda(x)
+    _check_float(x)
+    B, H, S, Cc = x.shape
+    assert S % k == 0, "sequence length must be divisible by the pooling factor"
+    x = x if x.stride(-1) == 1 else x.contiguous()
+    y = torch.empty((B, H, S // k, Cc), device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        dx, dy = desc(x), desc(y)
+        _lib.check(_lib.lib().llsa_mean_pool_fwd(ref(dx), ref(dy), k, _stream(x)), "mean_pool_fwd")
+    return y
+
+
+def _pool_bwd_impl(dy: torch.Tensor, k: int) -> torch.Tensor:
+    _need_cuda(dy)
+    dy = dy if dy.stride(-1) == 1 else dy.contiguous()
+    B, H, S, Cc = dy.shape
+    dx = torch.empty((B, H, S * k, Cc), device=dy.device, dtype=dy.dtype)
+    with torch.cuda.device(dy.device):
+        a, b = desc(dy), desc(dx)
+        _lib.check(_lib.lib().llsa_mean_pool_bwd(ref(a), ref(b), k, _stream(dy)), "mean_pool_bwd")
+    return dx
+
+
+@torch.library.custom_op("llsa_b200::mean_pool_fwd", mutates_args=())
+def _mean_pool_fwd_op(x: torch.Tensor, k: int) -> torch.Tensor:
+    return _pool_fwd_impl(x, k)
+
+
+@_mean_pool_fwd_op.register_fake
+def _(x, k):
+    return x.new_empty((x.shape[0], x.shape[1], x.shape[2] // k, x.shape[3]))
+
+
+@torch.library.custom_op("llsa_b200::mean_pool_bwd", mutates_args=())
+def _mean_pool_bwd_op(dy: torch.Tensor, k: int) -> torch.Tensor:
+    return _pool_bwd_impl(dy, k)
+
+
+@_mean_pool_bwd_op.register_fake
+def _(dy, k):
+    return dy.new_empty((dy.shape[0], dy.shape[1], dy.shape[2] * k, dy.shape[3]))
+
+
+def _pool_setup(ctx, inputs, output):
+    ctx.k = inputs[1]
+
+
+def _pool_backward(ctx, dy):
+    return _mean_pool_bwd_op(dy, ctx.k), None
+
+
+_mean_pool_fwd_op.register_autograd(_pool_backward, setup_context=_pool_setup)
+
+
+def mean_pool1d(x: torch.Tensor, k: int, format: str = "bhsc") -> torch.Tensor:
+    """Mean over k consecutive tokens of a [B,H,S,C] tensor, accumulated in x's
+    dtype; differentiable.  Mirrors mean_pool1d (triton/mean_pool.py:209-216);
+    only the 'bhsc' layout the attention path uses is provided."""
+    if format != "bhsc":
+        raise NotImplementedError("format %r is not part of the attention hot path" % (format,))
+    return _mean_pool_fwd_op(x, k)
+
+
+def pool_pyramid(xs: List[torch.Tensor], block_size: int, levels: int):
+    """All pyramid levels of up to three [B,H,N,D] tensors in one launch.
+    Returns (level-1 list, level-2 list or None).  Not differentiable by itself."""
+    _need_cuda(*xs)
+    _check_float(*xs)
+    xs = [_prep(x) for x in xs]
+    B, H, N, D = xs[0].shape
+    bs = block_size
+    y1 = [torch.empty((B, H, N // bs, D), device=x.device, dtype=x.dtype) for x in xs]
+    y2 = [torch.empty((B, H, N // bs // bs, D), device=x.device, dtype=x.dtype) for x in xs] if levels == 2 else None
+    n = len(xs)
+    XA = (_lib.LlsaTensor * n)(*[desc(x) for x in xs])
+    Y1 = (_lib.LlsaTensor * n)(*[desc(y) for y in y1])
+    Y2 = (_lib.LlsaTensor * n)(*[desc(y) for y in y2]) if y2 is not None else None
+    _mark("pool_pyramid")
+    with torch.cuda.device(xs[0].device):
+        _lib.check(_lib.lib().llsa_pool_pyramid_fwd(n, XA, Y1, Y2, bs, _stream(xs[0])), "pool_pyramid_fwd")
+    return y1, y2
+
+
+# ----------------------------------------------------------------------------- RoPE
+def _rope_impl(x: torch.Tensor, freq: torch.Tensor, bwd: bool) -> torch.Tensor:
+    _need_cuda(x, freq)
+    assert x.dim() == 4 and freq.dim() == 2, "x:[B,H,S,D], freq:[S,D]"
+    assert x.shape[-1] % 2 == 0, "D must be even (pairs of cos/sin)."
+    assert freq.shape[0] == x.shape[2] and freq.shape[1] == x.shape[3]
+    if freq.dtype == torch.float64 or (x.dtype == torch.float32 and freq.dtype == torch.bfloat16):
+        freq = freq.to(torch.float32)
+    x = _prep(x)
+    freq = freq if (freq.stride(-1) == 1 and freq.data_ptr() % 16 == 0) else freq.contiguous()
+    y = torch.empty_like(x)     # keeps x's strides, as the reference does (rope.py:109)
+    with torch.cuda.device(x.device):
+        a, f, b = desc(x), desc(freq), desc(y)
+        fn = _lib.lib().llsa_rope_bwd if bwd else _lib.lib().llsa_rope_fwd
+        _lib.check(fn(ref(a), ref(f), ref(b), _stream(x)), "rope")
+    return y
+
+
+@torch.library.custom_op("llsa_b200::rope_fwd", mutates_args=())
+def _rope_fwd_op(x: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    return _rope_impl(x, freq, False)
+
+
+@_rope_fwd_op.register_fake
+def _(x, freq):
+    return torch.empty_like(x)
+
+
+@torch.library.custom_op("llsa_b200::rope_bwd", mutates_args=())
+def _rope_bwd_op(dy: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    return _rope_impl(dy, freq, True)
+
+
+@_rope_bwd_op.register_fake
+def _(dy, freq):
+    return torch.empty_like(dy)
+
+
+def _rope_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[1])
+
+
+def _rope_backward(ctx, dy):
+    (freq,) = ctx.saved_tensors
+    return _rope_bwd_op(dy, freq), None
+
+
+_rope_fwd_op.register_autograd(_rope_backward, setup_context=_rope_setup)
+
+
+def my_rope_fn(x: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    """Interleaved-pair RoPE by a [S,D] (sin, cos) table; differentiable in x.
+    Mirrors my_rope_fn = MyRopeFunction.apply (triton/rope.py:100-148)."""
+    return _rope_fwd_op(x, freq)
+
+
+# ----------------------------------------------------------------------------- selection
+def _coarse_topk(pq: torch.Tensor, pk: torch.Tensor, topk: int, out_dtype=torch.int32) -> torch.Tensor:
+    _need_cuda(pq, pk)
+    _check_float(pq, pk)
+    pq, pk = pq.contiguous(), pk.contiguous()
+    topk = min(topk, pk.shape[2])
+    idx = torch.empty((*pq.shape[:3], topk), device=pq.device, dtype=out_dtype)
+    _mark("coarse_topk")
+    with torch.cuda.device(pq.device):
+        a, b, c = desc(pq), desc(pk), desc(idx)
+        _lib.check(_lib.lib().llsa_coarse_topk(ref(a), ref(b), ref(c), topk, _stream(pq)), "coarse_topk")
+    return idx
+
+
+def gen_sparse_indices(pq: torch.Tensor, pk: torch.Tensor, topk: int) -> torch.Tensor:
+    """Top-k key blocks per query block from pooled scores (scores rounded to the
+    input dtype, descending, ties to the smallest index); int64 like
+    torch.topk.  Mirrors gen_sparse_indices (triton/topk.py:6-9)."""
+    return _coarse_topk(pq.detach(), pk.detach(), topk, torch.int64)
+
+
+def _refine_topk(pq, pk, p_indices, topk, p_topk, block_size) -> torch.Tensor:
+    _need_cuda(pq, pk, p_indices)
+    _check_float(pq, pk)
+    pq, pk, p_indices = pq.contiguous(), pk.contiguous(), p_indices.contiguous()
+    idx = torch.empty((*pq.shape[:3], topk), device=pq.device, dtype=torch.int32)
+    _mark("refine_topk")
+    with torch.cuda.device(pq.device):
+        a, b, c, d = desc(pq), desc(pk), desc(p_indices), desc(idx)
+        _lib.check(_lib.lib().llsa_refine_topk(ref(a), ref(b), ref(c), ref(d), topk, p_topk, block_size, _stream(pq)), "refine_topk")
+    return idx
+
+
+def compute_topk_indices_sparse(pq, pk, p_indices, topk=8, p_topk=8, block_size=16) -> torch.Tensor:
+    """Fine top-k among the children of the selected parent blocks; int32
+    [B,H,M,topk].  Mirrors compute_topk_indices_sparse (triton/topk.py:172-197)."""
+    return _refine_topk(pq.detach(), pk.detach(), p_indices, topk, p_topk, block_size)
+
+
+def transpose_indices(q_topk_indices: torch.Tensor, k_ntx: Optional[int] = None, offsets_dtype=torch.int64):
+    """Query-major top-k lists -> (offsets [B,H,k_ntx+1], flat [B,H,M*T]) with every
+    bucket in ascending query order.  Mirrors transpose_indices
+    (triton/indices_transpose.py:104-109); `flat` is int32 (the reference's
+    uint32 holds the same values)."""
+    _need_cuda(q_topk_indices)
+    idx = q_topk_indices.contiguous()
+    B, H, M, T = idx.shape
+    if k_ntx is None:
+        k_ntx = M
+    offsets = torch.empty((B, H, k_ntx + 1), device=idx.device, dtype=offsets_dtype)
+    flat = torch.empty((B, H, M * T), device=idx.device, dtype=torch.int32)
+    _mark("transpose_indices")
+    with torch.cuda.device(idx.device):
+        L = _lib.lib()
+        nbytes = L.llsa_transpose_scratch_bytes(B, H, M, T, k_ntx)
+        scratch = torch.empty((max(nbytes, 1),), device=idx.device, dtype=torch.uint8) if nbytes else None
+        a, b, c = desc(idx), desc(offsets), desc(flat)
+        _lib.check(L.llsa_transpose_indices(ref(a), ref(b), ref(c), k_ntx, C.c_void_p(scratch.data_ptr() if nbytes else 0), nbytes, None,
+                                            _stream(idx)), "transpose_indices")
+    return offsets, flat
+
+
+# ----------------------------------------------------------------------------- attention core
+def _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2):
+    keep = dict(q=desc(q), k=desc(k), v=desc(v), pk=desc(pk), pv=desc(pv), pk2=desc(pk2), pv2=desc(pv2),
+                indices=desc(indices), p_indices=desc(p_indices), o=desc(o), lse=desc(lse))
+    a = _lib.LlsaAttnArgs()
+    for name, d in keep.items():
+        setattr(a, name, ptr(d))
+    a.topk, a.topk_p, a.block_size = int(topk), int(topk_p), int(block_size)
+    a.token_weight, a.token_weight_2 = float(w1), float(w2)
+    a.force_generic = 1 if _force_generic else 0
+    return a, keep
+
+
+def _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk_p, block_size, w1, w2):
+    _need_cuda(q, k, v)
+    _check_float(q, k, v, pk, pv)
+    q, k, v = _prep(q), _prep(k), _prep(v)
+    pk, pv = pk.contiguous(), pv.contiguous()
+    if pk2 is not None:
+        pk2, pv2, p_indices = pk2.contiguous(), pv2.contiguous(), p_indices.contiguous()
+    indices = indices.contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
+    a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
+    _mark("attn_fwd")
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().llsa_attn_fwd(C.byref(a), _stream(q)), "attn_fwd")
+    _mark("end")
+    return o, lse
+
+
+def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, topk_p, block_size, w1, w2, kvw1, kvw2, fold):
+    _need_cuda(do, q, k, v)
+    q, k, v, o, do = _prep(q), _prep(k), _prep(v), _prep(o), _prep(do)
+    pk, pv = pk.contiguous(), pv.contiguous()
+    if pk2 is not None:
+        pk2, pv2, p_indices = pk2.contiguous(), pv2.contiguous(), p_indices.contiguous()
+    indices = indices.contiguous()
+    lse = lse.contiguous()
+    offsets, flat = transpose_indices(indices, offsets_dtype=torch.int32)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty_like(lse)
+    f32 = dict(device=q.device, dtype=torch.float32)
+    dpk, dpv = torch.empty(pk.shape, **f32), torch.empty(pv.shape, **f32)
+    dpk2 = torch.empty(pk2.shape, **f32) if pk2 is not None else None
+    dpv2 = torch.empty(pv2.shape, **f32) if pv2 is not None else None
+    a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
+    extra = dict(d_o=desc(do), dq=desc(dq), dk=desc(dk), dv=desc(dv), offsets=desc(offsets), flat=desc(flat), delta=desc(delta),
+                 dpk_acc=desc(dpk), dpv_acc=desc(dpv), dpk2_acc=desc(dpk2), dpv2_acc=desc(dpv2))
+    for name, d in extra.items():
+        setattr(a, name, ptr(d))
+    a.fold_pool_bwd = 1 if fold else 0
+    a.kv_weight, a.kv_weight_2 = float(kvw1), float(kvw2)
+    with torch.cuda.device(q.device):
+        if _stage_hook is None:
+            _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), "attn_bwd")
+        else:
+            for mask, name in ((1, "attn_bwd_dq"), (2, "attn_bwd_dkv_pooled"), (4, "attn_bwd_dkv_fine")):
+                _mark(name)
+                a.stage_mask = mask
+                _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), name)
+            _mark("end")
+    return dq, dk, dv, dpk, dpv, dpk2, dpv2
+
+
+def sparse_indices_attn_res_fwd(q, k, v, pk, pv, indices, topk, token_weight=1, down_scale=4):
+    """One-level forward -> (o, m) with m the fp32 log-sum-exp.  Mirrors
+    sparse_indices_attn_res_fwd (triton/sparse_attention_res_1.py:123-150)."""
+    return _attn_fwd(q, k, v, pk, pv, None, None, indices, None, topk, 0, down_scale * down_scale, token_weight, 1.0)
+
+
+def sparse_indices_attn_res_2_2_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk_p,
+                                    token_weight=1, token_weight_2=1, down_scale=4):
+    """Two-level forward -> (o, m).  Mirrors sparse_indices_attn_res_2_2_fwd
+    (triton/sparse_attention_res_2.py:166-199)."""
+    return _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk_p, down_scale * down_scale,
+                     token_weight, token_weight_2)
+
+
+def sparse_indices_attn_res_scatter_bwd_v2(do, q, k, v, pk, pv, o, m, indices, topk, block_size, token_weight):
+    """One-level backward -> (dq, dk, dv, None, dpk, dpv) in the tensors' dtype.
+    Mirrors sparse_indices_attn_res_scatter_bwd_v2 (triton/sparse_attention_res_1.py:403-471),
+    including its unweighted pooled-key gradients unless set_exact_pooled_grad(True)."""
+    kvw = token_weight if _exact_pooled_grad else 1.0
+    dq, dk, dv, dpk, dpv, _, _ = _attn_bwd(do, q, k, v, pk, pv, None, None, o, m, indices, None, topk, 0, block_size,
+                                           token_weight, 1.0, kvw, 1.0, False)
+    return dq, dk, dv, None, dpk.to(pk.dtype), dpv.to(pv.dtype)
+
+
+def sparse_indices_attn_res_scatter_2_2_bwd_v2(do, q, k, v, pk, pv, pk2, pv2, o, m, indices, prev_indices, topk, topk_p,
+                                               block_size, token_weight, token_weight_2):
+    """Two-level backward -> (dq, dk, dv, None, dpk, dpv, None, dpk2, dpv2).  Mirrors
+    sparse_indices_attn_res_scatter_2_2_bwd_v2 (triton/sparse_attention_res_2.py:578-681)."""
+    dq, dk, dv, dpk, dpv, dpk2, dpv2 = _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, m, indices, prev_indices, topk, topk_p,
+                                                 block_size, token_weight, token_weight_2, token_weight, token_weight_2, False)
+    return dq, dk, dv, None, dpk.to(pk.dtype), dpv.to(pv.dtype), None, dpk2.to(pk2.dtype), dpv2.to(pv2.dtype)
+
+
+# ----------------------------------------------------------------------------- operators with explicit pooled inputs
+class _FlashSparseResidualAttentionL1(torch.autograd.Function):
+    """torch_op/flash_sparse_attention_res_1.py:10-35."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, pq, pk, pv, topk, token_weight=1, block_size=16):
+        indices = _coarse_topk(pq, pk, topk)
+        o, m = _attn_fwd(q, k, v, pk, pv, None, None, indices, None, topk, 0, block_size, token_weight, 1.0)
+        ctx.save_for_backward(q, k, v, pk, pv, o, m, indices)
+        ctx.topk, ctx.block_size, ctx.token_weight = topk, block_size, token_weight
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, pk, pv, o, m, indices = ctx.saved_tensors
+        g = sparse_indices_attn_res_scatter_bwd_v2(do, q, k, v, pk, pv, o, m, indices, ctx.topk, ctx.block_size, ctx.token_weight)
+        return (*g, None, None, None)
+
+
+class _FlashSparseResidualAttentionL2(torch.autograd.Function):
+    """torch_op/flash_sparse_attention_res_2.py:10-42."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, pq, pk, pv, pq2, pk2, pv2, topk, topk2, token_weight=1, token_weight_2=1, block_size=16):
+        p_indices = _coarse_topk(pq2, pk2, topk2)
+        indices = _refine_topk(pq, pk, p_indices, topk, topk2, block_size)
+        o, m = _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk2, block_size, token_weight, token_weight_2)
+        ctx.save_for_backward(q, k, v, pk, pv, pk2, pv2, o, m, indices, p_indices)
+        ctx.cfg = (topk, topk2, block_size, token_weight, token_weight_2)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, pk, pv, pk2, pv2, o, m, indices, p_indices = ctx.saved_tensors
+        topk, topk2, bs, w1, w2 = ctx.cfg
+        g = sparse_indices_attn_res_scatter_2_2_bwd_v2(do, q, k, v, pk, pv, pk2, pv2, o, m, indices, p_indices, topk, topk2, bs, w1, w2)
+        return (*g, None, None, None, None, None)
+
+
+flash_sparse_residual_attention_l1_op = _FlashSparseResidualAttentionL1.apply
+flash_sparse_residual_attention_l2_op = _FlashSparseResidualAttentionL2.apply
+
+
+# ----------------------------------------------------------------------------- fused drop-in operators
+@torch.library.custom_op("llsa_b200::llsa_l1_fwd", mutates_args=())
+def _llsa_l1_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk: int, block_size: int) -> List[torch.Tensor]:
+    (pq, pk, pv), _ = pool_pyramid([q, k, v], block_size, 1)
+    indices = _coarse_topk(pq, pk, topk)
+    o, lse = _attn_fwd(q, k, v, pk, pv, None, None, indices, None, indices.shape[-1], 0, block_size, float(block_size), 1.0)
+    return [o, lse, indices, pk, pv]
+
+
+@_llsa_l1_fwd.register_fake
+def _(q, k, v, topk, block_size):
+    B, H, N, D = q.shape
+    n1 = N // block_size
+    return [torch.empty_like(q), q.new_empty((B, H, N), dtype=torch.float32), q.new_empty((B, H, n1, min(topk, n1)), dtype=torch.int32),
+            k.new_empty((B, H, n1, D)), v.new_empty((B, H, n1, D))]
+
+
+@torch.library.custom_op("llsa_b200::llsa_l1_bwd", mutates_args=())
+def _llsa_l1_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                 indices: torch.Tensor, pk: torch.Tensor, pv: torch.Tensor, block_size: int, exact: bool) -> List[torch.Tensor]:
+    w = float(block_size)
+    dq, dk, dv, _, _, _, _ = _attn_bwd(do, q, k, v, pk, pv, None, None, o, lse, indices, None, indices.shape[-1], 0, block_size,
+                                       w, 1.0, w if exact else 1.0, 1.0, True)
+    return [dq, dk, dv]
+
+
+@_llsa_l1_bwd.register_fake
+def _(do, q, k, v, o, lse, indices, pk, pv, block_size, exact):
+    return [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+
+
+def _l1_setup(ctx, inputs, output):
+    q, k, v, topk, block_size = inputs
+    o, lse, indices, pk, pv = output
+    ctx.save_for_backward(q, k, v, o, lse, indices, pk, pv)
+    ctx.block_size = block_size
+
+
+def _l1_backward(ctx, grads):
+    q, k, v, o, lse, indices, pk, pv = ctx.saved_tensors
+    dq, dk, dv = _llsa_l1_bwd(grads[0], q, k, v, o, lse, indices, pk, pv, ctx.block_size, _exact_pooled_grad)
+    return dq, dk, dv, None, None
+
+
+_llsa_l1_fwd.register_autograd(_l1_backward, setup_context=_l1_setup)
+
+
+@torch.library.custom_op("llsa_b200::llsa_l2_fwd", mutates_args=())
+def _llsa_l2_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk1: int, topk2: int, block_size: int) -> List[torch.Tensor]:
+    (pq, pk, pv), (pq2, pk2, pv2) = pool_pyramid([q, k, v], block_size, 2)
+    p_indices = _coarse_topk(pq2, pk2, topk2)
+    indices = _refine_topk(pq, pk, p_indices, topk1, p_indices.shape[-1], block_size)
+    o, lse = _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk1, p_indices.shape[-1], block_size,
+                       float(block_size), float(block_size * block_size))
+    return [o, lse, indices, p_indices, pk, pv, pk2, pv2]
+
+
+@_llsa_l2_fwd.register_fake
+def _(q, k, v, topk1, topk2, block_size):
+    B, H, N, D = q.shape
+    n1 = N // block_size
+    n2 = n1 // block_size
+    return [torch.empty_like(q), q.new_empty((B, H, N), dtype=torch.float32), q.new_empty((B, H, n1, topk1), dtype=torch.int32),
+            q.new_empty((B, H, n2, min(topk2, n2)), dtype=torch.int32), k.new_empty((B, H, n1, D)), v.new_empty((B, H, n1, D)),
+            k.new_empty((B, H, n2, D)), v.new_empty((B, H, n2, D))]
+
+
+@torch.library.custom_op("llsa_b200::llsa_l2_bwd", mutates_args=())
+def _llsa_l2_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                 indices: torch.Tensor, p_indices: torch.Tensor, pk: torch.Tensor, pv: torch.Tensor, pk2: torch.Tensor,
+                 pv2: torch.Tensor, block_size: int) -> List[torch.Tensor]:
+    w1, w2 = float(block_size), float(block_size * block_size)
+    dq, dk, dv, _, _, _, _ = _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, indices.shape[-1],
+                                       p_indices.shape[-1], block_size, w1, w2, w1, w2, True)
+    return [dq, dk, dv]
+
+
+@_llsa_l2_bwd.register_fake
+def _(do, q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2, block_size):
+    return [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+
+
+def _l2_setup(ctx, inputs, output):
+    q, k, v, topk1, topk2, block_size = inputs
+    o, lse, indices, p_indices, pk, pv, pk2, pv2 = output
+    ctx.save_for_backward(q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2)
+    ctx.block_size = block_size
+
+
+def _l2_backward(ctx, grads):
+    q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2 = ctx.saved_tensors
+    dq, dk, dv = _llsa_l2_bwd(grads[0], q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2, ctx.block_size)
+    return dq, dk, dv, None, None, None
+
+
+_llsa_l2_fwd.register_autograd(_l2_backward, setup_context=_l2_setup)
+
+
+def llsa_l1(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk: int = 8, block_size: int = 16) -> torch.Tensor:
+    """One-level log-linear sparse attention; q, k, v [B,H,N,D] (any batch/head/token
+    strides), returns o like q; differentiable in q, k, v.  Drop-in for llsa_l1
+    (torch_op/flash_sparse_attention_res_1.py:41-47)."""
+    return _llsa_l1_fwd(q, k, v, topk, block_size)[0]
+
+
+def llsa_l2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk1: int = 8, topk2: int = 8, block_size: int = 16) -> torch.Tensor:
+    """Two-level log-linear sparse attention.  Drop-in for llsa_l2
+    (torch_op/flash_sparse_attention_res_2.py:48-59)."""
+    return _llsa_l2_fwd(q, k, v, topk1, topk2, block_size)[0]
+
+
+def llsa_l1_debug(q, k, v, topk=8, block_size=16):
+    """llsa_l1 returning its intermediates: dict(o, lse, indices, pk, pv)."""
+    o, lse, indices, pk, pv = _llsa_l1_fwd(q, k, v, topk, block_size)
+    return dict(o=o, lse=lse, indices=indices, pk=pk, pv=pv)
+
+
+def llsa_l2_debug(q, k, v, topk1=8, topk2=8, block_size=16):
+    """llsa_l2 returning its intermediates: dict(o, lse, indices, p_indices, pk, pv, pk2, pv2)."""
+    o, lse, indices, p_indices, pk, pv, pk2, pv2 = _llsa_l2_fwd(q, k, v, topk1, topk2, block_size)
+    return dict(o=o, lse=lse, indices=indices, p_indices=p_indices, pk=pk, pv=pv, pk2=pk2, pv2=pv2)

@@ -1,0 +1,368 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU
+oracle and the golden vectors of the reference on the same seeded inputs.
+
+Tolerances
+  * pooling, RoPE, index transpose, offsets: bit-exact.
+  * block indices: bit-exact as ordered lists, except rows where the scores of
+    the differing entries agree within 1e-6 (exact ties / last-ulp accumulation
+    order), which are counted and bounded.
+  * fp32 tensors: rel-L2 <= 2e-5 against the fp32 reference values.
+  * bf16 tensors (o, dq, dk, dv): rel-L2 <= 1e-2 and |err| <= 2e-2 + 2^-7*|ref|
+    against an fp32 evaluation on the same (bf16) inputs and the same indices;
+    the second term is the rounding of the bf16 result itself.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import csr_canonical, load_golden, max_abs, rel_l2, sha, topk_mismatch_rows
+from llsa_b200 import synth
+from oracle import llsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops():
+    import llsa_b200
+    return llsa_b200
+
+
+def assert_bf16_close(got, ref, name):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    r = rel_l2(got, ref)
+    err = (got - ref).abs()
+    bound = 2e-2 + ref.abs() * 2.0 ** -7
+    worst = float((err - bound).max())
+    assert r <= 1e-2, "%s: rel-L2 %.3e" % (name, r)
+    assert worst <= 0, "%s: |err| exceeds 2e-2 + 2^-7|ref| by %.3e (max err %.3e)" % (name, worst, float(err.max()))
+
+
+# ------------------------------------------------------------------ pooling / rope
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mean_pool_bit_exact(dtype):
+    L = _ops()
+    x, dy = synth.gaussian_qkv(31, 2, 3, 1024, 64, n_tensors=2, dtype=dtype)
+    xg = x.to(DEV).requires_grad_(True)
+    y = L.mean_pool1d(xg, 16)
+    assert torch.equal(y.cpu(), O.mean_pool1d(x, 16))
+    y2 = L.mean_pool1d(y, 16)
+    assert torch.equal(y2.cpu(), O.mean_pool1d(O.mean_pool1d(x, 16), 16))
+    y.backward(dy[:, :, :64].to(DEV))
+    assert torch.equal(xg.grad.cpu(), O.mean_pool1d_bwd(dy[:, :, :64], 16))
+    # [B,H,N,D] view of [B,N,H,D] storage, as the model passes it
+    xs = x.transpose(1, 2).contiguous().transpose(1, 2)
+    assert torch.equal(L.mean_pool1d(xs.to(DEV).transpose(1, 2).contiguous().transpose(1, 2), 16).cpu(), O.mean_pool1d(x, 16))
+    # odd pooling factor and channel count
+    x3 = synth.gaussian_qkv(32, 1, 2, 60, 20, n_tensors=1, dtype=dtype)[0]
+    assert torch.equal(L.mean_pool1d(x3.to(DEV), 5).cpu(), O.mean_pool1d(x3, 5))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("levels", [1, 2])
+def test_pool_pyramid_bit_exact(dtype, levels):
+    L = _ops()
+    q, k, v = synth.gaussian_qkv(33, 2, 2, 1024, 64, n_tensors=3, dtype=dtype)
+    kv = k.transpose(1, 2).contiguous().transpose(1, 2)         # one strided operand
+    y1, y2 = L.pool_pyramid([q.to(DEV), kv.to(DEV).transpose(1, 2).contiguous().transpose(1, 2), v.to(DEV)], 16, levels)
+    for got, x in zip(y1, (q, k, v)):
+        assert torch.equal(got.cpu(), O.mean_pool1d(x, 16))
+    if levels == 2:
+        for got, x in zip(y2, (q, k, v)):
+            assert torch.equal(got.cpu(), O.mean_pool1d(O.mean_pool1d(x, 16), 16))
+
+
+def test_pool_matches_reference_golden():
+    L = _ops()
+    g = load_golden("pool_fp32.npz")
+    x, dy = synth.gaussian_qkv(int(g["seed"]), *[int(s) for s in g["shape"]], n_tensors=2)
+    assert sha(x, dy) == str(g["input_sha"])
+    y = L.mean_pool1d(x.to(DEV), 16)
+    assert np.array_equal(y.cpu().numpy(), g["y"])
+    assert np.array_equal(L.mean_pool1d(y, 16).cpu().numpy(), g["y2"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_bit_exact(dtype):
+    L = _ops()
+    B, H, S, D = 2, 3, 1024, 64
+    x, dy = synth.gaussian_qkv(34, B, S, H, D, n_tensors=2, dtype=dtype)      # physical [B,S,H,D]
+    table = synth.rope_table_2d(32, dtype=dtype)
+    xg = x.to(DEV).transpose(1, 2).requires_grad_(True)
+    y = L.my_rope_fn(xg, table.to(DEV))
+    assert y.stride() == xg.stride()
+    assert torch.equal(y.cpu(), O.rope_fwd(x.transpose(1, 2), table))
+    y.backward(dy.to(DEV).transpose(1, 2))
+    assert torch.equal(xg.grad.cpu(), O.rope_bwd(dy.transpose(1, 2), table))
+
+
+def test_rope_matches_reference_golden():
+    L = _ops()
+    g = load_golden("rope_fp32.npz")
+    B, H, S, D = [int(s) for s in g["shape"]]
+    x, dy = synth.gaussian_qkv(int(g["seed"]), B, S, H, D, n_tensors=2)
+    table = synth.rope_table_2d(16).to(DEV)
+    assert np.array_equal(L.my_rope_fn(x.to(DEV).transpose(1, 2), table).cpu().numpy(), g["y"])
+
+
+# ------------------------------------------------------------------ selection
+@pytest.mark.parametrize("dtype,n", [(torch.float32, 64), (torch.bfloat16, 64), (torch.bfloat16, 256), (torch.bfloat16, 2048)])
+def test_coarse_topk(dtype, n):
+    L = _ops()
+    pq, pk = synth.gaussian_qkv(35, 2, 2, n, 64, n_tensors=2, dtype=dtype)
+    pq, pk = pq * 0.25, pk * 0.25
+    got = L.gen_sparse_indices(pq.to(DEV), pk.to(DEV), 8)
+    assert got.dtype == torch.int64 and got.shape == (2, 2, n, 8)
+    want = O.gen_sparse_indices(pq, pk, 8)
+    scores = (pq.float() @ pk.float().transpose(-1, -2)).to(dtype).float()
+    differ, bad = topk_mismatch_rows(got.cpu(), want, scores, margin=2.0 ** -7 if dtype == torch.bfloat16 else 1e-6)
+    assert bad == 0
+    assert differ <= 0.01 * got.numel() / 8
+    assert (got.cpu().sort(-1).values.diff(dim=-1) > 0).all(), "duplicate block in a row"
+
+
+def test_coarse_topk_ties_go_to_smallest_index():
+    L = _ops()
+    pq = torch.zeros(1, 1, 64, 64)
+    pk = torch.zeros(1, 1, 64, 64)          # every score equal -> indices 0..7 in order
+    got = L.gen_sparse_indices(pq.to(DEV), pk.to(DEV), 8)
+    assert torch.equal(got.cpu(), torch.arange(8).expand(1, 1, 64, 8))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_refine_topk(dtype):
+    L = _ops()
+    pq, pk = synth.gaussian_qkv(36, 1, 2, 1024, 64, n_tensors=2, dtype=dtype)
+    pq2, pk2 = O.mean_pool1d(pq, 16), O.mean_pool1d(pk, 16)
+    pidx = O.gen_sparse_indices(pq2, pk2, 8)
+    got = L.compute_topk_indices_sparse(pq.to(DEV), pk.to(DEV), pidx.to(DEV), 8, 8, 16)
+    want = O.compute_topk_indices_sparse(pq, pk, pidx, 8, 8, 16)
+    assert got.dtype == torch.int32
+    scores = pq.float() @ pk.float().transpose(-1, -2)
+    differ, bad = topk_mismatch_rows(got.cpu(), want, scores, margin=1e-6)
+    assert bad == 0 and differ <= 2
+    # every selected block is a child of one of the parent's selected level-2 blocks
+    par = (got.cpu().long() // 16).reshape(1, 2, 64, 16, 8)
+    assert (par[..., None] == pidx[:, :, :, None, None, :]).any(-1).all()
+
+
+# ------------------------------------------------------------------ transpose
+@pytest.mark.parametrize("M,T,dtype", [(1024, 8, torch.int32), (64, 8, torch.int64), (4096, 8, torch.int32), (16384, 4, torch.int32)])
+def test_transpose_indices(M, T, dtype):
+    L = _ops()
+    gen = torch.Generator().manual_seed(M + T)
+    # skewed selection: a few hot blocks, many empty buckets
+    hot = torch.randint(0, max(M // 16, 1), (2, 3, M, T // 2), generator=gen)
+    cold = torch.randint(0, M, (2, 3, M, T - T // 2), generator=gen)
+    idx = torch.cat([hot, cold], -1).to(dtype)
+    off, flat = L.transpose_indices(idx.to(DEV))
+    want_off, want_flat = O.transpose_indices(idx)
+    assert off.dtype == torch.int64
+    assert torch.equal(off.cpu(), want_off)
+    assert torch.equal(flat.cpu().long(), want_flat)            # ascending inside each bucket, no sort needed
+    off2, flat2 = L.transpose_indices(idx.to(DEV))
+    assert torch.equal(flat, flat2) and torch.equal(off, off2)  # deterministic
+
+
+def test_transpose_matches_reference_golden():
+    L = _ops()
+    g = load_golden("l2_n16384_fp32.npz")
+    idx = torch.from_numpy(g["indices"].astype(np.int32)).to(DEV)
+    pidx = torch.from_numpy(g["p_indices"].astype(np.int64)).to(DEV)
+    assert np.array_equal(L.transpose_indices(idx)[0].cpu().numpy(), g["offsets"])
+    assert np.array_equal(L.transpose_indices(pidx)[0].cpu().numpy(), g["offsets_p"])
+
+
+# ------------------------------------------------------------------ attention, fp32, against the reference's golden vectors
+def test_llsa_l1_cfg1_fp32_vs_reference_golden():
+    L = _ops()
+    g = load_golden("l1_cfg1_fp32.npz")
+    q, k, v, do, _ = synth.make_config_inputs("cfg1")
+    assert sha(q, k, v, do) == str(g["input_sha"])
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    dbg = L.llsa_l1_debug(qg, kg, vg, 8, 16)
+    assert np.array_equal(dbg["pk"].detach().cpu().numpy(), g["pk"])
+    assert np.array_equal(dbg["indices"].cpu().numpy(), g["indices"].astype(np.int32))
+    rows = int(g["rows"])
+    assert rel_l2(dbg["lse"], g["lse"]) < 2e-5
+    dbg["o"].backward(do.to(DEV))
+    assert rel_l2(dbg["o"].detach()[:, :, ::rows], g["o"]) < 2e-5
+    for name, t in (("dq", qg), ("dk", kg), ("dv", vg)):
+        assert rel_l2(t.grad[:, :, ::rows], g[name]) < 2e-5, name
+
+
+def test_llsa_l2_fp32_vs_reference_golden():
+    L = _ops()
+    g = load_golden("l2_n16384_fp32.npz")
+    B, H, N, D = [int(s) for s in g["shape"]]
+    q, k, v, do = synth.correlated_qkv(int(g["seed"]), B, H, N, D, dtype=torch.float32)
+    assert sha(q, k, v, do) == str(g["input_sha"])
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    dbg = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
+    assert np.array_equal(dbg["pk2"].detach().cpu().numpy(), g["pk2"])
+    assert np.array_equal(dbg["p_indices"].cpu().numpy(), g["p_indices"].astype(np.int32))
+    assert np.array_equal(dbg["indices"].cpu().numpy(), g["indices"].astype(np.int32))
+    rows = int(g["rows"])
+    assert rel_l2(dbg["lse"], g["lse"]) < 2e-5
+    dbg["o"].backward(do.to(DEV))
+    assert rel_l2(dbg["o"].detach()[:, :, ::rows], g["o"]) < 2e-5
+    for name, t in (("dq", qg), ("dk", kg), ("dv", vg)):
+        assert rel_l2(t.grad[:, :, ::rows], g[name]) < 2e-5, name
+
+
+def test_l2_stage_ops_fp32_pooled_grads_vs_reference_golden():
+    """The operator with explicit pooled inputs returns separate pooled-key gradients."""
+    L = _ops()
+    g = load_golden("l2_n16384_fp32.npz")
+    B, H, N, D = [int(s) for s in g["shape"]]
+    q, k, v, do = synth.correlated_qkv(int(g["seed"]), B, H, N, D, dtype=torch.float32)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    pq, pk, pv = L.mean_pool1d(qg, 16), L.mean_pool1d(kg, 16), L.mean_pool1d(vg, 16)
+    pq2, pk2, pv2 = L.mean_pool1d(pq, 16), L.mean_pool1d(pk, 16), L.mean_pool1d(pv, 16)
+    for t in (pk, pv, pk2, pv2):
+        t.retain_grad()
+    o = L.flash_sparse_residual_attention_l2_op(qg, kg, vg, pq, pk, pv, pq2, pk2, pv2, 8, 8, 16, 256, 16)
+    o.backward(do.to(DEV))
+    rows = int(g["rows"])
+    assert rel_l2(pk.grad[:, :, ::rows], g["dpk_total"]) < 2e-5
+    assert rel_l2(pv.grad[:, :, ::rows], g["dpv_total"]) < 2e-5
+    assert rel_l2(pk2.grad, g["dpk2"]) < 2e-5 and rel_l2(pv2.grad, g["dpv2"]) < 2e-5
+    for name, t in (("dq", qg), ("dk", kg), ("dv", vg)):
+        assert rel_l2(t.grad[:, :, ::rows], g[name]) < 2e-5, name
+
+
+# ------------------------------------------------------------------ attention, bf16, against the oracle
+def _bf16_case(op, B, H, N, seed, rope=False):
+    q, k, v, do = synth.correlated_qkv(seed, B, H, N, 64, dtype=torch.bfloat16)
+    if rope:
+        table = synth.rope_table_2d(int(math.isqrt(N)), dtype=torch.bfloat16)
+        q, k = O.rope_fwd(q, table), O.rope_fwd(k, table)
+    return q, k, v, do
+
+
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_llsa_l2_bf16_vs_oracle(force_generic, monkeypatch):
+    L = _ops()
+    from llsa_b200 import ops
+    monkeypatch.setattr(ops, "_force_generic", force_generic)
+    q, k, v, do = _bf16_case("l2", 1, 2, 16384, 41)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    dbg = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
+    # selection: dtype-faithful oracle
+    sel = O.llsa_l2_fwd_bwd(q, k, v, None)
+    assert torch.equal(dbg["pk"].detach().cpu(), sel["pk"]) and torch.equal(dbg["pk2"].detach().cpu(), sel["pk2"])
+    s2 = (sel["pq2"].float() @ sel["pk2"].float().transpose(-1, -2)).to(torch.bfloat16).float()
+    differ2, bad2 = topk_mismatch_rows(dbg["p_indices"].cpu(), sel["p_indices"], s2, margin=2.0 ** -7)
+    assert bad2 == 0 and differ2 <= 2
+    # stage isolation: refine with the GPU's parents on both sides
+    want_idx = O.compute_topk_indices_sparse(sel["pq"], sel["pk"], dbg["p_indices"].cpu().long(), 8, 8, 16)
+    s1 = sel["pq"].float() @ sel["pk"].float().transpose(-1, -2)
+    differ1, bad1 = topk_mismatch_rows(dbg["indices"].cpu(), want_idx, s1, margin=1e-6)
+    assert bad1 == 0 and differ1 <= 4
+    # attention: fp32 evaluation on the same inputs and the same indices
+    idx, pidx = dbg["indices"].cpu(), dbg["p_indices"].cpu().long()
+    o_ref, lse_ref = O.attn_fwd_l2(q, k, v, sel["pk"], sel["pv"], sel["pk2"], sel["pv2"], idx, pidx, faithful=False)
+    assert_bf16_close(dbg["o"].detach(), o_ref, "o")
+    assert max_abs(dbg["lse"], lse_ref) < 2e-2
+    dbg["o"].backward(do.to(DEV))
+    ref = O.attn_bwd_l2(do, q, k, v, sel["pk"], sel["pv"], sel["pk2"], sel["pv2"], o_ref.float(), lse_ref, idx, pidx, faithful=False)
+    dq, dk, dv, dpk, dpv, dpk2, dpv2 = ref
+    dk_t = dk + O.mean_pool1d_bwd(dpk + O.mean_pool1d_bwd(dpk2, 16), 16)
+    dv_t = dv + O.mean_pool1d_bwd(dpv + O.mean_pool1d_bwd(dpv2, 16), 16)
+    assert_bf16_close(qg.grad, dq, "dq")
+    assert_bf16_close(kg.grad, dk_t, "dk")
+    assert_bf16_close(vg.grad, dv_t, "dv")
+
+
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_llsa_l1_bf16_rope_vs_oracle(force_generic, monkeypatch):
+    """BASELINE config 2 shape (N=4096, RoPE'd q/k, correlated inputs), one batch element, two heads."""
+    L = _ops()
+    from llsa_b200 import ops
+    monkeypatch.setattr(ops, "_force_generic", force_generic)
+    q, k, v, do = _bf16_case("l1", 1, 2, 4096, 42, rope=True)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    dbg = L.llsa_l1_debug(qg, kg, vg, 8, 16)
+    sel = O.llsa_l1_fwd_bwd(q, k, v, None)
+    s1 = (sel["pq"].float() @ sel["pk"].float().transpose(-1, -2)).to(torch.bfloat16).float()
+    differ, bad = topk_mismatch_rows(dbg["indices"].cpu(), sel["indices"], s1, margin=2.0 ** -7)
+    assert bad == 0 and differ <= 8
+    idx = dbg["indices"].cpu()
+    o_ref, lse_ref = O.attn_fwd_l1(q, k, v, sel["pk"], sel["pv"], idx, faithful=False)
+    assert_bf16_close(dbg["o"].detach(), o_ref, "o")
+    dbg["o"].backward(do.to(DEV))
+    dq, dk, dv, dpk, dpv = O.attn_bwd_l1(do, q, k, v, sel["pk"], sel["pv"], o_ref.float(), lse_ref, idx, faithful=False)
+    assert_bf16_close(qg.grad, dq, "dq")
+    assert_bf16_close(kg.grad, dk + O.mean_pool1d_bwd(dpk, 16), "dk")
+    assert_bf16_close(vg.grad, dv + O.mean_pool1d_bwd(dpv, 16), "dv")
+
+
+def test_llsa_l1_exact_pooled_grad_switch():
+    L = _ops()
+    q, k, v, do = synth.gaussian_qkv(43, 1, 1, 1024, 64, dtype=torch.float32)
+    r = O.llsa_l1_fwd_bwd(q, k, v, do, exact_pooled_grad=True, faithful=False)
+    try:
+        L.set_exact_pooled_grad(True)
+        qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+        L.llsa_l1(qg, kg, vg, 8, 16).backward(do.to(DEV))
+    finally:
+        L.set_exact_pooled_grad(False)
+    assert rel_l2(kg.grad, r["dk"]) < 2e-5 and rel_l2(vg.grad, r["dv"]) < 2e-5
+
+
+def test_strided_bnhd_inputs_match_contiguous():
+    """[B,H,N,D] views of [B,N,H,D] storage (what the model passes) give the same bits; o keeps q's strides."""
+    L = _ops()
+    q, k, v, do = _bf16_case("l2", 2, 3, 16384, 44)
+    to_view = lambda t: t.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)
+    qc, kc, vc = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    qs, ks, vs = [to_view(t).requires_grad_(True) for t in (q, k, v)]
+    oc = L.llsa_l2(qc, kc, vc, 8, 8, 16)
+    os_ = L.llsa_l2(qs, ks, vs, 8, 8, 16)
+    assert os_.stride() == qs.stride()
+    assert torch.equal(oc, os_)
+    oc.backward(do.to(DEV))
+    os_.backward(to_view(do))
+    assert torch.equal(qc.grad, qs.grad)
+    assert rel_l2(ks.grad, kc.grad) < 1e-3 and rel_l2(vs.grad, vc.grad) < 1e-3   # fp32 atomics: order may differ
+
+
+# ------------------------------------------------------------------ full-size properties (BASELINE config 3 shape)
+def test_cfg3_full_size_properties():
+    L = _ops()
+    q, k, v, do, _ = synth.make_config_inputs("cfg3")
+    B, H, N, D = q.shape
+    qg, kg = q.to(DEV), k.to(DEV)
+    # (1) softmax weights sum to one: v == 1 everywhere -> every pooled v is 1 -> o == 1
+    ones = torch.ones_like(qg)
+    dbg = L.llsa_l2_debug(qg, kg, ones, 8, 8, 16)
+    assert float((dbg["o"].float() - 1).abs().max()) <= 2.0 ** -7
+    idx, pidx = dbg["indices"], dbg["p_indices"]
+    assert int(idx.min()) >= 0 and int(idx.max()) < N // 16 and int(pidx.max()) < N // 256
+    assert (idx.long().sort(-1).values.diff(dim=-1) > 0).all()                       # 8 distinct blocks per row
+    assert ((idx.long() // 16).reshape(B, H, N // 256, 16, 8)[..., None] == pidx.long()[:, :, :, None, None, :]).any(-1).all()
+    # (2) CSR: totals and sortedness
+    off, flat = L.transpose_indices(idx)
+    assert int(off[..., -1].min()) == N // 16 * 8 and int(off[..., 0].max()) == 0
+    assert (off.diff(dim=-1) >= 0).all()
+    cnt = torch.zeros(B * H, N // 16, dtype=torch.long, device=DEV).scatter_add_(
+        1, idx.long().reshape(B * H, -1), torch.ones(B * H, N // 16 * 8, dtype=torch.long, device=DEV))
+    assert torch.equal(off.reshape(B * H, -1).diff(dim=-1), cnt)
+    # (3) gradient checksum: attention weights sum to one, so sum_tokens dv == sum_rows do per (b,h,channel)
+    vg = v.to(DEV).requires_grad_(True)
+    qg.requires_grad_(True)
+    kg.requires_grad_(True)
+    o = L.llsa_l2(qg, kg, vg, 8, 8, 16)
+    dog = do.to(DEV)
+    o.backward(dog)
+    lhs, rhs = vg.grad.float().sum(2), dog.float().sum(2)
+    assert rel_l2(lhs, rhs) < 5e-3
+    # (4) softmax shift invariance: sum_d dq.q == sum_d dk.k per head (both equal sum ds*s)
+    a = (qg.grad.float() * qg.detach().float()).sum((2, 3))
+    b = (kg.grad.float() * kg.detach().float()).sum((2, 3))
+    assert rel_l2(a, b) < 2e-2
+    # (5) the same call twice gives the same forward bits and indices
+    dbg2 = L.llsa_l2_debug(qg.detach(), kg.detach(), ones, 8, 8, 16)
+    assert torch.equal(dbg2["indices"], idx) and torch.equal(dbg2["o"], dbg["o"])
