@@ -42,6 +42,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg3")
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling a smaller case)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     return ap.parse_args()
@@ -139,7 +140,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     cfg = synth.CONFIGS[args.config]
-    B, H, N, D = cfg["B"], cfg["H"], cfg["N"], cfg["D"]
+    B, H, N, D = args.batch or cfg["B"], cfg["H"], cfg["N"], cfg["D"]
     fn = llsa_b200.llsa_l2 if cfg["op"] == "llsa_l2" else llsa_b200.llsa_l1
     call = (lambda q, k, v: fn(q, k, v, 8, 8, 16)) if cfg["op"] == "llsa_l2" else (lambda q, k, v: fn(q, k, v, 8, 16))
 

@@ -20,13 +20,13 @@ def sha(*tensors):
 
 
 def rel_l2(a, b):
-    a = torch.as_tensor(a).double().cpu()
-    b = torch.as_tensor(b).double().cpu()
+    a = torch.as_tensor(a).detach().double().cpu()
+    b = torch.as_tensor(b).detach().double().cpu()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
 
 
 def max_abs(a, b):
-    return float((torch.as_tensor(a).double().cpu() - torch.as_tensor(b).double().cpu()).abs().max())
+    return float((torch.as_tensor(a).detach().double().cpu() - torch.as_tensor(b).detach().double().cpu()).abs().max())
 
 
 def topk_mismatch_rows(idx_a, idx_b, scores, margin=1e-6):

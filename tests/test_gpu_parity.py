@@ -7,9 +7,8 @@ Tolerances
     the differing entries agree within 1e-6 (exact ties / last-ulp accumulation
     order), which are counted and bounded.
   * fp32 tensors: rel-L2 <= 2e-5 against the fp32 reference values.
-  * bf16 tensors (o, dq, dk, dv): rel-L2 <= 1e-2 and |err| <= 2e-2 + 2^-7*|ref|
-    against an fp32 evaluation on the same (bf16) inputs and the same indices;
-    the second term is the rounding of the bf16 result itself.
+  * bf16 tensors (o, dq, dk, dv): rel-L2 <= 1e-2 and max |err| <= 2e-2 against
+    an fp32 evaluation on the same (bf16) inputs and the same indices.
 """
 import math
 
@@ -34,10 +33,8 @@ def assert_bf16_close(got, ref, name):
     got, ref = got.float().cpu(), ref.float().cpu()
     r = rel_l2(got, ref)
     err = (got - ref).abs()
-    bound = 2e-2 + ref.abs() * 2.0 ** -7
-    worst = float((err - bound).max())
     assert r <= 1e-2, "%s: rel-L2 %.3e" % (name, r)
-    assert worst <= 0, "%s: |err| exceeds 2e-2 + 2^-7|ref| by %.3e (max err %.3e)" % (name, worst, float(err.max()))
+    assert float(err.max()) <= 2e-2, "%s: max |err| %.3e" % (name, float(err.max()))
 
 
 # ------------------------------------------------------------------ pooling / rope
