@@ -67,6 +67,8 @@ int build_attn_params_check(const LlsaAttnArgs* g, bool bwd);
 template <typename T>
 AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd);
 
+bool mma_path_ok(const LlsaAttnArgs* g, bool bwd);   // operands meet the tensor-core kernels' alignment / top-k limits
+int pooled_smem_tiles(int n_pooled);                 // pooled key tiles a CTA keeps in shared memory
 int launch_attn_fwd_generic(const LlsaAttnArgs* g, cudaStream_t st);
 int launch_attn_bwd_generic(const LlsaAttnArgs* g, cudaStream_t st);
 int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st);

@@ -2,15 +2,19 @@
 // Reference: sparse_indices_attn_res_scatter_bwd_v2 (sparse_attention_res_1.py:403-471)
 // and sparse_indices_attn_res_scatter_2_2_bwd_v2 (sparse_attention_res_2.py:578-681).
 //
-// Three kernels, all with register-direct operand fragments (mma_frag.cuh):
+// Three kernels on mma.sync.m16n8k16 with the operand fragments of mma_frag.cuh:
 //   attn_dq_mma_kernel     one warp per query block: delta = rowsum(o*do) (the
 //                          reference's separate _attn_bwd_preprocess pass), then
 //                          S, dP and dQ over the fine, pooled-1 and pooled-2 keys.
+//                          Pooled K/V tiles are shared by the CTA through shared
+//                          memory (cp.async), fine blocks stream from global memory.
 //   attn_dkv_pooled_kernel one CTA per group of 16 query blocks (= one parent):
-//                          its warps share out the pooled key tiles the group
-//                          attends to, run the transposed products S^T, dP^T,
-//                          dV += P^T.dO, dK += dS^T.Q over the group's 256 rows and
-//                          add the 16x64 results into fp32 accumulators.
+//                          the group's 256 rows of Q and dO (+ lse, delta) are
+//                          staged once in shared memory; the warps share out the
+//                          pooled key tiles the group attends to, run the transposed
+//                          products S^T, dP^T, dV += P^T.dO, dK += dS^T.Q over the
+//                          16 query blocks and add the 16x64 results into fp32
+//                          accumulators (one red.add per element and group).
 //   attn_dkv_fine_kernel   one CTA per KV block: its warps share out the block's
 //                          CSR list of query blocks, partial sums meet in shared
 //                          memory, and the epilogue folds in the pooling backward
@@ -24,30 +28,6 @@ namespace llsa {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-struct BwdBlockRef {
-  const bf16* k;
-  const bf16* v;
-  int64_t ks, vs;
-  float lw;
-};
-
-__device__ __forceinline__ BwdBlockRef resolve_bwd_block(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int i, int my_fine, int my_p1,
-                                                         float lw1, float lw2) {
-  BwdBlockRef r;
-  if (i < a.topk) {
-    const int64_t j = __shfl_sync(0xffffffffu, my_fine, i);
-    r.k = a.k.row(b, h, j * kBS); r.v = a.v.row(b, h, j * kBS); r.ks = a.k.sn; r.vs = a.v.sn; r.lw = 0.f;
-  } else if (i < a.topk + a.p1_blocks) {
-    const int ii = i - a.topk;
-    const int64_t j = a.two_level ? (int64_t) __shfl_sync(0xffffffffu, my_p1, ii) : (int64_t) ii;
-    r.k = a.pk + (bh * a.n1 + j * kBS) * kD; r.v = a.pv + (bh * a.n1 + j * kBS) * kD; r.ks = r.vs = kD; r.lw = lw1;
-  } else {
-    const int64_t j = i - a.topk - a.p1_blocks;
-    r.k = a.pk2 + (bh * a.n2 + j * kBS) * kD; r.v = a.pv2 + (bh * a.n2 + j * kBS) * kD; r.ks = r.vs = kD; r.lw = lw2;
-  }
-  return r;
-}
-
 __device__ __forceinline__ float rowfrag_dot(const RowFrag& x, const RowFrag& y) {
   float acc = 0.f;
 #pragma unroll
@@ -58,13 +38,80 @@ __device__ __forceinline__ float rowfrag_dot(const RowFrag& x, const RowFrag& y)
   return acc;
 }
 
+struct DqRow {
+  float L0, L1, delta0, delta1;   // lse (log2 domain) and delta of rows g and g+8
+};
+
+// dS (bf16, as A registers) of one 16-key block from its S and dP accumulators
+__device__ __forceinline__ void dq_ds(float (&s0)[4], float (&s1)[4], const float (&p0)[4], const float (&p1)[4], const DqRow& r, float sl2,
+                                      float lw, uint32_t (&da)[4]) {
+  // ds = w * exp(s*scale - lse) * (dp - delta)
+  s0[0] = fast_exp2(fmaf(s0[0], sl2, lw - r.L0)) * (p0[0] - r.delta0);
+  s0[1] = fast_exp2(fmaf(s0[1], sl2, lw - r.L0)) * (p0[1] - r.delta0);
+  s0[2] = fast_exp2(fmaf(s0[2], sl2, lw - r.L1)) * (p0[2] - r.delta1);
+  s0[3] = fast_exp2(fmaf(s0[3], sl2, lw - r.L1)) * (p0[3] - r.delta1);
+  s1[0] = fast_exp2(fmaf(s1[0], sl2, lw - r.L0)) * (p1[0] - r.delta0);
+  s1[1] = fast_exp2(fmaf(s1[1], sl2, lw - r.L0)) * (p1[1] - r.delta0);
+  s1[2] = fast_exp2(fmaf(s1[2], sl2, lw - r.L1)) * (p1[2] - r.delta1);
+  s1[3] = fast_exp2(fmaf(s1[3], sl2, lw - r.L1)) * (p1[3] - r.delta1);
+  da[0] = pack_bf16(s0[0], s0[1]); da[1] = pack_bf16(s0[2], s0[3]); da[2] = pack_bf16(s1[0], s1[1]); da[3] = pack_bf16(s1[2], s1[3]);
+}
+
+struct GlobalKV {
+  const bf16* k;
+  const bf16* v;
+  int64_t ks, vs;
+  float lw;
+};
+
+__device__ __forceinline__ GlobalKV global_kv(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t qb, int gi, int my_fine,
+                                              int n_smem_tiles, float lw1, float lw2) {
+  GlobalKV r;
+  if (gi < a.topk) {
+    const int64_t j = __shfl_sync(0xffffffffu, my_fine, gi);
+    r.k = a.k.row(b, h, j * kBS); r.v = a.v.row(b, h, j * kBS); r.ks = a.k.sn; r.vs = a.v.sn; r.lw = 0.f;
+  } else {
+    const int ip = n_smem_tiles + gi - a.topk;
+    if (ip < a.p1_blocks) {
+      const int64_t off = (bh * a.n1 + p1_block(a, bh, qb, ip) * kBS) * kD;
+      r.k = a.pk + off; r.v = a.pv + off; r.lw = lw1;
+    } else {
+      const int64_t off = (bh * a.n2 + (int64_t) (ip - a.p1_blocks) * kBS) * kD;
+      r.k = a.pk2 + off; r.v = a.pv2 + off; r.lw = lw2;
+    }
+    r.ks = r.vs = kD;
+  }
+  return r;
+}
+
+__device__ __forceinline__ void stage_pooled_tiles_bwd(const AttnP<bf16>& a, int64_t bh, int64_t qb0, int n_tiles, bf16* sk, bf16* sv) {
+  for (int c = threadIdx.x; c < n_tiles * kBS * 8; c += blockDim.x) {
+    const int tile = c >> 7, row = (c >> 3) & 15, ch = (c & 7) * 8;
+    const bf16 *gk, *gv;
+    if (tile < a.p1_blocks) {
+      const int64_t off = (bh * a.n1 + p1_block(a, bh, qb0, tile) * kBS + row) * kD + ch;
+      gk = a.pk + off; gv = a.pv + off;
+    } else {
+      const int64_t off = (bh * a.n2 + (int64_t) (tile - a.p1_blocks) * kBS + row) * kD + ch;
+      gk = a.pk2 + off; gv = a.pv2 + off;
+    }
+    const int so = (tile * kBS + row) * kSmemPitch + ch;
+    cp_async16(sk + so, gk);
+    cp_async16(sv + so, gv);
+  }
+  cp_async_commit();
+}
+
 template <int NW>
-__global__ void __launch_bounds__(NW * 32) attn_dq_mma_kernel(AttnP<bf16> a) {
+__global__ void __launch_bounds__(NW * 32, 3) attn_dq_mma_kernel(AttnP<bf16> a, int n_smem_tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sk = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sv = sk + n_smem_tiles * kBS * kSmemPitch;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int64_t qb = (int64_t) blockIdx.x * NW + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  if (qb >= a.n1) return;
+  const int64_t qb0 = (int64_t) blockIdx.x * NW, qb = qb0 + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  stage_pooled_tiles_bwd(a, bh, qb0, n_smem_tiles, sk, sv);
+
   const int my_fine = lane < a.topk ? (int) fine_block(a, bh, qb, lane) : 0;
-  const int my_p1 = (a.two_level && lane < a.topk_p) ? (int) p1_block(a, bh, qb, lane) : 0;
   const float lw1 = log2f(a.w1), lw2 = log2f(a.w2);
   const float sl2 = a.scale * kLog2e;
 
@@ -73,60 +120,97 @@ __global__ void __launch_bounds__(NW * 32) attn_dq_mma_kernel(AttnP<bf16> a) {
   load_rowfrag(qhi, a.q.row(b, h, qb * kBS + g + 8), t);
   load_rowfrag(dlo, a.d_o.row(b, h, qb * kBS + g), t);
   load_rowfrag(dhi, a.d_o.row(b, h, qb * kBS + g + 8), t);
-  float delta0, delta1;
+  DqRow row;
   {
     RowFrag olo, ohi;
     load_rowfrag(olo, a.o_in.row(b, h, qb * kBS + g), t);
     load_rowfrag(ohi, a.o_in.row(b, h, qb * kBS + g + 8), t);
-    delta0 = quad_sum(rowfrag_dot(olo, dlo));
-    delta1 = quad_sum(rowfrag_dot(ohi, dhi));
+    row.delta0 = quad_sum(rowfrag_dot(olo, dlo));
+    row.delta1 = quad_sum(rowfrag_dot(ohi, dhi));
   }
   const int64_t rbase = bh * a.N + qb * kBS;
-  if (t == 0) { a.delta[rbase + g] = delta0; a.delta[rbase + g + 8] = delta1; }
-  const float L0 = a.lse[rbase + g] * kLog2e, L1 = a.lse[rbase + g + 8] * kLog2e;
+  if (t == 0) { a.delta[rbase + g] = row.delta0; a.delta[rbase + g + 8] = row.delta1; }
+  row.L0 = a.lse[rbase + g] * kLog2e;
+  row.L1 = a.lse[rbase + g + 8] * kLog2e;
 
   float dq[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) dq[j][0] = dq[j][1] = dq[j][2] = dq[j][3] = 0.f;
 
-  const int nblk = a.topk + a.p1_blocks + a.p2_blocks;
-  BwdBlockRef r = resolve_bwd_block(a, b, h, bh, 0, my_fine, my_p1, lw1, lw2);
-  RowFrag k0, k1, v0, v1;
-  load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
-  load_rowfrag(k1, r.k + (int64_t) (g + 8) * r.ks, t);
-  load_rowfrag(v0, r.v + (int64_t) g * r.vs, t);
-  load_rowfrag(v1, r.v + (int64_t) (g + 8) * r.vs, t);
-  for (int i = 0; i < nblk; ++i) {
-    ColFrag kc;
-    load_colfrag(kc, r.k, r.ks, g, t);
-    const float lw = r.lw;
+  const int n_pooled = a.p1_blocks + a.p2_blocks;
+  const int n_glob = a.topk + (n_pooled - n_smem_tiles);
+  {
+    GlobalKV r = global_kv(a, b, h, bh, qb, 0, my_fine, n_smem_tiles, lw1, lw2);
+    RowFrag k0, k1, v0, v1;
+    load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
+    load_rowfrag(k1, r.k + (int64_t) (g + 8) * r.ks, t);
+    load_rowfrag(v0, r.v + (int64_t) g * r.vs, t);
+    load_rowfrag(v1, r.v + (int64_t) (g + 8) * r.vs, t);
+    for (int gi = 0; gi < n_glob; ++gi) {
+      if (gi + 2 < n_glob) {   // two blocks ahead: K rows (lanes 0..15) and V rows (lanes 16..31) towards L1
+        const GlobalKV f = global_kv(a, b, h, bh, qb, gi + 2, my_fine, n_smem_tiles, lw1, lw2);
+        if (lane < 16) prefetch_tile_rows(f.k, f.ks, lane);
+        else prefetch_tile_rows(f.v, f.vs, lane - 16);
+      }
+      ColFrag kc;
+      load_colfrag(kc, r.k, r.ks, g, t);
+      const float lw = r.lw;
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_rows_x_keys(s0, s1, qlo, qhi, k0, k1);
+      mma_rows_x_keys(p0, p1, dlo, dhi, v0, v1);
+      if (gi + 1 < n_glob) {
+        r = global_kv(a, b, h, bh, qb, gi + 1, my_fine, n_smem_tiles, lw1, lw2);
+        load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
+        load_rowfrag(k1, r.k + (int64_t) (g + 8) * r.ks, t);
+        load_rowfrag(v0, r.v + (int64_t) g * r.vs, t);
+        load_rowfrag(v1, r.v + (int64_t) (g + 8) * r.vs, t);
+      }
+      uint32_t da[4];
+      dq_ds(s0, s1, p0, p1, row, sl2, lw, da);
+      mma_x_cols(dq, da[0], da[1], da[2], da[3], kc);
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  for (int ip = 0; ip < n_smem_tiles; ++ip) {
+    const bf16* tk = sk + ip * kBS * kSmemPitch;
+    const bf16* tv = sv + ip * kBS * kSmemPitch;
+    RowFrag k0, k1, v0, v1;
+    load_rowfrag_smem(k0, tk + g * kSmemPitch, t);
+    load_rowfrag_smem(k1, tk + (g + 8) * kSmemPitch, t);
+    load_rowfrag_smem(v0, tv + g * kSmemPitch, t);
+    load_rowfrag_smem(v1, tv + (g + 8) * kSmemPitch, t);
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
     mma_rows_x_keys(s0, s1, qlo, qhi, k0, k1);
     mma_rows_x_keys(p0, p1, dlo, dhi, v0, v1);
-    if (i + 1 < nblk) {
-      r = resolve_bwd_block(a, b, h, bh, i + 1, my_fine, my_p1, lw1, lw2);
-      load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
-      load_rowfrag(k1, r.k + (int64_t) (g + 8) * r.ks, t);
-      load_rowfrag(v0, r.v + (int64_t) g * r.vs, t);
-      load_rowfrag(v1, r.v + (int64_t) (g + 8) * r.vs, t);
-    }
-    // ds = w * exp(s*scale - lse) * (dp - delta)
-    s0[0] = fast_exp2(fmaf(s0[0], sl2, lw - L0)) * (p0[0] - delta0);
-    s0[1] = fast_exp2(fmaf(s0[1], sl2, lw - L0)) * (p0[1] - delta0);
-    s0[2] = fast_exp2(fmaf(s0[2], sl2, lw - L1)) * (p0[2] - delta1);
-    s0[3] = fast_exp2(fmaf(s0[3], sl2, lw - L1)) * (p0[3] - delta1);
-    s1[0] = fast_exp2(fmaf(s1[0], sl2, lw - L0)) * (p1[0] - delta0);
-    s1[1] = fast_exp2(fmaf(s1[1], sl2, lw - L0)) * (p1[1] - delta0);
-    s1[2] = fast_exp2(fmaf(s1[2], sl2, lw - L1)) * (p1[2] - delta1);
-    s1[3] = fast_exp2(fmaf(s1[3], sl2, lw - L1)) * (p1[3] - delta1);
-    mma_x_cols(dq, pack_bf16(s0[0], s0[1]), pack_bf16(s0[2], s0[3]), pack_bf16(s1[0], s1[1]), pack_bf16(s1[2], s1[3]), kc);
+    uint32_t da[4];
+    dq_ds(s0, s1, p0, p1, row, sl2, ip < a.p1_blocks ? lw1 : lw2, da);
+    ColFrag kc;
+    load_colfrag_smem(kc, tk, g, t);
+    mma_x_cols(dq, da[0], da[1], da[2], da[3], kc);
   }
   store_acc_row<0>(a.dq.row(b, h, qb * kBS + g), dq, t, a.scale);
   store_acc_row<1>(a.dq.row(b, h, qb * kBS + g + 8), dq, t, a.scale);
 }
 
-// One (key tile) x (query block) step of the dK/dV side.  ka/kb, va/vb: the key
-// tile's rows g / g+8 as the A operand.  Accumulates dV += P^T.dO, dK += dS^T.Q (unscaled).
+// P^T and dS^T (bf16, as A registers) of one (key tile) x (query block) pair from the
+// transposed accumulators: rows = keys (g, g+8), columns = query rows (tile 0: 0..7, tile 1: 8..15).
+__device__ __forceinline__ void dkv_p_ds(float (&s0)[4], float (&s1)[4], float (&e0)[4], float (&e1)[4], float2 la, float2 lb, float2 da,
+                                         float2 db, float sl2, float lw, uint32_t (&pa)[4], uint32_t (&ea)[4]) {
+  const float a0 = lw - la.x * kLog2e, a1 = lw - la.y * kLog2e, b0 = lw - lb.x * kLog2e, b1 = lw - lb.y * kLog2e;
+  // c0: (key g, row 2t)  c1: (key g, row 2t+1)  c2: (key g+8, row 2t)  c3: (key g+8, row 2t+1)
+  s0[0] = fast_exp2(fmaf(s0[0], sl2, a0)); s0[1] = fast_exp2(fmaf(s0[1], sl2, a1));
+  s0[2] = fast_exp2(fmaf(s0[2], sl2, a0)); s0[3] = fast_exp2(fmaf(s0[3], sl2, a1));
+  s1[0] = fast_exp2(fmaf(s1[0], sl2, b0)); s1[1] = fast_exp2(fmaf(s1[1], sl2, b1));
+  s1[2] = fast_exp2(fmaf(s1[2], sl2, b0)); s1[3] = fast_exp2(fmaf(s1[3], sl2, b1));
+  e0[0] = s0[0] * (e0[0] - da.x); e0[1] = s0[1] * (e0[1] - da.y); e0[2] = s0[2] * (e0[2] - da.x); e0[3] = s0[3] * (e0[3] - da.y);
+  e1[0] = s1[0] * (e1[0] - db.x); e1[1] = s1[1] * (e1[1] - db.y); e1[2] = s1[2] * (e1[2] - db.x); e1[3] = s1[3] * (e1[3] - db.y);
+  pa[0] = pack_bf16(s0[0], s0[1]); pa[1] = pack_bf16(s0[2], s0[3]); pa[2] = pack_bf16(s1[0], s1[1]); pa[3] = pack_bf16(s1[2], s1[3]);
+  ea[0] = pack_bf16(e0[0], e0[1]); ea[1] = pack_bf16(e0[2], e0[3]); ea[2] = pack_bf16(e1[0], e1[1]); ea[3] = pack_bf16(e1[2], e1[3]);
+}
+
+// One (key tile) x (query block) step of the dK/dV side with Q and dO read from global memory.
+// ka/kb, va/vb: the key tile's rows g / g+8 as the A operand.  dV += P^T.dO, dK += dS^T.Q (unscaled).
 __device__ __forceinline__ void dkv_step(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t qb, const RowFrag& ka, const RowFrag& kb,
                                          const RowFrag& va, const RowFrag& vb, float lw, float sl2, int g, int t, float (&dk)[8][4],
                                          float (&dv)[8][4]) {
@@ -138,42 +222,54 @@ __device__ __forceinline__ void dkv_step(const AttnP<bf16>& a, int64_t b, int64_
   load_rowfrag(d0, dp + (int64_t) g * a.d_o.sn, t);
   load_rowfrag(d1, dp + (int64_t) (g + 8) * a.d_o.sn, t);
   ColFrag qc, dc;
-  load_colfrag(qc, qp, a.q.sn, g, t);
   load_colfrag(dc, dp, a.d_o.sn, g, t);
+  load_colfrag(qc, qp, a.q.sn, g, t);
   const int64_t rbase = bh * a.N + qb * kBS;
   const float2 la = *reinterpret_cast<const float2*>(a.lse + rbase + 2 * t);        // query rows 2t, 2t+1
   const float2 lb = *reinterpret_cast<const float2*>(a.lse + rbase + 8 + 2 * t);    // query rows 8+2t, 9+2t
   const float2 da = *reinterpret_cast<const float2*>(a.delta + rbase + 2 * t);
   const float2 db = *reinterpret_cast<const float2*>(a.delta + rbase + 8 + 2 * t);
-  // transposed tiles: rows = keys (g, g+8), columns = query rows (tile 0: 0..7, tile 1: 8..15)
   float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
   mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
   mma_rows_x_keys(e0, e1, va, vb, d0, d1);
-  const float a0 = lw - la.x * kLog2e, a1 = lw - la.y * kLog2e, b0 = lw - lb.x * kLog2e, b1 = lw - lb.y * kLog2e;
-  // c0: (key g, row 2t)  c1: (key g, row 2t+1)  c2: (key g+8, row 2t)  c3: (key g+8, row 2t+1)
-  s0[0] = fast_exp2(fmaf(s0[0], sl2, a0)); s0[1] = fast_exp2(fmaf(s0[1], sl2, a1));
-  s0[2] = fast_exp2(fmaf(s0[2], sl2, a0)); s0[3] = fast_exp2(fmaf(s0[3], sl2, a1));
-  s1[0] = fast_exp2(fmaf(s1[0], sl2, b0)); s1[1] = fast_exp2(fmaf(s1[1], sl2, b1));
-  s1[2] = fast_exp2(fmaf(s1[2], sl2, b0)); s1[3] = fast_exp2(fmaf(s1[3], sl2, b1));
-  e0[0] = s0[0] * (e0[0] - da.x); e0[1] = s0[1] * (e0[1] - da.y); e0[2] = s0[2] * (e0[2] - da.x); e0[3] = s0[3] * (e0[3] - da.y);
-  e1[0] = s1[0] * (e1[0] - db.x); e1[1] = s1[1] * (e1[1] - db.y); e1[2] = s1[2] * (e1[2] - db.x); e1[3] = s1[3] * (e1[3] - db.y);
-  mma_x_cols(dv, pack_bf16(s0[0], s0[1]), pack_bf16(s0[2], s0[3]), pack_bf16(s1[0], s1[1]), pack_bf16(s1[2], s1[3]), dc);
-  mma_x_cols(dk, pack_bf16(e0[0], e0[1]), pack_bf16(e0[2], e0[3]), pack_bf16(e1[0], e1[1]), pack_bf16(e1[2], e1[3]), qc);
+  uint32_t pa[4], ea[4];
+  dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, lw, pa, ea);
+  mma_x_cols(dv, pa[0], pa[1], pa[2], pa[3], dc);
+  mma_x_cols(dk, ea[0], ea[1], ea[2], ea[3], qc);
 }
 
 template <int NW>
-__global__ void __launch_bounds__(NW * 32) attn_dkv_pooled_kernel(AttnP<bf16> a) {
+__global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sq = reinterpret_cast<bf16*>(smem_raw);              // [256][kSmemPitch]
+  bf16* sd = sq + kBS * kBS * kSmemPitch;                    // [256][kSmemPitch]
+  float* sl = reinterpret_cast<float*>(sd + kBS * kBS * kSmemPitch);   // lse [256]
+  float* sdel = sl + kBS * kBS;                                        // delta [256]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int64_t grp = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const float sl2 = a.scale * kLog2e;
+  // stage the group's 256 rows of Q and dO
+  const int64_t row0 = grp * kBS * kBS;
+  for (int c = threadIdx.x; c < kBS * kBS * 8; c += blockDim.x) {
+    const int r = c >> 3, ch = (c & 7) * 8;
+    cp_async16(sq + r * kSmemPitch + ch, a.q.row(b, h, row0 + r) + ch);
+    cp_async16(sd + r * kSmemPitch + ch, a.d_o.row(b, h, row0 + r) + ch);
+  }
+  cp_async_commit();
+  for (int r = threadIdx.x; r < kBS * kBS; r += blockDim.x) {
+    sl[r] = a.lse[bh * a.N + row0 + r];
+    sdel[r] = a.delta[bh * a.N + row0 + r];
+  }
+  cp_async_wait_all();
+  __syncthreads();
+
   const int ntiles = a.p1_blocks + a.p2_blocks;
   for (int i = warp; i < ntiles; i += NW) {
     const bf16 *kp, *vp;
     float *gk, *gv;
     float lw;
     if (i < a.p1_blocks) {
-      const int64_t j = p1_block(a, bh, grp * kBS, i);
-      const int64_t off = (bh * a.n1 + j * kBS) * kD;
+      const int64_t off = (bh * a.n1 + p1_block(a, bh, grp * kBS, i) * kBS) * kD;
       kp = a.pk + off; vp = a.pv + off; gk = a.dpk + off; gv = a.dpv + off; lw = log2f(a.kvw1);
     } else {
       const int64_t off = (bh * a.n2 + (int64_t) (i - a.p1_blocks) * kBS) * kD;
@@ -187,19 +283,43 @@ __global__ void __launch_bounds__(NW * 32) attn_dkv_pooled_kernel(AttnP<bf16> a)
     float dk[8][4], dv[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) dk[j][0] = dk[j][1] = dk[j][2] = dk[j][3] = dv[j][0] = dv[j][1] = dv[j][2] = dv[j][3] = 0.f;
-    for (int qi = 0; qi < kBS; ++qi) dkv_step(a, b, h, bh, grp * kBS + qi, ka, kb, va, vb, lw, sl2, g, t, dk, dv);
-    // accumulator tile j: channels 16t + j (c0, c2) and 16t + 8 + j (c1, c3); rows g (c0, c1) and g + 8 (c2, c3)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      atomicAdd(gk + g * kD + 16 * t + j, dk[j][0] * a.scale);
-      atomicAdd(gk + g * kD + 16 * t + 8 + j, dk[j][1] * a.scale);
-      atomicAdd(gk + (g + 8) * kD + 16 * t + j, dk[j][2] * a.scale);
-      atomicAdd(gk + (g + 8) * kD + 16 * t + 8 + j, dk[j][3] * a.scale);
-      atomicAdd(gv + g * kD + 16 * t + j, dv[j][0]);
-      atomicAdd(gv + g * kD + 16 * t + 8 + j, dv[j][1]);
-      atomicAdd(gv + (g + 8) * kD + 16 * t + j, dv[j][2]);
-      atomicAdd(gv + (g + 8) * kD + 16 * t + 8 + j, dv[j][3]);
+#pragma unroll 1
+    for (int qi = 0; qi < kBS; ++qi) {
+      const bf16* tq = sq + qi * kBS * kSmemPitch;
+      const bf16* td = sd + qi * kBS * kSmemPitch;
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        RowFrag q0, q1;
+        load_rowfrag_smem(q0, tq + g * kSmemPitch, t);
+        load_rowfrag_smem(q1, tq + (g + 8) * kSmemPitch, t);
+        mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
+      }
+      {
+        RowFrag d0, d1;
+        load_rowfrag_smem(d0, td + g * kSmemPitch, t);
+        load_rowfrag_smem(d1, td + (g + 8) * kSmemPitch, t);
+        mma_rows_x_keys(e0, e1, va, vb, d0, d1);
+      }
+      const float2 la = *reinterpret_cast<const float2*>(sl + qi * kBS + 2 * t), lb = *reinterpret_cast<const float2*>(sl + qi * kBS + 8 + 2 * t);
+      const float2 da = *reinterpret_cast<const float2*>(sdel + qi * kBS + 2 * t), db = *reinterpret_cast<const float2*>(sdel + qi * kBS + 8 + 2 * t);
+      uint32_t pa[4], ea[4];
+      dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, lw, pa, ea);
+      {
+        ColFrag dc;
+        load_colfrag_smem(dc, td, g, t);
+        mma_x_cols(dv, pa[0], pa[1], pa[2], pa[3], dc);
+      }
+      {
+        ColFrag qc;
+        load_colfrag_smem(qc, tq, g, t);
+        mma_x_cols(dk, ea[0], ea[1], ea[2], ea[3], qc);
+      }
     }
+    // a lane owns channels [16t, 16t+16) of key rows g and g+8: four 128-bit reductions per row
+    red_acc_row<0>(gk + g * kD, dk, t, a.scale);
+    red_acc_row<1>(gk + (g + 8) * kD, dk, t, a.scale);
+    red_acc_row<0>(gv + g * kD, dv, t, 1.f);
+    red_acc_row<1>(gv + (g + 8) * kD, dv, t, 1.f);
   }
 }
 
@@ -220,6 +340,8 @@ __global__ void __launch_bounds__(NW * 32) attn_dkv_fine_kernel(AttnP<bf16> a) {
   float dk[8][4], dv[8][4];
 #pragma unroll
   for (int u = 0; u < 8; ++u) dk[u][0] = dk[u][1] = dk[u][2] = dk[u][3] = dv[u][0] = dv[u][1] = dv[u][2] = dv[u][3] = 0.f;
+  const bool empty = list0 == list1;      // nobody selected this block: only the pooling-backward term remains
+  if (empty && warp > 0) return;
   if (list0 + warp < list1) {
     const bf16* kp = a.k.row(b, h, j * kBS);
     const bf16* vp = a.v.row(b, h, j * kBS);
@@ -232,6 +354,12 @@ __global__ void __launch_bounds__(NW * 32) attn_dkv_fine_kernel(AttnP<bf16> a) {
     for (int64_t it = list0 + warp; it < list1; it += NW) {
       int64_t qb = fl[it];
       qb = qb < 0 ? 0 : (qb >= a.n1 ? a.n1 - 1 : qb);
+      if (it + NW < list1) {   // next entry's Q (lanes 0..15) and dO (lanes 16..31) rows towards L1
+        int64_t qn = fl[it + NW];
+        qn = qn < 0 ? 0 : (qn >= a.n1 ? a.n1 - 1 : qn);
+        if (lane < 16) prefetch_tile_rows(a.q.row(b, h, qn * kBS), a.q.sn, lane);
+        else prefetch_tile_rows(a.d_o.row(b, h, qn * kBS), a.d_o.sn, lane - 16);
+      }
       dkv_step(a, b, h, bh, qb, ka, kb, va, vb, 0.f, sl2, g, t, dk, dv);
     }
   }
@@ -245,17 +373,19 @@ __global__ void __launch_bounds__(NW * 32) attn_dkv_fine_kernel(AttnP<bf16> a) {
         red[warp - 1][32 + u * 4 + c][lane] = dv[u][c];
       }
   }
-  __syncthreads();
+  if (!empty) __syncthreads();
   if (warp == 0) {
+    if (!empty) {
 #pragma unroll
-    for (int w = 0; w < NW - 1; ++w)
+      for (int w = 0; w < NW - 1; ++w)
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < 8; ++u)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          dk[u][c] += red[w][u * 4 + c][lane];
-          dv[u][c] += red[w][32 + u * 4 + c][lane];
-        }
+          for (int c = 0; c < 4; ++c) {
+            dk[u][c] += red[w][u * 4 + c][lane];
+            dv[u][c] += red[w][32 + u * 4 + c][lane];
+          }
+    }
     float ek[2][8], ev[2][8];   // pooling-backward term for channels 16t + {0..7} and 16t + 8 + {0..7}
 #pragma unroll
     for (int u = 0; u < 8; ++u) ek[0][u] = ek[1][u] = ev[0][u] = ev[1][u] = 0.f;
@@ -291,7 +421,7 @@ __global__ void __launch_bounds__(NW * 32) attn_dkv_fine_kernel(AttnP<bf16> a) {
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st);
 
 int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
-  if (g->topk > 32 || (g->pk2 && g->topk_p > 32)) return launch_attn_bwd_generic(g, st);
+  if (!mma_path_ok(g, true)) return launch_attn_bwd_generic(g, st);
   AttnP<bf16> a = build_attn_params<bf16>(g, true);
   const unsigned BH = (unsigned) (g->q->shape[0] * a.H);
   const int mask = g->stage_mask ? g->stage_mask : 7;
@@ -299,12 +429,18 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     int rc = zero_pooled_acc(g, st);
     if (rc) return rc;
     constexpr int NWQ = 4;
-    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) ((a.n1 + NWQ - 1) / NWQ), BH), NWQ * 32, 0, st>>>(a);
+    const int n_all = a.p1_blocks + a.p2_blocks;
+    const int n_smem = n_all < 12 ? n_all : 12;   // 12 tiles = 54 KB of K+V, three CTAs per SM
+    const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
+    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_mma_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.n1 / NWQ), BH), NWQ * 32, smem, st>>>(a, n_smem);
     LLSA_LAUNCH_OK("attn_dq_mma_kernel");
   }
   if ((mask & 2) && a.p1_blocks + a.p2_blocks > 0) {
-    constexpr int NWP = 4;
-    attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.n1 / kBS), BH), NWP * 32, 0, st>>>(a);
+    constexpr int NWP = 8;
+    const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
+    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.n1 / kBS), BH), NWP * 32, smem, st>>>(a);
     LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
   }
   if (mask & 4) {

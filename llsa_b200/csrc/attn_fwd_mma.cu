@@ -4,138 +4,198 @@
 //
 // One warp owns one 16-row query block (the m16 of mma.sync.m16n8k16); a CTA of
 // NW warps owns NW consecutive query blocks, which always share their parent
-// block, so the pooled keys the parent selected are fetched from L2 once per
-// CTA and served from L1 afterwards.  Key/value blocks go from global memory
-// straight into mma operand registers (mma_frag.cuh) -- no shared memory.
-// The softmax runs online over chunks of 32 keys (two blocks) in the exp2
-// domain; a pooled key's weight enters as +log2(weight) on its logit, which is
-// what `l += l_ij * W; acc += P.V * W` in the reference amounts to.
+// block and therefore the same pooled keys.
+//   * Pooled key/value tiles (the children of the parent's selected level-2
+//     blocks and the level-2 keys; all level-1 keys in the one-level form) are
+//     copied once per CTA into shared memory with cp.async while the fine stage
+//     runs, then read by every warp as conflict-free 128-bit fragments.  Tiles
+//     beyond the shared-memory budget are streamed like fine blocks.
+//   * Fine key/value blocks are private to a query block: they go from global
+//     memory straight into mma operand registers (mma_frag.cuh) with the next
+//     block's loads in flight behind the current block's math.
+// The softmax runs online, one 16-key block at a time, in the exp2 domain; a
+// pooled key's weight enters as +log2(weight) on its logit, which is what
+// `l += l_ij * W; acc += P.V * W` in the reference amounts to.
 #include "attn.cuh"
 #include "mma_frag.cuh"
 
 namespace llsa {
 
-struct BlockRef {
+struct FwdState {
+  float o[8][4];
+  float m0, m1, l0, l1;
+};
+
+// First half of a 16-key block: S = Q.K^T and the online-softmax update; returns P (bf16) as the
+// four A registers of the P.V product.  The key fragments are dead afterwards.
+__device__ __forceinline__ void fwd_scores(FwdState& st, const RowFrag& qlo, const RowFrag& qhi, const RowFrag& k0, const RowFrag& k1,
+                                           float sl2, float lw, uint32_t (&pa)[4]) {
+  float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+  mma_rows_x_keys(s0, s1, qlo, qhi, k0, k1);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) { s0[c] = fmaf(s0[c], sl2, lw); s1[c] = fmaf(s1[c], sl2, lw); }
+  const float mn0 = fmaxf(st.m0, quad_max(fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]))));
+  const float mn1 = fmaxf(st.m1, quad_max(fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]))));
+  const float al0 = fast_exp2(st.m0 - mn0), al1 = fast_exp2(st.m1 - mn1);
+  st.m0 = mn0; st.m1 = mn1;
+  s0[0] = fast_exp2(s0[0] - mn0); s0[1] = fast_exp2(s0[1] - mn0); s1[0] = fast_exp2(s1[0] - mn0); s1[1] = fast_exp2(s1[1] - mn0);
+  s0[2] = fast_exp2(s0[2] - mn1); s0[3] = fast_exp2(s0[3] - mn1); s1[2] = fast_exp2(s1[2] - mn1); s1[3] = fast_exp2(s1[3] - mn1);
+  st.l0 = st.l0 * al0 + (s0[0] + s0[1] + s1[0] + s1[1]);   // per-lane partial sums; reduced over the quad at the end
+  st.l1 = st.l1 * al1 + (s0[2] + s0[3] + s1[2] + s1[3]);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
+  // the two C tiles of S are the k16 halves of the A operand
+  pa[0] = pack_bf16(s0[0], s0[1]); pa[1] = pack_bf16(s0[2], s0[3]); pa[2] = pack_bf16(s1[0], s1[1]); pa[3] = pack_bf16(s1[2], s1[3]);
+}
+
+struct GlobalBlock {
   const bf16* k;
   const bf16* v;
   int64_t ks, vs;
-  float lw;  // log2 of the token weight
+  float lw;
 };
 
-// Resolves key block i of the list [fine | pooled-1 | pooled-2]; i is warp-uniform.
-// my_fine / my_p1: lane i holds the i-th selected fine block / parent block index.
-__device__ __forceinline__ BlockRef resolve_block(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int i, int my_fine, int my_p1,
-                                                  float lw1, float lw2) {
-  BlockRef r;
-  if (i < a.topk) {
-    const int64_t j = __shfl_sync(0xffffffffu, my_fine, i);
+// Block gi of the list streamed from global memory: the fine blocks, then the pooled tiles that
+// did not fit in shared memory.  gi is warp-uniform; lane i of my_fine holds fine block i.
+__device__ __forceinline__ GlobalBlock global_block(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t qb, int gi, int my_fine,
+                                                    int n_smem_tiles, float lw1, float lw2) {
+  GlobalBlock r;
+  if (gi < a.topk) {
+    const int64_t j = __shfl_sync(0xffffffffu, my_fine, gi);
     r.k = a.k.row(b, h, j * kBS); r.v = a.v.row(b, h, j * kBS); r.ks = a.k.sn; r.vs = a.v.sn; r.lw = 0.f;
-  } else if (i < a.topk + a.p1_blocks) {
-    const int ii = i - a.topk;
-    const int64_t j = a.two_level ? (int64_t) __shfl_sync(0xffffffffu, my_p1, ii) : (int64_t) ii;
-    r.k = a.pk + (bh * a.n1 + j * kBS) * kD; r.v = a.pv + (bh * a.n1 + j * kBS) * kD; r.ks = r.vs = kD; r.lw = lw1;
   } else {
-    const int64_t j = i - a.topk - a.p1_blocks;
-    r.k = a.pk2 + (bh * a.n2 + j * kBS) * kD; r.v = a.pv2 + (bh * a.n2 + j * kBS) * kD; r.ks = r.vs = kD; r.lw = lw2;
+    const int ip = n_smem_tiles + gi - a.topk;
+    if (ip < a.p1_blocks) {
+      const int64_t off = (bh * a.n1 + p1_block(a, bh, qb, ip) * kBS) * kD;
+      r.k = a.pk + off; r.v = a.pv + off; r.lw = lw1;
+    } else {
+      const int64_t off = (bh * a.n2 + (int64_t) (ip - a.p1_blocks) * kBS) * kD;
+      r.k = a.pk2 + off; r.v = a.pv2 + off; r.lw = lw2;
+    }
+    r.ks = r.vs = kD;
   }
   return r;
 }
 
+// Copies pooled tiles 0..n_tiles-1 of the query group of `qb0` into shared memory (K and V), asynchronously.
+__device__ __forceinline__ void stage_pooled_tiles(const AttnP<bf16>& a, int64_t bh, int64_t qb0, int n_tiles, bf16* sk, bf16* sv) {
+  for (int c = threadIdx.x; c < n_tiles * kBS * 8; c += blockDim.x) {
+    const int tile = c >> 7, row = (c >> 3) & 15, ch = (c & 7) * 8;
+    int64_t off;
+    const bf16 *gk, *gv;
+    if (tile < a.p1_blocks) {
+      off = (bh * a.n1 + p1_block(a, bh, qb0, tile) * kBS + row) * kD + ch;
+      gk = a.pk + off; gv = a.pv + off;
+    } else {
+      off = (bh * a.n2 + (int64_t) (tile - a.p1_blocks) * kBS + row) * kD + ch;
+      gk = a.pk2 + off; gv = a.pv2 + off;
+    }
+    const int so = (tile * kBS + row) * kSmemPitch + ch;
+    cp_async16(sk + so, gk);
+    cp_async16(sv + so, gv);
+  }
+  cp_async_commit();
+}
+
 template <int NW>
-__global__ void __launch_bounds__(NW * 32) attn_fwd_mma_kernel(AttnP<bf16> a) {
+__global__ void __launch_bounds__(NW * 32, 2) attn_fwd_mma_kernel(AttnP<bf16> a, int n_smem_tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sk = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sv = sk + n_smem_tiles * kBS * kSmemPitch;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int64_t qb = (int64_t) blockIdx.x * NW + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  if (qb >= a.n1) return;
+  const int64_t qb0 = (int64_t) blockIdx.x * NW, qb = qb0 + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  stage_pooled_tiles(a, bh, qb0, n_smem_tiles, sk, sv);
+
   const int my_fine = lane < a.topk ? (int) fine_block(a, bh, qb, lane) : 0;
-  const int my_p1 = (a.two_level && lane < a.topk_p) ? (int) p1_block(a, bh, qb, lane) : 0;
   const float lw1 = log2f(a.w1), lw2 = log2f(a.w2);
   const float sl2 = a.scale * 1.4426950408889634f;
-
   RowFrag qlo, qhi;
   load_rowfrag(qlo, a.q.row(b, h, qb * kBS + g), t);
   load_rowfrag(qhi, a.q.row(b, h, qb * kBS + g + 8), t);
 
-  float o[8][4];
+  FwdState st;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  for (int j = 0; j < 8; ++j) st.o[j][0] = st.o[j][1] = st.o[j][2] = st.o[j][3] = 0.f;
+  st.m0 = st.m1 = -INFINITY;
+  st.l0 = st.l1 = 0.f;
 
-  const int nchunks = (a.topk + a.p1_blocks + a.p2_blocks) >> 1;
-  RowFrag k00, k01, k10, k11;   // block 0 keys g / g+8, block 1 keys g / g+8
-  ColFrag v0, v1;
-  BlockRef r0 = resolve_block(a, b, h, bh, 0, my_fine, my_p1, lw1, lw2);
-  BlockRef r1 = resolve_block(a, b, h, bh, 1, my_fine, my_p1, lw1, lw2);
-  load_rowfrag(k00, r0.k + (int64_t) g * r0.ks, t);
-  load_rowfrag(k01, r0.k + (int64_t) (g + 8) * r0.ks, t);
-  load_rowfrag(k10, r1.k + (int64_t) g * r1.ks, t);
-  load_rowfrag(k11, r1.k + (int64_t) (g + 8) * r1.ks, t);
-  load_colfrag(v0, r0.v, r0.vs, g, t);
-  load_colfrag(v1, r1.v, r1.vs, g, t);
-
-  for (int c = 0; c < nchunks; ++c) {
-    float s[4][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    mma_rows_x_keys(s[0], s[1], qlo, qhi, k00, k01);
-    mma_rows_x_keys(s[2], s[3], qlo, qhi, k10, k11);
-    const float lw = r0.lw;
-    const bool more = c + 1 < nchunks;
-    if (more) {  // next chunk's keys: the registers are free as soon as the products above have issued
-      r0 = resolve_block(a, b, h, bh, 2 * c + 2, my_fine, my_p1, lw1, lw2);
-      r1 = resolve_block(a, b, h, bh, 2 * c + 3, my_fine, my_p1, lw1, lw2);
-      load_rowfrag(k00, r0.k + (int64_t) g * r0.ks, t);
-      load_rowfrag(k01, r0.k + (int64_t) (g + 8) * r0.ks, t);
-      load_rowfrag(k10, r1.k + (int64_t) g * r1.ks, t);
-      load_rowfrag(k11, r1.k + (int64_t) (g + 8) * r1.ks, t);
-    }
-    // logits in the exp2 domain
-    float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      s[j][0] = fmaf(s[j][0], sl2, lw); s[j][1] = fmaf(s[j][1], sl2, lw);
-      s[j][2] = fmaf(s[j][2], sl2, lw); s[j][3] = fmaf(s[j][3], sl2, lw);
-      mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
-      mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
-    }
-    const float mn0 = fmaxf(m0, quad_max(mx0)), mn1 = fmaxf(m1, quad_max(mx1));
-    const float al0 = fast_exp2(m0 - mn0), al1 = fast_exp2(m1 - mn1);
-    m0 = mn0; m1 = mn1;
-    float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      s[j][0] = fast_exp2(s[j][0] - mn0); s[j][1] = fast_exp2(s[j][1] - mn0);
-      s[j][2] = fast_exp2(s[j][2] - mn1); s[j][3] = fast_exp2(s[j][3] - mn1);
-      sum0 += s[j][0] + s[j][1];
-      sum1 += s[j][2] + s[j][3];
-    }
-    l0 = l0 * al0 + sum0;   // per-lane partial sums; reduced over the quad at the end
-    l1 = l1 * al1 + sum1;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
-    // P (bf16) as the A operand: C tiles (2j, 2j+1) of S are the k16 halves of block j
-    mma_x_cols(o, pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3]), v0);
-    mma_x_cols(o, pack_bf16(s[2][0], s[2][1]), pack_bf16(s[2][2], s[2][3]), pack_bf16(s[3][0], s[3][1]), pack_bf16(s[3][2], s[3][3]), v1);
-    if (more) {
-      load_colfrag(v0, r0.v, r0.vs, g, t);
-      load_colfrag(v1, r1.v, r1.vs, g, t);
+  // ---- blocks streamed from global memory, next block's loads in flight behind the math
+  const int n_pooled = a.p1_blocks + a.p2_blocks;
+  const int n_glob = a.topk + (n_pooled - n_smem_tiles);
+  {
+    RowFrag k0, k1;
+    ColFrag v;
+    GlobalBlock r = global_block(a, b, h, bh, qb, 0, my_fine, n_smem_tiles, lw1, lw2);
+    load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
+    load_rowfrag(k1, r.k + (int64_t) (g + 8) * r.ks, t);
+    load_colfrag(v, r.v, r.vs, g, t);
+    for (int gi = 0; gi < n_glob; ++gi) {
+      if (gi + 2 < n_glob) {   // two blocks ahead: K rows (lanes 0..15) and V rows (lanes 16..31) towards L1
+        const GlobalBlock f = global_block(a, b, h, bh, qb, gi + 2, my_fine, n_smem_tiles, lw1, lw2);
+        if (lane < 16) prefetch_tile_rows(f.k, f.ks, lane);
+        else prefetch_tile_rows(f.v, f.vs, lane - 16);
+      }
+      uint32_t pa[4];
+      fwd_scores(st, qlo, qhi, k0, k1, sl2, r.lw, pa);
+      const bool more = gi + 1 < n_glob;
+      if (more) {   // the key registers are free: start the next block's keys
+        r = global_block(a, b, h, bh, qb, gi + 1, my_fine, n_smem_tiles, lw1, lw2);
+        load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
+        load_rowfrag(k1, r.k + (int64_t) (g + 8) * r.ks, t);
+      }
+      mma_x_cols(st.o, pa[0], pa[1], pa[2], pa[3], v);
+      if (more) load_colfrag(v, r.v, r.vs, g, t);
     }
   }
-  l0 = quad_sum(l0);
-  l1 = quad_sum(l1);
-  store_acc_row<0>(a.o.row(b, h, qb * kBS + g), o, t, 1.f / l0);
-  store_acc_row<1>(a.o.row(b, h, qb * kBS + g + 8), o, t, 1.f / l1);
+  // ---- pooled tiles shared by the CTA
+  cp_async_wait_all();
+  __syncthreads();
+  for (int ip = 0; ip < n_smem_tiles; ++ip) {
+    RowFrag k0, k1;
+    ColFrag v;
+    const bf16* tk = sk + ip * kBS * kSmemPitch;
+    load_rowfrag_smem(k0, tk + g * kSmemPitch, t);
+    load_rowfrag_smem(k1, tk + (g + 8) * kSmemPitch, t);
+    load_colfrag_smem(v, sv + ip * kBS * kSmemPitch, g, t);
+    uint32_t pa[4];
+    fwd_scores(st, qlo, qhi, k0, k1, sl2, ip < a.p1_blocks ? lw1 : lw2, pa);
+    mma_x_cols(st.o, pa[0], pa[1], pa[2], pa[3], v);
+  }
+
+  const float l0 = quad_sum(st.l0), l1 = quad_sum(st.l1);
+  store_acc_row<0>(a.o.row(b, h, qb * kBS + g), st.o, t, 1.f / l0);
+  store_acc_row<1>(a.o.row(b, h, qb * kBS + g + 8), st.o, t, 1.f / l1);
   if (t == 0) {
-    a.lse[bh * a.N + qb * kBS + g] = (m0 + log2f(l0)) * 0.6931471805599453f;
-    a.lse[bh * a.N + qb * kBS + g + 8] = (m1 + log2f(l1)) * 0.6931471805599453f;
+    a.lse[bh * a.N + qb * kBS + g] = (st.m0 + log2f(l0)) * 0.6931471805599453f;
+    a.lse[bh * a.N + qb * kBS + g + 8] = (st.m1 + log2f(l1)) * 0.6931471805599453f;
   }
 }
 
+bool mma_path_ok(const LlsaAttnArgs* g, bool bwd) {
+  if (g->topk > 32 || (g->pk2 && g->topk_p > 32)) return false;
+  // 256-bit fragment loads need 32-byte aligned rows
+  const LlsaTensor* ts[8] = {g->q, g->k, g->v, g->o, bwd ? g->d_o : nullptr, bwd ? g->dq : nullptr, bwd ? g->dk : nullptr, bwd ? g->dv : nullptr};
+  for (const LlsaTensor* t : ts) {
+    if (!t) continue;
+    if ((uintptr_t) t->ptr % 32) return false;
+    for (int i = 0; i < 3; ++i)
+      if (t->shape[i] != 1 && t->stride[i] % 16) return false;
+  }
+  return ((uintptr_t) g->pk->ptr % 32) == 0 && ((uintptr_t) g->pv->ptr % 32) == 0 &&
+         (!g->pk2 || (((uintptr_t) g->pk2->ptr % 32) == 0 && ((uintptr_t) g->pv2->ptr % 32) == 0));
+}
+
+int pooled_smem_tiles(int n_pooled) { return n_pooled < 20 ? n_pooled : 20; }   // 20 tiles = 90 KB of K+V, two CTAs per SM
+
 int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
-  if (g->topk > 32 || (g->pk2 && g->topk_p > 32)) return launch_attn_fwd_generic(g, st);
+  if (!mma_path_ok(g, false)) return launch_attn_fwd_generic(g, st);
   AttnP<bf16> a = build_attn_params<bf16>(g, false);
-  constexpr int NW = 4;
-  dim3 grid((unsigned) ((a.n1 + NW - 1) / NW), (unsigned) (g->q->shape[0] * a.H));
-  attn_fwd_mma_kernel<NW><<<grid, NW * 32, 0, st>>>(a);
+  constexpr int NW = 8;
+  const int n_smem = pooled_smem_tiles(a.p1_blocks + a.p2_blocks);
+  const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
+  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_mma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  dim3 grid((unsigned) (a.n1 / NW), (unsigned) (g->q->shape[0] * a.H));
+  attn_fwd_mma_kernel<NW><<<grid, NW * 32, smem, st>>>(a, n_smem);
   LLSA_LAUNCH_OK("attn_fwd_mma_kernel");
   return LLSA_OK;
 }

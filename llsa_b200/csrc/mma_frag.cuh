@@ -11,9 +11,9 @@
 //
 // * RowFrag -- "channel-contraction" layout, for products that sum over the 64
 //   channels (S = Q.K^T, dP = dO.V^T).  Lane (g,t) holds, for row g of the tile,
-//   channels [8t, 8t+8) and [32+8t, 32+8t+8): two 128-bit loads; the four lanes
-//   of a quad cover one 64-byte half row each time.  k-step s (0..3) uses
-//   registers r[2s] (logical k = 2t,2t+1) and r[2s+1] (logical k = 2t+8,2t+9).
+//   the 16 channels [16t, 16t+16): ONE 256-bit load; the four lanes of a quad
+//   cover the whole 128-byte row.  k-step s (0..3) uses registers r[2s]
+//   (logical k = 2t,2t+1) and r[2s+1] (logical k = 2t+8,2t+9).
 //   The same struct is the A operand (rows g and g+8 -> two RowFrags) and the B
 //   operand (key n = g -> one RowFrag per 8 keys).
 //
@@ -36,8 +36,19 @@ struct RowFrag {
   uint32_t r[8];
 };
 
+// One 256-bit load (sm_100): lane (g,t) takes channels [16t, 16t+16) of its row, so the
+// four lanes of a quad read one whole 128-byte row and a warp-wide load touches 8 lines.
+// `row` must be 32-byte aligned.
 __device__ __forceinline__ void load_rowfrag(RowFrag& f, const bf16* row, int t) {
-  const uint4 a = ldg128(row + 8 * t), b = ldg128(row + 32 + 8 * t);
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(f.r[0]), "=r"(f.r[1]), "=r"(f.r[2]), "=r"(f.r[3]), "=r"(f.r[4]), "=r"(f.r[5]), "=r"(f.r[6]), "=r"(f.r[7])
+               : "l"(row + 16 * t));
+}
+
+// The same fragment from a shared-memory tile (rows padded to kSmemPitch elements).
+constexpr int kSmemPitch = 72;   // 144 bytes: consecutive rows shift by 4 banks -> conflict-free 128-bit reads
+__device__ __forceinline__ void load_rowfrag_smem(RowFrag& f, const bf16* row, int t) {
+  const uint4 a = *reinterpret_cast<const uint4*>(row + 16 * t), b = *reinterpret_cast<const uint4*>(row + 16 * t + 8);
   f.r[0] = a.x; f.r[1] = a.y; f.r[2] = a.z; f.r[3] = a.w;
   f.r[4] = b.x; f.r[5] = b.y; f.r[6] = b.z; f.r[7] = b.w;
 }
@@ -52,6 +63,28 @@ __device__ __forceinline__ void load_colfrag(ColFrag& f, const bf16* tile, int64
   f.row[1] = ldg128(p + (int64_t) (2 * t + 1) * stride);
   f.row[2] = ldg128(p + (int64_t) (2 * t + 8) * stride);
   f.row[3] = ldg128(p + (int64_t) (2 * t + 9) * stride);
+}
+
+__device__ __forceinline__ void load_colfrag_smem(ColFrag& f, const bf16* tile, int g, int t) {
+  const bf16* p = tile + 8 * g;
+  f.row[0] = *reinterpret_cast<const uint4*>(p + (2 * t) * kSmemPitch);
+  f.row[1] = *reinterpret_cast<const uint4*>(p + (2 * t + 1) * kSmemPitch);
+  f.row[2] = *reinterpret_cast<const uint4*>(p + (2 * t + 8) * kSmemPitch);
+  f.row[3] = *reinterpret_cast<const uint4*>(p + (2 * t + 9) * kSmemPitch);
+}
+
+// 16 bytes global -> shared without passing through registers
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = (uint32_t) __cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Pulls the 16 rows of a tile (128 bytes each) towards L1 without using registers:
+// lanes 0..15 of `lane16` each touch one row.
+__device__ __forceinline__ void prefetch_tile_rows(const bf16* tile, int64_t stride, int lane16) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(tile + (int64_t) lane16 * stride));
 }
 
 __device__ __forceinline__ uint32_t u4_get(const uint4& v, int m) { return m == 0 ? v.x : (m == 1 ? v.y : (m == 2 ? v.z : v.w)); }
@@ -110,6 +143,21 @@ __device__ __forceinline__ void store_acc_row(bf16* row, const float (&acc)[8][4
   y.z = pack_bf16(acc[4][hi] * mul, acc[5][hi] * mul); y.w = pack_bf16(acc[6][hi] * mul, acc[7][hi] * mul);
   *reinterpret_cast<uint4*>(row + 16 * t) = x;
   *reinterpret_cast<uint4*>(row + 16 * t + 8) = y;
+}
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Adds the same 16 channels of one row into an fp32 row in global memory with four 128-bit reductions
+template <int ROW>
+__device__ __forceinline__ void red_acc_row(float* row, const float (&acc)[8][4], int t, float mul) {
+  constexpr int lo = ROW * 2, hi = ROW * 2 + 1;
+  float* p = row + 16 * t;
+  red_add_v4(p, acc[0][lo] * mul, acc[1][lo] * mul, acc[2][lo] * mul, acc[3][lo] * mul);
+  red_add_v4(p + 4, acc[4][lo] * mul, acc[5][lo] * mul, acc[6][lo] * mul, acc[7][lo] * mul);
+  red_add_v4(p + 8, acc[0][hi] * mul, acc[1][hi] * mul, acc[2][hi] * mul, acc[3][hi] * mul);
+  red_add_v4(p + 12, acc[4][hi] * mul, acc[5][hi] * mul, acc[6][hi] * mul, acc[7][hi] * mul);
 }
 
 }  // namespace llsa

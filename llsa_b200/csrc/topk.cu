@@ -13,6 +13,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "mma_frag.cuh"
 
 namespace llsa {
 
@@ -134,7 +135,9 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
 }
 
 // pq1, pk1: contiguous [B*H, M, D]; p_idx [B*H, M/bs, p_topk]; out [B*H, M, topk].
-template <typename T>
+// MMA = true (bf16, D = 64, bs = 16): the 16 x C score tile comes from mma.sync with fp32
+// accumulation of the exact bf16 products, as the reference's tl.dot does.
+template <typename T, bool MMA>
 __global__ void __launch_bounds__(128)
 refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
                    int D, int topk, int p_topk, int bs) {
@@ -153,9 +156,57 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
     cand[j] = (int) (p * bs + j % bs);
   }
   __syncthreads();
+  if constexpr (MMA) {
+    const int warp_ = threadIdx.x >> 5, lane_ = threadIdx.x & 31, g = lane_ >> 2, t = lane_ & 3;
+    if constexpr (sizeof(T) == 2) {
+      RowFrag qlo, qhi;
+      load_rowfrag(qlo, reinterpret_cast<const bf16*>(q0) + g * D, t);
+      load_rowfrag(qhi, reinterpret_cast<const bf16*>(q0) + (g + 8) * D, t);
+      for (int tile = warp_ * 2; tile < C / 8; tile += 8) {      // two 8-candidate n-tiles per step and warp
+        RowFrag ka, kb;
+        load_rowfrag(ka, reinterpret_cast<const bf16*>(k0) + (int64_t) cand[tile * 8 + g] * D, t);
+        load_rowfrag(kb, reinterpret_cast<const bf16*>(k0) + (int64_t) cand[tile * 8 + 8 + g] * D, t);
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_rows_x_keys(s0, s1, qlo, qhi, ka, kb);
+        // C fragment: rows g / g+8, candidates tile*8 + 2t, +1 (and +8 for the second tile)
+        sc[g * C + tile * 8 + 2 * t] = s0[0];       sc[g * C + tile * 8 + 2 * t + 1] = s0[1];
+        sc[(g + 8) * C + tile * 8 + 2 * t] = s0[2]; sc[(g + 8) * C + tile * 8 + 2 * t + 1] = s0[3];
+        sc[g * C + tile * 8 + 8 + 2 * t] = s1[0];       sc[g * C + tile * 8 + 9 + 2 * t] = s1[1];
+        sc[(g + 8) * C + tile * 8 + 8 + 2 * t] = s1[2]; sc[(g + 8) * C + tile * 8 + 9 + 2 * t] = s1[3];
+      }
+    }
+  } else
+  // each thread owns a candidate: its key row is read once per group of 16 query rows and
+  // meets the rows (broadcast from shared memory) in 16 independent accumulators
   for (int j = threadIdx.x; j < C; j += blockDim.x) {
     const T* kr = k0 + (int64_t) cand[j] * D;
-    for (int r = 0; r < bs; ++r) sc[r * C + j] = dot_row<T>(qs + r * D, kr, D);
+    for (int r0 = 0; r0 < bs; r0 += 16) {
+      float acc[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) acc[r] = 0.f;
+      for (int d = 0; d < D; d += 8) {
+        float kv[8];
+        if constexpr (sizeof(T) == 2) {
+          const uint4 x = ldg128(kr + d);
+          kv[0] = bf16_lo(x.x); kv[1] = bf16_hi(x.x); kv[2] = bf16_lo(x.y); kv[3] = bf16_hi(x.y);
+          kv[4] = bf16_lo(x.z); kv[5] = bf16_hi(x.z); kv[6] = bf16_lo(x.w); kv[7] = bf16_hi(x.w);
+        } else {
+          const float4 x = __ldg(reinterpret_cast<const float4*>(kr + d)), y = __ldg(reinterpret_cast<const float4*>(kr + d + 4));
+          kv[0] = x.x; kv[1] = x.y; kv[2] = x.z; kv[3] = x.w; kv[4] = y.x; kv[5] = y.y; kv[6] = y.z; kv[7] = y.w;
+        }
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          if (r0 + r < bs) {
+            const float* qr = qs + (r0 + r) * D + d;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[r] = fmaf(qr[u], kv[u], acc[r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 16; ++r)
+        if (r0 + r < bs) sc[(r0 + r) * C + j] = acc[r];
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -237,13 +288,17 @@ extern "C" int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, co
   dim3 grid((unsigned) (M / bs), (unsigned) (B * H));
   cudaStream_t st = (cudaStream_t) stream;
   if (pq1->dtype == LLSA_F32) {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    refine_topk_kernel<float><<<grid, 128, smem, st>>>((const float*) pq1->ptr, (const float*) pk1->ptr, make_idx(p_idx), idx->ptr,
-                                                       idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    refine_topk_kernel<float, false><<<grid, 128, smem, st>>>((const float*) pq1->ptr, (const float*) pk1->ptr, make_idx(p_idx), idx->ptr,
+                                                              idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+  } else if (D == 64 && bs == 16 && p_topk % 2 == 0 && ((uintptr_t) pq1->ptr % 32) == 0 && ((uintptr_t) pk1->ptr % 32) == 0) {
+    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    refine_topk_kernel<__nv_bfloat16, true><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
+                                                                     make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
   } else {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    refine_topk_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
-                                                               make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    refine_topk_kernel<__nv_bfloat16, false><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
+                                                                      make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
   }
   LLSA_LAUNCH_OK("refine_topk_kernel");
   return LLSA_OK;
