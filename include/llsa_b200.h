@@ -100,6 +100,29 @@ size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t T, 
 int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
                            void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
 
+/* The same transpose for hosts that cannot provide device scratch.  This entry
+ * point has no counterpart in the reference: it exists for callers that never
+ * get to call cudaMalloc themselves -- a process that handed the whole device to
+ * its own memory arena at start-up, or a plugin runtime that only passes input
+ * and output buffers across its boundary -- and that still need the
+ * long-sequence case, where llsa_transpose_indices asks for scratch.
+ *   - It allocates nothing.  The count table [B*H][32][n_kv] of 16-bit counters
+ *     lives in an 8 MiB array built into the library, resident on every GPU that
+ *     loads the library until the process exits.  B*H*32*n_kv*2 bytes must fit
+ *     in those 8 MiB (e.g. B*H = 6 with n_kv = 16384, or B*H = 48 with
+ *     n_kv = 2048); larger problems are refused with LLSA_ERR_WORKSPACE and must
+ *     use llsa_transpose_indices with caller scratch.
+ *   - The first call on a device looks up the array's device address (with that
+ *     device current) and caches it; make that first call before any stream
+ *     capture is started on the device.
+ *   - All calls share the one array and it keeps the previous call's contents;
+ *     the kernel clears the part it uses before counting.  Two calls whose
+ *     kernels overlap on the GPU (different streams, or different threads on the
+ *     same device) race on it: issue them on one stream or order them yourself.
+ * Inputs and outputs are exactly those of llsa_transpose_indices. */
+int llsa_transpose_indices_noalloc(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
+                                   int32_t* status, void* stream);
+
 /* ---- attention ------------------------------------------------------------ */
 typedef struct LlsaAttnArgs {
   /* forward operands */

@@ -41,7 +41,7 @@ class LlsaAttnArgs(C.Structure):
 EXPORTS = [
     "llsa_version", "llsa_last_error_string", "llsa_mean_pool_fwd", "llsa_mean_pool_bwd", "llsa_pool_pyramid_fwd",
     "llsa_rope_fwd", "llsa_rope_bwd", "llsa_coarse_topk", "llsa_refine_topk", "llsa_transpose_scratch_bytes",
-    "llsa_transpose_indices", "llsa_attn_fwd", "llsa_attn_bwd",
+    "llsa_transpose_indices", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd",
 ]
 
 _lib: Optional[C.CDLL] = None
@@ -62,6 +62,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.llsa_transpose_scratch_bytes.argtypes = [C.c_int64] * 5
     lib.llsa_transpose_scratch_bytes.restype = C.c_size_t
     lib.llsa_transpose_indices.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+    lib.llsa_transpose_indices_noalloc.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_void_p]
     lib.llsa_attn_fwd.argtypes = [C.POINTER(LlsaAttnArgs), C.c_void_p]
     lib.llsa_attn_bwd.argtypes = [C.POINTER(LlsaAttnArgs), C.c_void_p]
     for name in EXPORTS:

@@ -16,6 +16,8 @@
 //      + (rank inside its match group).
 // Entries keep their original relative order, so every bucket lists its query
 // blocks in ascending order and the output is bit-reproducible.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace llsa {
@@ -209,6 +211,93 @@ extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* o
   // a segment holds at most 65535 entries, so the 16-bit counters cannot overflow
   LLSA_CUDA_OK(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
   transpose_kernel<<<(unsigned) (B * H), W * 32, smem, (cudaStream_t) stream>>>(a);
+  LLSA_LAUNCH_OK("transpose_kernel");
+  return LLSA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// llsa_transpose_indices_noalloc: the same index transpose for callers that
+// cannot hand over a scratch buffer.
+//
+// Some hosts of this library never get to call cudaMalloc themselves: a
+// serving or training process that gave the whole device to its own memory
+// arena at start-up, or a plugin runtime that only passes input and output
+// buffers across its boundary.  For the long-sequence shapes (n_kv above a few
+// thousand KV blocks) llsa_transpose_indices needs B*H*32*n_kv*2 bytes of
+// device scratch for its count table; here that table lives in a fixed array
+// inside the library image instead.  Every GPU that loads the library carries
+// the array (kNoAllocScratchBytes) until the process exits.
+//
+// The array's name is only a host-side handle: its device address is looked up
+// once per device with cudaGetSymbolAddress (with that device current) and the
+// address -- not the symbol -- is what the kernel receives.
+namespace llsa {
+
+constexpr size_t kNoAllocScratchBytes = 8u << 20;   // 8 MiB: e.g. B*H = 6 heads of 262144 tokens (n_kv = 16384)
+static __device__ __align__(256) unsigned char g_transpose_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices];   // device address of g_transpose_scratch, per device ordinal
+static bool g_scratch_ready[kMaxDevices];
+static std::mutex g_scratch_mutex;
+
+// Device address of the static scratch on the CURRENT device (looked up on first use there).
+static int noalloc_scratch(void** out) {
+  int dev = -1;
+  LLSA_CUDA_OK(cudaGetDevice(&dev));
+  LLSA_REQUIRE(dev >= 0 && dev < kMaxDevices, LLSA_ERR_ARG, "transpose_indices_noalloc: device ordinal %d unsupported", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ready[dev]) {
+    void* p = nullptr;
+    LLSA_CUDA_OK(cudaGetSymbolAddress(&p, g_transpose_scratch));
+    LLSA_REQUIRE(p != nullptr, LLSA_ERR_CUDA, "transpose_indices_noalloc: no device address for the static scratch");
+    g_scratch_addr[dev] = p;
+    g_scratch_ready[dev] = true;
+  }
+  *out = g_scratch_addr[dev];
+  return LLSA_OK;
+}
+
+}  // namespace llsa
+
+extern "C" int llsa_transpose_indices_noalloc(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
+                                              int32_t* status, void* stream) {
+  LLSA_REQUIRE(idx && offsets && flat && idx->ptr && offsets->ptr && flat->ptr, LLSA_ERR_NULL, "transpose_indices_noalloc: null tensor");
+  LLSA_REQUIRE(idx->ndim == 4, LLSA_ERR_SHAPE, "transpose_indices_noalloc: idx must be [B,H,M,T]");
+  const int64_t B = idx->shape[0], H = idx->shape[1], M = idx->shape[2], T = idx->shape[3];
+  LLSA_REQUIRE(is_index_dtype(idx->dtype) && is_index_dtype(offsets->dtype) && flat->dtype == LLSA_I32, LLSA_ERR_DTYPE,
+               "transpose_indices_noalloc: idx/offsets must be i32 or i64, flat i32");
+  LLSA_REQUIRE(n_kv >= 1 && n_kv < (1ll << 31) && T >= 1, LLSA_ERR_ARG, "transpose_indices_noalloc: bad n_kv=%lld", (long long) n_kv);
+  const int64_t E = M * T;
+  LLSA_REQUIRE(E <= 32ll * 65504, LLSA_ERR_SHAPE, "transpose_indices_noalloc: M*T=%lld exceeds the supported %lld", (long long) E,
+               32ll * 65504);
+  const int64_t si[4] = {B, H, M, T}, so[3] = {B, H, n_kv + 1}, sf[3] = {B, H, E};
+  int rc;
+  if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
+  if ((rc = check_contig(offsets, "offsets", offsets->dtype, 3, so))) return rc;
+  if ((rc = check_contig(flat, "flat", LLSA_I32, 3, sf))) return rc;
+  // the count table [B*H][32 warps][n_kv] of 16-bit counters always goes to the static array
+  const size_t need = (size_t) B * H * 32 * (size_t) n_kv * 2;
+  LLSA_REQUIRE(need <= kNoAllocScratchBytes, LLSA_ERR_WORKSPACE,
+               "transpose_indices_noalloc: B*H*n_kv = %lld needs %zu bytes of count table, the built-in scratch holds %zu "
+               "(use llsa_transpose_indices with caller scratch)", (long long) (B * H * n_kv), need, (size_t) kNoAllocScratchBytes);
+  const size_t smem = (size_t) n_kv * 4;   // per-key bases stay in shared memory
+  LLSA_REQUIRE(smem <= 200 * 1024, LLSA_ERR_SHAPE, "transpose_indices_noalloc: n_kv=%lld too large", (long long) n_kv);
+  if (B * H == 0) return LLSA_OK;
+  void* tab = nullptr;
+  if ((rc = noalloc_scratch(&tab))) return rc;
+  TransposeArgs a;
+  a.idx = make_idx(idx);
+  a.offsets = offsets->ptr;
+  a.off64 = offsets->dtype == LLSA_I64;
+  a.flat = (int32_t*) flat->ptr;
+  a.E = E;
+  a.T = (int) T;
+  a.n_kv = n_kv;
+  a.gtab = (uint16_t*) tab;     // the kernel zero-fills the part of the table it uses before counting
+  a.status = status;
+  LLSA_CUDA_OK(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  transpose_kernel<<<(unsigned) (B * H), 32 * 32, smem, (cudaStream_t) stream>>>(a);
   LLSA_LAUNCH_OK("transpose_kernel");
   return LLSA_OK;
 }
