@@ -161,6 +161,10 @@ typedef struct LlsaAttnArgs {
                                   1: zero the *_acc tensors + delta + dq,  2: pooled-key
                                   gradients,  4: dk, dv -- to be issued in this order
                                   (lets a caller time the three kernels separately) */
+  const LlsaTensor* dkv_partial; /* backward, bf16 tensors only: F32 scratch
+                                  [B,H,ceil(N/16*topk/128),4096] for dK/dV tiles of KV blocks whose
+                                  list of query blocks straddles two work windows (not read before
+                                  it is written; may be NULL for f32 tensors) */
 } LlsaAttnArgs;
 
 /* Forward: o, lse.  One level (pk2 == NULL) replaces sparse_indices_attn_res_fwd

@@ -34,7 +34,7 @@ class LlsaAttnArgs(C.Structure):
         ("d_o", _P), ("dq", _P), ("dk", _P), ("dv", _P), ("offsets", _P), ("flat", _P), ("delta", _P),
         ("dpk_acc", _P), ("dpv_acc", _P), ("dpk2_acc", _P), ("dpv2_acc", _P),
         ("fold_pool_bwd", C.c_int32), ("kv_weight", C.c_float), ("kv_weight_2", C.c_float),
-        ("force_generic", C.c_int32), ("stage_mask", C.c_int32),
+        ("force_generic", C.c_int32), ("stage_mask", C.c_int32), ("dkv_partial", _P),
     ]
 
 

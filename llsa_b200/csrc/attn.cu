@@ -57,6 +57,13 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
     if ((rc = check_contig(g->delta, "delta", LLSA_F32, 3, sl))) return rc;
     if ((rc = check_contig(g->dpk_acc, "dpk_acc", LLSA_F32, 4, s1))) return rc;
     if ((rc = check_contig(g->dpv_acc, "dpv_acc", LLSA_F32, 4, s1))) return rc;
+    if (dt == LLSA_BF16 && !g->force_generic) {
+      LLSA_REQUIRE(g->dkv_partial, LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial scratch missing");
+      const int64_t need = B * H * ((n1 * g->topk + 127) / 128) * 4096;
+      LLSA_REQUIRE(g->dkv_partial->ptr && g->dkv_partial->dtype == LLSA_F32 && g->dkv_partial->ndim == 4 && is_contiguous(g->dkv_partial) &&
+                       g->dkv_partial->shape[0] * g->dkv_partial->shape[1] * g->dkv_partial->shape[2] * g->dkv_partial->shape[3] >= need,
+                   LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial must be a contiguous F32 tensor of at least %lld elements", (long long) need);
+    }
     if (two) {
       LLSA_REQUIRE(g->dpk2_acc && g->dpv2_acc, LLSA_ERR_NULL, "attn_bwd: dpk2_acc / dpv2_acc missing");
       if ((rc = check_contig(g->dpk2_acc, "dpk2_acc", LLSA_F32, 4, s2))) return rc;

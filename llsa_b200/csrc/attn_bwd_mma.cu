@@ -15,10 +15,13 @@
 //                          products S^T, dP^T, dV += P^T.dO, dK += dS^T.Q over the
 //                          16 query blocks and add the 16x64 results into fp32
 //                          accumulators (one red.add per element and group).
-//   attn_dkv_fine_kernel   one CTA per KV block: its warps share out the block's
-//                          CSR list of query blocks, partial sums meet in shared
-//                          memory, and the epilogue folds in the pooling backward
-//                          (dk += (dpk[j] + dpk2[j/16]/16)/16) before one bf16 store.
+//   attn_dkv_fine_kernel   the CSR of a head is cut into equal windows of 128 entries
+//                          (one CTA, 32 entries per warp) so every warp runs the
+//                          same number of steps however skewed the fan-in is;
+//                          tiles of buckets that straddle a range meet in shared
+//                          memory / a global partial tensor (no atomics), and
+//   attn_dkv_finish_kernel sums the window partials; every store folds in the pooling
+//                          backward (dk += (dpk[j] + dpk2[j/16]/16)/16), one bf16 store.
 // The reference multiplies k by scale into new tensors first (res_1.py:420-422);
 // here scale rides in the exp2 argument and in the epilogues.
 #include "attn.cuh"
@@ -323,99 +326,219 @@ __global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16>
   }
 }
 
-template <int NW>
-__global__ void __launch_bounds__(NW * 32) attn_dkv_fine_kernel(AttnP<bf16> a) {
-  __shared__ float red[NW - 1][64][32];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int64_t j = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  const float sl2 = a.scale * kLog2e;
-  int64_t list0, list1;
-  if (a.off64) {
-    list0 = reinterpret_cast<const int64_t*>(a.offsets)[bh * (a.n1 + 1) + j];
-    list1 = reinterpret_cast<const int64_t*>(a.offsets)[bh * (a.n1 + 1) + j + 1];
-  } else {
-    list0 = reinterpret_cast<const int32_t*>(a.offsets)[bh * (a.n1 + 1) + j];
-    list1 = reinterpret_cast<const int32_t*>(a.offsets)[bh * (a.n1 + 1) + j + 1];
+// Adds the pooling-backward term to a finished 16x64 dK/dV tile of KV block j and stores it (bf16).
+__device__ __forceinline__ void dkv_fine_store(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t j, float (&dk)[8][4],
+                                               float (&dv)[8][4], int g, int t) {
+  float ek[2][8], ev[2][8];   // pooling-backward term for channels 16t + {0..7} and 16t + 8 + {0..7}
+#pragma unroll
+  for (int u = 0; u < 8; ++u) ek[0][u] = ek[1][u] = ev[0][u] = ev[1][u] = 0.f;
+  if (a.fold) {
+    const float* g1k = a.dpk + (bh * a.n1 + j) * kD + 16 * t;
+    const float* g1v = a.dpv + (bh * a.n1 + j) * kD + 16 * t;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { ek[0][u] = g1k[u]; ek[1][u] = g1k[8 + u]; ev[0][u] = g1v[u]; ev[1][u] = g1v[8 + u]; }
+    if (a.two_level) {
+      const float* g2k = a.dpk2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
+      const float* g2v = a.dpv2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        ek[0][u] += g2k[u] * (1.f / kBS); ek[1][u] += g2k[8 + u] * (1.f / kBS);
+        ev[0][u] += g2v[u] * (1.f / kBS); ev[1][u] += g2v[8 + u] * (1.f / kBS);
+      }
+    }
   }
-  float dk[8][4], dv[8][4];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    dk[u][0] = dk[u][0] * a.scale + ek[0][u] * (1.f / kBS); dk[u][1] = dk[u][1] * a.scale + ek[1][u] * (1.f / kBS);
+    dk[u][2] = dk[u][2] * a.scale + ek[0][u] * (1.f / kBS); dk[u][3] = dk[u][3] * a.scale + ek[1][u] * (1.f / kBS);
+    dv[u][0] += ev[0][u] * (1.f / kBS); dv[u][1] += ev[1][u] * (1.f / kBS);
+    dv[u][2] += ev[0][u] * (1.f / kBS); dv[u][3] += ev[1][u] * (1.f / kBS);
+  }
+  store_acc_row<0>(a.dk.row(b, h, j * kBS + g), dk, t, 1.f);
+  store_acc_row<1>(a.dk.row(b, h, j * kBS + g + 8), dk, t, 1.f);
+  store_acc_row<0>(a.dv.row(b, h, j * kBS + g), dv, t, 1.f);
+  store_acc_row<1>(a.dv.row(b, h, j * kBS + g + 8), dv, t, 1.f);
+}
+
+// ---- fine dK/dV: equal windows of the CSR, whatever the fan-in ---------------------------------
+// The CSR of a head lists, bucket after bucket (KV block after KV block), the query blocks that
+// selected each KV block.  Fan-in is very uneven (0 ... >150 on correlated inputs), so the work
+// is cut by ENTRIES, not by buckets: a CTA owns a window of kFineWindow consecutive entries of
+// `flat`, each of its warps a contiguous quarter.  A warp walks its range in order, keeps the
+// dK/dV tile of the current bucket in registers and, when the bucket changes, either stores
+// the tile (bucket wholly inside its range) or parks it in one of its two shared-memory slots
+// (bucket shared with a neighbour warp).  After a barrier every shared bucket is summed in slot
+// order; if it lies inside the CTA's window it is stored, otherwise the CTA-level partial goes
+// to one of the CTA's two slots in a global scratch tensor, and attn_dkv_finish_kernel sums
+// those (in CTA order) for the buckets that straddle windows.  No atomics: bit-reproducible.
+constexpr int kFineWarps = 4;
+constexpr int kFineWindow = 128;                // entries per CTA
+constexpr int kTileFloats = 64 * 32;            // a dK + dV tile pair as [64 accumulators][32 lanes]
+
+__device__ __forceinline__ int64_t csr_off(const AttnP<bf16>& a, int64_t bh, int64_t j) {
+  const int64_t o = bh * (a.n1 + 1) + j;
+  return a.off64 ? reinterpret_cast<const int64_t*>(a.offsets)[o] : (int64_t) reinterpret_cast<const int32_t*>(a.offsets)[o];
+}
+
+__device__ __forceinline__ void tile_to_mem(float* s, const float (&dk)[8][4], const float (&dv)[8][4], int lane) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s[(u * 4 + c) * 32 + lane] = dk[u][c];
+      s[(32 + u * 4 + c) * 32 + lane] = dv[u][c];
+    }
+}
+__device__ __forceinline__ void tile_add_mem(const float* s, float (&dk)[8][4], float (&dv)[8][4], int lane) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      dk[u][c] += s[(u * 4 + c) * 32 + lane];
+      dv[u][c] += s[(32 + u * 4 + c) * 32 + lane];
+    }
+}
+__device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) {
 #pragma unroll
   for (int u = 0; u < 8; ++u) dk[u][0] = dk[u][1] = dk[u][2] = dk[u][3] = dv[u][0] = dv[u][1] = dv[u][2] = dv[u][3] = 0.f;
-  const bool empty = list0 == list1;      // nobody selected this block: only the pooling-backward term remains
-  if (empty && warp > 0) return;
-  if (list0 + warp < list1) {
-    const bf16* kp = a.k.row(b, h, j * kBS);
-    const bf16* vp = a.v.row(b, h, j * kBS);
+}
+
+__global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_kernel(AttnP<bf16> a, float* __restrict__ partial) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* slots = reinterpret_cast<float*>(smem_raw);        // [kFineWarps*2][kTileFloats]
+  __shared__ int s_slot_bucket[kFineWarps * 2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const float sl2 = a.scale * kLog2e;
+  const int E = (int) (a.n1 * a.topk);
+  const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E);
+  constexpr int L = kFineWindow / kFineWarps;
+  const int rb = cb + warp * L, re = min(rb + L, ce);
+  const int32_t* fl = a.flat + bh * (int64_t) E;
+  if (threadIdx.x < kFineWarps * 2) s_slot_bucket[threadIdx.x] = -1;
+  __syncthreads();
+
+  float dk[8][4], dv[8][4];
+  if (rb < re) {
+    // bucket of entry rb: the j with off[j] <= rb < off[j+1]
+    int lo = 0, hi = (int) a.n1;          // invariant: off[lo] <= rb < off[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (csr_off(a, bh, mid) <= rb) lo = mid; else hi = mid;
+    }
+    int j = lo;
+    int bo = (int) csr_off(a, bh, j), nxt = (int) csr_off(a, bh, j + 1);
     RowFrag ka, kb, va, vb;
-    load_rowfrag(ka, kp + (int64_t) g * a.k.sn, t);
-    load_rowfrag(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
-    load_rowfrag(va, vp + (int64_t) g * a.v.sn, t);
-    load_rowfrag(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
-    const int32_t* fl = a.flat + bh * a.n1 * a.topk;
-    for (int64_t it = list0 + warp; it < list1; it += NW) {
-      int64_t qb = fl[it];
-      qb = qb < 0 ? 0 : (qb >= a.n1 ? a.n1 - 1 : qb);
-      if (it + NW < list1) {   // next entry's Q (lanes 0..15) and dO (lanes 16..31) rows towards L1
-        int64_t qn = fl[it + NW];
-        qn = qn < 0 ? 0 : (qn >= a.n1 ? a.n1 - 1 : qn);
-        if (lane < 16) prefetch_tile_rows(a.q.row(b, h, qn * kBS), a.q.sn, lane);
-        else prefetch_tile_rows(a.d_o.row(b, h, qn * kBS), a.d_o.sn, lane - 16);
+    auto load_kv = [&](int jj) {
+      const bf16* kp = a.k.row(b, h, (int64_t) jj * kBS);
+      const bf16* vp = a.v.row(b, h, (int64_t) jj * kBS);
+      load_rowfrag(ka, kp + (int64_t) g * a.k.sn, t);
+      load_rowfrag(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
+      load_rowfrag(va, vp + (int64_t) g * a.v.sn, t);
+      load_rowfrag(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
+    };
+    auto flush = [&]() {
+      if (bo >= rb && nxt <= re) {
+        dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);              // the bucket is wholly this warp's
+      } else {
+        const int slot = warp * 2 + (bo < rb ? 0 : 1);              // shared with an earlier / a later warp
+        tile_to_mem(slots + slot * kTileFloats, dk, dv, lane);
+        if (lane == 0) s_slot_bucket[slot] = j;
       }
-      dkv_step(a, b, h, bh, qb, ka, kb, va, vb, 0.f, sl2, g, t, dk, dv);
+    };
+    auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.n1 ? (int) a.n1 - 1 : v); };
+    RowFrag q0, q1, d0, d1;
+    float2 la, lb, da, db;
+    auto load_rows = [&](int qb) {
+      const bf16* qp = a.q.row(b, h, (int64_t) qb * kBS);
+      const bf16* dp = a.d_o.row(b, h, (int64_t) qb * kBS);
+      load_rowfrag(q0, qp + (int64_t) g * a.q.sn, t);
+      load_rowfrag(q1, qp + (int64_t) (g + 8) * a.q.sn, t);
+      load_rowfrag(d0, dp + (int64_t) g * a.d_o.sn, t);
+      load_rowfrag(d1, dp + (int64_t) (g + 8) * a.d_o.sn, t);
+      const int64_t rbase = bh * a.N + (int64_t) qb * kBS;
+      la = *reinterpret_cast<const float2*>(a.lse + rbase + 2 * t);          // query rows 2t, 2t+1
+      lb = *reinterpret_cast<const float2*>(a.lse + rbase + 8 + 2 * t);      // query rows 8+2t, 9+2t
+      da = *reinterpret_cast<const float2*>(a.delta + rbase + 2 * t);
+      db = *reinterpret_cast<const float2*>(a.delta + rbase + 8 + 2 * t);
+    };
+    // software pipeline: the row fragments (and lse/delta) of entry e+1 are requested as soon as the
+    // S^T / dP^T products of entry e have consumed the registers; the query-block index runs two
+    // entries ahead so that no load waits for an index
+    int qb_cur = clampq(fl[rb]);
+    int qb_nxt = rb + 1 < re ? clampq(fl[rb + 1]) : 0;
+    load_kv(j);
+    load_rows(qb_cur);
+    tile_zero(dk, dv);
+    for (int e = rb; e < re; ++e) {
+      if (e >= nxt) {                     // next non-empty bucket
+        flush();
+        do { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); } while (nxt <= e);
+        load_kv(j);
+        tile_zero(dk, dv);
+      }
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
+      mma_rows_x_keys(e0, e1, va, vb, d0, d1);
+      const float2 cla = la, clb = lb, cda = da, cdb = db;
+      const bf16* qp = a.q.row(b, h, (int64_t) qb_cur * kBS);
+      const bf16* dp = a.d_o.row(b, h, (int64_t) qb_cur * kBS);
+      if (e + 1 < re) {
+        qb_cur = qb_nxt;
+        qb_nxt = e + 2 < re ? clampq(fl[e + 2]) : 0;
+        load_rows(qb_cur);
+      }
+      uint32_t pa[4], ea[4];
+      dkv_p_ds(s0, s1, e0, e1, cla, clb, cda, cdb, sl2, 0.f, pa, ea);
+      {
+        ColFrag dc;                       // the same lines the row fragments just pulled into L1
+        load_colfrag(dc, dp, a.d_o.sn, g, t);
+        mma_x_cols(dv, pa[0], pa[1], pa[2], pa[3], dc);
+      }
+      {
+        ColFrag qc;
+        load_colfrag(qc, qp, a.q.sn, g, t);
+        mma_x_cols(dk, ea[0], ea[1], ea[2], ea[3], qc);
+      }
+    }
+    flush();
+  }
+  __syncthreads();
+  // buckets shared between warps: the first slot that names a bucket sums the later ones
+  for (int s = warp; s < kFineWarps * 2; s += kFineWarps) {
+    const int j = s_slot_bucket[s];
+    if (j < 0) continue;
+    bool leader = true;
+    for (int p = 0; p < s; ++p) leader = leader && (s_slot_bucket[p] != j);
+    if (!leader) continue;
+    tile_zero(dk, dv);
+    for (int p = s; p < kFineWarps * 2; ++p)
+      if (s_slot_bucket[p] == j) tile_add_mem(slots + p * kTileFloats, dk, dv, lane);
+    const int bo = (int) csr_off(a, bh, j), be = (int) csr_off(a, bh, j + 1);
+    if (bo >= cb && be <= ce) {
+      dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);
+    } else {                              // straddles windows: head slot if it began in an earlier window
+      float* dst = partial + ((bh * gridDim.x + blockIdx.x) * 2 + (bo < cb ? 0 : 1)) * (int64_t) kTileFloats;
+      tile_to_mem(dst, dk, dv, lane);
     }
   }
-  // partial sums of warps 1..NW-1 meet in shared memory; warp 0 adds them up and stores
-  if (warp > 0) {
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        red[warp - 1][u * 4 + c][lane] = dk[u][c];
-        red[warp - 1][32 + u * 4 + c][lane] = dv[u][c];
-      }
-  }
-  if (!empty) __syncthreads();
-  if (warp == 0) {
-    if (!empty) {
-#pragma unroll
-      for (int w = 0; w < NW - 1; ++w)
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            dk[u][c] += red[w][u * 4 + c][lane];
-            dv[u][c] += red[w][32 + u * 4 + c][lane];
-          }
-    }
-    float ek[2][8], ev[2][8];   // pooling-backward term for channels 16t + {0..7} and 16t + 8 + {0..7}
-#pragma unroll
-    for (int u = 0; u < 8; ++u) ek[0][u] = ek[1][u] = ev[0][u] = ev[1][u] = 0.f;
-    if (a.fold) {
-      const float* g1k = a.dpk + (bh * a.n1 + j) * kD + 16 * t;
-      const float* g1v = a.dpv + (bh * a.n1 + j) * kD + 16 * t;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) { ek[0][u] = g1k[u]; ek[1][u] = g1k[8 + u]; ev[0][u] = g1v[u]; ev[1][u] = g1v[8 + u]; }
-      if (a.two_level) {
-        const float* g2k = a.dpk2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
-        const float* g2v = a.dpv2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          ek[0][u] += g2k[u] * (1.f / kBS); ek[1][u] += g2k[8 + u] * (1.f / kBS);
-          ev[0][u] += g2v[u] * (1.f / kBS); ev[1][u] += g2v[8 + u] * (1.f / kBS);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      dk[u][0] = dk[u][0] * a.scale + ek[0][u] * (1.f / kBS); dk[u][1] = dk[u][1] * a.scale + ek[1][u] * (1.f / kBS);
-      dk[u][2] = dk[u][2] * a.scale + ek[0][u] * (1.f / kBS); dk[u][3] = dk[u][3] * a.scale + ek[1][u] * (1.f / kBS);
-      dv[u][0] += ev[0][u] * (1.f / kBS); dv[u][1] += ev[1][u] * (1.f / kBS);
-      dv[u][2] += ev[0][u] * (1.f / kBS); dv[u][3] += ev[1][u] * (1.f / kBS);
-    }
-    store_acc_row<0>(a.dk.row(b, h, j * kBS + g), dk, t, 1.f);
-    store_acc_row<1>(a.dk.row(b, h, j * kBS + g + 8), dk, t, 1.f);
-    store_acc_row<0>(a.dv.row(b, h, j * kBS + g), dv, t, 1.f);
-    store_acc_row<1>(a.dv.row(b, h, j * kBS + g + 8), dv, t, 1.f);
-  }
+}
+
+// One warp per KV block: blocks nobody selected get their pooling-backward term, blocks whose bucket
+// straddles windows of attn_dkv_fine_kernel get the sum of the windows' partial tiles (window order).
+__global__ void __launch_bounds__(128) attn_dkv_finish_kernel(AttnP<bf16> a, const float* __restrict__ partial, int n_windows) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int64_t j = (int64_t) blockIdx.x * 4 + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  if (j >= a.n1) return;
+  const int bo = (int) csr_off(a, bh, j), be = (int) csr_off(a, bh, j + 1);
+  const int c_first = bo / kFineWindow, c_last = (be - 1) / kFineWindow;
+  if (be > bo && c_first == c_last) return;          // finished inside one window
+  float dk[8][4], dv[8][4];
+  tile_zero(dk, dv);
+  if (be > bo)
+    for (int c = c_first; c <= c_last; ++c)
+      tile_add_mem(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
+  dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);
 }
 
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st);
@@ -444,9 +567,15 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
   }
   if (mask & 4) {
-    constexpr int NWF = 4;
-    attn_dkv_fine_kernel<NWF><<<dim3((unsigned) a.n1, BH), NWF * 32, 0, st>>>(a);
+    const int64_t E = a.n1 * a.topk;
+    const int n_windows = (int) ((E + kFineWindow - 1) / kFineWindow);
+    float* partial = (float*) g->dkv_partial->ptr;
+    const size_t smem = (size_t) kFineWarps * 2 * kTileFloats * sizeof(float);
+    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    attn_dkv_fine_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
     LLSA_LAUNCH_OK("attn_dkv_fine_kernel");
+    attn_dkv_finish_kernel<<<dim3((unsigned) ((a.n1 + 3) / 4), BH), 128, 0, st>>>(a, partial, n_windows);
+    LLSA_LAUNCH_OK("attn_dkv_finish_kernel");
   }
   return LLSA_OK;
 }

@@ -81,6 +81,44 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ---- per-warp gather ring ------------------------------------------------------------------
+// Gathered 16x64 tiles (selected K/V blocks, or the Q/dO blocks of a CSR entry) have a
+// latency of well over a thousand cycles from L2/HBM; registers can hold one tile ahead at
+// most.  Each warp therefore owns a small ring of stages in shared memory that it fills with
+// cp.async several tiles ahead and drains with 128-bit ld.shared.  A stage holds two tiles of
+// 2 KB (16 rows x 128 B, no padding); the 16-byte chunk c of row r sits at chunk c ^ (r & 7),
+// which makes both fragment read patterns bank-conflict free.
+constexpr int kRingTileElems = 16 * 64;          // one tile, in bf16 elements
+
+// The 32 lanes copy two tiles (A rows: a + r*sa, B rows: b + r*sb) into one stage: 8 chunks per lane.
+__device__ __forceinline__ void ring_issue(bf16* stage, const bf16* a, int64_t sa, const bf16* b, int64_t sb, int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = i * 32 + lane, tile = idx >> 7, r = (idx >> 3) & 15, c = idx & 7;
+    const bf16* src = (tile ? b + (int64_t) r * sb : a + (int64_t) r * sa) + c * 8;
+    cp_async16(stage + tile * kRingTileElems + r * 64 + ((c ^ (r & 7)) << 3), src);
+  }
+}
+
+__device__ __forceinline__ void load_rowfrag_ring(RowFrag& f, const bf16* tile, int r, int t) {
+  const bf16* row = tile + r * 64;
+  const uint4 a = *reinterpret_cast<const uint4*>(row + (((2 * t) ^ (r & 7)) << 3));
+  const uint4 b = *reinterpret_cast<const uint4*>(row + (((2 * t + 1) ^ (r & 7)) << 3));
+  f.r[0] = a.x; f.r[1] = a.y; f.r[2] = a.z; f.r[3] = a.w;
+  f.r[4] = b.x; f.r[5] = b.y; f.r[6] = b.z; f.r[7] = b.w;
+}
+
+__device__ __forceinline__ void load_colfrag_ring(ColFrag& f, const bf16* tile, int g, int t) {
+  const int r0 = 2 * t, r1 = 2 * t + 1, r2 = 2 * t + 8, r3 = 2 * t + 9;
+  f.row[0] = *reinterpret_cast<const uint4*>(tile + r0 * 64 + ((g ^ (r0 & 7)) << 3));
+  f.row[1] = *reinterpret_cast<const uint4*>(tile + r1 * 64 + ((g ^ (r1 & 7)) << 3));
+  f.row[2] = *reinterpret_cast<const uint4*>(tile + r2 * 64 + ((g ^ (r2 & 7)) << 3));
+  f.row[3] = *reinterpret_cast<const uint4*>(tile + r3 * 64 + ((g ^ (r3 & 7)) << 3));
+}
+
 // Pulls the 16 rows of a tile (128 bytes each) towards L1 without using registers:
 // lanes 0..15 of `lane16` each touch one row.
 __device__ __forceinline__ void prefetch_tile_rows(const bf16* tile, int64_t stride, int lane16) {

@@ -47,7 +47,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layout_matches_header():
     # 11 + 11 tensor pointers, 5 + 5 scalars of 4 bytes, padded to pointer alignment
     assert C.sizeof(_lib.LlsaTensor) == 8 + 4 + 4 + 32 + 32
-    assert C.sizeof(_lib.LlsaAttnArgs) == 11 * 8 + 24 + 11 * 8 + 24
+    assert C.sizeof(_lib.LlsaAttnArgs) == 11 * 8 + 24 + 11 * 8 + 24 + 8
     assert _lib.LlsaAttnArgs.d_o.offset == 11 * 8 + 24
     assert _lib.LlsaAttnArgs.fold_pool_bwd.offset == 11 * 8 + 24 + 11 * 8
 
