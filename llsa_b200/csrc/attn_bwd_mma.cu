@@ -150,17 +150,13 @@ __global__ void __launch_bounds__(NW * 32, 3) attn_dq_mma_kernel(AttnP<bf16> a, 
     load_rowfrag(v0, r.v + (int64_t) g * r.vs, t);
     load_rowfrag(v1, r.v + (int64_t) (g + 8) * r.vs, t);
     for (int gi = 0; gi < n_glob; ++gi) {
-      if (gi + 2 < n_glob) {   // two blocks ahead: K rows (lanes 0..15) and V rows (lanes 16..31) towards L1
-        const GlobalKV f = global_kv(a, b, h, bh, qb, gi + 2, my_fine, n_smem_tiles, lw1, lw2);
-        if (lane < 16) prefetch_tile_rows(f.k, f.ks, lane);
-        else prefetch_tile_rows(f.v, f.vs, lane - 16);
-      }
-      ColFrag kc;
-      load_colfrag(kc, r.k, r.ks, g, t);
       const float lw = r.lw;
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
       mma_rows_x_keys(s0, s1, qlo, qhi, k0, k1);
       mma_rows_x_keys(p0, p1, dlo, dhi, v0, v1);
+      uint32_t tk0[8], tk1[8];   // K transposed in registers: the B operand of dQ += dS.K, no second load
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { tk0[i] = movmatrix_trans(k0.r[i]); tk1[i] = movmatrix_trans(k1.r[i]); }
       if (gi + 1 < n_glob) {
         r = global_kv(a, b, h, bh, qb, gi + 1, my_fine, n_smem_tiles, lw1, lw2);
         load_rowfrag(k0, r.k + (int64_t) g * r.ks, t);
@@ -170,7 +166,8 @@ __global__ void __launch_bounds__(NW * 32, 3) attn_dq_mma_kernel(AttnP<bf16> a, 
       }
       uint32_t da[4];
       dq_ds(s0, s1, p0, p1, row, sl2, lw, da);
-      mma_x_cols(dq, da[0], da[1], da[2], da[3], kc);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mma_bf16_16816(dq[i], da[0], da[1], da[2], da[3], tk0[i], tk1[i]);
     }
   }
   cp_async_wait_all();
@@ -188,12 +185,10 @@ __global__ void __launch_bounds__(NW * 32, 3) attn_dq_mma_kernel(AttnP<bf16> a, 
     mma_rows_x_keys(p0, p1, dlo, dhi, v0, v1);
     uint32_t da[4];
     dq_ds(s0, s1, p0, p1, row, sl2, ip < a.p1_blocks ? lw1 : lw2, da);
-    ColFrag kc;
-    load_colfrag_smem(kc, tk, g, t);
-    mma_x_cols(dq, da[0], da[1], da[2], da[3], kc);
+    mma_x_rowfrag_t(dq, da[0], da[1], da[2], da[3], k0, k1);
   }
-  store_acc_row<0>(a.dq.row(b, h, qb * kBS + g), dq, t, a.scale);
-  store_acc_row<1>(a.dq.row(b, h, qb * kBS + g + 8), dq, t, a.scale);
+  store_acc_row_t<0>(a.dq.row(b, h, qb * kBS + g), dq, t, a.scale);
+  store_acc_row_t<1>(a.dq.row(b, h, qb * kBS + g + 8), dq, t, a.scale);
 }
 
 // P^T and dS^T (bf16, as A registers) of one (key tile) x (query block) pair from the
@@ -291,59 +286,48 @@ __global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16>
       const bf16* tq = sq + qi * kBS * kSmemPitch;
       const bf16* td = sd + qi * kBS * kSmemPitch;
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
-      {
-        RowFrag q0, q1;
-        load_rowfrag_smem(q0, tq + g * kSmemPitch, t);
-        load_rowfrag_smem(q1, tq + (g + 8) * kSmemPitch, t);
-        mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
-      }
-      {
-        RowFrag d0, d1;
-        load_rowfrag_smem(d0, td + g * kSmemPitch, t);
-        load_rowfrag_smem(d1, td + (g + 8) * kSmemPitch, t);
-        mma_rows_x_keys(e0, e1, va, vb, d0, d1);
-      }
+      RowFrag q0, q1, d0, d1;
+      load_rowfrag_smem(q0, tq + g * kSmemPitch, t);
+      load_rowfrag_smem(q1, tq + (g + 8) * kSmemPitch, t);
+      mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
+      load_rowfrag_smem(d0, td + g * kSmemPitch, t);
+      load_rowfrag_smem(d1, td + (g + 8) * kSmemPitch, t);
+      mma_rows_x_keys(e0, e1, va, vb, d0, d1);
       const float2 la = *reinterpret_cast<const float2*>(sl + qi * kBS + 2 * t), lb = *reinterpret_cast<const float2*>(sl + qi * kBS + 8 + 2 * t);
       const float2 da = *reinterpret_cast<const float2*>(sdel + qi * kBS + 2 * t), db = *reinterpret_cast<const float2*>(sdel + qi * kBS + 8 + 2 * t);
       uint32_t pa[4], ea[4];
       dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, lw, pa, ea);
-      {
-        ColFrag dc;
-        load_colfrag_smem(dc, td, g, t);
-        mma_x_cols(dv, pa[0], pa[1], pa[2], pa[3], dc);
-      }
-      {
-        ColFrag qc;
-        load_colfrag_smem(qc, tq, g, t);
-        mma_x_cols(dk, ea[0], ea[1], ea[2], ea[3], qc);
-      }
+      // the same tiles, transposed in registers, are the B operands of dV and dK
+      mma_x_rowfrag_t(dv, pa[0], pa[1], pa[2], pa[3], d0, d1);
+      mma_x_rowfrag_t(dk, ea[0], ea[1], ea[2], ea[3], q0, q1);
     }
     // a lane owns channels [16t, 16t+16) of key rows g and g+8: four 128-bit reductions per row
-    red_acc_row<0>(gk + g * kD, dk, t, a.scale);
-    red_acc_row<1>(gk + (g + 8) * kD, dk, t, a.scale);
-    red_acc_row<0>(gv + g * kD, dv, t, 1.f);
-    red_acc_row<1>(gv + (g + 8) * kD, dv, t, 1.f);
+    red_acc_row_t<0>(gk + g * kD, dk, t, a.scale);
+    red_acc_row_t<1>(gk + (g + 8) * kD, dk, t, a.scale);
+    red_acc_row_t<0>(gv + g * kD, dv, t, 1.f);
+    red_acc_row_t<1>(gv + (g + 8) * kD, dv, t, 1.f);
   }
 }
 
 // Adds the pooling-backward term to a finished 16x64 dK/dV tile of KV block j and stores it (bf16).
 __device__ __forceinline__ void dkv_fine_store(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t j, float (&dk)[8][4],
                                                float (&dv)[8][4], int g, int t) {
-  float ek[2][8], ev[2][8];   // pooling-backward term for channels 16t + {0..7} and 16t + 8 + {0..7}
+  // the tiles come from mma_x_rowfrag_t-style products: acc[u][e] is channel 16t + 2u + e
+  float ek[2][8], ev[2][8];   // pooling-backward term: [e][u] for channel 16t + 2u + e
 #pragma unroll
   for (int u = 0; u < 8; ++u) ek[0][u] = ek[1][u] = ev[0][u] = ev[1][u] = 0.f;
   if (a.fold) {
     const float* g1k = a.dpk + (bh * a.n1 + j) * kD + 16 * t;
     const float* g1v = a.dpv + (bh * a.n1 + j) * kD + 16 * t;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) { ek[0][u] = g1k[u]; ek[1][u] = g1k[8 + u]; ev[0][u] = g1v[u]; ev[1][u] = g1v[8 + u]; }
+    for (int u = 0; u < 8; ++u) { ek[0][u] = g1k[2 * u]; ek[1][u] = g1k[2 * u + 1]; ev[0][u] = g1v[2 * u]; ev[1][u] = g1v[2 * u + 1]; }
     if (a.two_level) {
       const float* g2k = a.dpk2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
       const float* g2v = a.dpv2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        ek[0][u] += g2k[u] * (1.f / kBS); ek[1][u] += g2k[8 + u] * (1.f / kBS);
-        ev[0][u] += g2v[u] * (1.f / kBS); ev[1][u] += g2v[8 + u] * (1.f / kBS);
+        ek[0][u] += g2k[2 * u] * (1.f / kBS); ek[1][u] += g2k[2 * u + 1] * (1.f / kBS);
+        ev[0][u] += g2v[2 * u] * (1.f / kBS); ev[1][u] += g2v[2 * u + 1] * (1.f / kBS);
       }
     }
   }
@@ -354,10 +338,10 @@ __device__ __forceinline__ void dkv_fine_store(const AttnP<bf16>& a, int64_t b, 
     dv[u][0] += ev[0][u] * (1.f / kBS); dv[u][1] += ev[1][u] * (1.f / kBS);
     dv[u][2] += ev[0][u] * (1.f / kBS); dv[u][3] += ev[1][u] * (1.f / kBS);
   }
-  store_acc_row<0>(a.dk.row(b, h, j * kBS + g), dk, t, 1.f);
-  store_acc_row<1>(a.dk.row(b, h, j * kBS + g + 8), dk, t, 1.f);
-  store_acc_row<0>(a.dv.row(b, h, j * kBS + g), dv, t, 1.f);
-  store_acc_row<1>(a.dv.row(b, h, j * kBS + g + 8), dv, t, 1.f);
+  store_acc_row_t<0>(a.dk.row(b, h, j * kBS + g), dk, t, 1.f);
+  store_acc_row_t<1>(a.dk.row(b, h, j * kBS + g + 8), dk, t, 1.f);
+  store_acc_row_t<0>(a.dv.row(b, h, j * kBS + g), dv, t, 1.f);
+  store_acc_row_t<1>(a.dv.row(b, h, j * kBS + g + 8), dv, t, 1.f);
 }
 
 // ---- fine dK/dV: equal windows of the CSR, whatever the fan-in ---------------------------------
@@ -403,7 +387,7 @@ __device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) 
   for (int u = 0; u < 8; ++u) dk[u][0] = dk[u][1] = dk[u][2] = dk[u][3] = dv[u][0] = dv[u][1] = dv[u][2] = dv[u][3] = 0.f;
 }
 
-__global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_kernel(AttnP<bf16> a, float* __restrict__ partial) {
+__global__ void __launch_bounds__(kFineWarps * 32, 2) attn_dkv_fine_kernel(AttnP<bf16> a, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* slots = reinterpret_cast<float*>(smem_raw);        // [kFineWarps*2][kTileFloats]
   __shared__ int s_slot_bucket[kFineWarps * 2];
@@ -481,8 +465,13 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_kernel(AttnP
       mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
       mma_rows_x_keys(e0, e1, va, vb, d0, d1);
       const float2 cla = la, clb = lb, cda = da, cdb = db;
-      const bf16* qp = a.q.row(b, h, (int64_t) qb_cur * kBS);
-      const bf16* dp = a.d_o.row(b, h, (int64_t) qb_cur * kBS);
+      // the same Q / dO tiles, transposed in registers, are the B operands of dK / dV: no second load
+      uint32_t tq0[8], tq1[8], td0[8], td1[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        tq0[i] = movmatrix_trans(q0.r[i]); tq1[i] = movmatrix_trans(q1.r[i]);
+        td0[i] = movmatrix_trans(d0.r[i]); td1[i] = movmatrix_trans(d1.r[i]);
+      }
       if (e + 1 < re) {
         qb_cur = qb_nxt;
         qb_nxt = e + 2 < re ? clampq(fl[e + 2]) : 0;
@@ -490,16 +479,10 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_kernel(AttnP
       }
       uint32_t pa[4], ea[4];
       dkv_p_ds(s0, s1, e0, e1, cla, clb, cda, cdb, sl2, 0.f, pa, ea);
-      {
-        ColFrag dc;                       // the same lines the row fragments just pulled into L1
-        load_colfrag(dc, dp, a.d_o.sn, g, t);
-        mma_x_cols(dv, pa[0], pa[1], pa[2], pa[3], dc);
-      }
-      {
-        ColFrag qc;
-        load_colfrag(qc, qp, a.q.sn, g, t);
-        mma_x_cols(dk, ea[0], ea[1], ea[2], ea[3], qc);
-      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mma_bf16_16816(dv[i], pa[0], pa[1], pa[2], pa[3], td0[i], td1[i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mma_bf16_16816(dk[i], ea[0], ea[1], ea[2], ea[3], tq0[i], tq1[i]);
     }
     flush();
   }

@@ -40,7 +40,7 @@ struct RowFrag {
 // four lanes of a quad read one whole 128-byte row and a warp-wide load touches 8 lines.
 // `row` must be 32-byte aligned.
 __device__ __forceinline__ void load_rowfrag(RowFrag& f, const bf16* row, int t) {
-  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+  asm volatile("ld.global.ca.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(f.r[0]), "=r"(f.r[1]), "=r"(f.r[2]), "=r"(f.r[3]), "=r"(f.r[4]), "=r"(f.r[5]), "=r"(f.r[6]), "=r"(f.r[7])
                : "l"(row + 16 * t));
 }
@@ -155,6 +155,40 @@ __device__ __forceinline__ void mma_x_cols(float (&acc)[8][4], uint32_t a0, uint
   }
 }
 
+// ---- row-contraction operand from a RowFrag pair, without a second load ------------------------
+// movmatrix transposes the 8x8 b16 matrix a warp holds one register per lane.  Register i of a
+// RowFrag is the matrix M_i[row][c] = tile[row][16*(c/2) + 2i + c%2]; transposed, lane (g,t)
+// holds tile[rows 2t,2t+1][channel 16*(g/2) + 2i + g%2]: exactly a B register whose n-slot g is
+// that channel.  With `lo` = rows 0..7 and `hi` = rows 8..15 of the tile this gives b0 / b1 of
+// output tile i, whose accumulators c0,c1 (c2,c3) are channels 16t + 2i, 16t + 2i + 1 of rows
+// g (g + 8): again 16 consecutive channels per lane, in the order acc[0][0], acc[0][1], acc[1][0] ...
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+// acc (16 x 64) += A(16 x 16 as four A registers) . tile(16 rows x 64 channels given as its RowFrag pair)
+__device__ __forceinline__ void mma_x_rowfrag_t(float (&acc)[8][4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const RowFrag& lo,
+                                                const RowFrag& hi) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mma_bf16_16816(acc[i], a0, a1, a2, a3, movmatrix_trans(lo.r[i]), movmatrix_trans(hi.r[i]));
+}
+
+// Channel of accumulator acc[u][e] (e = 0/1, or 2/3 for row g+8) inside the lane's 16 channels, for
+// tiles produced by mma_x_rowfrag_t: 2u + e.  Stores one row (ROW 0: c0/c1, ROW 1: c2/c3) as bf16.
+template <int ROW>
+__device__ __forceinline__ void store_acc_row_t(bf16* row, const float (&acc)[8][4], int t, float mul) {
+  constexpr int lo = ROW * 2, hi = ROW * 2 + 1;
+  uint4 x, y;
+  x.x = pack_bf16(acc[0][lo] * mul, acc[0][hi] * mul); x.y = pack_bf16(acc[1][lo] * mul, acc[1][hi] * mul);
+  x.z = pack_bf16(acc[2][lo] * mul, acc[2][hi] * mul); x.w = pack_bf16(acc[3][lo] * mul, acc[3][hi] * mul);
+  y.x = pack_bf16(acc[4][lo] * mul, acc[4][hi] * mul); y.y = pack_bf16(acc[5][lo] * mul, acc[5][hi] * mul);
+  y.z = pack_bf16(acc[6][lo] * mul, acc[6][hi] * mul); y.w = pack_bf16(acc[7][lo] * mul, acc[7][hi] * mul);
+  *reinterpret_cast<uint4*>(row + 16 * t) = x;
+  *reinterpret_cast<uint4*>(row + 16 * t + 8) = y;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -196,6 +230,16 @@ __device__ __forceinline__ void red_acc_row(float* row, const float (&acc)[8][4]
   red_add_v4(p + 4, acc[4][lo] * mul, acc[5][lo] * mul, acc[6][lo] * mul, acc[7][lo] * mul);
   red_add_v4(p + 8, acc[0][hi] * mul, acc[1][hi] * mul, acc[2][hi] * mul, acc[3][hi] * mul);
   red_add_v4(p + 12, acc[4][hi] * mul, acc[5][hi] * mul, acc[6][hi] * mul, acc[7][hi] * mul);
+}
+
+// The same for tiles produced by mma_x_rowfrag_t (acc[u][e] = channel 16t + 2u + e)
+template <int ROW>
+__device__ __forceinline__ void red_acc_row_t(float* row, const float (&acc)[8][4], int t, float mul) {
+  constexpr int lo = ROW * 2, hi = ROW * 2 + 1;
+  float* p = row + 16 * t;
+#pragma unroll
+  for (int u = 0; u < 8; u += 2)
+    red_add_v4(p + 2 * u, acc[u][lo] * mul, acc[u][hi] * mul, acc[u + 1][lo] * mul, acc[u + 1][hi] * mul);
 }
 
 }  // namespace llsa
