@@ -69,6 +69,8 @@ AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd);
 
 bool mma_path_ok(const LlsaAttnArgs* g, bool bwd);   // operands meet the tensor-core kernels' alignment / top-k limits
 int pooled_smem_tiles(int n_pooled);                 // pooled key tiles a CTA keeps in shared memory
+int pooled_tc_keys(const AttnP<__nv_bfloat16>& a);   // pooled keys per row if the tcgen05 pooled kernels apply, else 0
+int launch_attn_fwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<__nv_bfloat16>& a, int64_t BH, cudaStream_t st);
 int launch_attn_fwd_generic(const LlsaAttnArgs* g, cudaStream_t st);
 int launch_attn_bwd_generic(const LlsaAttnArgs* g, cudaStream_t st);
 int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st);

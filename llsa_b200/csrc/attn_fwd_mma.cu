@@ -16,6 +16,8 @@
 // The softmax runs online, one 16-key block at a time, in the exp2 domain; a
 // pooled key's weight enters as +log2(weight) on its logit, which is what
 // `l += l_ij * W; acc += P.V * W` in the reference amounts to.
+#include <stdlib.h>
+
 #include "attn.cuh"
 #include "mma_frag.cuh"
 
@@ -171,6 +173,62 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_mma_kernel(AttnP<bf16> a,
   }
 }
 
+// Fine stage alone (the pooled stages then run on tcgen05, attn_pooled_tc.cu, and merge into the
+// o / lse written here).  Every selected K/V block costs a full L2/HBM round trip, far longer
+// than the 16 MMAs it feeds, so each warp keeps kFineStages-1 blocks in flight with cp.async
+// into its own ring of shared-memory stages (mma_frag.cuh) and reads the fragments from there.
+constexpr int kFineStages = 3;
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine_kernel(AttnP<bf16> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw) + warp * (kFineStages * 2 * kRingTileElems);
+  const int64_t qb = (int64_t) blockIdx.x * NW + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const int my_fine = lane < a.topk ? (int) fine_block(a, bh, qb, lane) : 0;
+  const float sl2 = a.scale * 1.4426950408889634f;
+  const int n_glob = a.topk;
+  auto issue = [&](int i) {
+    const int64_t j = __shfl_sync(0xffffffffu, my_fine, i);
+    ring_issue(ring + (i % kFineStages) * 2 * kRingTileElems, a.k.row(b, h, j * kBS), a.k.sn, a.v.row(b, h, j * kBS), a.v.sn, lane);
+  };
+#pragma unroll
+  for (int s = 0; s < kFineStages - 1; ++s) {
+    if (s < n_glob) issue(s);
+    cp_async_commit();
+  }
+  RowFrag qlo, qhi;
+  load_rowfrag(qlo, a.q.row(b, h, qb * kBS + g), t);
+  load_rowfrag(qhi, a.q.row(b, h, qb * kBS + g + 8), t);
+  FwdState st;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) st.o[j][0] = st.o[j][1] = st.o[j][2] = st.o[j][3] = 0.f;
+  st.m0 = st.m1 = -INFINITY;
+  st.l0 = st.l1 = 0.f;
+  for (int gi = 0; gi < n_glob; ++gi) {
+    cp_async_wait_group<kFineStages - 2>();     // block gi has landed (this lane's chunks) ...
+    __syncwarp();                               // ... and everybody else's; the stage read last time is free
+    if (gi + kFineStages - 1 < n_glob) issue(gi + kFineStages - 1);
+    cp_async_commit();
+    const bf16* tk = ring + (gi % kFineStages) * 2 * kRingTileElems;
+    RowFrag k0, k1;
+    load_rowfrag_ring(k0, tk, g, t);
+    load_rowfrag_ring(k1, tk, g + 8, t);
+    uint32_t pa[4];
+    fwd_scores(st, qlo, qhi, k0, k1, sl2, 0.f, pa);
+    ColFrag v;
+    load_colfrag_ring(v, tk + kRingTileElems, g, t);
+    mma_x_cols(st.o, pa[0], pa[1], pa[2], pa[3], v);
+  }
+  const float l0 = quad_sum(st.l0), l1 = quad_sum(st.l1);
+  store_acc_row<0>(a.o.row(b, h, qb * kBS + g), st.o, t, 1.f / l0);
+  store_acc_row<1>(a.o.row(b, h, qb * kBS + g + 8), st.o, t, 1.f / l1);
+  if (t == 0) {
+    a.lse[bh * a.N + qb * kBS + g] = (st.m0 + log2f(l0)) * 0.6931471805599453f;
+    a.lse[bh * a.N + qb * kBS + g + 8] = (st.m1 + log2f(l1)) * 0.6931471805599453f;
+  }
+}
+
 bool mma_path_ok(const LlsaAttnArgs* g, bool bwd) {
   if (g->topk > 32 || (g->pk2 && g->topk_p > 32)) return false;
   // 256-bit fragment loads need 32-byte aligned rows
@@ -191,6 +249,16 @@ int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   if (!mma_path_ok(g, false)) return launch_attn_fwd_generic(g, st);
   AttnP<bf16> a = build_attn_params<bf16>(g, false);
   constexpr int NW = 8;
+  const int64_t BH = g->q->shape[0] * a.H;
+  const char* tc_env = getenv("LLSA_B200_TC");
+  if (pooled_tc_keys(a) && tc_env && tc_env[0] == '1') {
+    // fine blocks on mma.sync (o and lse of the fine part alone), pooled keys on tcgen05, merged there
+    const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
+    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+    attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.n1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
+    LLSA_LAUNCH_OK("attn_fwd_fine_kernel");
+    return launch_attn_fwd_pooled_tc(g, a, BH, st);
+  }
   const int n_smem = pooled_smem_tiles(a.p1_blocks + a.p2_blocks);
   const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
   LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_mma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));

@@ -239,11 +239,13 @@ def _bf16_case(op, B, H, N, seed, rope=False):
     return q, k, v, do
 
 
-@pytest.mark.parametrize("force_generic", [False, True])
-def test_llsa_l2_bf16_vs_oracle(force_generic, monkeypatch):
+@pytest.mark.parametrize("path", ["mma", "generic", "tcgen05"])
+def test_llsa_l2_bf16_vs_oracle(path, monkeypatch):
+    """path: mma.sync kernels / scalar FFMA kernels / pooled stages of the forward on tcgen05 + TMA."""
     L = _ops()
     from llsa_b200 import ops
-    monkeypatch.setattr(ops, "_force_generic", force_generic)
+    monkeypatch.setattr(ops, "_force_generic", path == "generic")
+    monkeypatch.setenv("LLSA_B200_TC", "1" if path == "tcgen05" else "0")
     q, k, v, do = _bf16_case("l2", 1, 2, 16384, 41)
     qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
     dbg = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
@@ -309,9 +311,12 @@ def test_llsa_l1_exact_pooled_grad_switch():
     assert rel_l2(kg.grad, r["dk"]) < 2e-5 and rel_l2(vg.grad, r["dv"]) < 2e-5
 
 
-def test_strided_bnhd_inputs_match_contiguous():
-    """[B,H,N,D] views of [B,N,H,D] storage (what the model passes) give the same bits; o keeps q's strides."""
+@pytest.mark.parametrize("tc", ["0", "1"])
+def test_strided_bnhd_inputs_match_contiguous(tc, monkeypatch):
+    """[B,H,N,D] views of [B,N,H,D] storage (what the model passes) give the same bits; o keeps q's strides.
+    tc="1": the forward's pooled stages go through the 4-D tensor map of the strided q."""
     L = _ops()
+    monkeypatch.setenv("LLSA_B200_TC", tc)
     q, k, v, do = _bf16_case("l2", 2, 3, 16384, 44)
     to_view = lambda t: t.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)
     qc, kc, vc = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
