@@ -11,6 +11,7 @@ from .ops import (compute_topk_indices_sparse, flash_sparse_residual_attention_l
                   sparse_indices_attn_res_2_2_fwd, sparse_indices_attn_res_fwd,
                   sparse_indices_attn_res_scatter_2_2_bwd_v2, sparse_indices_attn_res_scatter_bwd_v2,
                   transpose_indices)
+from .hostpipe import HostPipeline  # noqa: F401
 from .shims import install_reference_shims  # noqa: F401
 
 __version__ = "0.1.0"

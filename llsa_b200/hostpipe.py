@@ -1,0 +1,66 @@
+"""Forward + backward of llsa_l1 / llsa_l2 for operands that live in pinned HOST memory.
+
+Every batch element is independent (sparse_attention_res_2.py:179: all grids are (..., B*H)),
+so the batch is cut into chunks and three streams run a software pipeline over them:
+
+    copy-in stream : q, k, v, d_o of chunk c+1   host -> device
+    compute stream : the operator and its backward on chunk c
+    copy-out stream: o, dq, dk, dv of chunk c-1  device -> host
+
+PCIe carries both directions at once, so a step costs about max(bytes in, bytes out) / link
+bandwidth instead of the sum of both copies plus the compute.  Device staging buffers are
+allocated once per pipeline object; nothing here touches the default stream.
+"""
+import torch
+
+
+class HostPipeline:
+    def __init__(self, call, shape, dtype, device, chunk_batch=1, depth=3):
+        """call(q, k, v) -> o on device tensors; shape = (B, H, N, D) of the full host operands."""
+        B, H, N, D = shape
+        if B % chunk_batch:
+            raise ValueError("chunk_batch must divide the batch")
+        self.call, self.B, self.cb, self.depth = call, B, chunk_batch, depth
+        self.dev = device
+        self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
+        self.slots = [[torch.empty((chunk_batch, H, N, D), dtype=dtype, device=device) for _ in range(4)] for _ in range(depth)]
+
+    def fwd_bwd(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv):
+        """Pinned host tensors in, pinned host tensors out.  The work is ordered after what the current
+        stream holds at the call and the current stream is made to wait for it, so the results are valid
+        once the current stream has been synchronised."""
+        cur = torch.cuda.current_stream(self.dev)
+        for s in (self.s_in, self.s_comp, self.s_out):
+            s.wait_stream(cur)
+        n_chunks = self.B // self.cb
+        ev_in = [torch.cuda.Event() for _ in range(n_chunks)]
+        ev_comp = [torch.cuda.Event() for _ in range(n_chunks)]
+        ev_free = [None] * self.depth          # slot's device inputs no longer needed (its backward has run)
+        keep = []
+        for c in range(n_chunks):
+            sl = slice(c * self.cb, (c + 1) * self.cb)
+            slot = self.slots[c % self.depth]
+            with torch.cuda.stream(self.s_in):
+                if ev_free[c % self.depth] is not None:
+                    self.s_in.wait_event(ev_free[c % self.depth])
+                for d_, h_ in zip(slot, (hq, hk, hv, hdo)):
+                    d_.copy_(h_[sl], non_blocking=True)
+                ev_in[c].record(self.s_in)
+            with torch.cuda.stream(self.s_comp):
+                self.s_comp.wait_event(ev_in[c])
+                q, k, v = [d_.detach().requires_grad_(True) for d_ in slot[:3]]
+                o = self.call(q, k, v)
+                o.backward(slot[3])
+                ev_comp[c].record(self.s_comp)
+                ev_free[c % self.depth] = ev_comp[c]
+            outs = (o.detach(), q.grad, k.grad, v.grad)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_comp[c])
+                for h_, d_ in zip((ho, hdq, hdk, hdv), outs):
+                    d_.record_stream(self.s_out)
+                    h_[sl].copy_(d_, non_blocking=True)
+            keep.append(outs)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_comp)
+        self._keep = keep                      # device results stay referenced until the next call
+        return ho, hdq, hdk, hdv

@@ -331,6 +331,23 @@ def test_strided_bnhd_inputs_match_contiguous(tc, monkeypatch):
     assert rel_l2(ks.grad, kc.grad) < 1e-3 and rel_l2(vs.grad, vc.grad) < 1e-3   # fp32 atomics: order may differ
 
 
+def test_host_pipeline_matches_direct_call():
+    """Pinned host operands through the three-stream chunk pipeline give the bits of one direct call."""
+    L = _ops()
+    q, k, v, do = _bf16_case("l2", 4, 2, 4096, 45)
+    hq, hk, hv, hdo = [t.pin_memory() for t in (q, k, v, do)]
+    outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    pipe = L.HostPipeline(lambda a, b, c: L.llsa_l2(a, b, c, 8, 8, 16), tuple(q.shape), q.dtype, torch.device(DEV), chunk_batch=1, depth=2)
+    for _ in range(2):          # the second call reuses every slot
+        pipe.fwd_bwd(hq, hk, hv, hdo, *outs)
+        torch.cuda.synchronize()
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    o = L.llsa_l2(qg, kg, vg, 8, 8, 16)
+    o.backward(do.to(DEV))
+    assert torch.equal(outs[0], o.detach().cpu()) and torch.equal(outs[1], qg.grad.cpu())
+    assert rel_l2(outs[2], kg.grad.cpu()) < 1e-3 and rel_l2(outs[3], vg.grad.cpu()) < 1e-3
+
+
 # ------------------------------------------------------------------ full-size properties (BASELINE config 3 shape)
 def test_cfg3_full_size_properties():
     L = _ops()
