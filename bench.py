@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling a smaller case)")
+    ap.add_argument("--seq-parallel", action="store_true", help="shard the sequence over the ranks even if B*H >= ranks")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     return ap.parse_args()
@@ -149,8 +150,18 @@ def main():
     fn = llsa_b200.llsa_l2 if cfg["op"] == "llsa_l2" else llsa_b200.llsa_l1
     call = (lambda q, k, v: fn(q, k, v, 8, 8, 16)) if cfg["op"] == "llsa_l2" else (lambda q, k, v: fn(q, k, v, 8, 16))
 
-    # every rank owns its own batch (seed offset by rank); host tensors are pinned for the e2e leg
-    hq, hk, hv, hdo = [t.pin_memory() for t in synth.correlated_qkv(cfg["seed"] + 100 * rank, B, H, N, D, dtype=cfg["dtype"])]
+    seq_parallel = B * H < world or args.seq_parallel          # too few (b,h) slices to go round: shard the sequence
+    if seq_parallel:
+        # strong scaling: ONE problem, rank r owns tokens [r*N/W, (r+1)*N/W) of q, k, v (llsa_b200/seqpar.py)
+        from llsa_b200 import seqpar
+        n_loc = N // world
+        full = synth.correlated_qkv(cfg["seed"], B, H, N, D, dtype=cfg["dtype"])
+        hq, hk, hv, hdo = [t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous().pin_memory() for t in full]
+        del full
+        call = lambda q, k, v: seqpar.llsa_l2_seq_parallel(q, k, v, 8, 8, 16)
+    else:
+        # every rank owns its own batch (seed offset by rank); host tensors are pinned for the e2e leg
+        hq, hk, hv, hdo = [t.pin_memory() for t in synth.correlated_qkv(cfg["seed"] + 100 * rank, B, H, N, D, dtype=cfg["dtype"])]
     q, k, v, do = [t.to(dev) for t in (hq, hk, hv, hdo)]
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
 
@@ -195,7 +206,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_step = ms / args.steps
-    value = world * B * N / (ms_step * 1e-3)
+    jobs = 1 if seq_parallel else world          # problems of B*N tokens finished per step
+    value = jobs * B * N / (ms_step * 1e-3)
 
     # per-kernel durations from the event marks
     per = {}
@@ -203,7 +215,7 @@ def main():
         if name != "end":
             per[name] = per.get(name, 0.0) + ev.elapsed_time(nxt)
     per = {kname: tms / args.steps for kname, tms in per.items()}
-    units = B * H * N * D
+    units = B * H * (N // world if seq_parallel else N) * D      # query rows x channels on this rank
     keys = dict(fine=128, p1=128, p2=N // 256 if N // 256 >= 64 else 0)
     ktot = sum(keys.values())
     flops = dict(attn_fwd=4 * units * ktot, attn_bwd_dq=6 * units * ktot, attn_bwd_dkv_fine=4 * units * keys["fine"],
@@ -218,18 +230,19 @@ def main():
     total_flops = 14 * units * ktot
 
     out = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
-               ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+               ms_per_step=ms_step, higher_is_better=True, scaling="strong" if seq_parallel else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
                config=dict(workload="%s: %s fwd+bwd bf16 B=%d H=%d N=%d D=%d block=16 topk=8/8 per GPU" % (args.config, cfg["op"], B, H, N, D),
                            inputs="N(0,1) + 0.5*low-frequency 2-D field, Morton order, seed %d+100*rank" % cfg["seed"],
                            l2_policy="inputs (4 x %.0f MB per step) exceed the 126 MB L2" % (units * 2 / 1e6),
-                           parallelism="%d independent rank(s), sharded by (batch, head), no collective" % world),
+                           parallelism=("%d rank(s), sequence sharded: all-gather of k, v and pooled levels, reduce-scatter of dk, dv" % world)
+                           if seq_parallel else "%d independent rank(s), sharded by (batch, head), no collective" % world),
                effective_tflops=total_flops * world / (ms_step * 1e-3) / 1e12,
                effective_tflops_frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / peak,
                kernel_ms={kname: round(tms, 4) for kname, tms in sorted(per.items())},
                roofline=roof, gpu_launches=len(KERNELS_PER_STEP) * args.steps, clocks=clocks)
 
     # ---- end to end: pinned host buffers -> device -> fwd+bwd -> o, dq, dk, dv back to the host
-    if not args.no_e2e:
+    if not args.no_e2e and not seq_parallel:
         from llsa_b200.hostpipe import HostPipeline
         ho = torch.empty_like(hq).pin_memory()
         hdq, hdk, hdv = [torch.empty_like(hq).pin_memory() for _ in range(3)]
@@ -257,7 +270,7 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ems = float(t.item())
         nbytes = hq.numel() * hq.element_size()
-        out["e2e"] = dict(value=world * B * N / (ems / n_e2e * 1e-3), unit="tokens/s", h2d_bytes_per_step=4 * nbytes,
+        out["e2e"] = dict(value=jobs * B * N / (ems / n_e2e * 1e-3), unit="tokens/s", h2d_bytes_per_step=4 * nbytes,
                           d2h_bytes_per_step=4 * nbytes, ms_per_step=ems / n_e2e, steps=n_e2e)
 
     # ---- CPU baseline on rank 0, N = 1 only

@@ -11,20 +11,23 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
   LLSA_REQUIRE(g->q->ndim == 4, LLSA_ERR_SHAPE, "attn: q must be [B,H,N,D]");
   const int dt = g->q->dtype;
   LLSA_REQUIRE(is_float_dtype(dt), LLSA_ERR_DTYPE, "attn: q must be f32 or bf16");
-  const int64_t B = g->q->shape[0], H = g->q->shape[1], N = g->q->shape[2], D = g->q->shape[3];
+  LLSA_REQUIRE(g->k->ndim == 4, LLSA_ERR_SHAPE, "attn: k must be [B,H,N,D]");
+  // Nq query tokens attend to N key tokens; Nq < N when q is a shard of the sequence (both multiples of 256)
+  const int64_t B = g->q->shape[0], H = g->q->shape[1], Nq = g->q->shape[2], D = g->q->shape[3], N = g->k->shape[2];
   LLSA_REQUIRE(D == kD, LLSA_ERR_SHAPE, "attn: head dim %lld unsupported (only 64)", (long long) D);
   LLSA_REQUIRE(g->block_size == kBS, LLSA_ERR_ARG, "attn: block size %d unsupported (only 16)", g->block_size);
   LLSA_REQUIRE(N >= 256 && N % 256 == 0, LLSA_ERR_SHAPE, "attn: N=%lld must be a positive multiple of 256", (long long) N);
-  const int64_t n1 = N / kBS, n2 = n1 / kBS;
+  LLSA_REQUIRE(Nq >= 256 && Nq % 256 == 0, LLSA_ERR_SHAPE, "attn: query length %lld must be a positive multiple of 256", (long long) Nq);
+  const int64_t n1 = N / kBS, n2 = n1 / kBS, nq1 = Nq / kBS, nq2 = nq1 / kBS;
   const bool two = g->pk2 != nullptr;
   LLSA_REQUIRE(g->topk >= 2 && g->topk % 2 == 0 && g->topk <= n1 && g->topk <= 64, LLSA_ERR_ARG,
                "attn: topk=%d must be even, in 2..min(64, N/16)", g->topk);
   int rc;
-  if ((rc = check_bhnd(g->q, "q", dt, B, H, N, D))) return rc;
+  if ((rc = check_bhnd(g->q, "q", dt, B, H, Nq, D))) return rc;
   if ((rc = check_bhnd(g->k, "k", dt, B, H, N, D))) return rc;
   if ((rc = check_bhnd(g->v, "v", dt, B, H, N, D))) return rc;
-  if ((rc = check_bhnd(g->o, "o", dt, B, H, N, D))) return rc;
-  const int64_t s1[4] = {B, H, n1, D}, s2[4] = {B, H, n2, D}, sl[3] = {B, H, N}, si[4] = {B, H, n1, g->topk};
+  if ((rc = check_bhnd(g->o, "o", dt, B, H, Nq, D))) return rc;
+  const int64_t s1[4] = {B, H, n1, D}, s2[4] = {B, H, n2, D}, sl[3] = {B, H, Nq}, si[4] = {B, H, nq1, g->topk};
   if ((rc = check_contig(g->pk, "pk", dt, 4, s1))) return rc;
   if ((rc = check_contig(g->pv, "pv", dt, 4, s1))) return rc;
   if ((rc = check_contig(g->lse, "lse", LLSA_F32, 3, sl))) return rc;
@@ -35,7 +38,7 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
     LLSA_REQUIRE(g->topk_p >= 2 && g->topk_p % 2 == 0 && g->topk_p <= n2 && g->topk_p <= 64, LLSA_ERR_ARG,
                  "attn: topk_p=%d must be even, in 2..min(64, N/256)", g->topk_p);
     LLSA_REQUIRE(n2 < 64 || n2 % 32 == 0, LLSA_ERR_SHAPE, "attn: N/256=%lld must be a multiple of 32", (long long) n2);
-    const int64_t sp[4] = {B, H, n2, g->topk_p};
+    const int64_t sp[4] = {B, H, nq2, g->topk_p};
     if ((rc = check_contig(g->pk2, "pk2", dt, 4, s2))) return rc;
     if ((rc = check_contig(g->pv2, "pv2", dt, 4, s2))) return rc;
     LLSA_REQUIRE(is_index_dtype(g->p_indices->dtype), LLSA_ERR_DTYPE, "attn: p_indices must be i32 or i64");
@@ -46,11 +49,11 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
   if (bwd) {
     LLSA_REQUIRE(g->d_o && g->dq && g->dk && g->dv && g->offsets && g->flat && g->delta && g->dpk_acc && g->dpv_acc, LLSA_ERR_NULL,
                  "attn_bwd: a required tensor is null");
-    if ((rc = check_bhnd(g->d_o, "d_o", dt, B, H, N, D))) return rc;
-    if ((rc = check_bhnd(g->dq, "dq", dt, B, H, N, D))) return rc;
+    if ((rc = check_bhnd(g->d_o, "d_o", dt, B, H, Nq, D))) return rc;
+    if ((rc = check_bhnd(g->dq, "dq", dt, B, H, Nq, D))) return rc;
     if ((rc = check_bhnd(g->dk, "dk", dt, B, H, N, D))) return rc;
     if ((rc = check_bhnd(g->dv, "dv", dt, B, H, N, D))) return rc;
-    const int64_t so[3] = {B, H, n1 + 1}, sf[3] = {B, H, n1 * g->topk};
+    const int64_t so[3] = {B, H, n1 + 1}, sf[3] = {B, H, nq1 * g->topk};
     LLSA_REQUIRE(is_index_dtype(g->offsets->dtype), LLSA_ERR_DTYPE, "attn_bwd: offsets must be i32 or i64");
     if ((rc = check_contig(g->offsets, "offsets", g->offsets->dtype, 3, so))) return rc;
     if ((rc = check_contig(g->flat, "flat", LLSA_I32, 3, sf))) return rc;
@@ -59,7 +62,7 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
     if ((rc = check_contig(g->dpv_acc, "dpv_acc", LLSA_F32, 4, s1))) return rc;
     if (dt == LLSA_BF16 && !g->force_generic) {
       LLSA_REQUIRE(g->dkv_partial, LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial scratch missing");
-      const int64_t need = B * H * ((n1 * g->topk + 127) / 128) * 4096;
+      const int64_t need = B * H * ((nq1 * g->topk + 127) / 128) * 4096;
       LLSA_REQUIRE(g->dkv_partial->ptr && g->dkv_partial->dtype == LLSA_F32 && g->dkv_partial->ndim == 4 && is_contiguous(g->dkv_partial) &&
                        g->dkv_partial->shape[0] * g->dkv_partial->shape[1] * g->dkv_partial->shape[2] * g->dkv_partial->shape[3] >= need,
                    LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial must be a contiguous F32 tensor of at least %lld elements", (long long) need);

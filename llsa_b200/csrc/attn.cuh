@@ -26,17 +26,18 @@ struct AttnP {
   const T* pk2;  // contiguous [BH, n2, D] or nullptr
   const T* pv2;
   IdxView idx, pidx;
-  float* lse;    // [BH, N]
-  float* delta;  // [BH, N]
+  float* lse;    // [BH, Nq]
+  float* delta;  // [BH, Nq]
   float* dpk;    // fp32 accumulators [BH, n1, D]
   float* dpv;
   float* dpk2;   // [BH, n2, D]
   float* dpv2;
   const void* offsets;  // CSR of idx: [BH, n1+1]
   int off64;
-  const int32_t* flat;  // [BH, n1*topk]
+  const int32_t* flat;  // [BH, nq1*topk]
   int H;
-  int64_t N, n1, n2;
+  int64_t N, n1, n2;      // KEY side: tokens, 16-token blocks, 256-token blocks of k / v
+  int64_t Nq, nq1, nq2;   // QUERY side: the same counts for q (equal to the key side unless q is a shard of the sequence)
   int topk, topk_p;
   int two_level;
   int p1_blocks;   // pooled-1 key blocks per query row (0 when the stage is skipped)
@@ -52,13 +53,13 @@ struct AttnP {
 template <typename T>
 __device__ __forceinline__ int64_t p1_block(const AttnP<T>& a, int64_t bh, int64_t qb, int i) {
   if (!a.two_level) return i;
-  int64_t p = a.pidx.at((bh * a.n2 + qb / kBS) * a.topk_p + i);
+  int64_t p = a.pidx.at((bh * a.nq2 + qb / kBS) * a.topk_p + i);
   return p < 0 ? 0 : (p >= a.n2 ? a.n2 - 1 : p);
 }
 
 template <typename T>
 __device__ __forceinline__ int64_t fine_block(const AttnP<T>& a, int64_t bh, int64_t qb, int i) {
-  int64_t j = a.idx.at((bh * a.n1 + qb) * a.topk + i);
+  int64_t j = a.idx.at((bh * a.nq1 + qb) * a.topk + i);
   return j < 0 ? 0 : (j >= a.n1 ? a.n1 - 1 : j);
 }
 
@@ -94,9 +95,12 @@ inline AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd) {
   a.idx = make_idx(g->indices);
   a.lse = (float*) g->lse->ptr;
   a.H = (int) g->q->shape[1];
-  a.N = g->q->shape[2];
+  a.N = g->k->shape[2];
   a.n1 = a.N / kBS;
   a.n2 = a.n1 / kBS;
+  a.Nq = g->q->shape[2];
+  a.nq1 = a.Nq / kBS;
+  a.nq2 = a.nq1 / kBS;
   a.topk = g->topk;
   a.topk_p = g->topk_p;
   a.w1 = g->token_weight;

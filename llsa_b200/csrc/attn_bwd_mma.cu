@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attn_dq_mma_kernel(AttnP<bf16> a, 
     row.delta0 = quad_sum(rowfrag_dot(olo, dlo));
     row.delta1 = quad_sum(rowfrag_dot(ohi, dhi));
   }
-  const int64_t rbase = bh * a.N + qb * kBS;
+  const int64_t rbase = bh * a.Nq + qb * kBS;
   if (t == 0) { a.delta[rbase + g] = row.delta0; a.delta[rbase + g + 8] = row.delta1; }
   row.L0 = a.lse[rbase + g] * kLog2e;
   row.L1 = a.lse[rbase + g + 8] * kLog2e;
@@ -222,7 +222,7 @@ __device__ __forceinline__ void dkv_step(const AttnP<bf16>& a, int64_t b, int64_
   ColFrag qc, dc;
   load_colfrag(dc, dp, a.d_o.sn, g, t);
   load_colfrag(qc, qp, a.q.sn, g, t);
-  const int64_t rbase = bh * a.N + qb * kBS;
+  const int64_t rbase = bh * a.Nq + qb * kBS;
   const float2 la = *reinterpret_cast<const float2*>(a.lse + rbase + 2 * t);        // query rows 2t, 2t+1
   const float2 lb = *reinterpret_cast<const float2*>(a.lse + rbase + 8 + 2 * t);    // query rows 8+2t, 9+2t
   const float2 da = *reinterpret_cast<const float2*>(a.delta + rbase + 2 * t);
@@ -255,8 +255,8 @@ __global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16>
   }
   cp_async_commit();
   for (int r = threadIdx.x; r < kBS * kBS; r += blockDim.x) {
-    sl[r] = a.lse[bh * a.N + row0 + r];
-    sdel[r] = a.delta[bh * a.N + row0 + r];
+    sl[r] = a.lse[bh * a.Nq + row0 + r];
+    sdel[r] = a.delta[bh * a.Nq + row0 + r];
   }
   cp_async_wait_all();
   __syncthreads();
@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(kFineWarps * 32, 2) attn_dkv_fine_kernel(AttnP
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const float sl2 = a.scale * kLog2e;
-  const int E = (int) (a.n1 * a.topk);
+  const int E = (int) (a.nq1 * a.topk);
   const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E);
   constexpr int L = kFineWindow / kFineWarps;
   const int rb = cb + warp * L, re = min(rb + L, ce);
@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(kFineWarps * 32, 2) attn_dkv_fine_kernel(AttnP
         if (lane == 0) s_slot_bucket[slot] = j;
       }
     };
-    auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.n1 ? (int) a.n1 - 1 : v); };
+    auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.nq1 ? (int) a.nq1 - 1 : v); };
     RowFrag q0, q1, d0, d1;
     float2 la, lb, da, db;
     auto load_rows = [&](int qb) {
@@ -440,7 +440,7 @@ __global__ void __launch_bounds__(kFineWarps * 32, 2) attn_dkv_fine_kernel(AttnP
       load_rowfrag(q1, qp + (int64_t) (g + 8) * a.q.sn, t);
       load_rowfrag(d0, dp + (int64_t) g * a.d_o.sn, t);
       load_rowfrag(d1, dp + (int64_t) (g + 8) * a.d_o.sn, t);
-      const int64_t rbase = bh * a.N + (int64_t) qb * kBS;
+      const int64_t rbase = bh * a.Nq + (int64_t) qb * kBS;
       la = *reinterpret_cast<const float2*>(a.lse + rbase + 2 * t);          // query rows 2t, 2t+1
       lb = *reinterpret_cast<const float2*>(a.lse + rbase + 8 + 2 * t);      // query rows 8+2t, 9+2t
       da = *reinterpret_cast<const float2*>(a.delta + rbase + 2 * t);
@@ -539,18 +539,18 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     const int n_smem = n_all < 12 ? n_all : 12;   // 12 tiles = 54 KB of K+V, three CTAs per SM
     const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_mma_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.n1 / NWQ), BH), NWQ * 32, smem, st>>>(a, n_smem);
+    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, smem, st>>>(a, n_smem);
     LLSA_LAUNCH_OK("attn_dq_mma_kernel");
   }
   if ((mask & 2) && a.p1_blocks + a.p2_blocks > 0) {
     constexpr int NWP = 8;
     const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.n1 / kBS), BH), NWP * 32, smem, st>>>(a);
+    attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.nq1 / kBS), BH), NWP * 32, smem, st>>>(a);
     LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
   }
   if (mask & 4) {
-    const int64_t E = a.n1 * a.topk;
+    const int64_t E = a.nq1 * a.topk;
     const int n_windows = (int) ((E + kFineWindow - 1) / kFineWindow);
     float* partial = (float*) g->dkv_partial->ptr;
     const size_t smem = (size_t) kFineWarps * 2 * kTileFloats * sizeof(float);

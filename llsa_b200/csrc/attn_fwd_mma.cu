@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_mma_kernel(AttnP<bf16> a,
   store_acc_row<0>(a.o.row(b, h, qb * kBS + g), st.o, t, 1.f / l0);
   store_acc_row<1>(a.o.row(b, h, qb * kBS + g + 8), st.o, t, 1.f / l1);
   if (t == 0) {
-    a.lse[bh * a.N + qb * kBS + g] = (st.m0 + log2f(l0)) * 0.6931471805599453f;
-    a.lse[bh * a.N + qb * kBS + g + 8] = (st.m1 + log2f(l1)) * 0.6931471805599453f;
+    a.lse[bh * a.Nq + qb * kBS + g] = (st.m0 + log2f(l0)) * 0.6931471805599453f;
+    a.lse[bh * a.Nq + qb * kBS + g + 8] = (st.m1 + log2f(l1)) * 0.6931471805599453f;
   }
 }
 
@@ -224,8 +224,8 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine_kernel(AttnP<bf16> a
   store_acc_row<0>(a.o.row(b, h, qb * kBS + g), st.o, t, 1.f / l0);
   store_acc_row<1>(a.o.row(b, h, qb * kBS + g + 8), st.o, t, 1.f / l1);
   if (t == 0) {
-    a.lse[bh * a.N + qb * kBS + g] = (st.m0 + log2f(l0)) * 0.6931471805599453f;
-    a.lse[bh * a.N + qb * kBS + g + 8] = (st.m1 + log2f(l1)) * 0.6931471805599453f;
+    a.lse[bh * a.Nq + qb * kBS + g] = (st.m0 + log2f(l0)) * 0.6931471805599453f;
+    a.lse[bh * a.Nq + qb * kBS + g + 8] = (st.m1 + log2f(l1)) * 0.6931471805599453f;
   }
 }
 
@@ -255,14 +255,14 @@ int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     // fine blocks on mma.sync (o and lse of the fine part alone), pooled keys on tcgen05, merged there
     const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
-    attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.n1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
+    attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
     LLSA_LAUNCH_OK("attn_fwd_fine_kernel");
     return launch_attn_fwd_pooled_tc(g, a, BH, st);
   }
   const int n_smem = pooled_smem_tiles(a.p1_blocks + a.p2_blocks);
   const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
   LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_mma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-  dim3 grid((unsigned) (a.n1 / NW), (unsigned) (g->q->shape[0] * a.H));
+  dim3 grid((unsigned) (a.nq1 / NW), (unsigned) (g->q->shape[0] * a.H));
   attn_fwd_mma_kernel<NW><<<grid, NW * 32, smem, st>>>(a, n_smem);
   LLSA_LAUNCH_OK("attn_fwd_mma_kernel");
   return LLSA_OK;

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(128) attn_fwd_generic(AttnP<T> a) {
   T* op = a.o.row(b, h, qb * kBS + r) + c * 8;
 #pragma unroll
   for (int d = 0; d < 8; ++d) op[d] = from_f32<T>(acc[d] / l);
-  if (c == 0) a.lse[bh * a.N + qb * kBS + r] = m + logf(l);
+  if (c == 0) a.lse[bh * a.Nq + qb * kBS + r] = m + logf(l);
 }
 
 template <typename T>
@@ -128,8 +128,8 @@ __global__ void __launch_bounds__(128) attn_dq_generic(AttnP<T> a) {
     for (int d = 0; d < 8; ++d) part = fmaf(to_f32<T>(op[d]), dos[r * kLd + c * 8 + d], part);
   }
   const float delta = reduce8_sum(part);
-  const float lse = a.lse[bh * a.N + qb * kBS + r];
-  if (c == 0) a.delta[bh * a.N + qb * kBS + r] = delta;
+  const float lse = a.lse[bh * a.Nq + qb * kBS + r];
+  if (c == 0) a.delta[bh * a.Nq + qb * kBS + r] = delta;
   float dq[8];
 #pragma unroll
   for (int d = 0; d < 8; ++d) dq[d] = 0.f;
@@ -204,13 +204,13 @@ __global__ void __launch_bounds__(128) attn_dkv_generic(AttnP<T> a) {
 #pragma unroll
   for (int d = 0; d < 8; ++d) dk[d] = dv[d] = 0.f;
   for (int64_t it = list0; it < list1; ++it) {
-    const int64_t qb = MODE == 0 ? (int64_t) a.flat[bh * a.n1 * a.topk + it] : grp * kBS + it;
+    const int64_t qb = MODE == 0 ? (int64_t) a.flat[bh * a.nq1 * a.topk + it] : grp * kBS + it;
     __syncthreads();
     load_block_smem<T>(qs, a.q.row(b, h, qb * kBS), a.q.sn, 1.f, false);
     load_block_smem<T>(dos, a.d_o.row(b, h, qb * kBS), a.d_o.sn, 1.f, false);
     if (threadIdx.x < kBS) {
-      lses[threadIdx.x] = a.lse[bh * a.N + qb * kBS + threadIdx.x];
-      deltas[threadIdx.x] = a.delta[bh * a.N + qb * kBS + threadIdx.x];
+      lses[threadIdx.x] = a.lse[bh * a.Nq + qb * kBS + threadIdx.x];
+      deltas[threadIdx.x] = a.delta[bh * a.Nq + qb * kBS + threadIdx.x];
     }
     __syncthreads();
     // thread (r, c): key r against query rows c and c+8
@@ -269,14 +269,14 @@ __global__ void __launch_bounds__(128) attn_dkv_generic(AttnP<T> a) {
 template <typename T>
 static int fwd_generic_t(const LlsaAttnArgs* g, cudaStream_t st) {
   AttnP<T> a = build_attn_params<T>(g, false);
-  dim3 grid((unsigned) a.n1, (unsigned) (g->q->shape[0] * a.H));
+  dim3 grid((unsigned) a.nq1, (unsigned) (g->q->shape[0] * a.H));
   attn_fwd_generic<T><<<grid, 128, 0, st>>>(a);
   LLSA_LAUNCH_OK("attn_fwd_generic");
   return LLSA_OK;
 }
 
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st) {
-  const int64_t BH = g->q->shape[0] * g->q->shape[1], n1 = g->q->shape[2] / kBS, n2 = n1 / kBS;
+  const int64_t BH = g->q->shape[0] * g->q->shape[1], n1 = g->k->shape[2] / kBS, n2 = n1 / kBS;
   LLSA_CUDA_OK(cudaMemsetAsync(g->dpk_acc->ptr, 0, (size_t) BH * n1 * kD * 4, st));
   LLSA_CUDA_OK(cudaMemsetAsync(g->dpv_acc->ptr, 0, (size_t) BH * n1 * kD * 4, st));
   if (g->pk2) {
@@ -294,12 +294,12 @@ static int bwd_generic_t(const LlsaAttnArgs* g, cudaStream_t st) {
   if (mask & 1) {
     int rc = zero_pooled_acc(g, st);
     if (rc) return rc;
-    attn_dq_generic<T><<<dim3((unsigned) a.n1, BH), 128, 0, st>>>(a);
+    attn_dq_generic<T><<<dim3((unsigned) a.nq1, BH), 128, 0, st>>>(a);
     LLSA_LAUNCH_OK("attn_dq_generic");
   }
   const int ptiles = a.p1_blocks + a.p2_blocks;
   if ((mask & 2) && ptiles > 0) {
-    attn_dkv_generic<T, 1><<<dim3((unsigned) ptiles, BH, (unsigned) (a.n1 / kBS)), 128, 0, st>>>(a);
+    attn_dkv_generic<T, 1><<<dim3((unsigned) ptiles, BH, (unsigned) (a.nq1 / kBS)), 128, 0, st>>>(a);
     LLSA_LAUNCH_OK("attn_dkv_generic<pooled>");
   }
   if (mask & 4) {

@@ -192,7 +192,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       }
       float lse_out = __int_as_float(0x7fc00000);               // NaN unless everything completed
       if (ok) {
-        const float Lf = a.lse[bh * a.N + row] * 1.4426950408889634f;    // fine part, log2 domain
+        const float Lf = a.lse[bh * a.Nq + row] * 1.4426950408889634f;    // fine part, log2 domain
         const float Lp = mx + log2f(lsum);
         const float Lm = fmaxf(Lf, Lp);
         const float ef = fast_exp2(Lf - Lm), ep = fast_exp2(Lp - Lm);
@@ -218,7 +218,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
         tc::fence_before_sync();
         tma::mbar_arrive(&bars.tmem_free[s]);                    // this row's S / O columns may be overwritten
       }
-      a.lse[bh * a.N + row] = lse_out;
+      a.lse[bh * a.Nq + row] = lse_out;
       if (!ok) break;
     }
   }
@@ -231,7 +231,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
 int pooled_tc_keys(const AttnP<bf16>& a) {
   const int p1_keys = a.p1_blocks * kBS, np = (a.p1_blocks + a.p2_blocks) * kBS;
   if (np < 64 || np > 192 || np % 64 || p1_keys % 32 || (np - p1_keys) % 64) return 0;
-  if (a.N % kTcRows) return 0;
+  if (a.Nq % kTcRows) return 0;
   return np;
 }
 
@@ -247,7 +247,7 @@ int launch_attn_fwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64
     if ((rc = tma::make_map_rows(&maps.pk2, a.pk2, (uint64_t) BH * a.n2, 64))) return rc;
     if ((rc = tma::make_map_rows(&maps.pv2, a.pv2, (uint64_t) BH * a.n2, 64))) return rc;
   }
-  const int tiles_per_head = (int) (a.N / kTcRows), n_tiles = (int) (BH * tiles_per_head);
+  const int tiles_per_head = (int) (a.Nq / kTcRows), n_tiles = (int) (BH * tiles_per_head);
   int dev = 0, sms = 148;
   LLSA_CUDA_OK(cudaGetDevice(&dev));
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

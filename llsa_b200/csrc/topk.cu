@@ -134,24 +134,25 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
   }
 }
 
-// pq1, pk1: contiguous [B*H, M, D]; p_idx [B*H, M/bs, p_topk]; out [B*H, M, topk].
+// pq1: contiguous [B*H, M, D] (M query blocks); pk1: contiguous [B*H, Mk, D] (Mk key blocks, Mk != M when the
+// queries are a shard of the sequence); p_idx [B*H, M/bs, p_topk] with values in [0, Mk/bs); out [B*H, M, topk].
 // MMA = true (bf16, D = 64, bs = 16): the 16 x C score tile comes from mma.sync with fp32
 // accumulation of the exact bf16 products, as the reference's tl.dot does.
 template <typename T, bool MMA>
 __global__ void __launch_bounds__(128)
 refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
-                   int D, int topk, int p_topk, int bs) {
+                   int64_t Mk, int D, int topk, int p_topk, int bs) {
   extern __shared__ float sm[];
   const int C = p_topk * bs;
   float* qs = sm;                 // [bs][D]
   float* sc = qs + bs * D;        // [bs][C]
   int* cand = reinterpret_cast<int*>(sc + bs * C);  // [C] block index of each candidate
-  const int64_t bh = blockIdx.y, P = blockIdx.x, n2 = M / bs;
+  const int64_t bh = blockIdx.y, P = blockIdx.x, n2q = M / bs, n2 = Mk / bs;
   const T* q0 = pq1 + (bh * M + P * bs) * D;
-  const T* k0 = pk1 + bh * M * D;
+  const T* k0 = pk1 + bh * Mk * D;
   for (int i = threadIdx.x; i < bs * D; i += blockDim.x) qs[i] = to_f32<T>(q0[i]);
   for (int j = threadIdx.x; j < C; j += blockDim.x) {
-    int64_t p = p_idx.at((bh * n2 + P) * p_topk + j / bs);
+    int64_t p = p_idx.at((bh * n2q + P) * p_topk + j / bs);
     p = p < 0 ? 0 : (p >= n2 ? n2 - 1 : p);      // never read outside the tensor
     cand[j] = (int) (p * bs + j % bs);
   }
@@ -268,20 +269,21 @@ extern "C" int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, cons
 extern "C" int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTensor* p_idx, const LlsaTensor* idx, int topk,
                                 int p_topk, int block_size, void* stream) {
   LLSA_REQUIRE(pq1 && pk1 && p_idx && idx && pq1->ptr && pk1->ptr && p_idx->ptr && idx->ptr, LLSA_ERR_NULL, "refine_topk: null tensor");
-  LLSA_REQUIRE(pq1->ndim == 4, LLSA_ERR_SHAPE, "refine_topk: pq1 must be [B,H,M,D]");
-  const int64_t B = pq1->shape[0], H = pq1->shape[1], M = pq1->shape[2], D = pq1->shape[3];
+  LLSA_REQUIRE(pq1->ndim == 4 && pk1->ndim == 4, LLSA_ERR_SHAPE, "refine_topk: pq1, pk1 must be [B,H,M,D]");
+  const int64_t B = pq1->shape[0], H = pq1->shape[1], M = pq1->shape[2], D = pq1->shape[3], Mk = pk1->shape[2];
   const int bs = block_size;
   LLSA_REQUIRE(is_float_dtype(pq1->dtype) && pk1->dtype == pq1->dtype, LLSA_ERR_DTYPE, "refine_topk: pq1/pk1 must both be f32 or bf16");
   LLSA_REQUIRE(is_index_dtype(idx->dtype) && is_index_dtype(p_idx->dtype), LLSA_ERR_DTYPE, "refine_topk: index tensors must be i32 or i64");
-  LLSA_REQUIRE(bs >= 1 && M % bs == 0, LLSA_ERR_ARG, "refine_topk: M=%lld not divisible by block size %d", (long long) M, bs);
-  LLSA_REQUIRE(p_topk >= 1 && topk >= 1 && topk <= p_topk * bs && p_topk <= M / bs, LLSA_ERR_ARG, "refine_topk: bad topk=%d / p_topk=%d", topk, p_topk);
+  LLSA_REQUIRE(bs >= 1 && M % bs == 0 && Mk % bs == 0, LLSA_ERR_ARG, "refine_topk: M=%lld / Mk=%lld not divisible by block size %d", (long long) M,
+               (long long) Mk, bs);
+  LLSA_REQUIRE(p_topk >= 1 && topk >= 1 && topk <= p_topk * bs && p_topk <= Mk / bs, LLSA_ERR_ARG, "refine_topk: bad topk=%d / p_topk=%d", topk, p_topk);
   LLSA_REQUIRE(D % 8 == 0, LLSA_ERR_SHAPE, "refine_topk: D=%lld must be a multiple of 8", (long long) D);
   const size_t smem = ((size_t) bs * D + (size_t) bs * p_topk * bs + (size_t) p_topk * bs) * 4;
   LLSA_REQUIRE(smem <= 200 * 1024, LLSA_ERR_ARG, "refine_topk: bs*p_topk too large");
-  const int64_t sq[4] = {B, H, M, D}, sp[4] = {B, H, M / bs, p_topk}, si[4] = {B, H, M, topk};
+  const int64_t sq[4] = {B, H, M, D}, sk[4] = {B, H, Mk, D}, sp[4] = {B, H, M / bs, p_topk}, si[4] = {B, H, M, topk};
   int rc;
   if ((rc = check_contig(pq1, "pq1", pq1->dtype, 4, sq))) return rc;
-  if ((rc = check_contig(pk1, "pk1", pq1->dtype, 4, sq))) return rc;
+  if ((rc = check_contig(pk1, "pk1", pq1->dtype, 4, sk))) return rc;
   if ((rc = check_contig(p_idx, "p_idx", p_idx->dtype, 4, sp))) return rc;
   if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
   if (B * H * M == 0) return LLSA_OK;
@@ -290,15 +292,15 @@ extern "C" int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, co
   if (pq1->dtype == LLSA_F32) {
     LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     refine_topk_kernel<float, false><<<grid, 128, smem, st>>>((const float*) pq1->ptr, (const float*) pk1->ptr, make_idx(p_idx), idx->ptr,
-                                                              idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+                                                              idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
   } else if (D == 64 && bs == 16 && p_topk % 2 == 0 && ((uintptr_t) pq1->ptr % 32) == 0 && ((uintptr_t) pk1->ptr % 32) == 0) {
     LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     refine_topk_kernel<__nv_bfloat16, true><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
-                                                                     make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+                                                                     make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
   } else {
     LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     refine_topk_kernel<__nv_bfloat16, false><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
-                                                                      make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, (int) D, topk, p_topk, bs);
+                                                                      make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
   }
   LLSA_LAUNCH_OK("refine_topk_kernel");
   return LLSA_OK;

@@ -340,7 +340,7 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
         pk2, pv2, p_indices = pk2.contiguous(), pv2.contiguous(), p_indices.contiguous()
     indices = indices.contiguous()
     lse = lse.contiguous()
-    offsets, flat = transpose_indices(indices, offsets_dtype=torch.int32)
+    offsets, flat = transpose_indices(indices, k_ntx=k.shape[2] // block_size, offsets_dtype=torch.int32)   # buckets = KEY blocks
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
     f32 = dict(device=q.device, dtype=torch.float32)

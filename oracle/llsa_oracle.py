@@ -142,8 +142,8 @@ def _gather_blocks(x: torch.Tensor, idx: torch.Tensor, bs: int) -> torch.Tensor:
 def _key_sets(q, k, v, pk, pv, pk2, pv2, indices, p_indices, bs, w1, w2):
     """For one (b,h): the attended keys/values grouped per level-2 query block.
     Returns lists of (K [G, nk, D], V [G, nk, D], log-weight, rows-per-group)."""
-    N, D = q.shape
-    n1 = N // bs
+    N, D = q.shape                      # query rows; k / v / pk may be longer (q a shard of the sequence)
+    n1 = pk.shape[0]
     sets = []
     # fine tokens of the selected blocks: per 16-row query block
     sets.append((_gather_blocks(k, indices, bs), _gather_blocks(v, indices, bs), 0.0, bs))
@@ -268,7 +268,7 @@ def attn_bwd_l2(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk=
 
 def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, bs, w1, w2, kv_weights, faithful):
     B, H, N, D = q.shape
-    n1 = N // bs
+    nq1, n1 = N // bs, k.shape[2] // bs          # query-side / key-side block counts (equal in the reference)
     scale = 1.0 / math.sqrt(D)
     f = lambda t: torch.zeros(t.shape, dtype=torch.float32)
     dq, dk, dv, dpk, dpv = f(q), f(k), f(v), f(pk), f(pv)
@@ -285,16 +285,16 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, bs, w1,
                                        scale, q.dtype, faithful, kv_weights[:len(sets)])
             dq[b, h] = dqb
             dKf, dVf = grads[0]
-            dk[b, h] = _scatter_fine(dKf.reshape(n1, -1, bs, D), indices[b, h], n1, bs, D)
-            dv[b, h] = _scatter_fine(dVf.reshape(n1, -1, bs, D), indices[b, h], n1, bs, D)
+            dk[b, h] = _scatter_fine(dKf.reshape(nq1, -1, bs, D), indices[b, h], n1, bs, D)
+            dv[b, h] = _scatter_fine(dVf.reshape(nq1, -1, bs, D), indices[b, h], n1, bs, D)
             if p_indices is None:
                 if len(grads) > 1:
                     dpk[b, h], dpv[b, h] = grads[1][0][0], grads[1][1][0]
             else:
-                n2 = n1 // bs
+                nq2, n2 = nq1 // bs, n1 // bs
                 pi = p_indices[b, h]
-                dpk[b, h] = _scatter_fine(grads[1][0].reshape(n2, -1, bs, D), pi, n2, bs, D)
-                dpv[b, h] = _scatter_fine(grads[1][1].reshape(n2, -1, bs, D), pi, n2, bs, D)
+                dpk[b, h] = _scatter_fine(grads[1][0].reshape(nq2, -1, bs, D), pi, n2, bs, D)
+                dpv[b, h] = _scatter_fine(grads[1][1].reshape(nq2, -1, bs, D), pi, n2, bs, D)
                 if len(grads) > 2:
                     dpk2[b, h], dpv2[b, h] = grads[2][0][0], grads[2][1][0]
     if p_indices is None:
