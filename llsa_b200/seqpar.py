@@ -29,6 +29,9 @@ import torch.distributed as dist
 __all__ = ["llsa_l2_seq_parallel", "llsa_l1_seq_parallel", "CudaBackend", "gather_seq", "reduce_scatter_seq", "local_forward"]
 
 
+_PER_SLICE_MAX = 16     # up to this many (b,h) slices the exchange runs per slice, straight into / out of place
+
+
 def gather_seq(x: torch.Tensor, group=None) -> torch.Tensor:
     """[B,H,n_local,D] on every rank -> [B,H,W*n_local,D], ranks in order along dim 2."""
     world = dist.get_world_size(group)
@@ -36,7 +39,14 @@ def gather_seq(x: torch.Tensor, group=None) -> torch.Tensor:
         return x
     x = x.contiguous()
     B, H, n, D = x.shape
-    out = x.new_empty((world * B, H, n, D))           # rank-major concatenation along dim 0
+    if B * H <= _PER_SLICE_MAX:
+        # a slice's full sequence [W*n, D] is the rank-major concatenation of the ranks' [n, D]: gather in place
+        out = x.new_empty((B, H, world * n, D))
+        works = [dist.all_gather_into_tensor(out[b, h], x[b, h], group=group, async_op=True) for b in range(B) for h in range(H)]
+        for w in works:
+            w.wait()
+        return out
+    out = x.new_empty((world * B, H, n, D))           # rank-major concatenation along dim 0, then one transposing copy
     dist.all_gather_into_tensor(out, x, group=group)
     return out.view(world, B, H, n, D).permute(1, 2, 0, 3, 4).reshape(B, H, world * n, D)
 
@@ -48,9 +58,16 @@ def reduce_scatter_seq(x: torch.Tensor, group=None) -> torch.Tensor:
         return x
     B, H, N, D = x.shape
     n = N // world
-    parts = x.reshape(B, H, world, n, D).permute(2, 0, 1, 3, 4).contiguous()
     out = x.new_empty((B, H, n, D))
-    if dist.get_backend(group) == "gloo":          # gloo has no reduce_scatter: all-reduce and keep the own part
+    gloo = dist.get_backend(group) == "gloo"          # gloo has no reduce_scatter: all-reduce and keep the own part
+    if B * H <= _PER_SLICE_MAX and not gloo:
+        x = x.contiguous()
+        works = [dist.reduce_scatter_tensor(out[b, h], x[b, h], group=group, async_op=True) for b in range(B) for h in range(H)]
+        for w in works:
+            w.wait()
+        return out
+    parts = x.reshape(B, H, world, n, D).permute(2, 0, 1, 3, 4).contiguous()
+    if gloo:
         dist.all_reduce(parts, group=group)
         out.copy_(parts[dist.get_rank(group)])
     else:
