@@ -36,7 +36,8 @@ METRIC = "llsa_l2 fwd+bwd tokens/sec @N=16384,B*H=48,D=64"
 
 
 # this library's kernels launched by one llsa_l2 forward + backward (torch's own zero fills are not counted)
-KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_kernel", "refine_topk_kernel", "attn_fwd_mma_kernel", "transpose_kernel",
+KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_kernel", "refine_topk_kernel", "attn_fwd_fine_kernel", "attn_fwd_pooled_tc_kernel",
+                    "transpose_kernel",
                     "attn_dq_mma_kernel", "attn_dkv_pooled_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
 
 

@@ -250,8 +250,8 @@ int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   AttnP<bf16> a = build_attn_params<bf16>(g, false);
   constexpr int NW = 8;
   const int64_t BH = g->q->shape[0] * a.H;
-  const char* tc_env = getenv("LLSA_B200_TC");
-  if (pooled_tc_keys(a) && tc_env && tc_env[0] == '1') {
+  const char* tc_env = getenv("LLSA_B200_TC");      // "0" keeps the pooled stages on mma.sync (cross-check)
+  if (pooled_tc_keys(a) && !(tc_env && tc_env[0] == '0')) {
     // fine blocks on mma.sync (o and lse of the fine part alone), pooled keys on tcgen05, merged there
     const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));

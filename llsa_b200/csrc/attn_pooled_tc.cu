@@ -10,15 +10,21 @@
 // through their log-sum-exp.
 //
 // attn_fwd_pooled_tc_kernel: one persistent CTA per SM walks tiles of 128 query rows.
-//   warp 4, one lane : TMA producer.  Per tile: Q [128x64], pooled K [NPx64], pooled V [NPx64]
-//                      as 128-byte swizzled tiles into one of two stages (mbarrier expect_tx).
-//   warp 5, one lane : MMA issuer.  S = Q.PK^T (M=128, N=NP, K=64) into one of two TMEM buffers,
-//                      issued one tile ahead; O_p = P.PV (M=128, N=64, K=NP) when P is ready.
-//   warps 0-3        : thread r owns query row r = TMEM lane r.  Reads its NP scores
-//                      (tcgen05.ld), softmax in the exp2 domain with +log2(weight) per key
-//                      class, writes P (bf16) as a K-major tile; later reads its O_p row,
-//                      merges it with the fine part (o, lse written by the fine kernel for
-//                      this row) and stores the final o and lse.
+//   warp 8, one lane : TMA producer.  Per tile: Q [128x64], pooled K [NPx64], pooled V [NPx64]
+//                      as 128-byte swizzled tiles into one of three stages (mbarrier expect_tx).
+//   warp 9, one lane : MMA issuer.  S = Q.PK^T (M=128, N=NP, K=64, both operands from shared
+//                      memory) into TMEM buffer (tile & 1), two tiles ahead of the P.PV product;
+//                      O_p = P.PV (M=128, N=64, K=NP) with P read from TENSOR MEMORY (it overwrites
+//                      the first NP/2 columns of S as packed bf16 pairs) and PV from shared memory.
+//   warps 0-3, 4-7   : two softmax warpgroups, tiles alternate between them so that one group's
+//                      TMEM / MMA / global latencies hide behind the other's arithmetic.  Thread r
+//                      of a group owns query row r = TMEM lane r: reads its NP scores (tcgen05.ld),
+//                      softmax in the exp2 domain with +log2(weight) per key class, writes P back
+//                      (tcgen05.st); later reads its O_p row, merges it with the fine part (o, lse
+//                      written by the fine kernel for this row, fetched at the top of the tile)
+//                      and stores the final o and lse.
+// tcgen05.mma operations of one thread execute in issue order, which is what lets S of tile i+2
+// reuse the buffer of tile i right behind P.PV of tile i without a barrier.
 // All mbarrier waits are bounded; a wait that expires raises a CTA-wide abort flag, every
 // role leaves its loop, lse of the unfinished rows is poisoned with NaN and TMEM is freed.
 #include <string.h>
@@ -31,7 +37,8 @@
 namespace llsa {
 
 constexpr int kTcRows = 128;
-constexpr int kTcThreads = 192;       // 4 softmax warps + producer warp + MMA warp
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 320;       // 2 x 4 softmax warps + producer warp + MMA warp
 
 struct TcMaps {
   CUtensorMap q;      // [B,H,N,64] 4-D, box 128 rows
@@ -42,7 +49,7 @@ struct TcMaps {
 };
 
 struct TcBars {
-  uint64_t full[2], empty[2], s_ready[2], o_ready[2], tmem_free[2], p_ready, p_free;
+  uint64_t full[kTcStages], empty[kTcStages], s_ready[2], p_ready[2], o_ready[2];
 };
 
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -62,21 +69,20 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
   __shared__ int s_abort;
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int stage_elems = kTcRows * 64 + 2 * np * 64;
-  bf16* sP = base + 2 * stage_elems;               // [np/64][128][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &s_abort;
 
   if (tid == 0) {
     s_abort = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kTcStages; ++i) {
       tc::mbar_init(&bars.full[i], 1);
       tc::mbar_init(&bars.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.s_ready[i], 1);
       tc::mbar_init(&bars.o_ready[i], 1);
-      tc::mbar_init(&bars.tmem_free[i], kTcRows);
+      tc::mbar_init(&bars.p_ready[i], 4);       // one arrival per softmax warp
     }
-    tc::mbar_init(&bars.p_ready, kTcRows);
-    tc::mbar_init(&bars.p_free, 1);
     tc::fence_mbar_init();
   }
   if (warp == 0) tc::tmem_alloc(&s_tmem, 512);
@@ -86,12 +92,12 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
   const uint32_t tmem = s_tmem;
   const int n_my = (n_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       const uint32_t bytes = (uint32_t) stage_elems * 2;
       for (int i = 0; i < n_my; ++i) {
-        const int tile = blockIdx.x + i * gridDim.x, s = i & 1, u = i >> 1;
+        const int tile = blockIdx.x + i * gridDim.x, s = i % kTcStages, u = i / kTcStages;
         const int64_t bh = tile / tiles_per_head, row0 = (int64_t) (tile % tiles_per_head) * kTcRows;
         if (!tc_wait(&bars.empty[s], (u & 1) ^ 1, abort_flag)) break;
         bf16* sQ = base + s * stage_elems;
@@ -112,100 +118,120 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc_s = tc::instr_desc(kTcRows, np, 0, 0), idesc_o = tc::instr_desc(kTcRows, 64, 0, 1);
       auto issue_s = [&](int i) -> bool {          // S(i) = Q.PK^T into TMEM buffer i & 1
-        const int s = i & 1, u = i >> 1;
+        const int s = i % kTcStages, u = i / kTcStages, b = i & 1;
         if (!tc_wait(&bars.full[s], u & 1, abort_flag)) return false;
-        if (!tc_wait(&bars.tmem_free[s], (u & 1) ^ 1, abort_flag)) return false;
         tc::fence_after_sync();
         const uint32_t qa = tc::smem_u32(base + s * stage_elems), ka = qa + kTcRows * 128;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          tc::umma_ss(tmem + s * 256, tc::smem_desc(qa + ks * 32, 16, 1024), tc::smem_desc(ka + ks * 32, 16, 1024), idesc_s, ks > 0);
-        tc::umma_commit(&bars.s_ready[s]);
+          tc::umma_ss(tmem + b * 256, tc::smem_desc(qa + ks * 32, 16, 1024), tc::smem_desc(ka + ks * 32, 16, 1024), idesc_s, ks > 0);
+        tc::umma_commit(&bars.s_ready[b]);
         return true;
       };
       bool ok = n_my > 0 && issue_s(0);
+      if (ok && n_my > 1) ok = issue_s(1);
       for (int i = 0; ok && i < n_my; ++i) {
-        const int s = i & 1;
-        if (i + 1 < n_my && !issue_s(i + 1)) break;
-        if (!tc_wait(&bars.p_ready, i & 1, abort_flag)) break;
+        const int s = i % kTcStages, b = i & 1;
+        if (!tc_wait(&bars.p_ready[b], (i >> 1) & 1, abort_flag)) break;
         tc::fence_after_sync();
         const uint32_t va = tc::smem_u32(base + s * stage_elems) + (kTcRows + np) * 128;
-        for (int ks = 0; ks < np / 16; ++ks) {
-          const uint32_t pa = tc::smem_u32(sP) + (ks >> 2) * (kTcRows * 128) + (ks & 3) * 32;   // K-major A, 64 keys per K-block
-          tc::umma_ss(tmem + s * 256 + np, tc::smem_desc(pa, 16, 1024), tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
-        }
-        tc::umma_commit(&bars.o_ready[s]);
-        tc::umma_commit(&bars.p_free);
+        for (int ks = 0; ks < np / 16; ++ks)       // P: 16 keys = 8 packed columns per k-step; PV: 16 key rows = 2048 bytes
+          tc::umma_ts(tmem + b * 256 + np, tmem + b * 256 + ks * 8, tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
+        tc::umma_commit(&bars.o_ready[b]);
         tc::umma_commit(&bars.empty[s]);
+        if (i + 2 < n_my && !issue_s(i + 2)) break;
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue, thread = query row
+    const int wg = warp >> 2, r_tile = (warp & 3) * 32 + lane;
     const float sl2 = a.scale * 1.4426950408889634f;
     const float lw1 = log2f(a.w1), lw2 = log2f(a.w2);
-    const uint32_t lane_addr = (uint32_t) (warp * 32) << 16;
-    for (int i = 0; i < n_my; ++i) {
-      const int tile = blockIdx.x + i * gridDim.x, s = i & 1, u = i >> 1;
-      const int64_t bh = tile / tiles_per_head, row = (int64_t) (tile % tiles_per_head) * kTcRows + tid;
+    const uint32_t t_s = tmem + wg * 256 + ((uint32_t) ((warp & 3) * 32) << 16), t_o = t_s + np;
+    for (int i = wg; i < n_my; i += 2) {
+      const int tile = blockIdx.x + i * gridDim.x, u = i >> 1;
+      const int64_t bh = tile / tiles_per_head, row = (int64_t) (tile % tiles_per_head) * kTcRows + r_tile;
       const int64_t b = bh / a.H, h = bh % a.H;
-      // `ok` is kept warp-uniform: the TMEM loads below are warp-wide instructions
-      bool ok = __all_sync(0xffffffffu, tc_wait(&bars.s_ready[s], u & 1, abort_flag));
+      // the fine part of this row: requested now, consumed in the epilogue
+      bf16* orow = a.o.row(b, h, row);
+      uint4 of[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) of[q] = *reinterpret_cast<const uint4*>(orow + 8 * q);
+      const float lse_f = a.lse[bh * a.Nq + row];
+      // `ok` is kept warp-uniform: the TMEM accesses below are warp-wide instructions
+      bool ok = __all_sync(0xffffffffu, tc_wait(&bars.s_ready[wg], u & 1, abort_flag));
       tc::fence_after_sync();
-      const uint32_t t_s = tmem + s * 256 + lane_addr, t_o = t_s + np;
-      float mx = -INFINITY, lsum = 0.f;
+      float mx = 0.f, lsum = 0.f;
+      float va[32], vb[32];
       if (ok) {
-        for (int c0 = 0; c0 < np; c0 += 32) {
-          float v[32];
-          tc::tmem_ld32(t_s + c0, v);
-          const float lw = c0 < p1_keys ? lw1 : lw2;
+        float m1 = -INFINITY, m2 = -INFINITY;
+        auto chunk_max = [&](const float (&v)[32], int c0) {
+          float m = v[0];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaf(v[j], sl2, lw));
+          for (int j = 1; j < 32; ++j) m = fmaxf(m, v[j]);
+          if (c0 < p1_keys) m1 = fmaxf(m1, m); else m2 = fmaxf(m2, m);
+        };
+        tc::tmem_ld32_async(t_s, va);
+        tc::tmem_ld_wait(va);
+        for (int c0 = 0; c0 < np; c0 += 64) {        // chunk c0+32 is in flight while chunk c0 is reduced
+          tc::tmem_ld32_async(t_s + c0 + 32, vb);
+          chunk_max(va, c0);
+          tc::tmem_ld_wait(vb);
+          if (c0 + 64 < np) tc::tmem_ld32_async(t_s + c0 + 64, va);
+          chunk_max(vb, c0 + 32);
+          if (c0 + 64 < np) tc::tmem_ld_wait(va);
         }
-        ok = __all_sync(0xffffffffu, tc_wait(&bars.p_free, (i & 1) ^ 1, abort_flag));      // the previous tile's P.PV has consumed sP
-      }
-      if (ok) {
-        for (int c0 = 0; c0 < np; c0 += 32) {
-          float v[32];
-          tc::tmem_ld32(t_s + c0, v);
-          const float lw = c0 < p1_keys ? lw1 : lw2;
+        mx = fmaxf(fmaf(m1, sl2, lw1), fmaf(m2, sl2, lw2));
+        auto chunk_exp = [&](const float (&v)[32], int c0) {
+          const float off = (c0 < p1_keys ? lw1 : lw2) - mx;
+          uint32_t pk[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) { v[j] = fast_exp2(fmaf(v[j], sl2, lw) - mx); lsum += v[j]; }
-          bf16* pt = sP + (c0 >> 6) * (kTcRows * 64);          // K-block of 64 keys
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 w;
-            w.x = pack_bf16(v[8 * q], v[8 * q + 1]); w.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
-            w.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]); w.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-            *reinterpret_cast<uint4*>(pt + tc::swz(tid, ((c0 & 63) >> 3) + q)) = w;
+          for (int j = 0; j < 16; ++j) {
+            const float e0 = fast_exp2(fmaf(v[2 * j], sl2, off)), e1 = fast_exp2(fmaf(v[2 * j + 1], sl2, off));
+            lsum += e0 + e1;
+            pk[j] = pack_bf16(e0, e1);
           }
+          tc::tmem_st16(t_s + (c0 >> 1), pk);       // P columns [c0/2, c0/2+16): scores read long before
+        };
+        tc::tmem_ld32_async(t_s, va);
+        tc::tmem_ld_wait(va);
+        for (int c0 = 0; c0 < np; c0 += 64) {
+          tc::tmem_ld32_async(t_s + c0 + 32, vb);
+          chunk_exp(va, c0);
+          tc::tmem_ld_wait(vb);
+          if (c0 + 64 < np) tc::tmem_ld32_async(t_s + c0 + 64, va);
+          chunk_exp(vb, c0 + 32);
+          if (c0 + 64 < np) tc::tmem_ld_wait(va);
         }
-        tc::fence_async_smem();          // P must be visible to the tensor core's (async proxy) reads
+        tc::tmem_st_wait();
         tc::fence_before_sync();
-        tma::mbar_arrive(&bars.p_ready);
-        ok = __all_sync(0xffffffffu, tc_wait(&bars.o_ready[s], u & 1, abort_flag));
+        __syncwarp();
+        if (lane == 0) tma::mbar_arrive(&bars.p_ready[wg]);
+        ok = __all_sync(0xffffffffu, tc_wait(&bars.o_ready[wg], u & 1, abort_flag));
         tc::fence_after_sync();
       }
       float lse_out = __int_as_float(0x7fc00000);               // NaN unless everything completed
       if (ok) {
-        const float Lf = a.lse[bh * a.Nq + row] * 1.4426950408889634f;    // fine part, log2 domain
+        tc::tmem_ld32_async(t_o, va);
+        tc::tmem_ld32_async(t_o + 32, vb);
+        const float Lf = lse_f * 1.4426950408889634f;            // fine part, log2 domain
         const float Lp = mx + log2f(lsum);
         const float Lm = fmaxf(Lf, Lp);
         const float ef = fast_exp2(Lf - Lm), ep = fast_exp2(Lp - Lm);
         const float inv = 1.f / (ef + ep);
         const float wf = ef * inv, wp = ep * inv / lsum;
-        bf16* orow = a.o.row(b, h, row);
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          float v[32];
-          tc::tmem_ld32(t_o + c0, v);
+        lse_out = (Lm + log2f(ef + ep)) * 0.6931471805599453f;
+        tc::tmem_ld_wait(va);
+        tc::tmem_ld_wait(vb);
+        auto merge = [&](const float (&v)[32], int c0) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const uint4 f = *reinterpret_cast<const uint4*>(orow + c0 + 8 * q);
+            const uint4 f = of[(c0 >> 3) + q];
             uint4 w;
             w.x = pack_bf16(bf16_lo(f.x) * wf + v[8 * q] * wp, bf16_hi(f.x) * wf + v[8 * q + 1] * wp);
             w.y = pack_bf16(bf16_lo(f.y) * wf + v[8 * q + 2] * wp, bf16_hi(f.y) * wf + v[8 * q + 3] * wp);
@@ -213,10 +239,9 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
             w.w = pack_bf16(bf16_lo(f.w) * wf + v[8 * q + 6] * wp, bf16_hi(f.w) * wf + v[8 * q + 7] * wp);
             *reinterpret_cast<uint4*>(orow + c0 + 8 * q) = w;
           }
-        }
-        lse_out = (Lm + log2f(ef + ep)) * 0.6931471805599453f;
-        tc::fence_before_sync();
-        tma::mbar_arrive(&bars.tmem_free[s]);                    // this row's S / O columns may be overwritten
+        };
+        merge(va, 0);
+        merge(vb, 32);
       }
       a.lse[bh * a.Nq + row] = lse_out;
       if (!ok) break;
@@ -252,7 +277,7 @@ int launch_attn_fwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64
   LLSA_CUDA_OK(cudaGetDevice(&dev));
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = n_tiles < sms ? n_tiles : sms;
-  const size_t smem = 1024 + (size_t) (2 * (kTcRows * 64 + 2 * np * 64) + (np / 64) * kTcRows * 64) * sizeof(bf16);
+  const size_t smem = 1024 + (size_t) kTcStages * (kTcRows * 64 + 2 * np * 64) * sizeof(bf16);
   LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_pooled_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
   attn_fwd_pooled_tc_kernel<<<grid, kTcThreads, smem, st>>>(a, maps, p1_keys, np, n_tiles, tiles_per_head);
   LLSA_LAUNCH_OK("attn_fwd_pooled_tc_kernel");
