@@ -24,6 +24,8 @@
 //                          backward (dk += (dpk[j] + dpk2[j/16]/16)/16), one bf16 store.
 // The reference multiplies k by scale into new tensors first (res_1.py:420-422);
 // here scale rides in the exp2 argument and in the epilogues.
+#include <stdlib.h>
+
 #include "attn.cuh"
 #include "mma_frag.cuh"
 
@@ -531,18 +533,27 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   AttnP<bf16> a = build_attn_params<bf16>(g, true);
   const unsigned BH = (unsigned) (g->q->shape[0] * a.H);
   const int mask = g->stage_mask ? g->stage_mask : 7;
+  // pooled keys on tcgen05 (attn_pooled_bwd_tc.cu): the dQ kernel then covers the fine blocks only and the
+  // tensor-core kernel adds the pooled part of dq and produces the pooled-key gradients
+  const char* tc_env = getenv("LLSA_B200_TC");
+  const bool tc = pooled_bwd_tc_ok(a) && !(tc_env && tc_env[0] == '0');
   if (mask & 1) {
     int rc = zero_pooled_acc(g, st);
     if (rc) return rc;
     constexpr int NWQ = 4;
-    const int n_all = a.p1_blocks + a.p2_blocks;
+    AttnP<bf16> aq = a;
+    if (tc) aq.p1_blocks = aq.p2_blocks = 0;
+    const int n_all = aq.p1_blocks + aq.p2_blocks;
     const int n_smem = n_all < 12 ? n_all : 12;   // 12 tiles = 54 KB of K+V, three CTAs per SM
     const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_mma_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, smem, st>>>(a, n_smem);
+    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, smem, st>>>(aq, n_smem);
     LLSA_LAUNCH_OK("attn_dq_mma_kernel");
   }
-  if ((mask & 2) && a.p1_blocks + a.p2_blocks > 0) {
+  if ((mask & 2) && tc) {
+    int rc = launch_attn_bwd_pooled_tc(g, a, BH, st);
+    if (rc) return rc;
+  } else if ((mask & 2) && a.p1_blocks + a.p2_blocks > 0) {
     constexpr int NWP = 8;
     const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
