@@ -12,25 +12,29 @@
 //     dPK = dS^T . Q        [192 x 64],  K = 128
 // with P = exp(S*scale + ln w - lse) and dS = P * (dP - delta) * scale computed by the softmax warps
 // between the first two and the last three.  The 64 level-2 keys would need an M = 64 product; instead
-// P(tile 2) and dS(tile 2) are laid out next to each other and used as ONE M = 128 operand, so that
-// [P2 | dS2]^T . dO holds dPV2 in TMEM lanes 0..63 and [P2 | dS2]^T . Q holds dPK2 in lanes 64..127.
+// P(tile 2) and dS(tile 2) are laid out next to each other and used as ONE M = 128 operand against
+// [Q | dO] (N = 128): the result holds dPK2 in TMEM lanes 64..127 of its first 64 columns and dPV2 in
+// lanes 0..63 of its last 64.
 //
 // TMEM columns: S, then dP, share [0,192) (the softmax warps keep P in registers between the two);
-// dQ [192,256); dPV1 [256,320); dPK1 [320,384); [P2|dS2]^T.dO [384,448); [P2|dS2]^T.Q [448,512).
+// dQ [192,256); dPV1 [256,320); dPK1 [320,384); [P2|dS2]^T.[Q|dO] [384,512).
 // The level-1 results accumulate in TMEM over the two tiles of a parent, the level-2 results over all
-// tiles of a head that the CTA walks, so the fp32 reductions to global memory happen once per parent /
-// once per head and CTA instead of once per tile.
+// tiles of a head that the CTA walks, so the fp32 reductions to global memory (whose rate at the L2
+// is what bounds them) happen once per parent / once per head and CTA, and a warpgroup of their own
+// issues them while the others are already on the next tile.
 //
-// One persistent CTA per SM walks a contiguous range of tiles (the two tiles of a parent share their
-// level-1 keys, all tiles of a head share the level-2 keys: those are loaded only when they change).
-//   warp 12, one lane: TMA producer (Q, dO double-buffered; pooled keys single-buffered)
-//   warp 13, one lane: tcgen05.mma issuer.  tcgen05.mma operations execute in issue order, so S of the
-//                      next tile is issued as soon as dP of this tile has been read, ahead of this
-//                      tile's three output products.
-//   warps 0-11       : three softmax warpgroups; group g owns key tile g (64 keys), thread r of a
-//                      group owns query row r = TMEM lane r.  Afterwards group 0 adds dQ to the fine
-//                      part already in dq, group 1 adds dPV1 / dPK1 and group 2 the level-2 results to
-//                      the fp32 pooled-gradient accumulators (red.global.add.v4.f32).
+// One persistent CTA per SM walks a contiguous range of tiles.
+//   warps 0-11        : three softmax warpgroups; group g owns key tile g (64 keys), thread r of a
+//                       group owns query row r = TMEM lane r.  Group 0 also adds dQ to the fine part
+//                       already in dq (through shared memory, so that global rows are touched whole).
+//   warps 12-15       : drain warpgroup: at the end of a parent adds dPV1 / dPK1 (TMEM lane = pooled
+//                       key) to the fp32 pooled-gradient accumulators with red.global.add.v4.f32, at
+//                       the end of a head the level-2 results.
+//   warp 16, one lane : TMA producer (Q, dO and the level-1 keys double-buffered; level-1 values
+//                       reloaded as soon as dP of the parent's last tile has read them)
+//   warp 17, one lane : tcgen05.mma issuer.  tcgen05.mma operations execute in issue order, so S of the
+//                       next tile is issued as soon as dP of this tile has been read, ahead of this
+//                       tile's three output products.
 // Every mbarrier wait is bounded; a wait that expires raises a CTA-wide abort flag, every role leaves
 // its loop, the host-visible status word is set and TMEM is freed.
 #include <string.h>
@@ -45,9 +49,10 @@ namespace llsa {
 namespace {
 
 constexpr int kRows = 128;
-constexpr int kThreads = 448;         // 12 softmax warps + producer warp + MMA warp
+constexpr int kThreads = 576;         // 12 softmax warps + 4 drain warps + producer warp + MMA warp
 constexpr int kTile = kRows * 64;     // elements of a [128 x 64] bf16 tile (16 KB)
 constexpr float kLog2eF = 1.4426950408889634f;
+constexpr uint32_t kColDQ = 192, kColPV1 = 256, kColPK1 = 320, kColYX = 384, kColY = 384, kColX = 448;
 
 struct BwdMaps {
   CUtensorMap q, d_o;          // [B,H,Nq,64] 4-D, box 128 rows
@@ -55,11 +60,11 @@ struct BwdMaps {
   CUtensorMap pk2, pv2;        // [BH*n2, 64], box 64 rows
 };
 
+// Phases: full / mma_done / v_free alternate between two barriers by tile parity; the others complete once per
+// tile (acc_free: once per parent).
 struct BwdBars {
-  uint64_t full[2], mma_done[2], s_ready, s_consumed, dp_ready, pds_ready, out_ready;
+  uint64_t full[2], mma_done[2], v_free[2], s_ready, s_consumed, dp_ready, pds_ready, out_ready, dq_free, acc_free;
 };
-
-constexpr uint32_t kColDQ = 192, kColPV1 = 256, kColPK1 = 320, kColX = 384, kColY = 448;
 
 __device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (int i = 0; i < 400000; ++i) {
@@ -79,10 +84,10 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   bf16* sQ = base;                      // [2][128][64]
   bf16* sDO = sQ + 2 * kTile;           // [2][128][64]
-  bf16* sK1 = sDO + 2 * kTile;          // [128][64] level-1 keys of the parent
-  bf16* sV1 = sK1 + kTile;
-  bf16* sK2 = sV1 + kTile;              // [64][64] level-2 keys of the head
-  bf16* sV2 = sK2 + kTile / 2;
+  bf16* sK1 = sDO + 2 * kTile;          // [2][128][64] level-1 keys, buffer = parity of the parent
+  bf16* sK2 = sK1 + 2 * kTile;          // [64][64] level-2 keys of the head
+  bf16* sV1 = sK2 + kTile / 2;          // [128][64] level-1 values, then
+  bf16* sV2 = sV1 + kTile;              // [64][64] level-2 values: 192 contiguous rows
   bf16* sP = sV2 + kTile / 2;           // P tiles 0, 1, 2, then dS tiles 2, 0, 1 (tile = [128 rows][64 keys])
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile int* abort_flag = &s_abort;
@@ -92,12 +97,15 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.full[i], 1);
       tc::mbar_init(&bars.mma_done[i], 1);
+      tc::mbar_init(&bars.v_free[i], 1);
     }
     tc::mbar_init(&bars.s_ready, 1);
     tc::mbar_init(&bars.dp_ready, 1);
     tc::mbar_init(&bars.out_ready, 1);
     tc::mbar_init(&bars.s_consumed, 12);     // one arrival per softmax warp
     tc::mbar_init(&bars.pds_ready, 12);
+    tc::mbar_init(&bars.dq_free, 4);         // one arrival per drain warp
+    tc::mbar_init(&bars.acc_free, 4);
     tc::fence_mbar_init();
   }
   if (warp == 0) tc::tmem_alloc(&s_tmem, 512);
@@ -109,178 +117,223 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
   const int t_begin = (int) ((int64_t) n_tiles * blockIdx.x / gridDim.x), t_end = (int) ((int64_t) n_tiles * (blockIdx.x + 1) / gridDim.x);
   const int n_my = t_end - t_begin;
 
-  if (warp == 12) {
+  if (warp == 16) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       for (int i = 0; i < n_my; ++i) {
         const int tile = t_begin + i, s = i & 1;
-        const int64_t bh = tile / tiles_per_head, row0 = (int64_t) (tile % tiles_per_head) * kRows;
+        const int bh = tile / tiles_per_head, row0 = (tile % tiles_per_head) * kRows;
         const bool new_parent = i == 0 || (tile >> 1) != ((tile - 1) >> 1);
         const bool new_head = i == 0 || bh != (tile - 1) / tiles_per_head;
-        if (i >= 2 && !bw_wait(&bars.mma_done[s], ((i - 2) >> 1) & 1, abort_flag)) break;          // stage s is free
-        if (i >= 1 && new_parent && !bw_wait(&bars.mma_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;   // key buffers are free
-        tma::expect_tx(&bars.full[s], 2u * kTile * 2 + (new_parent ? 2u * kTile * 2 : 0u) + (new_head ? (uint32_t) kTile * 2 : 0u));
-        tma::load_4d(sQ + s * kTile, &maps.q, &bars.full[s], 0, (int) row0, (int) (bh % a.H), (int) (bh / a.H));
-        tma::load_4d(sDO + s * kTile, &maps.d_o, &bars.full[s], 0, (int) row0, (int) (bh % a.H), (int) (bh / a.H));
+        int krow[8];                      // rows of the parent's 8 selected level-1 key blocks: independent loads, ahead of the waits
         if (new_parent) {
-          for (int j = 0; j < 8; ++j) {
-            const int r = (int) (bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS);
-            tma::load_2d(sK1 + j * kBS * 64, &maps.pk1, &bars.full[s], 0, r);
-            tma::load_2d(sV1 + j * kBS * 64, &maps.pv1, &bars.full[s], 0, r);
-          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) krow[j] = (int) ((int64_t) bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS);
         }
+        // stage s (and the level-1 key buffer of the parent two back) is free once every product of tile i - 2 has completed
+        if (i >= 2 && !bw_wait(&bars.mma_done[s], ((i - 2) >> 1) & 1, abort_flag)) break;
+        // the level-2 buffers are free once every product of the previous tile has completed
+        if (i >= 1 && new_head && !bw_wait(&bars.mma_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;
+        tma::expect_tx(&bars.full[s], 2u * kTile * 2 + (new_parent ? 2u * kTile * 2 : 0u) + (new_head ? (uint32_t) kTile * 2 : 0u));
+        tma::load_4d(sQ + s * kTile, &maps.q, &bars.full[s], 0, row0, bh % a.H, bh / a.H);
+        tma::load_4d(sDO + s * kTile, &maps.d_o, &bars.full[s], 0, row0, bh % a.H, bh / a.H);
         if (new_head) {
-          tma::load_2d(sK2, &maps.pk2, &bars.full[s], 0, (int) (bh * a.n2));
-          tma::load_2d(sV2, &maps.pv2, &bars.full[s], 0, (int) (bh * a.n2));
+          tma::load_2d(sK2, &maps.pk2, &bars.full[s], 0, (int) ((int64_t) bh * a.n2));
+          tma::load_2d(sV2, &maps.pv2, &bars.full[s], 0, (int) ((int64_t) bh * a.n2));
+        }
+        if (new_parent) {
+          bf16* k1 = sK1 + ((tile >> 1) & 1) * kTile;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) tma::load_2d(k1 + j * kBS * 64, &maps.pk1, &bars.full[s], 0, krow[j]);
+          // the level-1 values are last read by dP of the previous tile.  New parents come every other tile, so one of
+          // the two v_free barriers is waited on at each of its phases and the other never.
+          if (i >= 1 && !bw_wait(&bars.v_free[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) tma::load_2d(sV1 + j * kBS * 64, &maps.pv1, &bars.full[s], 0, krow[j]);
         }
       }
     }
-  } else if (warp == 13) {
+  } else if (warp == 17) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t id_s128 = tc::instr_desc(128, 128, 0, 0), id_s64 = tc::instr_desc(128, 64, 0, 0);
-      const uint32_t id_dq = tc::instr_desc(128, 64, 0, 1), id_kv = tc::instr_desc(128, 64, 1, 1);
-      const uint32_t k1a = tc::smem_u32(sK1), v1a = tc::smem_u32(sV1), k2a = tc::smem_u32(sK2), v2a = tc::smem_u32(sV2);
+      const uint32_t id_s128 = tc::instr_desc(128, 128, 0, 0), id_s64 = tc::instr_desc(128, 64, 0, 0), id_s192 = tc::instr_desc(128, 192, 0, 0);
+      const uint32_t id_dq = tc::instr_desc(128, 64, 0, 1), id_kv = tc::instr_desc(128, 64, 1, 1), id_kv2 = tc::instr_desc(128, 128, 1, 1);
       const uint32_t pa = tc::smem_u32(sP), dsa2 = pa + 3 * kTile * 2, dsa0 = dsa2 + kTile * 2;
+      // Descriptors are built once; a k-step only adds its byte offset >> 4 to the address field (addresses stay
+      // below 2^18, so the 14-bit field never carries).  K-major operand: 32 bytes per k-step of 16 channels inside
+      // the swizzled 128-byte row; MN-major operand: 16 rows = 2048 bytes per k-step.
+      const uint64_t dK2_k = tc::smem_desc(tc::smem_u32(sK2), 16, 1024), dK2_m = tc::smem_desc(tc::smem_u32(sK2), 1024, 1024);
+      const uint64_t dV_k = tc::smem_desc(tc::smem_u32(sV1), 16, 1024);                                        // [V1;V2] as N = 192 rows
+      const uint64_t dDS_k[3] = {tc::smem_desc(dsa0, 16, 1024), tc::smem_desc(dsa0 + kTile * 2, 16, 1024), tc::smem_desc(dsa2, 16, 1024)};
+      const uint64_t dP1_m = tc::smem_desc(pa, kTile * 2, 1024), dDS1_m = tc::smem_desc(dsa0, kTile * 2, 1024);   // M = 128 keys over two tiles
+      const uint64_t dP2_m = tc::smem_desc(pa + 2 * kTile * 2, kTile * 2, 1024);                                  // [P2 | dS2]
+      const uint64_t dQ_k0 = tc::smem_desc(tc::smem_u32(sQ), 16, 1024), dDO_k0 = tc::smem_desc(tc::smem_u32(sDO), 16, 1024);
+      const uint64_t dQ_m0 = tc::smem_desc(tc::smem_u32(sQ), 1024, 1024), dDO_m0 = tc::smem_desc(tc::smem_u32(sDO), 1024, 1024);
+      const uint64_t dQDO_m0 = tc::smem_desc(tc::smem_u32(sQ), 2 * kTile * 2, 1024);           // N = 128: channels of Q, then of dO (32 KB further)
+      const uint64_t dK1_k0 = tc::smem_desc(tc::smem_u32(sK1), 16, 1024), dK1_m0 = tc::smem_desc(tc::smem_u32(sK1), 1024, 1024);
+      constexpr uint64_t kStage = (uint64_t) (kTile * 2) >> 4;      // one 16 KB buffer further, in descriptor address units
       auto issue_s = [&](int i) -> bool {          // S(i) = Q . [PK1 ; PK2]^T into columns [0,192)
         const int s = i & 1;
         if (!bw_wait(&bars.full[s], (i >> 1) & 1, abort_flag)) return false;
         tc::fence_after_sync();
-        const uint32_t qa = tc::smem_u32(sQ + s * kTile);
+        const uint64_t q_ = dQ_k0 + s * kStage, k1_ = dK1_k0 + (((t_begin + i) >> 1) & 1) * kStage;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {      // K-major operands: 32 bytes per k-step inside the swizzled 128-byte row
-          const uint64_t dq_ = tc::smem_desc(qa + ks * 32, 16, 1024);
-          tc::umma_ss(tmem + 0, dq_, tc::smem_desc(k1a + ks * 32, 16, 1024), id_s128, ks > 0);
-          tc::umma_ss(tmem + 128, dq_, tc::smem_desc(k2a + ks * 32, 16, 1024), id_s64, ks > 0);
+        for (int ks = 0; ks < 4; ++ks) {
+          tc::umma_ss(tmem, q_ + 2 * ks, k1_ + 2 * ks, id_s128, ks > 0);
+          tc::umma_ss(tmem + 128, q_ + 2 * ks, dK2_k + 2 * ks, id_s64, ks > 0);
         }
         tc::umma_commit(&bars.s_ready);
         return true;
       };
+      int parents_done = 0;
       bool ok = n_my > 0 && issue_s(0);
       for (int i = 0; ok && i < n_my; ++i) {
         const int s = i & 1, tile = t_begin + i;
-        const uint32_t qa = tc::smem_u32(sQ + s * kTile), doa = tc::smem_u32(sDO + s * kTile);
         // dP(i) = dO . [PV1 ; PV2]^T over the columns of S once every softmax warp has read S
         if (!bw_wait(&bars.s_consumed, i & 1, abort_flag)) break;
         tc::fence_after_sync();
+        {
+          const uint64_t d_ = dDO_k0 + s * kStage;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t dd_ = tc::smem_desc(doa + ks * 32, 16, 1024);
-          tc::umma_ss(tmem + 0, dd_, tc::smem_desc(v1a + ks * 32, 16, 1024), id_s128, ks > 0);
-          tc::umma_ss(tmem + 128, dd_, tc::smem_desc(v2a + ks * 32, 16, 1024), id_s64, ks > 0);
+          for (int ks = 0; ks < 4; ++ks) tc::umma_ss(tmem, d_ + 2 * ks, dV_k + 2 * ks, id_s192, ks > 0);
         }
         tc::umma_commit(&bars.dp_ready);
+        tc::umma_commit(&bars.v_free[s]);
         if (!bw_wait(&bars.pds_ready, i & 1, abort_flag)) break;
         tc::fence_after_sync();
-        // the next tile's S goes first when it uses the same level-1 keys (their buffer is reloaded only after
-        // this tile's products have completed, which a new parent's S would wait for)
-        const bool next_same_parent = i + 1 < n_my && ((tile + 1) >> 1) == (tile >> 1);
-        if (next_same_parent && !issue_s(i + 1)) break;
-        // dQ = dS . PK: 12 k-steps of 16 keys; dS tile kt = ks / 4 (memory order 2, 0, 1), PK rows 16 ks .. 16 ks + 15
-        for (int ks = 0; ks < 12; ++ks) {
-          const int kt = ks >> 2;
-          const uint32_t da = (kt == 2 ? dsa2 : dsa0 + kt * kTile * 2) + (ks & 3) * 32;
-          const uint32_t kb = ks < 8 ? k1a + ks * 2048 : k2a + (ks - 8) * 2048;
-          tc::umma_ss(tmem + kColDQ, tc::smem_desc(da, 16, 1024), tc::smem_desc(kb, 1024, 1024), id_dq, ks > 0);
+        // The next tile's S goes ahead of this tile's output products, unless it belongs to a new head: the level-2
+        // buffers are reloaded only after these products have completed.
+        const bool next_early = i + 1 < n_my && (tile + 1) % tiles_per_head != 0;
+        if (next_early && !issue_s(i + 1)) break;
+        // dQ = dS . [PK1 ; PK2]: 12 k-steps of 16 keys, dS tile ks / 4; its columns are free once the drain warps have read
+        // the previous tile's dQ
+        if (i > 0 && !bw_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) break;
+        tc::fence_after_sync();
+        {
+          const uint64_t k1_ = dK1_m0 + ((tile >> 1) & 1) * kStage;
+#pragma unroll
+          for (int ks = 0; ks < 12; ++ks)
+            tc::umma_ss(tmem + kColDQ, dDS_k[ks >> 2] + 2 * (ks & 3), ks < 8 ? k1_ + 128 * ks : dK2_m + 128 * (ks - 8), id_dq, ks > 0);
         }
-        // transposed products, K = 128 query rows in 8 k-steps of 16 rows (2048 bytes); the A operand spans two
-        // 64-key tiles 16 KB apart (leading-dimension byte offset).  Level-1 results accumulate over the tiles of
-        // a parent, level-2 results over the tiles of a head.
+        // transposed products, K = 128 query rows in 8 k-steps.  Level-1 results accumulate over the tiles of a
+        // parent, level-2 results over the tiles of a head; a fresh start waits for the drain warps to have read
+        // the previous parent's results.
         const uint32_t acc1 = (i > 0 && (tile & 1)) ? 1u : 0u;
         const uint32_t acc2 = (i > 0 && (tile % tiles_per_head) != 0) ? 1u : 0u;
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bdo = tc::smem_desc(doa + ks * 2048, 1024, 1024), bq = tc::smem_desc(qa + ks * 2048, 1024, 1024);
-          const uint64_t ap2 = tc::smem_desc(pa + 2 * kTile * 2 + ks * 2048, kTile * 2, 1024);
-          tc::umma_ss(tmem + kColPV1, tc::smem_desc(pa + ks * 2048, kTile * 2, 1024), bdo, id_kv, acc1 | (ks > 0));
-          tc::umma_ss(tmem + kColPK1, tc::smem_desc(dsa0 + ks * 2048, kTile * 2, 1024), bq, id_kv, acc1 | (ks > 0));
-          tc::umma_ss(tmem + kColX, ap2, bdo, id_kv, acc2 | (ks > 0));
-          tc::umma_ss(tmem + kColY, ap2, bq, id_kv, acc2 | (ks > 0));
+        if (!acc1 && parents_done > 0 && !bw_wait(&bars.acc_free, (parents_done - 1) & 1, abort_flag)) break;
+        tc::fence_after_sync();
+        {
+          const uint64_t do_ = dDO_m0 + s * kStage, q_ = dQ_m0 + s * kStage, qdo_ = dQDO_m0 + s * kStage;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            tc::umma_ss(tmem + kColPV1, dP1_m + 128 * ks, do_ + 128 * ks, id_kv, acc1 | (ks > 0));
+            tc::umma_ss(tmem + kColPK1, dDS1_m + 128 * ks, q_ + 128 * ks, id_kv, acc1 | (ks > 0));
+            tc::umma_ss(tmem + kColYX, dP2_m + 128 * ks, qdo_ + 128 * ks, id_kv2, acc2 | (ks > 0));
+          }
         }
         tc::umma_commit(&bars.out_ready);
         tc::umma_commit(&bars.mma_done[s]);
-        if (!next_same_parent && i + 1 < n_my && !issue_s(i + 1)) break;
+        if ((tile & 1) || i == n_my - 1) ++parents_done;
+        if (!next_early && i + 1 < n_my && !issue_s(i + 1)) break;
       }
     }
-  } else {
-    // ---------------------------------------------------------------- softmax / dS, then the drains; thread = query row
-    const int wg = warp >> 2, r = (warp & 3) * 32 + lane;
-    const float sl2 = a.scale * kLog2eF;
-    const float lw = log2f(wg < 2 ? a.w1 : a.w2);
-    const uint32_t t_row = tmem + ((uint32_t) ((warp & 3) * 32) << 16);
-    bf16* myP = sP + wg * kTile;
-    bf16* myDS = sP + (wg == 2 ? 3 : 4 + wg) * kTile;
-    float va[32], vb[32];
-    uint4 dqv[8];
-    // group 0: dq row of `tile` = fine part (already in memory, fetched into dqv) + pooled part (TMEM)
-    auto load_dq = [&](int tile) {
-      const int64_t bh = tile / tiles_per_head, row = (int64_t) (tile % tiles_per_head) * kRows + r;
-      const bf16* p = a.dq.row(bh / a.H, bh % a.H, row);
+  } else if (warp >= 12) {
+    // ---------------------------------------------------------------- drain warpgroup
+    const int qd = warp & 3, r = qd * 32 + lane;
+    const uint32_t t_row = tmem + ((uint32_t) (qd * 32) << 16);
+    float va[32];
+    auto red_cols = [&](float* dst, uint32_t col, float mul) {      // 64 columns of this lane -> dst[0..63]
 #pragma unroll
-      for (int q = 0; q < 8; ++q) dqv[q] = *reinterpret_cast<const uint4*>(p + 8 * q);
+      for (int half = 0; half < 2; ++half) {
+        tc::tmem_ld32_async(t_row + col + 32 * half, va);
+        tc::tmem_ld_wait(va);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) red_add_v4(dst + 32 * half + 4 * q, va[4 * q] * mul, va[4 * q + 1] * mul, va[4 * q + 2] * mul, va[4 * q + 3] * mul);
+      }
     };
-    auto drain_dq = [&](int tile) {
-      const int64_t bh = tile / tiles_per_head, row = (int64_t) (tile % tiles_per_head) * kRows + r;
-      bf16* dqrow = a.dq.row(bh / a.H, bh % a.H, row);
-      tc::tmem_ld32_async(t_row + kColDQ, va);
-      tc::tmem_ld32_async(t_row + kColDQ + 32, vb);
-      tc::tmem_ld_wait(va);
-      tc::tmem_ld_wait(vb);
-      auto add_store = [&](const float (&v)[32], int c0) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint4 f = dqv[(c0 >> 3) + q];
-          uint4 w;
-          w.x = pack_bf16(bf16_lo(f.x) + v[8 * q], bf16_hi(f.x) + v[8 * q + 1]);
-          w.y = pack_bf16(bf16_lo(f.y) + v[8 * q + 2], bf16_hi(f.y) + v[8 * q + 3]);
-          w.z = pack_bf16(bf16_lo(f.z) + v[8 * q + 4], bf16_hi(f.z) + v[8 * q + 5]);
-          w.w = pack_bf16(bf16_lo(f.w) + v[8 * q + 6], bf16_hi(f.w) + v[8 * q + 7]);
-          *reinterpret_cast<uint4*>(dqrow + c0 + 8 * q) = w;
-        }
-      };
-      add_store(va, 0);
-      add_store(vb, 32);
-    };
-    // groups 1, 2: TMEM lane r = pooled key r of the tile's key set, added to the fp32 accumulators in global memory
-    auto drain_cols = [&](float* dst, uint32_t col, float mul) {
-      tc::tmem_ld32_async(t_row + col, va);
-      tc::tmem_ld32_async(t_row + col + 32, vb);
-      tc::tmem_ld_wait(va);
-      tc::tmem_ld_wait(vb);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) red_add_v4(dst + 4 * q, va[4 * q] * mul, va[4 * q + 1] * mul, va[4 * q + 2] * mul, va[4 * q + 3] * mul);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) red_add_v4(dst + 32 + 4 * q, vb[4 * q] * mul, vb[4 * q + 1] * mul, vb[4 * q + 2] * mul, vb[4 * q + 3] * mul);
-    };
-    bool pending = false;        // the previous tile's products have not been waited for yet
     for (int i = 0; i < n_my; ++i) {
       const int tile = t_begin + i;
-      const int64_t bh = tile / tiles_per_head, row0 = (int64_t) (tile % tiles_per_head) * kRows, row = row0 + r;
-      const float off = lw - a.lse[bh * a.Nq + row] * kLog2eF;
-      const float dls = a.delta[bh * a.Nq + row] * a.scale;
-      if (pending && wg == 0) load_dq(tile - 1);
-      bool ok = __all_sync(0xffffffffu, bw_wait(&bars.s_ready, i & 1, abort_flag));
+      const int bh = tile / tiles_per_head, row0 = (tile % tiles_per_head) * kRows;
+      const bool parent_end = (tile & 1) || i == n_my - 1;
+      // every tile: dq row r of the tile = fine part (already in memory) + pooled part (TMEM lane r = query row r)
+      bf16* dqrow = a.dq.row(bh / a.H, bh % a.H, row0 + r);
+      uint4 old[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) old[q] = *reinterpret_cast<const uint4*>(dqrow + 8 * q);
+      const int64_t key = parent_end ? p1_block(a, bh, row0 / kBS, r >> 4) * kBS + (r & 15) : 0;
+      const bool ok = __all_sync(0xffffffffu, bw_wait(&bars.out_ready, i & 1, abort_flag));
+      tc::fence_after_sync();
+      if (!ok) break;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tc::tmem_ld32_async(t_row + kColDQ + 32 * half, va);
+        tc::tmem_ld_wait(va);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 f = old[4 * half + q];
+          uint4 w;
+          w.x = pack_bf16(bf16_lo(f.x) + va[8 * q], bf16_hi(f.x) + va[8 * q + 1]);
+          w.y = pack_bf16(bf16_lo(f.y) + va[8 * q + 2], bf16_hi(f.y) + va[8 * q + 3]);
+          w.z = pack_bf16(bf16_lo(f.z) + va[8 * q + 4], bf16_hi(f.z) + va[8 * q + 5]);
+          w.w = pack_bf16(bf16_lo(f.w) + va[8 * q + 6], bf16_hi(f.w) + va[8 * q + 7]);
+          *reinterpret_cast<uint4*>(dqrow + 32 * half + 8 * q) = w;
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(&bars.dq_free);
+      if (!parent_end) continue;
+      // end of a parent: TMEM lane r = level-1 pooled key r of the parent
+      red_cols(a.dpv + ((int64_t) bh * a.n1 + key) * kD, kColPV1, a.kvw1 / a.w1);
+      red_cols(a.dpk + ((int64_t) bh * a.n1 + key) * kD, kColPK1, a.kvw1 / a.w1);
+      if (i == n_my - 1 || (tile + 1) % tiles_per_head == 0) {
+        // level-2 keys: dPK2 of key r - 64 in lanes 64..127 of the first 64 columns, dPV2 of key r in lanes 0..63 of the last 64
+        if (qd < 2) red_cols(a.dpv2 + ((int64_t) bh * a.n2 + r) * kD, kColX, a.kvw2 / a.w2);
+        else red_cols(a.dpk2 + ((int64_t) bh * a.n2 + (r - 64)) * kD, kColY, a.kvw2 / a.w2);
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(&bars.acc_free);
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / dS; thread = query row
+    const int wg = warp >> 2, qd = warp & 3, r = qd * 32 + lane;
+    const float sl2 = a.scale * kLog2eF;
+    const float lw = log2f(wg < 2 ? a.w1 : a.w2);
+    const uint32_t t_row = tmem + ((uint32_t) (qd * 32) << 16);
+    bf16* myP = sP + wg * kTile;
+    bf16* myDS = sP + (wg == 2 ? 3 : 4 + wg) * kTile;
+    float va[32];
+    float lse_n = 0.f, delta_n = 0.f;
+    if (n_my > 0) {
+      const int bh = t_begin / tiles_per_head, row = (t_begin % tiles_per_head) * kRows + r;
+      lse_n = a.lse[(int64_t) bh * a.Nq + row];
+      delta_n = a.delta[(int64_t) bh * a.Nq + row];
+    }
+    bool ok = true;
+    for (int i = 0; i < n_my; ++i) {
+      const int tile = t_begin + i;
+      const float off = lw - lse_n * kLog2eF;
+      const float dls = delta_n * a.scale;
+      ok = __all_sync(0xffffffffu, bw_wait(&bars.s_ready, i & 1, abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
       uint32_t pk[32];          // this row's 64 probabilities, bf16 pairs, kept for dS
-      tc::tmem_ld32_async(t_row + wg * 64, va);
-      tc::tmem_ld32_async(t_row + wg * 64 + 32, vb);
-      tc::tmem_ld_wait(va);
-      tc::tmem_ld_wait(vb);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        pk[j] = pack_bf16(fast_exp2(fmaf(va[2 * j], sl2, off)), fast_exp2(fmaf(va[2 * j + 1], sl2, off)));
-        pk[16 + j] = pack_bf16(fast_exp2(fmaf(vb[2 * j], sl2, off)), fast_exp2(fmaf(vb[2 * j + 1], sl2, off)));
+      for (int half = 0; half < 2; ++half) {
+        tc::tmem_ld32_async(t_row + wg * 64 + 32 * half, va);
+        tc::tmem_ld_wait(va);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk[16 * half + j] = pack_bf16(fast_exp2(fmaf(va[2 * j], sl2, off)), fast_exp2(fmaf(va[2 * j + 1], sl2, off)));
       }
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) tma::mbar_arrive(&bars.s_consumed);
-      if (pending) {
-        // the previous tile's products still read its P / dS tiles: wait for them before overwriting (and finish its dq)
+      if (i > 0) {
+        // the previous tile's products read its P / dS tiles: wait for them before overwriting
         ok = __all_sync(0xffffffffu, bw_wait(&bars.out_ready, (i - 1) & 1, abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
-        if (wg == 0) drain_dq(tile - 1);
-        pending = false;
       }
 #pragma unroll
       for (int q = 0; q < 8; ++q)
@@ -288,11 +341,15 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       ok = __all_sync(0xffffffffu, bw_wait(&bars.dp_ready, i & 1, abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
-      tc::tmem_ld32_async(t_row + wg * 64, va);
-      tc::tmem_ld32_async(t_row + wg * 64 + 32, vb);
-      tc::tmem_ld_wait(va);
-      tc::tmem_ld_wait(vb);
-      auto ds_store = [&](const float (&v)[32], int half) {
+      if (i + 1 < n_my) {        // next tile's log-sum-exp and delta: in flight during the dS arithmetic
+        const int bhn = (tile + 1) / tiles_per_head, rown = ((tile + 1) % tiles_per_head) * kRows + r;
+        lse_n = a.lse[(int64_t) bhn * a.Nq + rown];
+        delta_n = a.delta[(int64_t) bhn * a.Nq + rown];
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tc::tmem_ld32_async(t_row + wg * 64 + 32 * half, va);
+        tc::tmem_ld_wait(va);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 w;
@@ -300,37 +357,15 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const uint32_t p2 = pk[half * 16 + 4 * q + e];
-            wp[e] = pack_bf16(bf16_lo(p2) * fmaf(v[8 * q + 2 * e], a.scale, -dls), bf16_hi(p2) * fmaf(v[8 * q + 2 * e + 1], a.scale, -dls));
+            wp[e] = pack_bf16(bf16_lo(p2) * fmaf(va[8 * q + 2 * e], a.scale, -dls), bf16_hi(p2) * fmaf(va[8 * q + 2 * e + 1], a.scale, -dls));
           }
           *reinterpret_cast<uint4*>(myDS + tc::swz(r, half * 4 + q)) = w;
         }
-      };
-      ds_store(va, 0);
-      ds_store(vb, 1);
+      }
       tc::fence_async_smem();          // P, dS must be visible to the tensor core's (async proxy) reads
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) tma::mbar_arrive(&bars.pds_ready);
-      // A tile that ends its parent inside this CTA's range is finished at once (the next tile's S has to wait for
-      // new keys anyway); otherwise the wait moves behind the next tile's exponentials.
-      const bool last = i == n_my - 1;
-      if (!((tile & 1) || last)) { pending = true; continue; }
-      if (wg == 0) load_dq(tile);
-      ok = __all_sync(0xffffffffu, bw_wait(&bars.out_ready, i & 1, abort_flag));
-      tc::fence_after_sync();
-      if (!ok) break;
-      if (wg == 0) {
-        drain_dq(tile);
-      } else if (wg == 1) {
-        const int64_t key = p1_block(a, bh, row0 / kBS, r >> 4) * kBS + (r & 15);
-        drain_cols(a.dpv + (bh * a.n1 + key) * kD, kColPV1, a.kvw1 / a.w1);
-        drain_cols(a.dpk + (bh * a.n1 + key) * kD, kColPK1, a.kvw1 / a.w1);
-      } else if (last || (tile + 1) % tiles_per_head == 0) {
-        // lanes 0..63: level-2 key r, dPV2 in [P2|dS2]^T.dO; lanes 64..127: level-2 key r - 64, dPK2 in [P2|dS2]^T.Q
-        if (r < 64) drain_cols(a.dpv2 + (bh * a.n2 + r) * kD, kColX, a.kvw2 / a.w2);
-        else drain_cols(a.dpk2 + (bh * a.n2 + (r - 64)) * kD, kColY, a.kvw2 / a.w2);
-      }
-      tc::fence_before_sync();      // the TMEM reads above are ordered before this warp's next barrier arrival
     }
   }
   tc::fence_before_sync();
@@ -362,7 +397,7 @@ int launch_attn_bwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64
   LLSA_CUDA_OK(cudaGetDevice(&dev));
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = n_tiles < sms ? n_tiles : sms;
-  const size_t smem = 1024 + (size_t) 13 * kTile * sizeof(bf16);     // Q, dO x 2, K1, V1, K2 + V2, P x 3, dS x 3
+  const size_t smem = 1024 + (size_t) 14 * kTile * sizeof(bf16);     // Q, dO x 2, K1 x 2, V1, K2 + V2, P x 3, dS x 3
   LLSA_CUDA_OK(cudaFuncSetAttribute(attn_bwd_pooled_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
   attn_bwd_pooled_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, n_tiles, tiles_per_head, nullptr);
   LLSA_LAUNCH_OK("attn_bwd_pooled_tc_kernel");
