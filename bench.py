@@ -37,8 +37,8 @@ METRIC = "llsa_l2 fwd+bwd tokens/sec @N=16384,B*H=48,D=64"
 
 # this library's kernels launched by one llsa_l2 forward + backward (torch's own zero fills are not counted)
 KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_kernel", "refine_topk_kernel", "attn_fwd_fine_kernel", "attn_fwd_pooled_tc_kernel",
-                    "transpose_kernel",
-                    "attn_dq_mma_kernel", "attn_dkv_pooled_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
+                    "transpose_kernel", "attn_bwd_pooled_tc_kernel",
+                    "attn_dq_mma_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
 
 
 def parse():
@@ -219,8 +219,13 @@ def main():
     units = B * H * (N // world if seq_parallel else N) * D      # query rows x channels on this rank
     keys = dict(fine=128, p1=128, p2=N // 256 if N // 256 >= 64 else 0)
     ktot = sum(keys.values())
-    flops = dict(attn_fwd=4 * units * ktot, attn_bwd_dq=6 * units * ktot, attn_bwd_dkv_fine=4 * units * keys["fine"],
-                 attn_bwd_dkv_pooled=4 * units * (keys["p1"] + keys["p2"]))
+    pooled = keys["p1"] + keys["p2"]
+    if N // 256 == 64:      # tcgen05 pooled backward: S, dP, dQ, dPK, dPV of the pooled keys in one kernel; the dQ kernel is fine-only
+        flops = dict(attn_fwd=4 * units * ktot, attn_bwd_dq=6 * units * keys["fine"], attn_bwd_dkv_fine=4 * units * keys["fine"],
+                     attn_bwd_dkv_pooled=10 * units * pooled)
+    else:
+        flops = dict(attn_fwd=4 * units * ktot, attn_bwd_dq=6 * units * ktot, attn_bwd_dkv_fine=4 * units * keys["fine"],
+                     attn_bwd_dkv_pooled=4 * units * pooled)
     peaks = load_peaks()
     top = max((n for n in per if n in flops), key=lambda n: per[n])
     ach = flops[top] / (per[top] * 1e-3) / 1e12

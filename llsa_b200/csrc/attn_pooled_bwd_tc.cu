@@ -158,29 +158,32 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
     if (lane == 0) {
       const uint32_t id_s128 = tc::instr_desc(128, 128, 0, 0), id_s64 = tc::instr_desc(128, 64, 0, 0), id_s192 = tc::instr_desc(128, 192, 0, 0);
       const uint32_t id_dq = tc::instr_desc(128, 64, 0, 1), id_kv = tc::instr_desc(128, 64, 1, 1), id_kv2 = tc::instr_desc(128, 128, 1, 1);
-      const uint32_t pa = tc::smem_u32(sP), dsa2 = pa + 3 * kTile * 2, dsa0 = dsa2 + kTile * 2;
-      // Descriptors are built once; a k-step only adds its byte offset >> 4 to the address field (addresses stay
-      // below 2^18, so the 14-bit field never carries).  K-major operand: 32 bytes per k-step of 16 channels inside
-      // the swizzled 128-byte row; MN-major operand: 16 rows = 2048 bytes per k-step.
-      const uint64_t dK2_k = tc::smem_desc(tc::smem_u32(sK2), 16, 1024), dK2_m = tc::smem_desc(tc::smem_u32(sK2), 1024, 1024);
-      const uint64_t dV_k = tc::smem_desc(tc::smem_u32(sV1), 16, 1024);                                        // [V1;V2] as N = 192 rows
-      const uint64_t dDS_k[3] = {tc::smem_desc(dsa0, 16, 1024), tc::smem_desc(dsa0 + kTile * 2, 16, 1024), tc::smem_desc(dsa2, 16, 1024)};
-      const uint64_t dP1_m = tc::smem_desc(pa, kTile * 2, 1024), dDS1_m = tc::smem_desc(dsa0, kTile * 2, 1024);   // M = 128 keys over two tiles
-      const uint64_t dP2_m = tc::smem_desc(pa + 2 * kTile * 2, kTile * 2, 1024);                                  // [P2 | dS2]
-      const uint64_t dQ_k0 = tc::smem_desc(tc::smem_u32(sQ), 16, 1024), dDO_k0 = tc::smem_desc(tc::smem_u32(sDO), 16, 1024);
-      const uint64_t dQ_m0 = tc::smem_desc(tc::smem_u32(sQ), 1024, 1024), dDO_m0 = tc::smem_desc(tc::smem_u32(sDO), 1024, 1024);
-      const uint64_t dQDO_m0 = tc::smem_desc(tc::smem_u32(sQ), 2 * kTile * 2, 1024);           // N = 128: channels of Q, then of dO (32 KB further)
-      const uint64_t dK1_k0 = tc::smem_desc(tc::smem_u32(sK1), 16, 1024), dK1_m0 = tc::smem_desc(tc::smem_u32(sK1), 1024, 1024);
-      constexpr uint64_t kStage = (uint64_t) (kTile * 2) >> 4;      // one 16 KB buffer further, in descriptor address units
+      // Shared-memory descriptors as (low word, high word).  The high word (stride between 8-row groups = 1024 bytes,
+      // descriptor version, 128-byte swizzle) is the same for every operand here; the low word holds the address
+      // (>> 4, 14 bits: addresses stay below 2^18) and the leading-dimension byte offset, so a k-step is one 32-bit add:
+      // K-major operand: 32 bytes (2 units) per k-step of 16 channels inside the swizzled 128-byte row;
+      // MN-major operand: 16 rows = 2048 bytes (128 units) per k-step.
+      const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
+      auto lo = [](const void* p, uint32_t lbo_bytes) { return ((tc::smem_u32(p) >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16); };
+      constexpr uint32_t kStage = (uint32_t) (kTile * 2) >> 4;      // one 16 KB buffer further
+      constexpr uint32_t kT = kTile * 2;                             // bytes of a tile
+      const uint32_t lK2_k = lo(sK2, 16), lK2_m = lo(sK2, 1024), lV_k = lo(sV1, 16);                // [V1;V2] as N = 192 rows
+      const uint32_t lDS_k0 = lo(sP + 4 * kTile, 16), lDS_k1 = lo(sP + 5 * kTile, 16), lDS_k2 = lo(sP + 3 * kTile, 16);
+      const uint32_t lP1_m = lo(sP, kT), lDS1_m = lo(sP + 4 * kTile, kT), lP2_m = lo(sP + 2 * kTile, kT);   // M = 128 over two tiles
+      const uint32_t lQ_k0 = lo(sQ, 16), lDO_k0 = lo(sDO, 16), lQ_m0 = lo(sQ, 1024), lDO_m0 = lo(sDO, 1024);
+      const uint32_t lQDO_m0 = lo(sQ, 2 * kT);                       // N = 128: channels of Q, then of dO (32 KB further)
+      const uint32_t lK1_k0 = lo(sK1, 16), lK1_m0 = lo(sK1, 1024);
       auto issue_s = [&](int i) -> bool {          // S(i) = Q . [PK1 ; PK2]^T into columns [0,192)
         const int s = i & 1;
         if (!bw_wait(&bars.full[s], (i >> 1) & 1, abort_flag)) return false;
         tc::fence_after_sync();
-        const uint64_t q_ = dQ_k0 + s * kStage, k1_ = dK1_k0 + (((t_begin + i) >> 1) & 1) * kStage;
+        const uint32_t q_ = lQ_k0 + s * kStage, k1_ = lK1_k0 + (((t_begin + i) >> 1) & 1) * kStage;
+        tc::umma_ss_lh<0>(tmem, q_, hi, k1_, hi, id_s128);
+        tc::umma_ss_lh<0>(tmem + 128, q_, hi, lK2_k, hi, id_s64);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          tc::umma_ss(tmem, q_ + 2 * ks, k1_ + 2 * ks, id_s128, ks > 0);
-          tc::umma_ss(tmem + 128, q_ + 2 * ks, dK2_k + 2 * ks, id_s64, ks > 0);
+        for (int ks = 1; ks < 4; ++ks) {
+          tc::umma_ss_lh<1>(tmem, q_ + 2 * ks, hi, k1_ + 2 * ks, hi, id_s128);
+          tc::umma_ss_lh<1>(tmem + 128, q_ + 2 * ks, hi, lK2_k + 2 * ks, hi, id_s64);
         }
         tc::umma_commit(&bars.s_ready);
         return true;
@@ -193,9 +196,10 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         if (!bw_wait(&bars.s_consumed, i & 1, abort_flag)) break;
         tc::fence_after_sync();
         {
-          const uint64_t d_ = dDO_k0 + s * kStage;
+          const uint32_t d_ = lDO_k0 + s * kStage;
+          tc::umma_ss_lh<0>(tmem, d_, hi, lV_k, hi, id_s192);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) tc::umma_ss(tmem, d_ + 2 * ks, dV_k + 2 * ks, id_s192, ks > 0);
+          for (int ks = 1; ks < 4; ++ks) tc::umma_ss_lh<1>(tmem, d_ + 2 * ks, hi, lV_k + 2 * ks, hi, id_s192);
         }
         tc::umma_commit(&bars.dp_ready);
         tc::umma_commit(&bars.v_free[s]);
@@ -210,10 +214,14 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         if (i > 0 && !bw_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) break;
         tc::fence_after_sync();
         {
-          const uint64_t k1_ = dK1_m0 + ((tile >> 1) & 1) * kStage;
+          const uint32_t k1_ = lK1_m0 + ((tile >> 1) & 1) * kStage;
+          tc::umma_ss_lh<0>(tmem + kColDQ, lDS_k0, hi, k1_, hi, id_dq);
 #pragma unroll
-          for (int ks = 0; ks < 12; ++ks)
-            tc::umma_ss(tmem + kColDQ, dDS_k[ks >> 2] + 2 * (ks & 3), ks < 8 ? k1_ + 128 * ks : dK2_m + 128 * (ks - 8), id_dq, ks > 0);
+          for (int ks = 1; ks < 4; ++ks) tc::umma_ss_lh<1>(tmem + kColDQ, lDS_k0 + 2 * ks, hi, k1_ + 128 * ks, hi, id_dq);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) tc::umma_ss_lh<1>(tmem + kColDQ, lDS_k1 + 2 * ks, hi, k1_ + 128 * (4 + ks), hi, id_dq);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) tc::umma_ss_lh<1>(tmem + kColDQ, lDS_k2 + 2 * ks, hi, lK2_m + 128 * ks, hi, id_dq);
         }
         // transposed products, K = 128 query rows in 8 k-steps.  Level-1 results accumulate over the tiles of a
         // parent, level-2 results over the tiles of a head; a fresh start waits for the drain warps to have read
@@ -223,12 +231,15 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         if (!acc1 && parents_done > 0 && !bw_wait(&bars.acc_free, (parents_done - 1) & 1, abort_flag)) break;
         tc::fence_after_sync();
         {
-          const uint64_t do_ = dDO_m0 + s * kStage, q_ = dQ_m0 + s * kStage, qdo_ = dQDO_m0 + s * kStage;
+          const uint32_t do_ = lDO_m0 + s * kStage, q_ = lQ_m0 + s * kStage, qdo_ = lQDO_m0 + s * kStage;
+          tc::umma_ss_lh(tmem + kColPV1, lP1_m, hi, do_, hi, id_kv, acc1);
+          tc::umma_ss_lh(tmem + kColPK1, lDS1_m, hi, q_, hi, id_kv, acc1);
+          tc::umma_ss_lh(tmem + kColYX, lP2_m, hi, qdo_, hi, id_kv2, acc2);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            tc::umma_ss(tmem + kColPV1, dP1_m + 128 * ks, do_ + 128 * ks, id_kv, acc1 | (ks > 0));
-            tc::umma_ss(tmem + kColPK1, dDS1_m + 128 * ks, q_ + 128 * ks, id_kv, acc1 | (ks > 0));
-            tc::umma_ss(tmem + kColYX, dP2_m + 128 * ks, qdo_ + 128 * ks, id_kv2, acc2 | (ks > 0));
+          for (int ks = 1; ks < 8; ++ks) {
+            tc::umma_ss_lh<1>(tmem + kColPV1, lP1_m + 128 * ks, hi, do_ + 128 * ks, hi, id_kv);
+            tc::umma_ss_lh<1>(tmem + kColPK1, lDS1_m + 128 * ks, hi, q_ + 128 * ks, hi, id_kv);
+            tc::umma_ss_lh<1>(tmem + kColYX, lP2_m + 128 * ks, hi, qdo_ + 128 * ks, hi, id_kv2);
           }
         }
         tc::umma_commit(&bars.out_ready);
