@@ -68,6 +68,14 @@ int llsa_mean_pool_bwd(const LlsaTensor* dy, const LlsaTensor* dx, int k, void* 
  * torch_op/flash_sparse_attention_res_1.py:42-44 and ..._res_2.py:49-55. */
 int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2,
                           int block_size, void* stream);
+/* The same pass with the 2-D RoPE apply fused in front (north-star item "fused 2D RoPE apply on Q/K ahead of
+ * pooling"): tensors whose bit is set in rope_mask (bit i = x[i]) are rotated by the [N,C] table `freq` (even
+ * columns sin, odd columns cos; same dtype as x) exactly as llsa_rope_fwd does, the rotated rows are written to
+ * xr[i] (x's shape, any strides) and the pyramid is pooled from the rotated values; the other tensors are pooled
+ * as they are and their xr entry is ignored.  Replaces my_rope_fn on q and k (rope_dit_transformer_2d.py:232-238)
+ * followed by the mean_pool1d launches, saving one read of q and k. */
+int llsa_rope_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr,
+                               const LlsaTensor* y1, const LlsaTensor* y2, int block_size, void* stream);
 
 /* ---- RoPE: src/llsa/kernel/triton/rope.py ---------------------------------
  * Interleaved-pair rotation by a [S,D] table whose even columns are sin and odd

@@ -10,6 +10,8 @@
 // HBM: one CTA owns one level-2 row (bs level-1 rows x bs tokens), each thread
 // a 16-byte channel group of one level-1 row; the bs loads of a thread are
 // independent 128-bit loads, the level-2 row is reduced through shared memory.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace llsa {
@@ -50,10 +52,28 @@ struct PyramidArgs {
   int H, C;
   int64_t n1;  // level-1 rows per (b,h)
   int bs;
+  // fused RoPE (ROPE kernels only): tensors whose bit is set in rope_mask are rotated by the [N, C] table `freq` of
+  // element type T (even columns sin, odd columns cos) before pooling, and the rotated rows are written to xr
+  const T* freq;
+  int64_t fs;      // table row stride in elements
+  View<T> xr[3];
+  int rope_mask;
 };
 
+// Interleaved-pair rotation of VEC channels of one token, every product and sum rounded to T separately
+// (rope.py:37-47 evaluated as an element-wise tensor program; the same arithmetic as rope_kernel in rope.cu).
+template <typename T, int VEC>
+__device__ __forceinline__ void rope_rotate(float (&v)[VEC], const float (&f)[VEC]) {
+#pragma unroll
+  for (int j = 0; j < VEC; j += 2) {
+    const float sn = f[j], cs = f[j + 1], xe = v[j], xo = v[j + 1];
+    v[j] = round_to<T>(__fsub_rn(round_to<T>(__fmul_rn(cs, xe)), round_to<T>(__fmul_rn(sn, xo))));
+    v[j + 1] = round_to<T>(__fadd_rn(round_to<T>(__fmul_rn(sn, xe)), round_to<T>(__fmul_rn(cs, xo))));
+  }
+}
+
 // blockDim.x = ROWS * (C / VEC); ROWS level-1 rows per CTA (== bs when LEVELS == 2).
-template <typename T, int LEVELS>
+template <typename T, int LEVELS, bool ROPE = false>
 __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t ctas_per_head) {
   constexpr int VEC = Vec16<T>::N;
   extern __shared__ float smem[];  // LEVELS==2: [rows][C] level-1 results as fp32 images of T
@@ -67,6 +87,9 @@ __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t 
   if (row1 < a.n1) {
     const T* xp = a.x[ti].row(b, h, row1 * a.bs) + c;
     const int64_t sn = a.x[ti].sn;
+    const bool rope = ROPE && ((a.rope_mask >> ti) & 1);
+    T* rp = rope ? a.xr[ti].row(b, h, row1 * a.bs) + c : nullptr;
+    const T* fp = rope ? a.freq + row1 * a.bs * a.fs + c : nullptr;
     float acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
@@ -76,6 +99,16 @@ __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t 
       float v[8][VEC];
 #pragma unroll
       for (int u = 0; u < 8; ++u) Vec16<T>::load(xp + (int64_t) (t + u) * sn, v[u]);
+      if (ROPE && rope) {
+        float f[8][VEC];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) Vec16<T>::load(fp + (int64_t) (t + u) * a.fs, f[u]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          rope_rotate<T, VEC>(v[u], f[u]);
+          Vec16<T>::store(rp + (int64_t) (t + u) * a.xr[ti].sn, v[u]);
+        }
+      }
 #pragma unroll
       for (int u = 0; u < 8; ++u)
 #pragma unroll
@@ -84,6 +117,12 @@ __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t 
     for (; t < a.bs; ++t) {
       float v[VEC];
       Vec16<T>::load(xp + (int64_t) t * sn, v);
+      if (ROPE && rope) {
+        float f[VEC];
+        Vec16<T>::load(fp + (int64_t) t * a.fs, f);
+        rope_rotate<T, VEC>(v, f);
+        Vec16<T>::store(rp + (int64_t) t * a.xr[ti].sn, v);
+      }
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[i] = round_to<T>(acc[i] + v[i]);
     }
@@ -209,9 +248,18 @@ extern "C" int llsa_mean_pool_bwd(const LlsaTensor* dy, const LlsaTensor* dx, in
 }
 
 template <typename T>
-static int launch_pyramid(int n, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2, int bs, cudaStream_t st) {
+static int launch_pyramid(int n, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2, int bs, cudaStream_t st,
+                          const LlsaTensor* freq = nullptr, int rope_mask = 0, const LlsaTensor* xr = nullptr) {
   constexpr int VEC = Vec16<T>::N;
   PyramidArgs<T> a;
+  memset(&a, 0, sizeof(a));
+  a.rope_mask = freq ? rope_mask : 0;
+  if (a.rope_mask) {
+    a.freq = (const T*) freq->ptr;
+    a.fs = freq->stride[0];
+    for (int i = 0; i < n; ++i)
+      if ((rope_mask >> i) & 1) a.xr[i] = make_view<T>(&xr[i]);
+  }
   const int64_t B = x[0].shape[0], H = x[0].shape[1], N = x[0].shape[2], C = x[0].shape[3];
   for (int i = 0; i < 3; ++i) {
     const int j = i < n ? i : 0;
@@ -224,19 +272,21 @@ static int launch_pyramid(int n, const LlsaTensor* x, const LlsaTensor* y1, cons
   if (y2) {
     const int64_t n2 = a.n1 / bs;
     dim3 grid((unsigned) (B * H * n2), n);
-    pool_pyramid_kernel<T, 2><<<grid, bs * lanes, bs * C * sizeof(float), st>>>(a, bs, n2);
+    if (a.rope_mask) pool_pyramid_kernel<T, 2, true><<<grid, bs * lanes, bs * C * sizeof(float), st>>>(a, bs, n2);
+    else pool_pyramid_kernel<T, 2><<<grid, bs * lanes, bs * C * sizeof(float), st>>>(a, bs, n2);
   } else {
     const int rows = 16;
     const int64_t per_head = (a.n1 + rows - 1) / rows;
     dim3 grid((unsigned) (B * H * per_head), n);
-    pool_pyramid_kernel<T, 1><<<grid, rows * lanes, 0, st>>>(a, rows, per_head);
+    if (a.rope_mask) pool_pyramid_kernel<T, 1, true><<<grid, rows * lanes, 0, st>>>(a, rows, per_head);
+    else pool_pyramid_kernel<T, 1><<<grid, rows * lanes, 0, st>>>(a, rows, per_head);
   }
   LLSA_LAUNCH_OK("pool_pyramid_kernel");
   return LLSA_OK;
 }
 
-extern "C" int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2,
-                                     int block_size, void* stream) {
+static int pyramid_entry(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2, int block_size, void* stream,
+                         const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr) {
   LLSA_REQUIRE(x && y1, LLSA_ERR_NULL, "pool_pyramid: null tensor list");
   LLSA_REQUIRE(n_tensors >= 1 && n_tensors <= 3, LLSA_ERR_ARG, "pool_pyramid: n_tensors must be 1..3");
   const int bs = block_size;
@@ -261,8 +311,33 @@ extern "C" int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const L
       if (rc) return rc;
     }
   }
+  if (freq) {
+    LLSA_REQUIRE(freq->ptr && xr, LLSA_ERR_NULL, "rope_pool_pyramid: null table or output list");
+    LLSA_REQUIRE(freq->ndim == 2 && freq->shape[0] == N && freq->shape[1] == C && freq->stride[1] == 1, LLSA_ERR_SHAPE,
+                 "rope_pool_pyramid: freq must be [N,C] with unit inner stride");
+    LLSA_REQUIRE(freq->dtype == dt, LLSA_ERR_DTYPE, "rope_pool_pyramid: the table must have the dtype of the data");
+    LLSA_REQUIRE(C % 2 == 0 && ((uintptr_t) freq->ptr % 16) == 0 && (freq->stride[0] * (int64_t) dtype_size(dt)) % 16 == 0, LLSA_ERR_STRIDE,
+                 "rope_pool_pyramid: table rows must be 16-byte aligned");
+    LLSA_REQUIRE(rope_mask >= 0 && rope_mask < (1 << n_tensors), LLSA_ERR_ARG, "rope_pool_pyramid: bad rope mask");
+    for (int i = 0; i < n_tensors; ++i) {
+      if (!((rope_mask >> i) & 1)) continue;
+      int rc = check_bhnd(&xr[i], "xr", dt, B, H, N, C);
+      if (rc) return rc;
+    }
+  }
   if (B * H * N * C == 0) return LLSA_OK;
   cudaStream_t st = (cudaStream_t) stream;
-  return dt == LLSA_F32 ? launch_pyramid<float>(n_tensors, x, y1, y2, bs, st)
-                        : launch_pyramid<__nv_bfloat16>(n_tensors, x, y1, y2, bs, st);
+  return dt == LLSA_F32 ? launch_pyramid<float>(n_tensors, x, y1, y2, bs, st, freq, rope_mask, xr)
+                        : launch_pyramid<__nv_bfloat16>(n_tensors, x, y1, y2, bs, st, freq, rope_mask, xr);
+}
+
+extern "C" int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2,
+                                     int block_size, void* stream) {
+  return pyramid_entry(n_tensors, x, y1, y2, block_size, stream, nullptr, 0, nullptr);
+}
+
+extern "C" int llsa_rope_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr,
+                                          const LlsaTensor* y1, const LlsaTensor* y2, int block_size, void* stream) {
+  LLSA_REQUIRE(freq, LLSA_ERR_NULL, "rope_pool_pyramid: null table");
+  return pyramid_entry(n_tensors, x, y1, y2, block_size, stream, freq, rope_mask, xr);
 }

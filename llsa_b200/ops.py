@@ -33,7 +33,7 @@ __all__ = [
     "sparse_indices_attn_res_fwd", "sparse_indices_attn_res_scatter_bwd_v2",
     "sparse_indices_attn_res_2_2_fwd", "sparse_indices_attn_res_scatter_2_2_bwd_v2",
     "flash_sparse_residual_attention_l1_op", "flash_sparse_residual_attention_l2_op",
-    "llsa_l1", "llsa_l2", "pool_pyramid", "set_exact_pooled_grad",
+    "llsa_l1", "llsa_l2", "llsa_l1_rope", "llsa_l2_rope", "pool_pyramid", "rope_pool_pyramid", "set_exact_pooled_grad",
 ]
 
 _FLOAT = (torch.float32, torch.bfloat16)
@@ -181,6 +181,38 @@ def pool_pyramid(xs: List[torch.Tensor], block_size: int, levels: int):
     with torch.cuda.device(xs[0].device):
         _lib.check(_lib.lib().llsa_pool_pyramid_fwd(n, XA, Y1, Y2, bs, _stream(xs[0])), "pool_pyramid_fwd")
     return y1, y2
+
+
+def rope_pool_pyramid(xs: List[torch.Tensor], freq: torch.Tensor, rope: List[bool], block_size: int, levels: int):
+    """RoPE on the flagged tensors and all pyramid levels of every tensor in ONE pass over HBM.
+    Returns (tensors after RoPE (unflagged ones unchanged), level-1 list, level-2 list or None); the
+    rotated tensors and the pooled levels carry the bits of my_rope_fn followed by mean_pool1d.
+    Falls back to the two separate kernels when the table's dtype differs from the data's."""
+    _need_cuda(*xs, freq)
+    _check_float(*xs)
+    if freq.dtype != xs[0].dtype or not any(rope):
+        out = [my_rope_fn(x, freq) if r else x for x, r in zip(xs, rope)]
+        y1, y2 = pool_pyramid(out, block_size, levels)
+        return out, y1, y2
+    xs = [_prep(x) for x in xs]
+    freq = freq if (freq.stride(-1) == 1 and freq.data_ptr() % 16 == 0 and (freq.stride(0) * freq.element_size()) % 16 == 0) else freq.contiguous()
+    B, H, N, D = xs[0].shape
+    assert freq.shape[0] == N and freq.shape[1] == D, "freq must be [N, D]"
+    bs = block_size
+    xr = [torch.empty_like(x) if r else x for x, r in zip(xs, rope)]     # empty_like keeps x's strides (rope.py:109)
+    y1 = [torch.empty((B, H, N // bs, D), device=x.device, dtype=x.dtype) for x in xs]
+    y2 = [torch.empty((B, H, N // bs // bs, D), device=x.device, dtype=x.dtype) for x in xs] if levels == 2 else None
+    n = len(xs)
+    XA = (_lib.LlsaTensor * n)(*[desc(x) for x in xs])
+    XR = (_lib.LlsaTensor * n)(*[desc(x) for x in xr])
+    Y1 = (_lib.LlsaTensor * n)(*[desc(y) for y in y1])
+    Y2 = (_lib.LlsaTensor * n)(*[desc(y) for y in y2]) if y2 is not None else None
+    mask = sum(1 << i for i, r in enumerate(rope) if r)
+    _mark("pool_pyramid")
+    with torch.cuda.device(xs[0].device):
+        f = desc(freq)
+        _lib.check(_lib.lib().llsa_rope_pool_pyramid_fwd(n, XA, ref(f), mask, XR, Y1, Y2, bs, _stream(xs[0])), "rope_pool_pyramid_fwd")
+    return xr, y1, y2
 
 
 # ----------------------------------------------------------------------------- RoPE
@@ -542,6 +574,68 @@ def _l2_backward(ctx, grads):
 
 
 _llsa_l2_fwd.register_autograd(_l2_backward, setup_context=_l2_setup)
+
+
+# ----------------------------------------------------------------------------- RoPE fused in front of the operators
+@torch.library.custom_op("llsa_b200::llsa_rope_fwd", mutates_args=())
+def _llsa_rope_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, freq: torch.Tensor, topk1: int, topk2: int, block_size: int,
+                   levels: int) -> List[torch.Tensor]:
+    (qr, kr, _), l1, l2 = rope_pool_pyramid([q, k, v], freq, [True, True, False], block_size, levels)
+    pq, pk, pv = l1
+    bs = block_size
+    if levels == 2:
+        pq2, pk2, pv2 = l2
+        p_indices = _coarse_topk(pq2, pk2, topk2)
+        indices = _refine_topk(pq, pk, p_indices, topk1, p_indices.shape[-1], bs)
+        o, lse = _attn_fwd(qr, kr, v, pk, pv, pk2, pv2, indices, p_indices, topk1, p_indices.shape[-1], bs, float(bs), float(bs * bs))
+        return [o, lse, qr, kr, indices, pk, pv, p_indices, pk2, pv2]
+    indices = _coarse_topk(pq, pk, topk1)
+    o, lse = _attn_fwd(qr, kr, v, pk, pv, None, None, indices, None, indices.shape[-1], 0, bs, float(bs), 1.0)
+    return [o, lse, qr, kr, indices, pk, pv]
+
+
+@_llsa_rope_fwd.register_fake
+def _(q, k, v, freq, topk1, topk2, block_size, levels):
+    B, H, N, D = q.shape
+    n1 = N // block_size
+    n2 = n1 // block_size
+    out = [torch.empty_like(q), q.new_empty((B, H, N), dtype=torch.float32), torch.empty_like(q), torch.empty_like(k),
+           q.new_empty((B, H, n1, min(topk1, n1) if levels == 1 else topk1), dtype=torch.int32), k.new_empty((B, H, n1, D)), v.new_empty((B, H, n1, D))]
+    if levels == 2:
+        out += [q.new_empty((B, H, n2, min(topk2, n2)), dtype=torch.int32), k.new_empty((B, H, n2, D)), v.new_empty((B, H, n2, D))]
+    return out
+
+
+def _rope_op_setup(ctx, inputs, output):
+    q, k, v, freq, topk1, topk2, block_size, levels = inputs
+    ctx.save_for_backward(v, freq, *output)
+    ctx.block_size, ctx.levels = block_size, levels
+
+
+def _rope_op_backward(ctx, grads):
+    v, freq, o, lse, qr, kr, indices, pk, pv = ctx.saved_tensors[:9]
+    if ctx.levels == 2:
+        p_indices, pk2, pv2 = ctx.saved_tensors[9:]
+        dqr, dkr, dv = _llsa_l2_bwd(grads[0], qr, kr, v, o, lse, indices, p_indices, pk, pv, pk2, pv2, ctx.block_size)
+    else:
+        dqr, dkr, dv = _llsa_l1_bwd(grads[0], qr, kr, v, o, lse, indices, pk, pv, ctx.block_size, _exact_pooled_grad)
+    return _rope_bwd_op(dqr, freq), _rope_bwd_op(dkr, freq), dv, None, None, None, None, None
+
+
+_llsa_rope_fwd.register_autograd(_rope_op_backward, setup_context=_rope_op_setup)
+
+
+def llsa_l1_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, freq: torch.Tensor, topk: int = 8, block_size: int = 16) -> torch.Tensor:
+    """llsa_l1(my_rope_fn(q, freq), my_rope_fn(k, freq), v, topk, block_size) -- what RopeAttnProcessor computes
+    (models/rope_dit_transformer_2d.py:232-241) -- with the rotation fused into the pooling pass."""
+    return _llsa_rope_fwd(q, k, v, freq, topk, 0, block_size, 1)[0]
+
+
+def llsa_l2_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, freq: torch.Tensor, topk1: int = 8, topk2: int = 8,
+                 block_size: int = 16) -> torch.Tensor:
+    """llsa_l2(my_rope_fn(q, freq), my_rope_fn(k, freq), v, topk1, topk2, block_size)
+    (models/rope_dit_transformer_2d.py:232-251) with the rotation fused into the pooling pass."""
+    return _llsa_rope_fwd(q, k, v, freq, topk1, topk2, block_size, 2)[0]
 
 
 def llsa_l1(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk: int = 8, block_size: int = 16) -> torch.Tensor:

@@ -331,6 +331,50 @@ def test_strided_bnhd_inputs_match_contiguous(tc, monkeypatch):
     assert rel_l2(ks.grad, kc.grad) < 1e-3 and rel_l2(vs.grad, vc.grad) < 1e-3   # fp32 atomics: order may differ
 
 
+@pytest.mark.parametrize("dtype,levels", [(torch.bfloat16, 2), (torch.float32, 2), (torch.bfloat16, 1)])
+def test_rope_pool_pyramid_fused_is_bit_exact(dtype, levels):
+    """One pass (RoPE on q, k + every pyramid level) == my_rope_fn followed by the pyramid, bit for bit; v is pooled unrotated."""
+    L = _ops()
+    N = 4096
+    q, k, v, _ = synth.gaussian_qkv(46, 2, 3, N, 64, dtype=dtype)
+    table = synth.rope_table_2d(int(math.isqrt(N)), dtype=dtype).to(DEV)
+    to_view = lambda t: t.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)       # [B,N,H,D] storage, as the model passes
+    xs = [to_view(q), to_view(k), v.to(DEV)]
+    xr, y1, y2 = L.rope_pool_pyramid(xs, table, [True, True, False], 16, levels)
+    want = [L.my_rope_fn(xs[0], table), L.my_rope_fn(xs[1], table), xs[2]]
+    w1, w2 = L.pool_pyramid(want, 16, levels)
+    assert xr[0].stride() == xs[0].stride() and xr[2] is xs[2]
+    for a, b in zip(xr[:2], want[:2]):
+        assert torch.equal(a, b)
+    for a, b in zip(y1, w1):
+        assert torch.equal(a, b)
+    if levels == 2:
+        for a, b in zip(y2, w2):
+            assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("levels", [1, 2])
+def test_llsa_rope_operators_match_rope_then_llsa(levels):
+    """llsa_l{1,2}_rope(q, k, v, table) == llsa_l{1,2}(my_rope_fn(q), my_rope_fn(k), v): output and q, k gradients bit for bit."""
+    L = _ops()
+    N = 16384 if levels == 2 else 4096
+    q, k, v, do = _bf16_case("l%d" % levels, 1, 2, N, 47)
+    table = synth.rope_table_2d(int(math.isqrt(N)), dtype=torch.bfloat16).to(DEV)
+    a = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    b = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    if levels == 2:
+        o1 = L.llsa_l2_rope(a[0], a[1], a[2], table, 8, 8, 16)
+        o2 = L.llsa_l2(L.my_rope_fn(b[0], table), L.my_rope_fn(b[1], table), b[2], 8, 8, 16)
+    else:
+        o1 = L.llsa_l1_rope(a[0], a[1], a[2], table, 8, 16)
+        o2 = L.llsa_l1(L.my_rope_fn(b[0], table), L.my_rope_fn(b[1], table), b[2], 8, 16)
+    assert torch.equal(o1, o2)
+    o1.backward(do.to(DEV))
+    o2.backward(do.to(DEV))
+    assert torch.equal(a[0].grad, b[0].grad)
+    assert rel_l2(a[1].grad, b[1].grad) < 1e-3 and rel_l2(a[2].grad, b[2].grad) < 1e-3     # fp32 reductions: order may differ
+
+
 def test_host_pipeline_matches_direct_call():
     """Pinned host operands through the three-stream chunk pipeline give the bits of one direct call."""
     L = _ops()
