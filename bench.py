@@ -234,6 +234,16 @@ def main():
                 peak_source=peaks["src"] + " (sustained bf16 GEMM)", ms_per_launch=per[top],
                 algorithmic_flops_per_launch=flops[top])
     total_flops = 14 * units * ktot
+    # memory-bound stages: algorithmic bytes per launch (this rank) against the measured copy bandwidth
+    T = units * 2                                             # one [B,H,N,D] bf16 tensor
+    nq1, n2k = B * H * (N // world if seq_parallel else N) // 16, N // 256
+    alg_bytes = dict(pool_pyramid=3 * T + 3 * T * (1 / 16 + 1 / 256),
+                     coarse_topk=2 * B * H * n2k * D * 2 + B * H * n2k * 8 * 4,
+                     refine_topk=nq1 * D * 2 + (nq1 // 16) * 128 * D * 2 + nq1 * 8 * 4,
+                     transpose_indices=nq1 * 8 * 4 * 2 + B * H * (N // 16 + 1) * 4)
+    memory_bound = {kname: dict(bytes=int(alg_bytes[kname]), gbs=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9,
+                                frac_of_hbm_peak=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9 / peaks["hbm_gbs"])
+                    for kname in alg_bytes if kname in per}
 
     out = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                ms_per_step=ms_step, higher_is_better=True, scaling="strong" if seq_parallel else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
@@ -245,6 +255,7 @@ def main():
                effective_tflops=total_flops * world / (ms_step * 1e-3) / 1e12,
                effective_tflops_frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / peak,
                kernel_ms={kname: round(tms, 4) for kname, tms in sorted(per.items())},
+               memory_bound_stages=memory_bound, hbm_peak_gbs=peaks["hbm_gbs"],
                roofline=roof, gpu_launches=len(KERNELS_PER_STEP) * args.steps, clocks=clocks)
 
     # ---- end to end: pinned host buffers -> device -> fwd+bwd -> o, dq, dk, dv back to the host
