@@ -138,6 +138,16 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
 // queries are a shard of the sequence); p_idx [B*H, M/bs, p_topk] with values in [0, Mk/bs); out [B*H, M, topk].
 // MMA = true (bf16, D = 64, bs = 16): the 16 x C score tile comes from mma.sync with fp32
 // accumulation of the exact bf16 products, as the reference's tl.dot does.
+constexpr int kRefineSlots = 8;        // register path of the refine selection: up to 256 candidates per row
+
+// Order-preserving map of a float onto uint32 (larger float <=> larger integer, -0 and +0 share one image so
+// that they tie like the float comparison does).
+__device__ __forceinline__ uint32_t orderable(float v) {
+  uint32_t u = __float_as_uint(v);
+  if (u == 0x80000000u) u = 0u;
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 template <typename T, bool MMA>
 __global__ void __launch_bounds__(128)
 refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
@@ -211,6 +221,37 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  if (C <= 32 * kRefineSlots) {
+    // A lane keeps its candidates (j = lane, lane + 32, ...) in registers as order-preserving 32-bit images of the
+    // scores; a round is two warp reductions: the largest score, then the smallest block index among its holders.
+    for (int r = warp; r < bs; r += nwarps) {
+      const float* s = sc + r * C;
+      uint32_t key[kRefineSlots], blk[kRefineSlots];
+#pragma unroll
+      for (int u = 0; u < kRefineSlots; ++u) {
+        const int j = lane + 32 * u;
+        key[u] = j < C ? orderable(s[j]) : 0u;            // 0 is below every real score's image (NaN images included)
+        blk[u] = j < C ? (uint32_t) cand[j] : 0xFFFFFFFFu;
+      }
+      for (int t = 0; t < topk; ++t) {
+        uint32_t bk = key[0], bb = blk[0];
+#pragma unroll
+        for (int u = 1; u < kRefineSlots; ++u)
+          if (key[u] > bk || (key[u] == bk && blk[u] < bb)) { bk = key[u]; bb = blk[u]; }
+        const uint32_t mk = __reduce_max_sync(0xffffffffu, bk);
+        const uint32_t mb = __reduce_min_sync(0xffffffffu, bk == mk ? bb : 0xFFFFFFFFu);
+#pragma unroll
+        for (int u = 0; u < kRefineSlots; ++u)
+          if (key[u] == mk && blk[u] == mb) { key[u] = 0u; blk[u] = 0xFFFFFFFFu; }      // candidates are distinct blocks: one owner
+        if (lane == 0) {
+          const int64_t o = (bh * M + P * bs + r) * topk + t;
+          if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = (int64_t) mb;
+          else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) mb;
+        }
+      }
+    }
+    return;
+  }
   for (int r = warp; r < bs; r += nwarps) {
     float* s = sc + r * C;
     for (int t = 0; t < topk; ++t) {
