@@ -1,7 +1,8 @@
 """Forward + backward of llsa_l1 / llsa_l2 for operands that live in pinned HOST memory.
 
 Every batch element is independent (sparse_attention_res_2.py:179: all grids are (..., B*H)),
-so the batch is cut into chunks and three streams run a software pipeline over them:
+so the (batch, head) slices are cut into chunks (whole batch elements, or groups of heads of one batch
+element) and three streams run a software pipeline over them:
 
     copy-in stream : q, k, v, d_o of chunk c+1   host -> device
     compute stream : the operator and its backward on chunk c
@@ -15,15 +16,24 @@ import torch
 
 
 class HostPipeline:
-    def __init__(self, call, shape, dtype, device, chunk_batch=1, depth=3):
-        """call(q, k, v) -> o on device tensors; shape = (B, H, N, D) of the full host operands."""
+    def __init__(self, call, shape, dtype, device, chunk_batch=1, chunk_heads=None, depth=3):
+        """call(q, k, v) -> o on device tensors; shape = (B, H, N, D) of the full host operands.
+        A chunk is `chunk_batch` batch elements, or, with chunk_heads (and chunk_batch = 1), `chunk_heads` heads
+        of one batch element: smaller chunks shorten the unoverlapped first copy-in and last copy-out."""
         B, H, N, D = shape
         if B % chunk_batch:
             raise ValueError("chunk_batch must divide the batch")
-        self.call, self.B, self.cb, self.depth = call, B, chunk_batch, depth
+        if chunk_heads is not None and (chunk_batch != 1 or H % chunk_heads):
+            raise ValueError("chunk_heads needs chunk_batch = 1 and must divide the head count")
+        self.call, self.B, self.H, self.cb, self.ch, self.depth = call, B, H, chunk_batch, chunk_heads or H, depth
         self.dev = device
         self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
-        self.slots = [[torch.empty((chunk_batch, H, N, D), dtype=dtype, device=device) for _ in range(4)] for _ in range(depth)]
+        self.slots = [[torch.empty((chunk_batch, self.ch, N, D), dtype=dtype, device=device) for _ in range(4)] for _ in range(depth)]
+
+    def _chunks(self):
+        for b0 in range(0, self.B, self.cb):
+            for h0 in range(0, self.H, self.ch):
+                yield (slice(b0, b0 + self.cb), slice(h0, h0 + self.ch))
 
     def fwd_bwd(self, hq, hk, hv, hdo, ho, hdq, hdk, hdv):
         """Pinned host tensors in, pinned host tensors out.  The work is ordered after what the current
@@ -32,13 +42,14 @@ class HostPipeline:
         cur = torch.cuda.current_stream(self.dev)
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_stream(cur)
-        n_chunks = self.B // self.cb
+        chunks = list(self._chunks())
+        n_chunks = len(chunks)
         ev_in = [torch.cuda.Event() for _ in range(n_chunks)]
         ev_comp = [torch.cuda.Event() for _ in range(n_chunks)]
         ev_free = [None] * self.depth          # slot's device inputs no longer needed (its backward has run)
         keep = []
         for c in range(n_chunks):
-            sl = slice(c * self.cb, (c + 1) * self.cb)
+            sl = chunks[c]
             slot = self.slots[c % self.depth]
             with torch.cuda.stream(self.s_in):
                 if ev_free[c % self.depth] is not None:
