@@ -108,7 +108,7 @@ __device__ __forceinline__ void stage_pooled_tiles_bwd(const AttnP<bf16>& a, int
 }
 
 template <int NW>
-__global__ void __launch_bounds__(NW * 32, 3) attn_dq_mma_kernel(AttnP<bf16> a, int n_smem_tiles) {
+__global__ void __launch_bounds__(NW * 32, 4) attn_dq_mma_kernel(AttnP<bf16> a, int n_smem_tiles) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sk = reinterpret_cast<bf16*>(smem_raw);
   bf16* sv = sk + n_smem_tiles * kBS * kSmemPitch;
