@@ -45,6 +45,15 @@ _exact_pooled_grad = os.environ.get("LLSA_B200_EXACT_POOLED_GRAD", "0") == "1"
 
 
 _stage_hook = None
+_overlap_transpose = os.environ.get("LLSA_B200_OVERLAP_TRANSPOSE", "1") != "0"
+_side_streams = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device)
+    return _side_streams[key]
 
 
 def set_stage_hook(fn) -> None:
@@ -372,7 +381,16 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
         pk2, pv2, p_indices = pk2.contiguous(), pv2.contiguous(), p_indices.contiguous()
     indices = indices.contiguous()
     lse = lse.contiguous()
-    offsets, flat = transpose_indices(indices, k_ntx=k.shape[2] // block_size, offsets_dtype=torch.int32)   # buckets = KEY blocks
+    # The index transpose (one CTA per (b,h): a latency-bound kernel that leaves most SMs idle) is needed only by the fine
+    # dK/dV stage, so it runs on a side stream next to the dQ and pooled stages.
+    cur = torch.cuda.current_stream(q.device)
+    side = _side_stream(q.device) if _overlap_transpose else None
+    if side is not None:
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            offsets, flat = transpose_indices(indices, k_ntx=k.shape[2] // block_size, offsets_dtype=torch.int32)   # buckets = KEY blocks
+    else:
+        offsets, flat = transpose_indices(indices, k_ntx=k.shape[2] // block_size, offsets_dtype=torch.int32)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
     f32 = dict(device=q.device, dtype=torch.float32)
@@ -391,10 +409,14 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
     a.fold_pool_bwd = 1 if fold else 0
     a.kv_weight, a.kv_weight_2 = float(kvw1), float(kvw2)
     with torch.cuda.device(q.device):
-        if _stage_hook is None:
+        if _stage_hook is None and side is None:
             _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), "attn_bwd")
         else:
             for mask, name in ((1, "attn_bwd_dq"), (2, "attn_bwd_dkv_pooled"), (4, "attn_bwd_dkv_fine")):
+                if mask == 4 and side is not None:
+                    cur.wait_stream(side)                 # the CSR is ready; its memory now also belongs to this stream
+                    offsets.record_stream(cur)
+                    flat.record_stream(cur)
                 _mark(name)
                 a.stage_mask = mask
                 _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), name)
