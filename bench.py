@@ -217,7 +217,7 @@ def main():
     for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
         if name != "end":
             per[name] = per.get(name, 0.0) + ev.elapsed_time(nxt)
-    per = {kname: tms / args.steps for kname, tms in per.items()}
+    per = {kname: max(tms, 0.0) / args.steps for kname, tms in per.items()}    # a stage moved to a side stream shows ~0 here
     units = B * H * (N // world if seq_parallel else N) * D      # query rows x channels on this rank
     keys = dict(fine=128, p1=128, p2=N // 256 if N // 256 >= 64 else 0)
     ktot = sum(keys.values())
@@ -251,6 +251,7 @@ def main():
                ms_per_step=ms_step, higher_is_better=True, scaling="strong" if seq_parallel else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
                config=dict(workload="%s: %s fwd+bwd bf16 B=%d H=%d N=%d D=%d block=16 topk=8/8 per GPU" % (args.config, cfg["op"], B, H, N, D),
                            inputs="N(0,1) + 0.5*low-frequency 2-D field, Morton order, seed %d+100*rank" % cfg["seed"],
+                           overlap="index transpose on a side stream next to the dQ / pooled backward stages (its kernel_ms entry is ~0)",
                            l2_policy="inputs (4 x %.0f MB per step) exceed the 126 MB L2" % (units * 2 / 1e6),
                            parallelism=("%d rank(s), sequence sharded: all-gather of k, v and pooled levels, reduce-scatter of dk, dv" % world)
                            if seq_parallel else "%d independent rank(s), sharded by (batch, head), no collective" % world),
