@@ -41,6 +41,13 @@ KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_kernel", "refine_topk_ke
                     "attn_dq_mma_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
 
 
+# DRAM read + write bytes of one launch on 12 (b,h) slices of the config-3 shape, from the ncu capture summarised in
+# profiles/attention_kernels_llsa_l2_batch2.md (dram__bytes_read.sum + dram__bytes_write.sum); traffic grows in
+# proportion to the slices (every slice is independent), so a full launch is scaled by B*H / 12.
+NCU_DRAM_BYTES_12_SLICES = dict(attn_fwd=(49.5 + 3.7 + 54.0 + 0.3) * 1e6, attn_bwd_dq=(100.6 + 11.1) * 1e6,
+                                attn_bwd_dkv_pooled=(85.6 + 6.4) * 1e6, attn_bwd_dkv_fine=(79.3 + 12.9 + 15.7 + 0.06) * 1e6)
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -232,7 +239,9 @@ def main():
     top = max((n for n in per if n in flops), key=lambda n: per[n])
     ach = flops[top] / (per[top] * 1e-3) / 1e12
     peak = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
-    roof = dict(kernel=top, bound="tensor", achieved=ach, peak=peak, unit="TFLOP/s", frac=ach / peak, traffic=None,
+    traffic = NCU_DRAM_BYTES_12_SLICES[top] * (B * H / 12.0) if (args.config == "cfg3" and not seq_parallel) else None
+    roof = dict(kernel=top, bound="tensor", achieved=ach, peak=peak, unit="TFLOP/s", frac=ach / peak, traffic=traffic,
+                traffic_source="ncu dram bytes of a 12-slice capture scaled to this launch (profiles/attention_kernels_llsa_l2_batch2.md)",
                 peak_source=peaks["src"] + " (sustained bf16 GEMM)", ms_per_launch=per[top],
                 algorithmic_flops_per_launch=flops[top])
     total_flops = 14 * units * ktot
