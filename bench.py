@@ -254,7 +254,7 @@ def main():
                      transpose_indices=nq1 * 8 * 4 * 2 + B * H * (N // 16 + 1) * 4)
     memory_bound = {kname: dict(bytes=int(alg_bytes[kname]), gbs=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9,
                                 frac_of_hbm_peak=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9 / peaks["hbm_gbs"])
-                    for kname in alg_bytes if kname in per}
+                    for kname in alg_bytes if per.get(kname, 0.0) > 1e-4}
 
     out = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                ms_per_step=ms_step, higher_is_better=True, scaling="strong" if seq_parallel else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
