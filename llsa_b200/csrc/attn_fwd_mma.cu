@@ -251,13 +251,14 @@ int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   constexpr int NW = 8;
   const int64_t BH = g->q->shape[0] * a.H;
   const char* tc_env = getenv("LLSA_B200_TC");      // "0" keeps the pooled stages on mma.sync (cross-check)
-  if (pooled_tc_keys(a) && !(tc_env && tc_env[0] == '0')) {
+  const bool loop_tc = pooled_loop_tc_keys(a) > 0;
+  if ((pooled_tc_keys(a) || loop_tc) && !(tc_env && tc_env[0] == '0')) {
     // fine blocks on mma.sync (o and lse of the fine part alone), pooled keys on tcgen05, merged there
     const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
     attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
     LLSA_LAUNCH_OK("attn_fwd_fine_kernel");
-    return launch_attn_fwd_pooled_tc(g, a, BH, st);
+    return loop_tc ? launch_attn_fwd_pooled_loop_tc(g, a, BH, st) : launch_attn_fwd_pooled_tc(g, a, BH, st);
   }
   const int n_smem = pooled_smem_tiles(a.p1_blocks + a.p2_blocks);
   const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;

@@ -1,0 +1,374 @@
+// Pooled stages of the LLSA forward on tcgen05 for LONG pooled key lists: a key loop over 128-key chunks.
+//
+// attn_pooled_tc.cu keeps all pooled keys of a tile in tensor memory at once and therefore stops at 192 keys.
+// Here a tile of 128 query rows walks its pooled keys chunk by chunk:
+//   one level  (sparse_attention_res_1.py:85-106): ALL N/16 level-1 pooled keys, weight token_weight;
+//   two levels (sparse_attention_res_2.py:94-149): chunk 0 = the 128 level-1 children of the parent's selected
+//              level-2 blocks (gathered, weight token_weight), then ALL N/256 level-2 keys (weight token_weight_2).
+// Two passes over the chunks make the softmax exact without rescaling an accumulator that lives in TMEM:
+//   pass 1: S = Q.K_c^T per chunk, row maxima only;
+//   pass 2: S again, P = exp2(S*scale*log2e + log2 w - max) written back into TMEM over S (packed bf16) and used as
+//           the A operand of O += P.V_c; row sums on the side.
+// Roles (one persistent CTA per SM, 10 warps):
+//   warp 8, one lane : TMA producer: Q per tile (2 stages), K chunks (ring of 3; every chunk is loaded in both
+//                      passes), V chunks (ring of 2, pass 2 only)
+//   warp 9, one lane : tcgen05.mma issuer.  "Jobs" j = 0 .. 2*chunks-1 per tile alternate between two S buffers
+//                      (TMEM columns [0,128) and [128,256)); O lives in [256,320).  tcgen05.mma executes in issue
+//                      order, so S of job j+2 is issued right behind P.V of job j into the same buffer.
+//   warps 0-3 / 4-7  : two softmax warpgroups, group w owns the jobs j = w (mod 2); thread r owns query row r
+//                      (TMEM lane r).  Row maxima and row sums of the two groups meet in shared memory (an
+//                      mbarrier with one arrival per softmax warp, so that this wait is bounded too).  Epilogue: group w merges O columns [32w, 32w+32)
+//                      with the fine part (o, lse written by the fine kernel) and stores them.
+// Every mbarrier wait is bounded; a wait that expires raises a CTA-wide abort flag, every role leaves its loops,
+// lse of the unfinished rows is poisoned with NaN and TMEM is freed.
+#include <string.h>
+
+#include "attn.cuh"
+#include "mma_frag.cuh"
+#include "tc05.cuh"
+#include "tma.cuh"
+
+namespace llsa {
+
+namespace {
+
+constexpr int kRows = 128;
+constexpr int kChunk = 128;                 // keys per chunk
+constexpr int kTile = kRows * 64;           // elements of a [128 x 64] bf16 tile (16 KB)
+constexpr int kKStages = 3, kVStages = 2;
+constexpr int kThreads = 320;
+constexpr float kLog2eF = 1.4426950408889634f;
+constexpr uint32_t kColO = 256;
+
+struct LoopMaps {
+  CUtensorMap q;              // [B,H,Nq,64] 4-D, box 128 rows
+  CUtensorMap kg, vg;         // gathered level-1 keys / values (two levels): [BH*n1, 64], box 16 rows
+  CUtensorMap kc, vc;         // contiguous pooled keys / values: [BH*n, 64], box 128 rows
+};
+
+struct LoopBars {
+  uint64_t q_full[2], q_empty[2], k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
+  uint64_t s_ready[2], wg_done[2], o_ready, o_free, xchg;
+};
+
+__device__ __forceinline__ bool lp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (int i = 0; i < 400000; ++i) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// n_chunks: chunks per tile; gathered: chunk 0 is the gathered level-1 set (two levels); n_c: rows per head of the
+// contiguous pooled tensor.
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps maps, int n_chunks, int gathered, int64_t n_c, int n_tiles,
+                               int tiles_per_head) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ LoopBars bars;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ float s_part[2][2][kRows];     // [exchange parity][group][row]: row maxima, then row sums
+  bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  bf16* sQ = base;                          // [2][128][64]
+  bf16* sK = sQ + 2 * kTile;                // [kKStages][128][64]
+  bf16* sV = sK + kKStages * kTile;         // [kVStages][128][64]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* abort_flag = &s_abort;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&bars.q_full[i], 1);
+      tc::mbar_init(&bars.q_empty[i], 1);
+      tc::mbar_init(&bars.s_ready[i], 1);
+      tc::mbar_init(&bars.wg_done[i], 4);         // one arrival per warp of the group
+    }
+    for (int i = 0; i < kKStages; ++i) { tc::mbar_init(&bars.k_full[i], 1); tc::mbar_init(&bars.k_empty[i], 1); }
+    for (int i = 0; i < kVStages; ++i) { tc::mbar_init(&bars.v_full[i], 1); tc::mbar_init(&bars.v_empty[i], 1); }
+    tc::mbar_init(&bars.o_ready, 1);
+    tc::mbar_init(&bars.o_free, 8);
+    tc::mbar_init(&bars.xchg, 8);
+    tc::fence_mbar_init();
+  }
+  if (warp == 0) tc::tmem_alloc(&s_tmem, 512);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+  const int n_my = (n_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x;
+  const int jobs = 2 * n_chunks;            // per tile; even, so a job's buffer is its parity in every tile
+
+  if (warp == 8) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int kjob = 0, vjob = 0;
+      for (int i = 0; i < n_my; ++i) {
+        const int tile = blockIdx.x + i * gridDim.x, qs = i & 1;
+        const int bh = tile / tiles_per_head, row0 = (tile % tiles_per_head) * kRows;
+        if (!lp_wait(&bars.q_empty[qs], ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        tma::expect_tx(&bars.q_full[qs], kTile * 2);
+        tma::load_4d(sQ + qs * kTile, &maps.q, &bars.q_full[qs], 0, row0, bh % a.H, bh / a.H);
+        int krow[8];
+        if (gathered) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) krow[j] = (int) ((int64_t) bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS);
+        }
+        bool ok = true;
+        for (int j = 0; ok && j < jobs; ++j) {
+          const int c = j % n_chunks, pass = j / n_chunks;
+          const int crow = (int) ((int64_t) bh * n_c + (int64_t) (c - gathered) * kChunk);      // contiguous chunk
+          const int ks = kjob % kKStages;
+          if (!(ok = lp_wait(&bars.k_empty[ks], ((kjob / kKStages) & 1) ^ 1, abort_flag))) break;
+          tma::expect_tx(&bars.k_full[ks], kTile * 2);
+          if (gathered && c == 0) {
+#pragma unroll
+            for (int b8 = 0; b8 < 8; ++b8) tma::load_2d(sK + ks * kTile + b8 * kBS * 64, &maps.kg, &bars.k_full[ks], 0, krow[b8]);
+          } else {
+            tma::load_2d(sK + ks * kTile, &maps.kc, &bars.k_full[ks], 0, crow);
+          }
+          ++kjob;
+          if (pass == 1) {
+            const int vs = vjob % kVStages;
+            if (!(ok = lp_wait(&bars.v_empty[vs], ((vjob / kVStages) & 1) ^ 1, abort_flag))) break;
+            tma::expect_tx(&bars.v_full[vs], kTile * 2);
+            if (gathered && c == 0) {
+#pragma unroll
+              for (int b8 = 0; b8 < 8; ++b8) tma::load_2d(sV + vs * kTile + b8 * kBS * 64, &maps.vg, &bars.v_full[vs], 0, krow[b8]);
+            } else {
+              tma::load_2d(sV + vs * kTile, &maps.vc, &bars.v_full[vs], 0, crow);
+            }
+            ++vjob;
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t id_s = tc::instr_desc(kRows, kChunk, 0, 0), id_o = tc::instr_desc(kRows, 64, 0, 1);
+      const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
+      auto lo = [](const void* p, uint32_t lbo_bytes) { return ((tc::smem_u32(p) >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16); };
+      constexpr uint32_t kStage = (uint32_t) (kTile * 2) >> 4;
+      const uint32_t lQ = lo(sQ, 16), lK = lo(sK, 16), lV = lo(sV, 1024);
+      int kjob = 0, vjob = 0;
+      int64_t J = 0;                                   // jobs issued so far by this CTA (buffer b has seen J/2 of them)
+      bool ok = true;
+      for (int i = 0; ok && i < n_my; ++i) {
+        const int qs = i & 1;
+        if (!(ok = lp_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
+        tc::fence_after_sync();
+        auto issue_s = [&](int j) -> bool {             // S of job j into buffer j & 1
+          const int ks = kjob % kKStages;
+          if (!lp_wait(&bars.k_full[ks], (kjob / kKStages) & 1, abort_flag)) return false;
+          tc::fence_after_sync();
+          const uint32_t q_ = lQ + qs * kStage, k_ = lK + ks * kStage, d = tmem + (j & 1) * kChunk;
+          tc::umma_ss_lh<0>(d, q_, hi, k_, hi, id_s);
+#pragma unroll
+          for (int s4 = 1; s4 < 4; ++s4) tc::umma_ss_lh<1>(d, q_ + 2 * s4, hi, k_ + 2 * s4, hi, id_s);
+          tc::umma_commit(&bars.s_ready[j & 1]);
+          tc::umma_commit(&bars.k_empty[ks]);
+          ++kjob;
+          return true;
+        };
+        auto issue_pv = [&](int j) -> bool {            // O (+)= P(job j, TMEM) . V chunk
+          const int vs = vjob % kVStages, c = j - n_chunks;
+          if (!lp_wait(&bars.v_full[vs], (vjob / kVStages) & 1, abort_flag)) return false;
+          if (c == 0 && i > 0 && !lp_wait(&bars.o_free, (i - 1) & 1, abort_flag)) return false;      // previous tile's O has been read
+          tc::fence_after_sync();
+          const uint64_t vdesc = ((uint64_t) hi << 32) | (uint64_t) (lV + vs * kStage);
+#pragma unroll
+          for (int s8 = 0; s8 < 8; ++s8)       // P: 16 keys = 8 packed columns per k-step; V: 16 key rows = 2048 bytes
+            tc::umma_ts(tmem + kColO, tmem + (j & 1) * kChunk + s8 * 8, vdesc + 128 * s8, id_o, (c > 0 || s8 > 0) ? 1u : 0u);
+          tc::umma_commit(&bars.v_empty[vs]);
+          ++vjob;
+          return true;
+        };
+        for (int j = 0; ok && j < jobs; ++j) {
+          if (j >= 2) {
+            // buffer j & 1 was used by job j - 2: wait until its group is done with it; a pass-2 job then feeds P.V,
+            // which precedes the new S in issue order
+            const int64_t Jp = J + j - 2;
+            if (!(ok = lp_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+            tc::fence_after_sync();
+            if (j - 2 >= n_chunks && !(ok = issue_pv(j - 2))) break;
+          } else if (J > 0) {
+            // first two jobs of a tile: the buffers' last users were the last two (pass-2) jobs of the previous tile,
+            // whose P.V was issued at the end of that tile
+          }
+          ok = issue_s(j);
+        }
+        if (!ok) break;
+        for (int j = jobs - 2; ok && j < jobs; ++j) {   // the last two jobs' P.V
+          const int64_t Jp = J + j;
+          if (!(ok = lp_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+          tc::fence_after_sync();
+          ok = issue_pv(j);
+        }
+        if (!ok) break;
+        tc::umma_commit(&bars.o_ready);
+        tc::umma_commit(&bars.q_empty[qs]);
+        J += jobs;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue, thread = query row
+    const int wg = warp >> 2, qd = warp & 3, r = qd * 32 + lane;
+    const float sl2 = a.scale * kLog2eF;
+    const float lw1 = log2f(a.w1), lw2 = log2f(a.w2);
+    const uint32_t t_s = tmem + wg * kChunk + ((uint32_t) (qd * 32) << 16);
+    const uint32_t t_o = tmem + kColO + wg * 32 + ((uint32_t) (qd * 32) << 16);
+    int64_t Jw = 0;                        // jobs this group has handled (its buffer's phase counter)
+    uint32_t n_x = 0;                      // exchanges so far
+    float va[32];
+    // Both groups publish a per-row value and read the other group's.  The buffer alternates with the exchange count:
+    // a buffer is rewritten two exchanges later, after every thread has passed the barrier in between.
+    auto exchange = [&](float mine, float& other) -> bool {
+      s_part[n_x & 1][wg][r] = mine;
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(&bars.xchg);
+      const bool ok_ = __all_sync(0xffffffffu, lp_wait(&bars.xchg, n_x & 1, abort_flag));
+      other = s_part[n_x & 1][wg ^ 1][r];
+      ++n_x;
+      return ok_;
+    };
+    for (int i = 0; i < n_my; ++i) {
+      const int tile = blockIdx.x + i * gridDim.x;
+      const int bh = tile / tiles_per_head, row = (tile % tiles_per_head) * kRows + r;
+      bf16* orow = a.o.row(bh / a.H, bh % a.H, row) + wg * 32;
+      // the fine part of this row (this group's 32 channels): requested now, consumed in the epilogue
+      uint4 of[4];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) of[q4] = *reinterpret_cast<const uint4*>(orow + 8 * q4);
+      const float lse_f = a.lse[(int64_t) bh * a.Nq + row];
+      float mx = -INFINITY, lsum = 0.f;
+      bool ok = true;
+      for (int j = wg; j < jobs; j += 2) {
+        const int c = j % n_chunks, pass = j / n_chunks;
+        const float lw = (gathered ? (c == 0) : !a.two_level) ? lw1 : lw2;
+        if (pass == 1 && j - 2 < n_chunks) {
+          // first pass-2 job of this group: exchange the row maxima of the two groups
+          float other;
+          if (!(ok = exchange(mx, other))) break;
+          mx = fmaxf(mx, other);
+        }
+        ok = __all_sync(0xffffffffu, lp_wait(&bars.s_ready[wg], (uint32_t) (Jw & 1), abort_flag));
+        tc::fence_after_sync();
+        if (!ok) break;
+        if (pass == 0) {
+          float m = -INFINITY;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            tc::tmem_ld32_async(t_s + 32 * q4, va);
+            tc::tmem_ld_wait(va);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) m = fmaxf(m, va[e]);
+          }
+          mx = fmaxf(mx, fmaf(m, sl2, lw));
+        } else {
+          const float off = lw - mx;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            tc::tmem_ld32_async(t_s + 32 * q4, va);
+            tc::tmem_ld_wait(va);
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float e0 = fast_exp2(fmaf(va[2 * e], sl2, off)), e1 = fast_exp2(fmaf(va[2 * e + 1], sl2, off));
+              lsum += e0 + e1;
+              pk[e] = pack_bf16(e0, e1);
+            }
+            tc::tmem_st16(t_s + 16 * q4, pk);          // P columns [16 q4, 16 q4 + 16): scores read before
+          }
+          tc::tmem_st_wait();
+        }
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tma::mbar_arrive(&bars.wg_done[wg]);
+        ++Jw;
+      }
+      float lse_out = __int_as_float(0x7fc00000);               // NaN unless everything completed
+      if (ok) {
+        float other;
+        ok = exchange(lsum, other);
+        lsum = wg == 0 ? lsum + other : other + lsum;          // the same order in both groups: identical bits
+      }
+      if (ok) {
+        ok = __all_sync(0xffffffffu, lp_wait(&bars.o_ready, (uint32_t) (i & 1), abort_flag));
+        tc::fence_after_sync();
+      }
+      if (ok) {
+        tc::tmem_ld32_async(t_o, va);
+        const float Lf = lse_f * kLog2eF;                        // fine part, log2 domain
+        const float Lp = mx + log2f(lsum);
+        const float Lm = fmaxf(Lf, Lp);
+        const float ef = fast_exp2(Lf - Lm), ep = fast_exp2(Lp - Lm);
+        const float inv = 1.f / (ef + ep);
+        const float wf = ef * inv, wp = ep * inv / lsum;
+        lse_out = (Lm + log2f(ef + ep)) * 0.6931471805599453f;
+        tc::tmem_ld_wait(va);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint4 f = of[q4];
+          uint4 w;
+          w.x = pack_bf16(bf16_lo(f.x) * wf + va[8 * q4] * wp, bf16_hi(f.x) * wf + va[8 * q4 + 1] * wp);
+          w.y = pack_bf16(bf16_lo(f.y) * wf + va[8 * q4 + 2] * wp, bf16_hi(f.y) * wf + va[8 * q4 + 3] * wp);
+          w.z = pack_bf16(bf16_lo(f.z) * wf + va[8 * q4 + 4] * wp, bf16_hi(f.z) * wf + va[8 * q4 + 5] * wp);
+          w.w = pack_bf16(bf16_lo(f.w) * wf + va[8 * q4 + 6] * wp, bf16_hi(f.w) * wf + va[8 * q4 + 7] * wp);
+          *reinterpret_cast<uint4*>(orow + 8 * q4) = w;
+        }
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tma::mbar_arrive(&bars.o_free);
+      }
+      // both groups read the fine lse above; group 0 replaces it only after both have (second exchange barrier)
+      if (wg == 0) a.lse[(int64_t) bh * a.Nq + row] = lse_out;
+      if (!ok) break;
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+// Pooled keys per row if the key-loop kernel applies (a multiple of 128, more than the 192 the single-shot kernel
+// holds), else 0.
+int pooled_loop_tc_keys(const AttnP<bf16>& a) {
+  const int64_t np = (int64_t) (a.p1_blocks + a.p2_blocks) * kBS;
+  if (np <= 192 || np % kChunk || a.Nq % kRows) return 0;
+  if (a.two_level && a.p1_blocks != 8) return 0;         // the gathered chunk is exactly 8 blocks
+  if (a.two_level && a.p2_blocks == 0) return 0;
+  return (int) np;
+}
+
+int launch_attn_fwd_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64_t BH, cudaStream_t st) {
+  const int np = pooled_loop_tc_keys(a);
+  LoopMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  int rc;
+  if ((rc = tma::make_map_bhnd(&maps.q, g->q, kRows))) return rc;
+  const int gathered = a.two_level ? 1 : 0;
+  const int64_t n_c = a.two_level ? a.n2 : a.n1;
+  if (gathered) {
+    if ((rc = tma::make_map_rows(&maps.kg, a.pk, (uint64_t) BH * a.n1, kBS))) return rc;
+    if ((rc = tma::make_map_rows(&maps.vg, a.pv, (uint64_t) BH * a.n1, kBS))) return rc;
+  }
+  if ((rc = tma::make_map_rows(&maps.kc, a.two_level ? a.pk2 : a.pk, (uint64_t) BH * n_c, kChunk))) return rc;
+  if ((rc = tma::make_map_rows(&maps.vc, a.two_level ? a.pv2 : a.pv, (uint64_t) BH * n_c, kChunk))) return rc;
+  const int tiles_per_head = (int) (a.Nq / kRows), n_tiles = (int) (BH * tiles_per_head);
+  int dev = 0, sms = 148;
+  LLSA_CUDA_OK(cudaGetDevice(&dev));
+  LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int grid = n_tiles < sms ? n_tiles : sms;
+  const size_t smem = 1024 + (size_t) (2 + kKStages + kVStages) * kTile * sizeof(bf16);
+  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_pooled_loop_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  attn_fwd_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, np / kChunk, gathered, n_c, n_tiles, tiles_per_head);
+  LLSA_LAUNCH_OK("attn_fwd_pooled_loop_tc_kernel");
+  return LLSA_OK;
+}
+
+}  // namespace llsa

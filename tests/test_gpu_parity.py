@@ -298,6 +298,24 @@ def test_llsa_l1_bf16_rope_vs_oracle(force_generic, monkeypatch):
     assert_bf16_close(vg.grad, dv + O.mean_pool1d_bwd(dpv, 16), "dv")
 
 
+@pytest.mark.parametrize("levels,N", [(1, 16384), (2, 65536)])
+def test_pooled_key_loop_on_tcgen05_matches_mma_path(levels, N, monkeypatch):
+    """Long pooled key lists (1024 level-1 keys; 128 gathered + 256 level-2 keys) go through the key-loop tcgen05 forward;
+    the mma.sync kernels (validated against the oracle above) are the reference here."""
+    L = _ops()
+    q, k, v, _ = synth.correlated_qkv(48, 1, 2, N, 64, dtype=torch.bfloat16)
+    q, k, v = [t.to(DEV) for t in (q, k, v)]
+    call = (lambda: L.llsa_l1_debug(q, k, v, 8, 16)) if levels == 1 else (lambda: L.llsa_l2_debug(q, k, v, 8, 8, 16))
+    monkeypatch.setenv("LLSA_B200_TC", "1")
+    a = call()
+    monkeypatch.setenv("LLSA_B200_TC", "0")
+    b = call()
+    assert torch.equal(a["indices"], b["indices"])
+    assert not torch.isnan(a["lse"]).any()
+    assert_bf16_close(a["o"], b["o"].float(), "o")
+    assert max_abs(a["lse"], b["lse"]) < 2e-3
+
+
 def test_llsa_l1_exact_pooled_grad_switch():
     L = _ops()
     q, k, v, do = synth.gaussian_qkv(43, 1, 1, 1024, 64, dtype=torch.float32)
