@@ -1,6 +1,7 @@
 // Coarse-to-fine top-k block selection (reference: src/llsa/kernel/triton/topk.py).
 //
-// coarse_topk_kernel  = gen_sparse_indices (topk.py:6-9): scores pq.pk^T rounded to
+// coarse_topk_kernel / coarse_topk_mma_kernel (bf16 on the tensor cores)
+//                     = gen_sparse_indices (topk.py:6-9): scores pq.pk^T rounded to
 //   the input dtype (torch.matmul writes its result in the input dtype), then the
 //   top-k columns per row, descending.  The score matrix never leaves the SM: a CTA
 //   owns ROWS query rows, streams the keys in chunks through shared memory and
@@ -138,6 +139,107 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
 // queries are a shard of the sequence); p_idx [B*H, M/bs, p_topk] with values in [0, Mk/bs); out [B*H, M, topk].
 // MMA = true (bf16, D = 64, bs = 16): the 16 x C score tile comes from mma.sync with fp32
 // accumulation of the exact bf16 products, as the reference's tl.dot does.
+
+// ---- coarse selection on the tensor cores (bf16, D = 64, top-k <= 8) ---------------------------
+// A CTA owns 64 query rows (16 per warp, the m16 of mma.sync.m16n8k16) and streams the keys through a
+// double-buffered shared-memory tile of 64 keys (cp.async).  Scores are rounded to bf16 as torch.matmul
+// would store them (topk.py:7); a lane sees columns 2t, 2t+1 (+8) of rows g and g+8 of every 16-key
+// block and keeps the best 8 of each of its two rows in sorted registers -- columns arrive in
+// increasing order and an equal score never displaces an earlier one, so ties go to the smallest index.
+// The four lanes of a quad cover a row between them; their 4 x 8 candidates are merged at the end by
+// the warp (two reductions per output, as in the refine kernel below).
+constexpr int kCmRows = 64, kCmKeys = 64, kCmTop = 8;
+
+__device__ __forceinline__ uint32_t orderable(float v);
+
+__device__ __forceinline__ void top8_insert(float (&val)[kCmTop], int (&idx)[kCmTop], float v, int i) {
+  if (!(v > val[kCmTop - 1])) return;
+  val[kCmTop - 1] = v;
+  idx[kCmTop - 1] = i;
+#pragma unroll
+  for (int u = kCmTop - 1; u > 0; --u) {
+    const bool sw = val[u] > val[u - 1];
+    const float tv = val[u];
+    const int ti = idx[u];
+    val[u] = sw ? val[u - 1] : tv;  idx[u] = sw ? idx[u - 1] : ti;
+    val[u - 1] = sw ? tv : val[u - 1];  idx[u - 1] = sw ? ti : idx[u - 1];
+  }
+}
+
+__global__ void __launch_bounds__(128)
+coarse_topk_mma_kernel(const bf16* __restrict__ pq, const bf16* __restrict__ pk, void* __restrict__ idx_out, int idx64, int64_t M, int64_t n,
+                       int topk) {
+  __shared__ __align__(16) bf16 sk[2][kCmKeys * kSmemPitch];
+  __shared__ float cand_v[4][16][32];
+  __shared__ int cand_i[4][16][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int64_t bh = blockIdx.y, row0 = (int64_t) blockIdx.x * kCmRows + warp * 16;
+  const bf16* k0 = pk + bh * n * 64;
+  auto stage = [&](int64_t kt, int buf) {               // 64 keys x 128 bytes: 4 chunks of 16 bytes per thread
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int ch = c * 128 + threadIdx.x, r = ch >> 3, col = (ch & 7) * 8;
+      cp_async16(&sk[buf][r * kSmemPitch + col], k0 + (kt * kCmKeys + r) * 64 + col);
+    }
+    cp_async_commit();
+  };
+  stage(0, 0);
+  RowFrag qlo, qhi;
+  {
+    const int64_t ra = min(row0 + g, M - 1), rb = min(row0 + g + 8, M - 1);     // rows past M are computed and dropped
+    load_rowfrag(qlo, pq + (bh * M + ra) * 64, t);
+    load_rowfrag(qhi, pq + (bh * M + rb) * 64, t);
+  }
+  float v0[kCmTop], v1[kCmTop];
+  int i0[kCmTop], i1[kCmTop];
+#pragma unroll
+  for (int u = 0; u < kCmTop; ++u) { v0[u] = v1[u] = -CUDART_INF_F; i0[u] = i1[u] = 0x7FFFFFFF; }
+  const int64_t n_tiles = n / kCmKeys;
+  for (int64_t kt = 0; kt < n_tiles; ++kt) {
+    if (kt + 1 < n_tiles) stage(kt + 1, (int) ((kt + 1) & 1));
+    else cp_async_commit();
+    cp_async_wait_group<1>();
+    __syncthreads();
+    const bf16* tile = sk[kt & 1];
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+      RowFrag ka, kb;
+      load_rowfrag_smem(ka, tile + (blk * 16 + g) * kSmemPitch, t);
+      load_rowfrag_smem(kb, tile + (blk * 16 + 8 + g) * kSmemPitch, t);
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_rows_x_keys(s0, s1, qlo, qhi, ka, kb);
+      const int c = (int) (kt * kCmKeys) + blk * 16 + 2 * t;
+      top8_insert(v0, i0, round_to<bf16>(s0[0]), c);     top8_insert(v0, i0, round_to<bf16>(s0[1]), c + 1);
+      top8_insert(v0, i0, round_to<bf16>(s1[0]), c + 8); top8_insert(v0, i0, round_to<bf16>(s1[1]), c + 9);
+      top8_insert(v1, i1, round_to<bf16>(s0[2]), c);     top8_insert(v1, i1, round_to<bf16>(s0[3]), c + 1);
+      top8_insert(v1, i1, round_to<bf16>(s1[2]), c + 8); top8_insert(v1, i1, round_to<bf16>(s1[3]), c + 9);
+    }
+    __syncthreads();          // the buffer read here is refilled by the next iteration's stage()
+  }
+#pragma unroll
+  for (int u = 0; u < kCmTop; ++u) {
+    cand_v[warp][g][t * kCmTop + u] = v0[u];      cand_i[warp][g][t * kCmTop + u] = i0[u];
+    cand_v[warp][g + 8][t * kCmTop + u] = v1[u];  cand_i[warp][g + 8][t * kCmTop + u] = i1[u];
+  }
+  __syncwarp();
+  for (int r = 0; r < 16; ++r) {
+    if (row0 + r >= M) break;
+    uint32_t key = orderable(cand_v[warp][r][lane]);
+    uint32_t blk = (uint32_t) cand_i[warp][r][lane];
+    if (blk == 0x7FFFFFFFu) key = 0u;                    // unused slot
+    for (int tt = 0; tt < topk; ++tt) {
+      const uint32_t mk = __reduce_max_sync(0xffffffffu, key);
+      const uint32_t mb = __reduce_min_sync(0xffffffffu, key == mk ? blk : 0xFFFFFFFFu);
+      if (key == mk && blk == mb) { key = 0u; blk = 0xFFFFFFFFu; }
+      if (lane == 0) {
+        const int64_t o = (bh * M + row0 + r) * topk + tt;
+        if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = (int64_t) mb;
+        else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) mb;
+      }
+    }
+  }
+}
+
 constexpr int kRefineSlots = 8;        // register path of the refine selection: up to 256 candidates per row
 
 // Order-preserving map of a float onto uint32 (larger float <=> larger integer, -0 and +0 share one image so
@@ -298,6 +400,10 @@ extern "C" int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, cons
     LLSA_CUDA_OK(cudaFuncSetAttribute(coarse_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     coarse_topk_kernel<float><<<grid, kCoarseThreads, smem, st>>>((const float*) pq->ptr, (const float*) pk->ptr, idx->ptr,
                                                                    idx->dtype == LLSA_I64, M, n, (int) D, topk);
+  } else if (D == 64 && topk <= kCmTop && n % kCmKeys == 0 && n >= topk && ((uintptr_t) pq->ptr % 32) == 0 && ((uintptr_t) pk->ptr % 16) == 0 &&
+             n * 64 < (int64_t) 1 << 31) {
+    coarse_topk_mma_kernel<<<dim3((unsigned) ((M + kCmRows - 1) / kCmRows), (unsigned) (B * H)), 128, 0, st>>>(
+        (const __nv_bfloat16*) pq->ptr, (const __nv_bfloat16*) pk->ptr, idx->ptr, idx->dtype == LLSA_I64, M, n, topk);
   } else {
     LLSA_CUDA_OK(cudaFuncSetAttribute(coarse_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     coarse_topk_kernel<__nv_bfloat16><<<grid, kCoarseThreads, smem, st>>>((const __nv_bfloat16*) pq->ptr, (const __nv_bfloat16*) pk->ptr,
