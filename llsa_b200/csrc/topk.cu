@@ -250,6 +250,40 @@ __device__ __forceinline__ uint32_t orderable(float v) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Refine selection with the candidates of a row in registers: lane l keeps candidates l, l + 32, ... (SLOTS of them) as
+// order-preserving 32-bit images of the scores; a round is two warp reductions: the largest score, then the smallest
+// block index among its holders.
+template <int SLOTS>
+__device__ __forceinline__ void refine_select_regs(const float* sc, const int* cand, int C, int bs, int topk, void* idx_out, int idx64,
+                                                   int64_t out_row0, int warp, int lane, int nwarps) {
+  for (int r = warp; r < bs; r += nwarps) {
+    const float* s = sc + r * C;
+    uint32_t key[SLOTS], blk[SLOTS];
+#pragma unroll
+    for (int u = 0; u < SLOTS; ++u) {
+      const int j = lane + 32 * u;
+      key[u] = j < C ? orderable(s[j]) : 0u;            // 0 is below every real score's image
+      blk[u] = j < C ? (uint32_t) cand[j] : 0xFFFFFFFFu;
+    }
+    for (int t = 0; t < topk; ++t) {
+      uint32_t bk = key[0], bb = blk[0];
+#pragma unroll
+      for (int u = 1; u < SLOTS; ++u)
+        if (key[u] > bk || (key[u] == bk && blk[u] < bb)) { bk = key[u]; bb = blk[u]; }
+      const uint32_t mk = __reduce_max_sync(0xffffffffu, bk);
+      const uint32_t mb = __reduce_min_sync(0xffffffffu, bk == mk ? bb : 0xFFFFFFFFu);
+#pragma unroll
+      for (int u = 0; u < SLOTS; ++u)
+        if (key[u] == mk && blk[u] == mb) { key[u] = 0u; blk[u] = 0xFFFFFFFFu; }      // candidates are distinct blocks: one owner
+      if (lane == 0) {
+        const int64_t o = (out_row0 + r) * topk + t;
+        if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = (int64_t) mb;
+        else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) mb;
+      }
+    }
+  }
+}
+
 template <typename T, bool MMA>
 __global__ void __launch_bounds__(128)
 refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
@@ -324,34 +358,8 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   if (C <= 32 * kRefineSlots) {
-    // A lane keeps its candidates (j = lane, lane + 32, ...) in registers as order-preserving 32-bit images of the
-    // scores; a round is two warp reductions: the largest score, then the smallest block index among its holders.
-    for (int r = warp; r < bs; r += nwarps) {
-      const float* s = sc + r * C;
-      uint32_t key[kRefineSlots], blk[kRefineSlots];
-#pragma unroll
-      for (int u = 0; u < kRefineSlots; ++u) {
-        const int j = lane + 32 * u;
-        key[u] = j < C ? orderable(s[j]) : 0u;            // 0 is below every real score's image (NaN images included)
-        blk[u] = j < C ? (uint32_t) cand[j] : 0xFFFFFFFFu;
-      }
-      for (int t = 0; t < topk; ++t) {
-        uint32_t bk = key[0], bb = blk[0];
-#pragma unroll
-        for (int u = 1; u < kRefineSlots; ++u)
-          if (key[u] > bk || (key[u] == bk && blk[u] < bb)) { bk = key[u]; bb = blk[u]; }
-        const uint32_t mk = __reduce_max_sync(0xffffffffu, bk);
-        const uint32_t mb = __reduce_min_sync(0xffffffffu, bk == mk ? bb : 0xFFFFFFFFu);
-#pragma unroll
-        for (int u = 0; u < kRefineSlots; ++u)
-          if (key[u] == mk && blk[u] == mb) { key[u] = 0u; blk[u] = 0xFFFFFFFFu; }      // candidates are distinct blocks: one owner
-        if (lane == 0) {
-          const int64_t o = (bh * M + P * bs + r) * topk + t;
-          if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = (int64_t) mb;
-          else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) mb;
-        }
-      }
-    }
+    if (C <= 128) refine_select_regs<4>(sc, cand, C, bs, topk, idx_out, idx64, bh * M + P * bs, warp, lane, nwarps);
+    else refine_select_regs<kRefineSlots>(sc, cand, C, bs, topk, idx_out, idx64, bh * M + P * bs, warp, lane, nwarps);
     return;
   }
   for (int r = warp; r < bs; r += nwarps) {
