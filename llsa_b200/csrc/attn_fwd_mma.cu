@@ -188,9 +188,32 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine_kernel(AttnP<bf16> a
   const int my_fine = lane < a.topk ? (int) fine_block(a, bh, qb, lane) : 0;
   const float sl2 = a.scale * 1.4426950408889634f;
   const int n_glob = a.topk;
+  // A lane copies the same four 16-byte chunks of every K tile and of every V tile (chunk = 4 i + lane / 8 -> row, lane % 8 ->
+  // column): their global and shared-memory offsets are computed once, a block costs two base pointers and eight adds.
+  int off_k[4], off_v[4], off_s[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 4 + (lane >> 3), c = lane & 7;
+    off_k[i] = r * (int) a.k.sn + c * 8;
+    off_v[i] = r * (int) a.v.sn + c * 8;
+    off_s[i] = r * 64 + ((c ^ (r & 7)) << 3);
+  }
+  // fragment read offsets inside a ring tile (rows r and r + 8 share r & 7, so the second row is 8 * 64 elements further)
+  const int rd_k[2] = {g * 64 + (((2 * t) ^ (g & 7)) << 3), g * 64 + (((2 * t + 1) ^ (g & 7)) << 3)};
+  const int rd_v[2] = {(2 * t) * 64 + ((g ^ ((2 * t) & 7)) << 3), (2 * t + 1) * 64 + ((g ^ ((2 * t + 1) & 7)) << 3)};
+  const bf16* kb0 = a.k.row(b, h, 0);
+  const bf16* vb0 = a.v.row(b, h, 0);
+  const int64_t kblk = (int64_t) kBS * a.k.sn, vblk = (int64_t) kBS * a.v.sn;
   auto issue = [&](int i) {
     const int64_t j = __shfl_sync(0xffffffffu, my_fine, i);
-    ring_issue(ring + (i % kFineStages) * 2 * kRingTileElems, a.k.row(b, h, j * kBS), a.k.sn, a.v.row(b, h, j * kBS), a.v.sn, lane);
+    bf16* stage = ring + (i % kFineStages) * 2 * kRingTileElems;
+    const bf16* kp = kb0 + j * kblk;
+    const bf16* vp = vb0 + j * vblk;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      cp_async16(stage + off_s[u], kp + off_k[u]);
+      cp_async16(stage + kRingTileElems + off_s[u], vp + off_v[u]);
+    }
   };
 #pragma unroll
   for (int s = 0; s < kFineStages - 1; ++s) {
@@ -212,12 +235,19 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine_kernel(AttnP<bf16> a
     cp_async_commit();
     const bf16* tk = ring + (gi % kFineStages) * 2 * kRingTileElems;
     RowFrag k0, k1;
-    load_rowfrag_ring(k0, tk, g, t);
-    load_rowfrag_ring(k1, tk, g + 8, t);
+    {
+      const uint4 x0 = *reinterpret_cast<const uint4*>(tk + rd_k[0]), x1 = *reinterpret_cast<const uint4*>(tk + rd_k[1]);
+      const uint4 y0 = *reinterpret_cast<const uint4*>(tk + 8 * 64 + rd_k[0]), y1 = *reinterpret_cast<const uint4*>(tk + 8 * 64 + rd_k[1]);
+      k0.r[0] = x0.x; k0.r[1] = x0.y; k0.r[2] = x0.z; k0.r[3] = x0.w; k0.r[4] = x1.x; k0.r[5] = x1.y; k0.r[6] = x1.z; k0.r[7] = x1.w;
+      k1.r[0] = y0.x; k1.r[1] = y0.y; k1.r[2] = y0.z; k1.r[3] = y0.w; k1.r[4] = y1.x; k1.r[5] = y1.y; k1.r[6] = y1.z; k1.r[7] = y1.w;
+    }
     uint32_t pa[4];
     fwd_scores(st, qlo, qhi, k0, k1, sl2, 0.f, pa);
     ColFrag v;
-    load_colfrag_ring(v, tk + kRingTileElems, g, t);
+    v.row[0] = *reinterpret_cast<const uint4*>(tk + kRingTileElems + rd_v[0]);
+    v.row[1] = *reinterpret_cast<const uint4*>(tk + kRingTileElems + rd_v[1]);
+    v.row[2] = *reinterpret_cast<const uint4*>(tk + kRingTileElems + 8 * 64 + rd_v[0]);
+    v.row[3] = *reinterpret_cast<const uint4*>(tk + kRingTileElems + 8 * 64 + rd_v[1]);
     mma_x_cols(st.o, pa[0], pa[1], pa[2], pa[3], v);
   }
   const float l0 = quad_sum(st.l0), l1 = quad_sum(st.l1);
