@@ -193,6 +193,89 @@ __global__ void __launch_bounds__(NW * 32, 4) attn_dq_mma_kernel(AttnP<bf16> a, 
   store_acc_row_t<1>(a.dq.row(b, h, qb * kBS + g + 8), dq, t, a.scale);
 }
 
+// Fine blocks only (the pooled keys are on the tcgen05 kernel): the selected K / V blocks go through a per-warp
+// cp.async ring in shared memory, two blocks ahead, instead of being held in registers one block ahead.
+constexpr int kDqStages = 3;
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 4) attn_dq_fine_kernel(AttnP<bf16> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw) + warp * (kDqStages * 2 * kRingTileElems);
+  const int64_t qb = (int64_t) blockIdx.x * NW + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const int my_fine = lane < a.topk ? (int) fine_block(a, bh, qb, lane) : 0;
+  const float sl2 = a.scale * kLog2e;
+  const int n_glob = a.topk;
+  // a lane copies the same four 16-byte chunks of every K tile and of every V tile: offsets computed once
+  int off_k[4], off_v[4], off_s[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 4 + (lane >> 3), c = lane & 7;
+    off_k[i] = r * (int) a.k.sn + c * 8;
+    off_v[i] = r * (int) a.v.sn + c * 8;
+    off_s[i] = r * 64 + ((c ^ (r & 7)) << 3);
+  }
+  const bf16* kb0 = a.k.row(b, h, 0);
+  const bf16* vb0 = a.v.row(b, h, 0);
+  const int64_t kblk = (int64_t) kBS * a.k.sn, vblk = (int64_t) kBS * a.v.sn;
+  auto issue = [&](int i) {
+    const int64_t j = __shfl_sync(0xffffffffu, my_fine, i);
+    bf16* stage = ring + (i % kDqStages) * 2 * kRingTileElems;
+    const bf16* kp = kb0 + j * kblk;
+    const bf16* vp = vb0 + j * vblk;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      cp_async16(stage + off_s[u], kp + off_k[u]);
+      cp_async16(stage + kRingTileElems + off_s[u], vp + off_v[u]);
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < kDqStages - 1; ++s) {
+    if (s < n_glob) issue(s);
+    cp_async_commit();
+  }
+  RowFrag qlo, qhi, dlo, dhi;
+  load_rowfrag(qlo, a.q.row(b, h, qb * kBS + g), t);
+  load_rowfrag(qhi, a.q.row(b, h, qb * kBS + g + 8), t);
+  load_rowfrag(dlo, a.d_o.row(b, h, qb * kBS + g), t);
+  load_rowfrag(dhi, a.d_o.row(b, h, qb * kBS + g + 8), t);
+  DqRow row;
+  {
+    RowFrag olo, ohi;
+    load_rowfrag(olo, a.o_in.row(b, h, qb * kBS + g), t);
+    load_rowfrag(ohi, a.o_in.row(b, h, qb * kBS + g + 8), t);
+    row.delta0 = quad_sum(rowfrag_dot(olo, dlo));
+    row.delta1 = quad_sum(rowfrag_dot(ohi, dhi));
+  }
+  const int64_t rbase = bh * a.Nq + qb * kBS;
+  if (t == 0) { a.delta[rbase + g] = row.delta0; a.delta[rbase + g + 8] = row.delta1; }
+  row.L0 = a.lse[rbase + g] * kLog2e;
+  row.L1 = a.lse[rbase + g + 8] * kLog2e;
+  float dq[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dq[j][0] = dq[j][1] = dq[j][2] = dq[j][3] = 0.f;
+  for (int gi = 0; gi < n_glob; ++gi) {
+    cp_async_wait_group<kDqStages - 2>();       // block gi has landed (this lane's chunks) ...
+    __syncwarp();                               // ... and everybody else's; the stage read last time is free
+    if (gi + kDqStages - 1 < n_glob) issue(gi + kDqStages - 1);
+    cp_async_commit();
+    const bf16* tk = ring + (gi % kDqStages) * 2 * kRingTileElems;
+    RowFrag k0, k1, v0, v1;
+    load_rowfrag_ring(k0, tk, g, t);
+    load_rowfrag_ring(k1, tk, g + 8, t);
+    load_rowfrag_ring(v0, tk + kRingTileElems, g, t);
+    load_rowfrag_ring(v1, tk + kRingTileElems, g + 8, t);
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_rows_x_keys(s0, s1, qlo, qhi, k0, k1);
+    mma_rows_x_keys(p0, p1, dlo, dhi, v0, v1);
+    uint32_t da[4];
+    dq_ds(s0, s1, p0, p1, row, sl2, 0.f, da);
+    mma_x_rowfrag_t(dq, da[0], da[1], da[2], da[3], k0, k1);      // K transposed in registers (movmatrix)
+  }
+  store_acc_row_t<0>(a.dq.row(b, h, qb * kBS + g), dq, t, a.scale);
+  store_acc_row_t<1>(a.dq.row(b, h, qb * kBS + g + 8), dq, t, a.scale);
+}
+
 // P^T and dS^T (bf16, as A registers) of one (key tile) x (query block) pair from the
 // transposed accumulators: rows = keys (g, g+8), columns = query rows (tile 0: 0..7, tile 1: 8..15).
 __device__ __forceinline__ void dkv_p_ds(float (&s0)[4], float (&s1)[4], float (&e0)[4], float (&e1)[4], float2 la, float2 lb, float2 da,
@@ -546,9 +629,16 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     const int n_all = aq.p1_blocks + aq.p2_blocks;
     const int n_smem = n_all < 12 ? n_all : 12;   // 12 tiles = 54 KB of K+V, three CTAs per SM
     const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
-    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_mma_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, smem, st>>>(aq, n_smem);
-    LLSA_LAUNCH_OK("attn_dq_mma_kernel");
+    if (n_all == 0) {
+      const size_t ring = (size_t) NWQ * kDqStages * 2 * kRingTileElems * sizeof(bf16);
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_fine_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+      attn_dq_fine_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, ring, st>>>(aq);
+      LLSA_LAUNCH_OK("attn_dq_fine_kernel");
+    } else {
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_mma_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, smem, st>>>(aq, n_smem);
+      LLSA_LAUNCH_OK("attn_dq_mma_kernel");
+    }
   }
   if ((mask & 2) && tc) {
     int rc = launch_attn_bwd_pooled_tc(g, a, BH, st);
