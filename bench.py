@@ -36,16 +36,16 @@ METRIC = "llsa_l2 fwd+bwd tokens/sec @N=16384,B*H=48,D=64"
 
 
 # this library's kernels launched by one llsa_l2 forward + backward (torch's own zero fills are not counted)
-KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_kernel", "refine_topk_kernel", "attn_fwd_fine_kernel", "attn_fwd_pooled_tc_kernel",
+KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_mma_kernel", "refine_topk_kernel", "attn_fwd_fine_kernel", "attn_fwd_pooled_tc_kernel",
                     "transpose_kernel", "attn_bwd_pooled_tc_kernel",
-                    "attn_dq_mma_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
+                    "attn_dq_fine_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
 
 
 # DRAM read + write bytes of one launch on 12 (b,h) slices of the config-3 shape, from the ncu capture summarised in
 # profiles/attention_kernels_llsa_l2_batch2.md (dram__bytes_read.sum + dram__bytes_write.sum); traffic grows in
 # proportion to the slices (every slice is independent), so a full launch is scaled by B*H / 12.
-NCU_DRAM_BYTES_12_SLICES = dict(attn_fwd=(49.5 + 3.7 + 54.0 + 0.3) * 1e6, attn_bwd_dq=(100.6 + 11.1) * 1e6,
-                                attn_bwd_dkv_pooled=(85.6 + 6.4) * 1e6, attn_bwd_dkv_fine=(79.3 + 12.9 + 15.7 + 0.06) * 1e6)
+NCU_DRAM_BYTES_12_SLICES = dict(attn_fwd=(49.4 + 2.1 + 54.0 + 0.4) * 1e6, attn_bwd_dq=(100.6 + 11.8) * 1e6,
+                                attn_bwd_dkv_pooled=(85.6 + 4.9) * 1e6, attn_bwd_dkv_fine=(79.2 + 13.2 + 15.7 + 0.0) * 1e6)
 
 
 def parse():
