@@ -620,12 +620,14 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   // tensor-core kernel adds the pooled part of dq and produces the pooled-key gradients
   const char* tc_env = getenv("LLSA_B200_TC");
   const bool tc = pooled_bwd_tc_ok(a) && !(tc_env && tc_env[0] == '0');
+  // long pooled key lists: the pooled part of dQ on the key-loop tcgen05 kernel (the pooled dK/dV stay on mma.sync)
+  const bool loop_dq = !tc && pooled_dq_loop_tc_keys(a) > 0 && !(tc_env && tc_env[0] == '0');
   if (mask & 1) {
     int rc = zero_pooled_acc(g, st);
     if (rc) return rc;
     constexpr int NWQ = 4;
     AttnP<bf16> aq = a;
-    if (tc) aq.p1_blocks = aq.p2_blocks = 0;
+    if (tc || loop_dq) aq.p1_blocks = aq.p2_blocks = 0;
     const int n_all = aq.p1_blocks + aq.p2_blocks;
     const int n_smem = n_all < 12 ? n_all : 12;   // 12 tiles = 54 KB of K+V, three CTAs per SM
     const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
@@ -644,6 +646,10 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     int rc = launch_attn_bwd_pooled_tc(g, a, BH, st);
     if (rc) return rc;
   } else if ((mask & 2) && a.p1_blocks + a.p2_blocks > 0) {
+    if (loop_dq) {
+      int rc = launch_attn_dq_pooled_loop_tc(g, a, BH, st);
+      if (rc) return rc;
+    }
     constexpr int NWP = 8;
     const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
     LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));

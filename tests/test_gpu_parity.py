@@ -300,20 +300,28 @@ def test_llsa_l1_bf16_rope_vs_oracle(force_generic, monkeypatch):
 
 @pytest.mark.parametrize("levels,N", [(1, 16384), (2, 65536)])
 def test_pooled_key_loop_on_tcgen05_matches_mma_path(levels, N, monkeypatch):
-    """Long pooled key lists (1024 level-1 keys; 128 gathered + 256 level-2 keys) go through the key-loop tcgen05 forward;
-    the mma.sync kernels (validated against the oracle above) are the reference here."""
+    """Long pooled key lists (1024 level-1 keys; 128 gathered + 256 level-2 keys) go through the key-loop tcgen05 kernels
+    (forward, pooled part of dQ); the mma.sync kernels (validated against the oracle above) are the reference here."""
     L = _ops()
-    q, k, v, _ = synth.correlated_qkv(48, 1, 2, N, 64, dtype=torch.bfloat16)
-    q, k, v = [t.to(DEV) for t in (q, k, v)]
-    call = (lambda: L.llsa_l1_debug(q, k, v, 8, 16)) if levels == 1 else (lambda: L.llsa_l2_debug(q, k, v, 8, 8, 16))
+    q, k, v, do = [t.to(DEV) for t in synth.correlated_qkv(48, 1, 2, N, 64, dtype=torch.bfloat16)]
+
+    def run():
+        qg, kg, vg = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        d = L.llsa_l1_debug(qg, kg, vg, 8, 16) if levels == 1 else L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
+        d["o"].backward(do)
+        return d, qg.grad, kg.grad, vg.grad
+
     monkeypatch.setenv("LLSA_B200_TC", "1")
-    a = call()
+    a, dqa, dka, dva = run()
     monkeypatch.setenv("LLSA_B200_TC", "0")
-    b = call()
+    b, dqb, dkb, dvb = run()
     assert torch.equal(a["indices"], b["indices"])
     assert not torch.isnan(a["lse"]).any()
-    assert_bf16_close(a["o"], b["o"].float(), "o")
+    assert_bf16_close(a["o"].detach(), b["o"].detach().float(), "o")
     assert max_abs(a["lse"], b["lse"]) < 2e-3
+    assert_bf16_close(dqa, dqb.float(), "dq")
+    assert_bf16_close(dka, dkb.float(), "dk")
+    assert_bf16_close(dva, dvb.float(), "dv")
 
 
 def test_llsa_l1_exact_pooled_grad_switch():
