@@ -650,11 +650,16 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
       int rc = launch_attn_dq_pooled_loop_tc(g, a, BH, st);
       if (rc) return rc;
     }
-    constexpr int NWP = 8;
-    const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
-    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.nq1 / kBS), BH), NWP * 32, smem, st>>>(a);
-    LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
+    if (loop_dq && pooled_dkv_loop_tc_ok(a)) {
+      int rc = launch_attn_dkv_pooled_loop_tc(g, a, BH, st);
+      if (rc) return rc;
+    } else {
+      constexpr int NWP = 8;
+      const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.nq1 / kBS), BH), NWP * 32, smem, st>>>(a);
+      LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
+    }
   }
   if (mask & 4) {
     const int64_t E = a.nq1 * a.topk;

@@ -76,6 +76,13 @@ __device__ __forceinline__ void load_4d(void* smem_dst, const CUtensorMap* map, 
                "l"(map), "r"((uint32_t) __cvta_generic_to_shared(mbar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                : "memory");
 }
+// Untiled bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) with completion on an mbarrier.
+__device__ __forceinline__ void load_bulk(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   (uint32_t) __cvta_generic_to_shared(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"((uint32_t) __cvta_generic_to_shared(mbar))
+               : "memory");
+}
 __device__ __forceinline__ void expect_tx(uint64_t* mbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"((uint32_t) __cvta_generic_to_shared(mbar)), "r"(bytes) : "memory");
 }
