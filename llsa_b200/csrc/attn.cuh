@@ -76,7 +76,7 @@ int pooled_loop_tc_keys(const AttnP<__nv_bfloat16>& a);   // pooled keys per row
 int launch_attn_fwd_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<__nv_bfloat16>& a, int64_t BH, cudaStream_t st);
 int pooled_dq_loop_tc_keys(const AttnP<__nv_bfloat16>& a);  // pooled keys per row if the key-loop tcgen05 dQ kernel applies, else 0
 int launch_attn_dq_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<__nv_bfloat16>& a, int64_t BH, cudaStream_t st);
-bool pooled_dkv_loop_tc_ok(const AttnP<__nv_bfloat16>& a);  // one level: the key-major tcgen05 pooled dK/dV kernel applies
+int pooled_dkv_loop_tc_level(const AttnP<__nv_bfloat16>& a);  // pooling level (1 or 2) the key-major tcgen05 pooled dK/dV kernel would take, else 0
 int launch_attn_dkv_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<__nv_bfloat16>& a, int64_t BH, cudaStream_t st);
 bool pooled_bwd_tc_ok(const AttnP<__nv_bfloat16>& a);  // the tcgen05 pooled backward applies (two levels, 128 + 64 pooled keys)
 int launch_attn_bwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<__nv_bfloat16>& a, int64_t BH, cudaStream_t st);

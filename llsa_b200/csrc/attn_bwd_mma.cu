@@ -650,14 +650,20 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
       int rc = launch_attn_dq_pooled_loop_tc(g, a, BH, st);
       if (rc) return rc;
     }
-    if (loop_dq && pooled_dkv_loop_tc_ok(a)) {
+    // the keys every query attends to (level 1 of one level, level 2 of two levels) on the key-major tcgen05 kernel; what is
+    // left for the mma.sync kernel is the gathered level-1 part of the two-level form
+    const int dense_level = loop_dq ? pooled_dkv_loop_tc_level(a) : 0;
+    AttnP<bf16> ap = a;
+    if (dense_level) {
       int rc = launch_attn_dkv_pooled_loop_tc(g, a, BH, st);
       if (rc) return rc;
-    } else {
+      if (dense_level == 1) ap.p1_blocks = 0; else ap.p2_blocks = 0;
+    }
+    if (ap.p1_blocks + ap.p2_blocks > 0) {
       constexpr int NWP = 8;
       const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
       LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-      attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.nq1 / kBS), BH), NWP * 32, smem, st>>>(a);
+      attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.nq1 / kBS), BH), NWP * 32, smem, st>>>(ap);
       LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
     }
   }

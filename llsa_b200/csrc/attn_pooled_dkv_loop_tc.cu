@@ -1,6 +1,7 @@
 // Pooled-key gradients on tcgen05 for the keys that EVERY query attends to: all level-1 pooled keys of the
-// one-level form (sparse_attention_res_1.py:362-400) -- the key-major half of the pooled backward, with a loop over
-// the queries.  (For two levels the dense level-2 keys have the same shape; that case still runs on mma.sync.)
+// one-level form (sparse_attention_res_1.py:362-400) and all level-2 keys of the two-level form
+// (_attn_bwd_res_dpkv2, sparse_attention_res_2.py:418-489) -- the key-major half of the pooled backward, with a
+// loop over the queries.
 //
 // A work unit is (head, chunk of 128 pooled keys); it walks all query rows of the head 64 at a time:
 //     S^T  = K_c . Q_t^T   [128 keys x 64 queries]  (K = 64 channels)   shared-memory operands
@@ -54,10 +55,12 @@ __device__ __forceinline__ bool kl_wait(uint64_t* bar, uint32_t parity, volatile
   return false;
 }
 
-// n_keys: pooled keys per head (a multiple of 128); jobs: Nq / 64 (even); units = BH * n_keys / 128.
+// n_keys: pooled keys per head (a multiple of 128); jobs: 64-row query jobs per unit (even); splits: units per (head, key chunk),
+// each walking its own range of the queries (with more than one, the results are added with reductions instead of stored);
+// units = BH * n_keys / 128 * splits.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps maps, float* __restrict__ dpk, float* __restrict__ dpv,
-                               int64_t n_keys, int jobs, int n_units, float lw_log2, float out_mul) {
+                               int64_t n_keys, int jobs, int splits, int n_units, float lw_log2, float out_mul) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ KvBars bars;
   __shared__ uint32_t s_tmem;
@@ -94,8 +97,8 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
     if (lane == 0) {
       int cj = 0;
       for (int i = 0; i < n_my; ++i) {
-        const int unit = blockIdx.x + i * gridDim.x;
-        const int bh = unit / chunks_per_head, c = unit % chunks_per_head;
+        const int unit = blockIdx.x + i * gridDim.x, sp = unit % splits;
+        const int bh = unit / splits / chunks_per_head, c = unit / splits % chunks_per_head;
         if (!kl_wait(&bars.kv_empty, (i & 1) ^ 1, abort_flag)) break;
         tma::expect_tx(&bars.kv_full, 2 * kKeyTile * 2);
         tma::load_2d(sK, &maps.k, &bars.kv_full, 0, (int) ((int64_t) bh * n_keys + (int64_t) c * kKeys));
@@ -105,10 +108,11 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
           const int st = cj % kStages;
           if (!(ok = kl_wait(&bars.q_empty[st], ((cj / kStages) & 1) ^ 1, abort_flag))) break;
           tma::expect_tx(&bars.q_full[st], 2 * kQTile * 2 + 2 * kQ * 4);
-          tma::load_4d(sQ + st * kQTile, &maps.q, &bars.q_full[st], 0, j * kQ, bh % a.H, bh / a.H);
-          tma::load_4d(sDO + st * kQTile, &maps.d_o, &bars.q_full[st], 0, j * kQ, bh % a.H, bh / a.H);
-          tma::load_bulk(s_lse[st], a.lse + (int64_t) bh * a.Nq + (int64_t) j * kQ, kQ * 4, &bars.q_full[st]);
-          tma::load_bulk(s_delta[st], a.delta + (int64_t) bh * a.Nq + (int64_t) j * kQ, kQ * 4, &bars.q_full[st]);
+          const int qrow = (sp * jobs + j) * kQ;
+          tma::load_4d(sQ + st * kQTile, &maps.q, &bars.q_full[st], 0, qrow, bh % a.H, bh / a.H);
+          tma::load_4d(sDO + st * kQTile, &maps.d_o, &bars.q_full[st], 0, qrow, bh % a.H, bh / a.H);
+          tma::load_bulk(s_lse[st], a.lse + (int64_t) bh * a.Nq + qrow, kQ * 4, &bars.q_full[st]);
+          tma::load_bulk(s_delta[st], a.delta + (int64_t) bh * a.Nq + qrow, kQ * 4, &bars.q_full[st]);
         }
         if (!ok) break;
       }
@@ -192,7 +196,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
     float vs[32], vd[32];
     for (int i = 0; i < n_my; ++i) {
       const int unit = blockIdx.x + i * gridDim.x;
-      const int bh = unit / chunks_per_head, c = unit % chunks_per_head;
+      const int bh = unit / splits / chunks_per_head, c = unit / splits % chunks_per_head;
       bool ok = true;
       for (int j = wg; j < jobs; j += 2, cj += 2) {
         const int st = cj % kStages;
@@ -237,9 +241,15 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
       for (int half = 0; half < 2; ++half) {
         tc::tmem_ld32_async(t_acc + 32 * half, vs);
         tc::tmem_ld_wait(vs);
+        if (splits == 1) {
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4)
-          *reinterpret_cast<float4*>(dst + 32 * half + 4 * q4) = make_float4(vs[4 * q4] * out_mul, vs[4 * q4 + 1] * out_mul, vs[4 * q4 + 2] * out_mul, vs[4 * q4 + 3] * out_mul);
+          for (int q4 = 0; q4 < 8; ++q4)
+            *reinterpret_cast<float4*>(dst + 32 * half + 4 * q4) = make_float4(vs[4 * q4] * out_mul, vs[4 * q4 + 1] * out_mul, vs[4 * q4 + 2] * out_mul, vs[4 * q4 + 3] * out_mul);
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            red_add_v4(dst + 32 * half + 4 * q4, vs[4 * q4] * out_mul, vs[4 * q4 + 1] * out_mul, vs[4 * q4 + 2] * out_mul, vs[4 * q4 + 3] * out_mul);
+        }
       }
       tc::fence_before_sync();
       __syncwarp();
@@ -253,31 +263,42 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
 
 }  // namespace
 
-// One level, every pooled key attended by every query: the key-major tcgen05 kernel applies when the key count is a multiple
-// of 128 and the query rows come in pairs of 64-row jobs.
-bool pooled_dkv_loop_tc_ok(const AttnP<bf16>& a) {
-  const int64_t np = (int64_t) a.p1_blocks * kBS;
-  return !a.two_level && np >= 128 && np % kKeys == 0 && a.Nq % (2 * kQ) == 0;
+// The pooled keys that every query attends to -- all level-1 keys of the one-level form, all level-2 keys of the two-level
+// form: the key-major tcgen05 kernel applies when their count is a multiple of 128 and the query rows come in pairs of
+// 64-row jobs.  Returns the pooling level it would handle (1 or 2), else 0.
+int pooled_dkv_loop_tc_level(const AttnP<bf16>& a) {
+  if (a.Nq % (2 * kQ)) return 0;
+  if (!a.two_level) return (a.p1_blocks > 0 && a.n1 % kKeys == 0) ? 1 : 0;
+  return (a.p2_blocks > 0 && a.n2 % kKeys == 0) ? 2 : 0;
 }
 
 int launch_attn_dkv_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64_t BH, cudaStream_t st) {
+  const int level = pooled_dkv_loop_tc_level(a);
   KvMaps maps;
   memset(&maps, 0, sizeof(maps));
   int rc;
   if ((rc = tma::make_map_bhnd(&maps.q, g->q, kQ))) return rc;
   if ((rc = tma::make_map_bhnd(&maps.d_o, g->d_o, kQ))) return rc;
-  const int64_t n_keys = a.n1;
-  if ((rc = tma::make_map_rows(&maps.k, a.pk, (uint64_t) BH * n_keys, kKeys))) return rc;
-  if ((rc = tma::make_map_rows(&maps.v, a.pv, (uint64_t) BH * n_keys, kKeys))) return rc;
-  const int n_units = (int) (BH * (n_keys / kKeys));
+  const int64_t n_keys = level == 1 ? a.n1 : a.n2;
+  if ((rc = tma::make_map_rows(&maps.k, level == 1 ? a.pk : a.pk2, (uint64_t) BH * n_keys, kKeys))) return rc;
+  if ((rc = tma::make_map_rows(&maps.v, level == 1 ? a.pv : a.pv2, (uint64_t) BH * n_keys, kKeys))) return rc;
   int dev = 0, sms = 148;
   LLSA_CUDA_OK(cudaGetDevice(&dev));
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  // enough units for two rounds over the SMs: split the query range (an even number of 64-row jobs per unit)
+  const int jobs_all = (int) (a.Nq / kQ), base_units = (int) (BH * (n_keys / kKeys));
+  int splits = 1;
+  while (base_units * splits < 2 * sms && jobs_all % (4 * splits) == 0 && jobs_all / (2 * splits) >= 16) splits *= 2;
+  const int n_units = base_units * splits, jobs = jobs_all / splits;
   const int grid = n_units < sms ? n_units : sms;
   const size_t smem = 1024 + (size_t) (2 * kKeyTile + 2 * kStages * kQTile) * sizeof(bf16);
   LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_loop_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-  attn_dkv_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, a.dpk, a.dpv, n_keys, (int) (a.Nq / kQ), n_units, log2f(a.w1),
-                                                               a.kvw1 / a.w1);
+  if (level == 1)
+    attn_dkv_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, a.dpk, a.dpv, n_keys, jobs, splits, n_units, log2f(a.w1),
+                                                                 a.kvw1 / a.w1);
+  else
+    attn_dkv_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, a.dpk2, a.dpv2, n_keys, jobs, splits, n_units, log2f(a.w2),
+                                                                 a.kvw2 / a.w2);
   LLSA_LAUNCH_OK("attn_dkv_pooled_loop_tc_kernel");
   return LLSA_OK;
 }
