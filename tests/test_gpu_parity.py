@@ -324,6 +324,37 @@ def test_pooled_key_loop_on_tcgen05_matches_mma_path(levels, N, monkeypatch):
     assert_bf16_close(dva, dvb.float(), "dv")
 
 
+@pytest.mark.parametrize("levels,N", [(1, 256), (1, 1024), (1, 2048), (2, 4096), (2, 8192)])
+def test_small_shapes_bf16_vs_oracle(levels, N):
+    """Sizes around the dispatch edges: pooled stages that are skipped (fewer than 64 pooled keys: llsa_l1 at N=256, llsa_l2 below
+    N=16384), 64 and 128 pooled keys (single-shot tcgen05 forward with one level)."""
+    L = _ops()
+    q, k, v, do = synth.gaussian_qkv(50 + levels, 2, 2, N, 64, dtype=torch.bfloat16)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    if levels == 1:
+        dbg = L.llsa_l1_debug(qg, kg, vg, 8, 16)
+        idx = dbg["indices"].cpu()
+        o_ref, lse_ref = O.attn_fwd_l1(q, k, v, dbg["pk"].cpu(), dbg["pv"].cpu(), idx, faithful=False)
+    else:
+        dbg = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
+        idx, pidx = dbg["indices"].cpu(), dbg["p_indices"].cpu().long()
+        o_ref, lse_ref = O.attn_fwd_l2(q, k, v, dbg["pk"].cpu(), dbg["pv"].cpu(), dbg["pk2"].cpu(), dbg["pv2"].cpu(), idx, pidx, faithful=False)
+    assert_bf16_close(dbg["o"].detach(), o_ref, "o")
+    assert max_abs(dbg["lse"], lse_ref) < 2e-2
+    dbg["o"].backward(do.to(DEV))
+    if levels == 1:
+        dq, dk, dv, dpk, dpv = O.attn_bwd_l1(do, q, k, v, dbg["pk"].cpu(), dbg["pv"].cpu(), o_ref.float(), lse_ref, idx, faithful=False)
+        dk, dv = dk + O.mean_pool1d_bwd(dpk, 16), dv + O.mean_pool1d_bwd(dpv, 16)
+    else:
+        dq, dk, dv, dpk, dpv, dpk2, dpv2 = O.attn_bwd_l2(do, q, k, v, dbg["pk"].cpu(), dbg["pv"].cpu(), dbg["pk2"].cpu(), dbg["pv2"].cpu(),
+                                                         o_ref.float(), lse_ref, idx, pidx, faithful=False)
+        dk = dk + O.mean_pool1d_bwd(dpk + O.mean_pool1d_bwd(dpk2, 16), 16)
+        dv = dv + O.mean_pool1d_bwd(dpv + O.mean_pool1d_bwd(dpv2, 16), 16)
+    assert_bf16_close(qg.grad, dq, "dq")
+    assert_bf16_close(kg.grad, dk, "dk")
+    assert_bf16_close(vg.grad, dv, "dv")
+
+
 def test_llsa_l1_exact_pooled_grad_switch():
     L = _ops()
     q, k, v, do = synth.gaussian_qkv(43, 1, 1, 1024, 64, dtype=torch.float32)
