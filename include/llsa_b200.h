@@ -167,8 +167,10 @@ typedef struct LlsaAttnArgs {
   int32_t force_generic;       /* 1: use the plain FFMA kernels for any dtype   */
   int32_t stage_mask;          /* backward only; 0 = everything.  Otherwise a bit set of
                                   1: zero the *_acc tensors + delta + dq,  2: pooled-key
-                                  gradients,  4: dk, dv -- to be issued in this order
-                                  (lets a caller time the three kernels separately) */
+                                  gradients (and the pooled part of dq where the tcgen05
+                                  kernels apply),  4: dk, dv -- to be issued in this order
+                                  (lets a caller time the kernels separately, or build the CSR
+                                  on another stream while 1 and 2 run) */
   const LlsaTensor* dkv_partial; /* backward, bf16 tensors only: F32 scratch
                                   [B,H,ceil(N/16*topk/128),4096] for dK/dV tiles of KV blocks whose
                                   list of query blocks straddles two work windows (not read before
@@ -185,6 +187,10 @@ int llsa_attn_fwd(const LlsaAttnArgs* args, void* stream);
  * (sparse_attention_res_2.py:578-681) and, with fold_pool_bwd, the
  * MeanPool1dFunction_BHSC.backward calls autograd runs after them. */
 int llsa_attn_bwd(const LlsaAttnArgs* args, void* stream);
+/* Element count of the F32 scratch tensor LlsaAttnArgs.dkv_partial that llsa_attn_bwd needs for bf16 tensors with
+ * Nq query rows per (b,h) and `topk` selected blocks per query block (the caller allocates it; any 4-D contiguous
+ * shape with at least this many elements is accepted).  The library itself never allocates device memory. */
+int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk);
 
 #ifdef __cplusplus
 }

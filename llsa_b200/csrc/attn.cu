@@ -80,6 +80,11 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
 
 using namespace llsa;
 
+extern "C" int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {
+  if (B <= 0 || H <= 0 || Nq <= 0 || topk <= 0) return 0;
+  return B * H * ((Nq / kBS * topk + 127) / 128) * 4096;
+}
+
 extern "C" int llsa_attn_fwd(const LlsaAttnArgs* args, void* stream) {
   int rc = check_attn_args(args, false);
   if (rc) return rc;

@@ -400,8 +400,8 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
     a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
     partial = None
     if q.dtype == torch.bfloat16:     # window partials of the fine dK/dV kernel (csrc/attn_bwd_mma.cu)
-        n_windows = (indices.shape[2] * indices.shape[3] + 127) // 128
-        partial = torch.empty((q.shape[0], q.shape[1], n_windows, 2 * 2048), **f32)
+        n_elems = _lib.lib().llsa_attn_bwd_partial_elems(q.shape[0], q.shape[1], q.shape[2], indices.shape[3])
+        partial = torch.empty((q.shape[0], q.shape[1], n_elems // (q.shape[0] * q.shape[1] * 4096), 4096), **f32)
     extra = dict(d_o=desc(do), dq=desc(dq), dk=desc(dk), dv=desc(dv), offsets=desc(offsets), flat=desc(flat), delta=desc(delta),
                  dpk_acc=desc(dpk), dpv_acc=desc(dpv), dpk2_acc=desc(dpk2), dpv2_acc=desc(dpv2), dkv_partial=desc(partial))
     for name, d in extra.items():

@@ -156,3 +156,10 @@ def test_reference_import_paths_resolve_to_this_package():
         for k in [k for k in sys.modules if k == "llsa" or k.startswith("llsa.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_bwd_partial_scratch_size():
+    L = _lib.lib()
+    assert L.llsa_attn_bwd_partial_elems(8, 6, 16384, 8) == 8 * 6 * 64 * 4096       # 8192 entries per slice / 128 per window
+    assert L.llsa_attn_bwd_partial_elems(1, 1, 256, 8) == 4096
+    assert L.llsa_attn_bwd_partial_elems(0, 6, 16384, 8) == 0
