@@ -59,6 +59,7 @@ def parse():
     ap.add_argument("--seq-parallel", action="store_true", help="shard the sequence over the ranks even if B*H >= ranks")
     ap.add_argument("--e2e-chunk-batch", type=int, default=1, help="batch elements per chunk of the host-operand pipeline")
     ap.add_argument("--e2e-chunk-heads", type=int, default=0, help="heads per chunk (with --e2e-chunk-batch 1; 0: whole batch elements)")
+    ap.add_argument("--e2e-graphs", type=int, default=1, help="1: one CUDA graph per staging slot replays a chunk's fwd+bwd; 0: eager launches")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     return ap.parse_args()
@@ -275,7 +276,8 @@ def main():
         from llsa_b200.hostpipe import HostPipeline
         ho = torch.empty_like(hq).pin_memory()
         hdq, hdk, hdv = [torch.empty_like(hq).pin_memory() for _ in range(3)]
-        pipe = HostPipeline(call, (B, H, N, D), cfg["dtype"], dev, chunk_batch=args.e2e_chunk_batch, chunk_heads=args.e2e_chunk_heads or None)
+        pipe = HostPipeline(call, (B, H, N, D), cfg["dtype"], dev, chunk_batch=args.e2e_chunk_batch, chunk_heads=args.e2e_chunk_heads or None,
+                            graphs=bool(args.e2e_graphs))
 
         def e2e_step():
             # the public host-operand call: per batch element copy-in, fwd+bwd and copy-out overlap on three streams

@@ -277,11 +277,17 @@ static int fwd_generic_t(const LlsaAttnArgs* g, cudaStream_t st) {
 
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st) {
   const int64_t BH = g->q->shape[0] * g->q->shape[1], n1 = g->k->shape[2] / kBS, n2 = n1 / kBS;
-  LLSA_CUDA_OK(cudaMemsetAsync(g->dpk_acc->ptr, 0, (size_t) BH * n1 * kD * 4, st));
-  LLSA_CUDA_OK(cudaMemsetAsync(g->dpv_acc->ptr, 0, (size_t) BH * n1 * kD * 4, st));
-  if (g->pk2) {
-    LLSA_CUDA_OK(cudaMemsetAsync(g->dpk2_acc->ptr, 0, (size_t) BH * n2 * kD * 4, st));
-    LLSA_CUDA_OK(cudaMemsetAsync(g->dpv2_acc->ptr, 0, (size_t) BH * n2 * kD * 4, st));
+  // accumulators that the caller carved out of one allocation, back to back, are cleared by one memset
+  char* ptr[4] = {(char*) g->dpk_acc->ptr, (char*) g->dpv_acc->ptr, g->pk2 ? (char*) g->dpk2_acc->ptr : nullptr,
+                  g->pk2 ? (char*) g->dpv2_acc->ptr : nullptr};
+  const size_t len[4] = {(size_t) BH * n1 * kD * 4, (size_t) BH * n1 * kD * 4, (size_t) BH * n2 * kD * 4, (size_t) BH * n2 * kD * 4};
+  for (int i = 0; i < 4;) {
+    if (!ptr[i]) { ++i; continue; }
+    size_t run = len[i];
+    int j = i + 1;
+    while (j < 4 && ptr[j] == ptr[i] + run) run += len[j++];
+    LLSA_CUDA_OK(cudaMemsetAsync(ptr[i], 0, run, st));
+    i = j;
   }
   return LLSA_OK;
 }

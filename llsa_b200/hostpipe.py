@@ -11,12 +11,17 @@ element) and three streams run a software pipeline over them:
 PCIe carries both directions at once, so a step costs about max(bytes in, bytes out) / link
 bandwidth instead of the sum of both copies plus the compute.  Device staging buffers are
 allocated once per pipeline object; nothing here touches the default stream.
+
+With graphs=True the forward + backward of a chunk is captured once per staging slot as a CUDA graph
+(static operands, static results) and replayed per chunk: the host then spends a graph launch instead of
+some twenty kernel launches plus autograd bookkeeping per chunk, which is what lets the chunks be small
+(a few heads) and the unoverlapped first copy-in and last copy-out short.
 """
 import torch
 
 
 class HostPipeline:
-    def __init__(self, call, shape, dtype, device, chunk_batch=1, chunk_heads=None, depth=3):
+    def __init__(self, call, shape, dtype, device, chunk_batch=1, chunk_heads=None, depth=3, graphs=False):
         """call(q, k, v) -> o on device tensors; shape = (B, H, N, D) of the full host operands.
         A chunk is `chunk_batch` batch elements, or, with chunk_heads (and chunk_batch = 1), `chunk_heads` heads
         of one batch element: smaller chunks shorten the unoverlapped first copy-in and last copy-out."""
@@ -29,6 +34,26 @@ class HostPipeline:
         self.dev = device
         self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
         self.slots = [[torch.empty((chunk_batch, self.ch, N, D), dtype=dtype, device=device) for _ in range(4)] for _ in range(depth)]
+        self.graphs = [self._capture(slot) for slot in self.slots] if graphs else None
+        self._out_done = [None] * depth        # the copy-out of a slot's static results has finished
+
+    def _capture(self, slot):
+        """(graph, (o, dq, dk, dv)) of one slot: leaves that alias the staging buffers, results in the graph's own pool."""
+        q, k, v = [t.detach().requires_grad_(True) for t in slot[:3]]
+        for t in slot:
+            t.zero_()
+        torch.cuda.synchronize(self.dev)
+        with torch.cuda.stream(self.s_comp):               # warm-up outside the capture: lazy initialisation, autotuned attributes
+            for _ in range(2):
+                q.grad = k.grad = v.grad = None
+                self.call(q, k, v).backward(slot[3])
+        torch.cuda.synchronize(self.dev)
+        q.grad = k.grad = v.grad = None
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.s_comp):
+            o = self.call(q, k, v)
+            o.backward(slot[3])
+        return g, (o.detach(), q.grad, k.grad, v.grad)
 
     def _chunks(self):
         for b0 in range(0, self.B, self.cb):
@@ -59,17 +84,27 @@ class HostPipeline:
                 ev_in[c].record(self.s_in)
             with torch.cuda.stream(self.s_comp):
                 self.s_comp.wait_event(ev_in[c])
-                q, k, v = [d_.detach().requires_grad_(True) for d_ in slot[:3]]
-                o = self.call(q, k, v)
-                o.backward(slot[3])
+                if self.graphs is not None:
+                    if self._out_done[c % self.depth] is not None:     # the replay overwrites the slot's static results
+                        self.s_comp.wait_event(self._out_done[c % self.depth])
+                    graph, outs = self.graphs[c % self.depth]
+                    graph.replay()
+                else:
+                    q, k, v = [d_.detach().requires_grad_(True) for d_ in slot[:3]]
+                    o = self.call(q, k, v)
+                    o.backward(slot[3])
+                    outs = (o.detach(), q.grad, k.grad, v.grad)
                 ev_comp[c].record(self.s_comp)
                 ev_free[c % self.depth] = ev_comp[c]
-            outs = (o.detach(), q.grad, k.grad, v.grad)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(ev_comp[c])
                 for h_, d_ in zip((ho, hdq, hdk, hdv), outs):
-                    d_.record_stream(self.s_out)
+                    if self.graphs is None:
+                        d_.record_stream(self.s_out)
                     h_[sl].copy_(d_, non_blocking=True)
+                if self.graphs is not None:
+                    self._out_done[c % self.depth] = torch.cuda.Event()
+                    self._out_done[c % self.depth].record(self.s_out)
             keep.append(outs)
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_comp)

@@ -394,9 +394,13 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
     f32 = dict(device=q.device, dtype=torch.float32)
-    dpk, dpv = torch.empty(pk.shape, **f32), torch.empty(pv.shape, **f32)
-    dpk2 = torch.empty(pk2.shape, **f32) if pk2 is not None else None
-    dpv2 = torch.empty(pv2.shape, **f32) if pv2 is not None else None
+    # the fp32 pooled-gradient accumulators sit back to back in one allocation: the library clears them with one memset
+    shapes = [pk.shape, pv.shape] + ([pk2.shape, pv2.shape] if pk2 is not None else [])
+    sizes = [int(torch.Size(s_).numel()) for s_ in shapes]
+    acc = torch.empty(sum(sizes), **f32)
+    views = [acc[sum(sizes[:i]):sum(sizes[:i + 1])].view(shapes[i]) for i in range(len(shapes))]
+    dpk, dpv = views[0], views[1]
+    dpk2, dpv2 = (views[2], views[3]) if pk2 is not None else (None, None)
     a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
     partial = None
     if q.dtype == torch.bfloat16:     # window partials of the fine dK/dV kernel (csrc/attn_bwd_mma.cu)
@@ -536,9 +540,12 @@ def _l1_setup(ctx, inputs, output):
     o, lse, indices, pk, pv = output
     ctx.save_for_backward(q, k, v, o, lse, indices, pk, pv)
     ctx.block_size = block_size
+    ctx.set_materialize_grads(False)       # only o carries a gradient: no zero-filled stand-ins for the other outputs
 
 
 def _l1_backward(ctx, grads):
+    if grads[0] is None:
+        return None, None, None, None, None
     q, k, v, o, lse, indices, pk, pv = ctx.saved_tensors
     dq, dk, dv = _llsa_l1_bwd(grads[0], q, k, v, o, lse, indices, pk, pv, ctx.block_size, _exact_pooled_grad)
     return dq, dk, dv, None, None
@@ -587,9 +594,12 @@ def _l2_setup(ctx, inputs, output):
     o, lse, indices, p_indices, pk, pv, pk2, pv2 = output
     ctx.save_for_backward(q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2)
     ctx.block_size = block_size
+    ctx.set_materialize_grads(False)
 
 
 def _l2_backward(ctx, grads):
+    if grads[0] is None:
+        return None, None, None, None, None, None
     q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2 = ctx.saved_tensors
     dq, dk, dv = _llsa_l2_bwd(grads[0], q, k, v, o, lse, indices, p_indices, pk, pv, pk2, pv2, ctx.block_size)
     return dq, dk, dv, None, None, None
@@ -632,9 +642,12 @@ def _rope_op_setup(ctx, inputs, output):
     q, k, v, freq, topk1, topk2, block_size, levels = inputs
     ctx.save_for_backward(v, freq, *output)
     ctx.block_size, ctx.levels = block_size, levels
+    ctx.set_materialize_grads(False)
 
 
 def _rope_op_backward(ctx, grads):
+    if grads[0] is None:
+        return (None,) * 8
     v, freq, o, lse, qr, kr, indices, pk, pv = ctx.saved_tensors[:9]
     if ctx.levels == 2:
         p_indices, pk2, pv2 = ctx.saved_tensors[9:]

@@ -432,14 +432,16 @@ def test_llsa_rope_operators_match_rope_then_llsa(levels):
     assert rel_l2(a[1].grad, b[1].grad) < 1e-3 and rel_l2(a[2].grad, b[2].grad) < 1e-3     # fp32 reductions: order may differ
 
 
-@pytest.mark.parametrize("chunk_heads", [None, 1])
-def test_host_pipeline_matches_direct_call(chunk_heads):
-    """Pinned host operands through the three-stream chunk pipeline give the bits of one direct call."""
+@pytest.mark.parametrize("chunk_heads,graphs", [(None, False), (1, False), (None, True), (1, True)])
+def test_host_pipeline_matches_direct_call(chunk_heads, graphs):
+    """Pinned host operands through the three-stream chunk pipeline (eager launches or one CUDA graph per staging slot)
+    give the bits of one direct call."""
     L = _ops()
     q, k, v, do = _bf16_case("l2", 4, 2, 4096, 45)
     hq, hk, hv, hdo = [t.pin_memory() for t in (q, k, v, do)]
     outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
-    pipe = L.HostPipeline(lambda a, b, c: L.llsa_l2(a, b, c, 8, 8, 16), tuple(q.shape), q.dtype, torch.device(DEV), chunk_batch=1, chunk_heads=chunk_heads, depth=2)
+    pipe = L.HostPipeline(lambda a, b, c: L.llsa_l2(a, b, c, 8, 8, 16), tuple(q.shape), q.dtype, torch.device(DEV), chunk_batch=1, chunk_heads=chunk_heads, depth=2,
+                          graphs=graphs)
     for _ in range(2):          # the second call reuses every slot
         pipe.fwd_bwd(hq, hk, hv, hdo, *outs)
         torch.cuda.synchronize()
