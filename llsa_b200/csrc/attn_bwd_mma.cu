@@ -26,6 +26,8 @@
 // here scale rides in the exp2 argument and in the epilogues.
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "attn.cuh"
 #include "mma_frag.cuh"
 
@@ -609,6 +611,391 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_kernel(AttnP<bf16> a, con
   dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);
 }
 
+// ---- fine dK/dV, second form: three CTAs per SM --------------------------------------------------
+// The kernel above is bound by latency at two CTAs (eight warps) per SM: 240 registers and 64 KB of
+// slots per CTA.  This form fits three: the Q / dO blocks of an entry (with their lse and delta) come
+// through a two-stage per-warp cp.async ring and are read as mma operands straight from shared memory
+// (128-bit loads for the channel contraction, ldmatrix.trans for the row contraction, so no fragment
+// is held across the entry and none is transposed in registers), and a warp parks only the tile of the
+// bucket it shares with EARLIER warps; the tile it shares with later warps stays in its accumulators
+// until the CTA has synchronised and is then completed from the later warps' parked tiles.
+// Accumulator layout (ldmatrix): tile u holds channels 8u + 2t, 8u + 2t + 1 of keys g (c0, c1) and g + 8 (c2, c3).
+constexpr int kRingFineStages = 2;
+constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16) + 128;   // Q tile, dO tile, 16 lse, 16 delta
+constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
+
+// Shared-memory accesses as [32-bit shared address + compile-time offset]: the per-lane part of every address is computed
+// once per kernel, the stage / tile / row part is an immediate, and the entry loop spends no integer instruction on them.
+template <int IMM>
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t sa) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(sa), "n"(IMM));
+}
+template <int IMM>
+__device__ __forceinline__ void lds128(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t sa) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(sa), "n"(IMM));
+}
+template <int IMM>
+__device__ __forceinline__ float2 lds64f(uint32_t sa) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(sa), "n"(IMM));
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ void cp_async16_sa(uint32_t sa, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0+%1], [%2], 16;" ::"r"(sa), "n"(IMM), "l"(gsrc) : "memory");
+}
+// RowFrag of tile row (g or g+8: ROWOFF) from a swizzled ring tile: chunks 2t and 2t+1 of the row sit at sa0 / sa1
+template <int IMM>
+__device__ __forceinline__ void rowfrag_sa(RowFrag& f, uint32_t sa0, uint32_t sa1) {
+  lds128<IMM>(f.r[0], f.r[1], f.r[2], f.r[3], sa0);
+  lds128<IMM>(f.r[4], f.r[5], f.r[6], f.r[7], sa1);
+}
+// D = A.B (no accumulator input: the zero is the hardware zero register, not sixteen moves per entry)
+__device__ __forceinline__ void mma_bf16_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void mma_rows_x_keys_z(float (&s0)[4], float (&s1)[4], const RowFrag& alo, const RowFrag& ahi, const RowFrag& k0,
+                                                  const RowFrag& k1) {
+  mma_bf16_16816_z(s0, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], k0.r[0], k0.r[1]);
+  mma_bf16_16816_z(s1, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], k1.r[0], k1.r[1]);
+#pragma unroll
+  for (int s = 1; s < 4; ++s) {
+    mma_bf16_16816(s0, alo.r[2 * s], ahi.r[2 * s], alo.r[2 * s + 1], ahi.r[2 * s + 1], k0.r[2 * s], k0.r[2 * s + 1]);
+    mma_bf16_16816(s1, alo.r[2 * s], ahi.r[2 * s], alo.r[2 * s + 1], ahi.r[2 * s + 1], k1.r[2 * s], k1.r[2 * s + 1]);
+  }
+}
+
+// Pooling-backward fold and scale for the ldmatrix accumulator layout: afterwards dk / dv hold the final fp32 values.
+__device__ __forceinline__ void dkv_fine_fold_ld(const AttnP<bf16>& a, int64_t bh, int64_t j, float (&dk)[8][4], float (&dv)[8][4], int t) {
+  if (a.fold) {
+    const float* g1k = a.dpk + (bh * a.n1 + j) * kD + 2 * t;
+    const float* g1v = a.dpv + (bh * a.n1 + j) * kD + 2 * t;
+    const float* g2k = a.two_level ? a.dpk2 + (bh * a.n2 + j / kBS) * kD + 2 * t : nullptr;
+    const float* g2v = a.two_level ? a.dpv2 + (bh * a.n2 + j / kBS) * kD + 2 * t : nullptr;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float2 ek = *reinterpret_cast<const float2*>(g1k + 8 * u), ev = *reinterpret_cast<const float2*>(g1v + 8 * u);
+      if (a.two_level) {
+        const float2 fk = *reinterpret_cast<const float2*>(g2k + 8 * u), fv = *reinterpret_cast<const float2*>(g2v + 8 * u);
+        ek.x += fk.x * (1.f / kBS); ek.y += fk.y * (1.f / kBS); ev.x += fv.x * (1.f / kBS); ev.y += fv.y * (1.f / kBS);
+      }
+      dk[u][0] = dk[u][0] * a.scale + ek.x * (1.f / kBS); dk[u][1] = dk[u][1] * a.scale + ek.y * (1.f / kBS);
+      dk[u][2] = dk[u][2] * a.scale + ek.x * (1.f / kBS); dk[u][3] = dk[u][3] * a.scale + ek.y * (1.f / kBS);
+      dv[u][0] += ev.x * (1.f / kBS); dv[u][1] += ev.y * (1.f / kBS); dv[u][2] += ev.x * (1.f / kBS); dv[u][3] += ev.y * (1.f / kBS);
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { dk[u][0] *= a.scale; dk[u][1] *= a.scale; dk[u][2] *= a.scale; dk[u][3] *= a.scale; }
+  }
+}
+
+// The same from this warp's copy of the four gradient rows in shared memory ([dpk | dpv | dpk2 | dpv2] x 64 fp32, fetched with
+// cp.async when the bucket began); sa_fold already includes the lane's 8t bytes.
+__device__ __forceinline__ void dkv_fine_fold_smem(const AttnP<bf16>& a, uint32_t sa_fold, float (&dk)[8][4], float (&dv)[8][4]) {
+  if (a.fold) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float2 ek, ev;
+      if (u == 0) { ek = lds64f<0>(sa_fold); ev = lds64f<256>(sa_fold); }
+      if (u == 1) { ek = lds64f<32>(sa_fold); ev = lds64f<256 + 32>(sa_fold); }
+      if (u == 2) { ek = lds64f<64>(sa_fold); ev = lds64f<256 + 64>(sa_fold); }
+      if (u == 3) { ek = lds64f<96>(sa_fold); ev = lds64f<256 + 96>(sa_fold); }
+      if (u == 4) { ek = lds64f<128>(sa_fold); ev = lds64f<256 + 128>(sa_fold); }
+      if (u == 5) { ek = lds64f<160>(sa_fold); ev = lds64f<256 + 160>(sa_fold); }
+      if (u == 6) { ek = lds64f<192>(sa_fold); ev = lds64f<256 + 192>(sa_fold); }
+      if (u == 7) { ek = lds64f<224>(sa_fold); ev = lds64f<256 + 224>(sa_fold); }
+      if (a.two_level) {
+        float2 fk, fv;
+        if (u == 0) { fk = lds64f<512>(sa_fold); fv = lds64f<768>(sa_fold); }
+        if (u == 1) { fk = lds64f<512 + 32>(sa_fold); fv = lds64f<768 + 32>(sa_fold); }
+        if (u == 2) { fk = lds64f<512 + 64>(sa_fold); fv = lds64f<768 + 64>(sa_fold); }
+        if (u == 3) { fk = lds64f<512 + 96>(sa_fold); fv = lds64f<768 + 96>(sa_fold); }
+        if (u == 4) { fk = lds64f<512 + 128>(sa_fold); fv = lds64f<768 + 128>(sa_fold); }
+        if (u == 5) { fk = lds64f<512 + 160>(sa_fold); fv = lds64f<768 + 160>(sa_fold); }
+        if (u == 6) { fk = lds64f<512 + 192>(sa_fold); fv = lds64f<768 + 192>(sa_fold); }
+        if (u == 7) { fk = lds64f<512 + 224>(sa_fold); fv = lds64f<768 + 224>(sa_fold); }
+        ek.x += fk.x * (1.f / kBS); ek.y += fk.y * (1.f / kBS); ev.x += fv.x * (1.f / kBS); ev.y += fv.y * (1.f / kBS);
+      }
+      dk[u][0] = dk[u][0] * a.scale + ek.x * (1.f / kBS); dk[u][1] = dk[u][1] * a.scale + ek.y * (1.f / kBS);
+      dk[u][2] = dk[u][2] * a.scale + ek.x * (1.f / kBS); dk[u][3] = dk[u][3] * a.scale + ek.y * (1.f / kBS);
+      dv[u][0] += ev.x * (1.f / kBS); dv[u][1] += ev.y * (1.f / kBS); dv[u][2] += ev.x * (1.f / kBS); dv[u][3] += ev.y * (1.f / kBS);
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { dk[u][0] *= a.scale; dk[u][1] *= a.scale; dk[u][2] *= a.scale; dk[u][3] *= a.scale; }
+  }
+}
+
+// Direct store of a finished tile from the ldmatrix layout: a lane owns two channels per 8-channel group, so these are
+// 4-byte stores (the finish kernel's rare path; the main kernel goes through stmatrix below).
+__device__ __forceinline__ void dkv_fine_store_ld(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t j, float (&dk)[8][4],
+                                                  float (&dv)[8][4], int g, int t) {
+  dkv_fine_fold_ld(a, bh, j, dk, dv, t);
+  bf16* k0 = a.dk.row(b, h, j * kBS + g) + 2 * t;
+  bf16* k1 = a.dk.row(b, h, j * kBS + g + 8) + 2 * t;
+  bf16* v0 = a.dv.row(b, h, j * kBS + g) + 2 * t;
+  bf16* v1 = a.dv.row(b, h, j * kBS + g + 8) + 2 * t;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    *reinterpret_cast<uint32_t*>(k0 + 8 * u) = pack_bf16(dk[u][0], dk[u][1]);
+    *reinterpret_cast<uint32_t*>(k1 + 8 * u) = pack_bf16(dk[u][2], dk[u][3]);
+    *reinterpret_cast<uint32_t*>(v0 + 8 * u) = pack_bf16(dv[u][0], dv[u][1]);
+    *reinterpret_cast<uint32_t*>(v1 + 8 * u) = pack_bf16(dv[u][2], dv[u][3]);
+  }
+}
+
+template <int IMM>
+__device__ __forceinline__ void stsm_x4(uint32_t sa, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0+%1], {%2,%3,%4,%5};" ::"r"(sa), "n"(IMM), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+
+// Store of a finished tile through a free ring stage at byte offset SB: stmatrix writes the bf16 tile in the ring's swizzled row
+// layout (the ldmatrix addresses sa_m), every lane reads back four 16-byte chunks per tensor (the cp.async addresses sa_cp0 /
+// sa_cp1) and eight lanes write one whole 128-byte row: full sectors, 8 store instructions instead of 32.
+template <int SB>
+__device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t j, float (&dk)[8][4],
+                                                      float (&dv)[8][4], const uint32_t (&sa_m)[4], uint32_t sa_cp0, uint32_t sa_cp1,
+                                                      uint32_t sa_fold, int lane) {
+  constexpr int TB = kRingTileElems * (int) sizeof(bf16);
+  dkv_fine_fold_smem(a, sa_fold, dk, dv);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    stsm_x4<SB>(sa_m[c], pack_bf16(dk[2 * c][0], dk[2 * c][1]), pack_bf16(dk[2 * c][2], dk[2 * c][3]),
+                pack_bf16(dk[2 * c + 1][0], dk[2 * c + 1][1]), pack_bf16(dk[2 * c + 1][2], dk[2 * c + 1][3]));
+    stsm_x4<SB + TB>(sa_m[c], pack_bf16(dv[2 * c][0], dv[2 * c][1]), pack_bf16(dv[2 * c][2], dv[2 * c][3]),
+                     pack_bf16(dv[2 * c + 1][0], dv[2 * c + 1][1]), pack_bf16(dv[2 * c + 1][2], dv[2 * c + 1][3]));
+  }
+  __syncwarp();
+  bf16* kp = a.dk.row(b, h, j * kBS + (lane >> 3)) + (lane & 7) * 8;
+  bf16* vp = a.dv.row(b, h, j * kBS + (lane >> 3)) + (lane & 7) * 8;
+  const int64_t ks = 4 * a.dk.sn, vs = 4 * a.dv.sn;
+  uint4 x;
+  lds128<SB>(x.x, x.y, x.z, x.w, sa_cp0);             *reinterpret_cast<uint4*>(kp) = x;
+  lds128<SB + 512>(x.x, x.y, x.z, x.w, sa_cp1);       *reinterpret_cast<uint4*>(kp + ks) = x;
+  lds128<SB + 1024>(x.x, x.y, x.z, x.w, sa_cp0);      *reinterpret_cast<uint4*>(kp + 2 * ks) = x;
+  lds128<SB + 1536>(x.x, x.y, x.z, x.w, sa_cp1);      *reinterpret_cast<uint4*>(kp + 3 * ks) = x;
+  lds128<SB + TB>(x.x, x.y, x.z, x.w, sa_cp0);        *reinterpret_cast<uint4*>(vp) = x;
+  lds128<SB + TB + 512>(x.x, x.y, x.z, x.w, sa_cp1);  *reinterpret_cast<uint4*>(vp + vs) = x;
+  lds128<SB + TB + 1024>(x.x, x.y, x.z, x.w, sa_cp0); *reinterpret_cast<uint4*>(vp + 2 * vs) = x;
+  lds128<SB + TB + 1536>(x.x, x.y, x.z, x.w, sa_cp1); *reinterpret_cast<uint4*>(vp + 3 * vs) = x;
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // the swizzle arithmetic below works on absolute shared addresses: start at a 128-byte boundary (the launch adds 128 bytes)
+  unsigned char* smem = smem_raw + ((128u - ((uint32_t) __cvta_generic_to_shared(smem_raw) & 127u)) & 127u);
+  float* slots = reinterpret_cast<float*>(smem);            // [kFineWarps][kTileFloats]: tile of the bucket a warp shares with earlier warps
+  __shared__ int s_head_bucket[kFineWarps];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  unsigned char* ring = smem + kFineWarps * kTileFloats * sizeof(float) + warp * (kRingFineStages * kRingFineStageBytes);
+  // this warp's copy of the pooled-gradient rows its current bucket folds in: 4 rows x 256 bytes
+  const uint32_t sa_foldbuf = (uint32_t) __cvta_generic_to_shared(smem + kFineWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes)) + warp * kRingFoldBytes;
+  const uint32_t sa_fold = sa_foldbuf + 8 * t;
+  const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const float sl2 = a.scale * kLog2e;
+  const int E = (int) (a.nq1 * a.topk);
+  const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E);
+  constexpr int L = kFineWindow / kFineWarps;
+  const int rb = cb + warp * L, re = min(rb + L, ce);
+  const int32_t* fl = a.flat + bh * (int64_t) E;
+  if (threadIdx.x < kFineWarps) s_head_bucket[threadIdx.x] = -1;
+  __syncthreads();
+
+  // Per-lane shared addresses, computed once (the ring is 128-byte aligned, so the chunk index of an address is its bits 4..6
+  // and a swizzle partner is one XOR away):
+  //   sa_cp0 / sa_cp1  where this lane's cp.async chunks of tile rows (lane/8) + {0, 8} / + {4, 12} land
+  //   sa_f0 / sa_f1    chunks 2t / 2t+1 of tile row g (row g+8: +1024), the channel-contraction fragments
+  //   sa_m[c]          ldmatrix.trans row address for output channels 16c..16c+15
+  //   sa_st            lse / delta of query rows 2t, 2t+1
+  const uint32_t ring_sa = (uint32_t) __cvta_generic_to_shared(ring);
+  const uint32_t sa_cp0 = ring_sa + (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4), sa_cp1 = sa_cp0 ^ 64;
+  const uint32_t sa_f0 = ring_sa + g * 128 + (((2 * t) ^ g) << 4), sa_f1 = sa_f0 ^ 16;
+  uint32_t sa_m[4];
+  {
+    const int lr = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const uint32_t base = ring_sa + lr * 128 + (((lane >> 4) ^ (lane & 7)) << 4);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) sa_m[c] = base ^ (c << 5);
+  }
+  float dk[8][4], dv[8][4];
+  int tail_j = -1;                          // bucket whose tile is still in dk / dv after the loop
+  if (rb < re) {
+    // bucket of entry rb (off[j] <= rb < off[j+1]) by a 32-way search: every round the lanes probe 32 evenly spaced offsets,
+    // so n1 = 1024 costs two dependent loads instead of ten
+    int lo = 0, span = (int) a.n1;          // invariant: off[lo] <= rb < off[lo + span]
+    while (span > 1) {
+      const int step = (span + 31) >> 5;
+      const int probe = lo + lane * step;
+      const bool le = probe < lo + span && (int) csr_off(a, bh, probe) <= rb;
+      const int last = 31 - __clz((int) __ballot_sync(0xffffffffu, le));     // lane 0 always qualifies
+      const int nlo = lo + last * step;
+      span = min(step, lo + span - nlo);
+      lo = nlo;
+    }
+    int j = lo;
+    int bo = (int) csr_off(a, bh, j), nxt = (int) csr_off(a, bh, j + 1);
+    int nxt2 = j + 2 <= (int) a.n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;      // one bucket ahead: no load to wait for at a switch
+    RowFrag ka, kb, va, vb;
+    auto load_kv = [&](int jj) {
+      const bf16* kp = a.k.row(b, h, (int64_t) jj * kBS);
+      const bf16* vp = a.v.row(b, h, (int64_t) jj * kBS);
+      load_rowfrag(ka, kp + (int64_t) g * a.k.sn, t);
+      load_rowfrag(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
+      load_rowfrag(va, vp + (int64_t) g * a.v.sn, t);
+      load_rowfrag(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
+    };
+    // what the NEXT bucket switch will wait for, pulled towards the SM while this bucket is being worked on: the K / V rows of the
+    // following KV block (one 128-byte row per lane) and the pooled-gradient rows that this bucket's store folds in
+    auto prefetch_next = [&](int jj) {
+      if (jj + 1 < (int) a.n1) {
+        const bf16* row = lane < 16 ? a.k.row(b, h, (int64_t) (jj + 1) * kBS + lane) : a.v.row(b, h, (int64_t) (jj + 1) * kBS + lane - 16);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(row));
+      }
+      if (a.fold) {     // lands with the entry group that is committed next; the bucket's store comes at least an entry later
+        const float* l1 = (lane < 16 ? a.dpk : a.dpv) + (bh * a.n1 + jj) * kD + (lane & 15) * 4;
+        cp_async16_sa<0>(sa_foldbuf + lane * 16, l1);
+        if (a.two_level) {
+          const float* l2 = (lane < 16 ? a.dpk2 : a.dpv2) + (bh * a.n2 + jj / kBS) * kD + (lane & 15) * 4;
+          cp_async16_sa<512>(sa_foldbuf + lane * 16, l2);
+        }
+      }
+    };
+    const uint32_t sa_st = ring_sa + 2 * kRingTileElems * (int) sizeof(bf16) + 8 * t;
+    const uint32_t sa_stat = ring_sa + 2 * kRingTileElems * (int) sizeof(bf16) + lane * 16;
+    // global side: row (lane/8), chunk (lane%8) of block 0; a block is qblk / dblk bytes further, four rows qstep / dstep bytes
+    const char* q_lane = reinterpret_cast<const char*>(a.q.row(b, h, lane >> 3) + (lane & 7) * 8);
+    const char* d_lane = reinterpret_cast<const char*>(a.d_o.row(b, h, lane >> 3) + (lane & 7) * 8);
+    const char* stat = reinterpret_cast<const char*>((lane < 4 ? a.lse : a.delta) + bh * a.Nq + (lane & 3) * 4);
+    const int qblk = (int) (kBS * a.q.sn * sizeof(bf16)), dblk = (int) (kBS * a.d_o.sn * sizeof(bf16));
+    const int64_t qstep = 4 * a.q.sn * (int64_t) sizeof(bf16), dstep = 4 * a.d_o.sn * (int64_t) sizeof(bf16);
+    auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.nq1 ? (int) a.nq1 - 1 : v); };
+    auto issue = [&](auto stage_tag, int qb) {
+      constexpr int SB = decltype(stage_tag)::value * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
+      const char* qp = q_lane + (int64_t) qb * qblk;
+      const char* dp = d_lane + (int64_t) qb * dblk;
+      cp_async16_sa<SB>(sa_cp0, qp);
+      cp_async16_sa<SB + 512>(sa_cp1, qp + qstep);
+      cp_async16_sa<SB + 1024>(sa_cp0, qp + 2 * qstep);
+      cp_async16_sa<SB + 1536>(sa_cp1, qp + 3 * qstep);
+      cp_async16_sa<SB + TB>(sa_cp0, dp);
+      cp_async16_sa<SB + TB + 512>(sa_cp1, dp + dstep);
+      cp_async16_sa<SB + TB + 1024>(sa_cp0, dp + 2 * dstep);
+      cp_async16_sa<SB + TB + 1536>(sa_cp1, dp + 3 * dstep);
+      if (lane < 8) cp_async16_sa<SB>(sa_stat, stat + (int64_t) qb * (kBS * (int) sizeof(float)));
+    };
+    int qb_nxt = rb + 1 < re ? clampq(fl[rb + 1]) : 0;
+    issue(std::integral_constant<int, 0>{}, clampq(fl[rb]));
+    cp_async_commit();
+    load_kv(j);
+    prefetch_next(j);
+    tile_zero(dk, dv);
+    // one entry; the ring stage is a template argument so that every shared-memory offset below is an immediate
+    auto entry = [&](auto stage_tag, int e) {
+      constexpr int S = decltype(stage_tag)::value;
+      constexpr int SB = S * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
+      cp_async_wait_all();                  // entry e has landed (this lane's chunks) ...
+      __syncwarp();                         // ... and everybody else's; the other stage was read an entry ago
+      if (e >= nxt) {                       // next non-empty bucket; the other stage is free until the copies below: it stages the store
+        if (bo >= rb) {
+          dkv_fine_store_staged<(1 - S) * kRingFineStageBytes>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+        } else {
+          tile_to_mem(slots + warp * kTileFloats, dk, dv, lane);   // began in an earlier warp's range
+          if (lane == 0) s_head_bucket[warp] = j;
+        }
+        ++j; bo = nxt; nxt = nxt2;
+        while (nxt <= e) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }      // empty buckets
+        nxt2 = j + 2 <= (int) a.n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;
+        load_kv(j);
+        prefetch_next(j);
+        tile_zero(dk, dv);
+      }
+      if (e + 1 < re) {
+        issue(std::integral_constant<int, 1 - S>{}, qb_nxt);
+        qb_nxt = e + 2 < re ? clampq(fl[e + 2]) : 0;
+      }
+      cp_async_commit();
+      float s0[4], s1[4], e0[4], e1[4];
+      {
+        RowFrag x0, x1;
+        rowfrag_sa<SB>(x0, sa_f0, sa_f1);
+        rowfrag_sa<SB + 1024>(x1, sa_f0, sa_f1);
+        mma_rows_x_keys_z(s0, s1, ka, kb, x0, x1);
+        rowfrag_sa<SB + TB>(x0, sa_f0, sa_f1);
+        rowfrag_sa<SB + TB + 1024>(x1, sa_f0, sa_f1);
+        mma_rows_x_keys_z(e0, e1, va, vb, x0, x1);
+      }
+      const float2 la = lds64f<SB>(sa_st), lb = lds64f<SB + 32>(sa_st), da = lds64f<SB + 64>(sa_st), db = lds64f<SB + 96>(sa_st);
+      uint32_t pa[4], ea[4];
+      dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, 0.f, pa, ea);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans<SB + TB>(r0, r1, r2, r3, sa_m[c]);
+        mma_bf16_16816(dv[2 * c], pa[0], pa[1], pa[2], pa[3], r0, r1);
+        mma_bf16_16816(dv[2 * c + 1], pa[0], pa[1], pa[2], pa[3], r2, r3);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans<SB>(r0, r1, r2, r3, sa_m[c]);
+        mma_bf16_16816(dk[2 * c], ea[0], ea[1], ea[2], ea[3], r0, r1);
+        mma_bf16_16816(dk[2 * c + 1], ea[0], ea[1], ea[2], ea[3], r2, r3);
+      }
+    };
+    for (int e = rb; e < re; e += 2) {
+      entry(std::integral_constant<int, 0>{}, e);
+      if (e + 1 < re) entry(std::integral_constant<int, 1>{}, e + 1);
+    }
+    cp_async_wait_all();                    // the last bucket's gradient rows
+    __syncwarp();
+    // the last bucket of the range (the ring is idle by now)
+    if (bo >= rb && nxt <= re) {
+      dkv_fine_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+    } else if (bo < rb) {                   // the whole range lies inside one bucket that began earlier
+      tile_to_mem(slots + warp * kTileFloats, dk, dv, lane);
+      if (lane == 0) s_head_bucket[warp] = j;
+    } else {
+      tail_j = j;                           // continues in later warps (or windows): completed below
+    }
+  }
+  __syncthreads();
+  if (tail_j >= 0) {
+    for (int w = warp + 1; w < kFineWarps && s_head_bucket[w] == tail_j; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
+    if ((int) csr_off(a, bh, tail_j + 1) <= ce) {
+      dkv_fine_store_staged<0>(a, b, h, tail_j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+    } else {                                // runs on into the next window: this window's tail slot
+      tile_to_mem(partial + ((bh * gridDim.x + blockIdx.x) * 2 + 1) * (int64_t) kTileFloats, dk, dv, lane);
+    }
+  }
+  if (warp == 0 && s_head_bucket[0] >= 0) { // began in an earlier window: this window's head slot
+    const int j0 = s_head_bucket[0];
+    tile_zero(dk, dv);
+    for (int w = 0; w < kFineWarps && s_head_bucket[w] == j0; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
+    tile_to_mem(partial + ((bh * gridDim.x + blockIdx.x) * 2 + 0) * (int64_t) kTileFloats, dk, dv, lane);
+  }
+}
+
+template <bool LD>
+__global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, const float* __restrict__ partial, int n_windows) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int64_t j = (int64_t) blockIdx.x * 4 + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  if (j >= a.n1) return;
+  const int bo = (int) csr_off(a, bh, j), be = (int) csr_off(a, bh, j + 1);
+  const int c_first = bo / kFineWindow, c_last = (be - 1) / kFineWindow;
+  if (be > bo && c_first == c_last) return;          // finished inside one window
+  float dk[8][4], dv[8][4];
+  tile_zero(dk, dv);
+  if (be > bo)
+    for (int c = c_first; c <= c_last; ++c)
+      tile_add_mem(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
+  dkv_fine_store_ld(a, b, h, bh, j, dk, dv, g, t);
+}
+
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st);
 
 int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
@@ -671,12 +1058,22 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     const int64_t E = a.nq1 * a.topk;
     const int n_windows = (int) ((E + kFineWindow - 1) / kFineWindow);
     float* partial = (float*) g->dkv_partial->ptr;
-    const size_t smem = (size_t) kFineWarps * 2 * kTileFloats * sizeof(float);
-    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-    attn_dkv_fine_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
-    LLSA_LAUNCH_OK("attn_dkv_fine_kernel");
-    attn_dkv_finish_kernel<<<dim3((unsigned) ((a.n1 + 3) / 4), BH), 128, 0, st>>>(a, partial, n_windows);
-    LLSA_LAUNCH_OK("attn_dkv_finish_kernel");
+    const char* form = getenv("LLSA_B200_DKV_FINE");      // "regs": the two-CTA form that keeps the fragments in registers
+    if (!(form && form[0] == 'r' && form[1] == 'e')) {
+      const size_t smem = (size_t) kFineWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
+      LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");
+      attn_dkv_finish_ld_kernel<true><<<dim3((unsigned) ((a.n1 + 3) / 4), BH), 128, 0, st>>>(a, partial, n_windows);
+      LLSA_LAUNCH_OK("attn_dkv_finish_ld_kernel");
+    } else {
+      const size_t smem = (size_t) kFineWarps * 2 * kTileFloats * sizeof(float);
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      attn_dkv_fine_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
+      LLSA_LAUNCH_OK("attn_dkv_fine_kernel");
+      attn_dkv_finish_kernel<<<dim3((unsigned) ((a.n1 + 3) / 4), BH), 128, 0, st>>>(a, partial, n_windows);
+      LLSA_LAUNCH_OK("attn_dkv_finish_kernel");
+    }
   }
   return LLSA_OK;
 }
