@@ -651,6 +651,7 @@ __device__ __forceinline__ void rowfrag_sa(RowFrag& f, uint32_t sa0, uint32_t sa
   lds128<IMM>(f.r[0], f.r[1], f.r[2], f.r[3], sa0);
   lds128<IMM>(f.r[4], f.r[5], f.r[6], f.r[7], sa1);
 }
+// (see half_rows_x_keys below)
 // D = A.B (no accumulator input: the zero is the hardware zero register, not sixteen moves per entry)
 __device__ __forceinline__ void mma_bf16_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -658,6 +659,25 @@ __device__ __forceinline__ void mma_bf16_16816_z(float (&d)[4], uint32_t a0, uin
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
+// Half of mma_rows_x_keys straight from a ring tile at byte offset IMM: the 128-bit chunk at `sa` (row g) and at sa + 1024 (row g + 8)
+// carries k-steps 0, 1 (FIRST, which also initialises the accumulators) or 2, 3 of the channel contraction.
+template <int IMM, bool FIRST>
+__device__ __forceinline__ void half_rows_x_keys(float (&s0)[4], float (&s1)[4], const RowFrag& alo, const RowFrag& ahi, uint32_t sa) {
+  uint32_t x0[4], x1[4];
+  lds128<IMM>(x0[0], x0[1], x0[2], x0[3], sa);
+  lds128<IMM + 1024>(x1[0], x1[1], x1[2], x1[3], sa);
+  constexpr int o = FIRST ? 0 : 4;
+  if (FIRST) {
+    mma_bf16_16816_z(s0, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], x0[0], x0[1]);
+    mma_bf16_16816_z(s1, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], x1[0], x1[1]);
+  } else {
+    mma_bf16_16816(s0, alo.r[o], ahi.r[o], alo.r[o + 1], ahi.r[o + 1], x0[0], x0[1]);
+    mma_bf16_16816(s1, alo.r[o], ahi.r[o], alo.r[o + 1], ahi.r[o + 1], x1[0], x1[1]);
+  }
+  mma_bf16_16816(s0, alo.r[o + 2], ahi.r[o + 2], alo.r[o + 3], ahi.r[o + 3], x0[2], x0[3]);
+  mma_bf16_16816(s1, alo.r[o + 2], ahi.r[o + 2], alo.r[o + 3], ahi.r[o + 3], x1[2], x1[3]);
+}
+
 __device__ __forceinline__ void mma_rows_x_keys_z(float (&s0)[4], float (&s1)[4], const RowFrag& alo, const RowFrag& ahi, const RowFrag& k0,
                                                   const RowFrag& k1) {
   mma_bf16_16816_z(s0, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], k0.r[0], k0.r[1]);
@@ -792,10 +812,9 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
   float* slots = reinterpret_cast<float*>(smem);            // [kFineWarps][kTileFloats]: tile of the bucket a warp shares with earlier warps
   __shared__ int s_head_bucket[kFineWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  unsigned char* ring = smem + kFineWarps * kTileFloats * sizeof(float) + warp * (kRingFineStages * kRingFineStageBytes);
-  // this warp's copy of the pooled-gradient rows its current bucket folds in: 4 rows x 256 bytes
-  const uint32_t sa_foldbuf = (uint32_t) __cvta_generic_to_shared(smem + kFineWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes)) + warp * kRingFoldBytes;
-  const uint32_t sa_fold = sa_foldbuf + 8 * t;
+  // per warp: the ring stages, then its copy of the pooled-gradient rows the current bucket folds in (4 rows x 256 bytes)
+  constexpr int kWarpBytes = kRingFineStages * kRingFineStageBytes + kRingFoldBytes;
+  unsigned char* ring = smem + kFineWarps * kTileFloats * sizeof(float) + warp * kWarpBytes;
   const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const float sl2 = a.scale * kLog2e;
   const int E = (int) (a.nq1 * a.topk);
@@ -813,6 +832,8 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
   //   sa_m[c]          ldmatrix.trans row address for output channels 16c..16c+15
   //   sa_st            lse / delta of query rows 2t, 2t+1
   const uint32_t ring_sa = (uint32_t) __cvta_generic_to_shared(ring);
+  const uint32_t sa_t8 = ring_sa + 8 * t, sa_l16 = ring_sa + lane * 16;      // + immediates: lse / delta / gradient rows
+  const uint32_t sa_fold = sa_t8 + kRingFineStages * kRingFineStageBytes;
   const uint32_t sa_cp0 = ring_sa + (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4), sa_cp1 = sa_cp0 ^ 64;
   const uint32_t sa_f0 = ring_sa + g * 128 + (((2 * t) ^ g) << 4), sa_f1 = sa_f0 ^ 16;
   uint32_t sa_m[4];
@@ -844,10 +865,10 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
     auto load_kv = [&](int jj) {
       const bf16* kp = a.k.row(b, h, (int64_t) jj * kBS);
       const bf16* vp = a.v.row(b, h, (int64_t) jj * kBS);
-      load_rowfrag(ka, kp + (int64_t) g * a.k.sn, t);
-      load_rowfrag(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
-      load_rowfrag(va, vp + (int64_t) g * a.v.sn, t);
-      load_rowfrag(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
+      load_rowfrag_cg(ka, kp + (int64_t) g * a.k.sn, t);
+      load_rowfrag_cg(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
+      load_rowfrag_cg(va, vp + (int64_t) g * a.v.sn, t);
+      load_rowfrag_cg(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
     };
     // what the NEXT bucket switch will wait for, pulled towards the SM while this bucket is being worked on: the K / V rows of the
     // following KV block (one 128-byte row per lane) and the pooled-gradient rows that this bucket's store folds in
@@ -858,23 +879,22 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
       }
       if (a.fold) {     // lands with the entry group that is committed next; the bucket's store comes at least an entry later
         const float* l1 = (lane < 16 ? a.dpk : a.dpv) + (bh * a.n1 + jj) * kD + (lane & 15) * 4;
-        cp_async16_sa<0>(sa_foldbuf + lane * 16, l1);
+        cp_async16_sa<kRingFineStages * kRingFineStageBytes>(sa_l16, l1);
         if (a.two_level) {
           const float* l2 = (lane < 16 ? a.dpk2 : a.dpv2) + (bh * a.n2 + jj / kBS) * kD + (lane & 15) * 4;
-          cp_async16_sa<512>(sa_foldbuf + lane * 16, l2);
+          cp_async16_sa<kRingFineStages * kRingFineStageBytes + 512>(sa_l16, l2);
         }
       }
     };
-    const uint32_t sa_st = ring_sa + 2 * kRingTileElems * (int) sizeof(bf16) + 8 * t;
-    const uint32_t sa_stat = ring_sa + 2 * kRingTileElems * (int) sizeof(bf16) + lane * 16;
     // global side: row (lane/8), chunk (lane%8) of block 0; a block is qblk / dblk bytes further, four rows qstep / dstep bytes
     const char* q_lane = reinterpret_cast<const char*>(a.q.row(b, h, lane >> 3) + (lane & 7) * 8);
     const char* d_lane = reinterpret_cast<const char*>(a.d_o.row(b, h, lane >> 3) + (lane & 7) * 8);
     const char* stat = reinterpret_cast<const char*>((lane < 4 ? a.lse : a.delta) + bh * a.Nq + (lane & 3) * 4);
     const int qblk = (int) (kBS * a.q.sn * sizeof(bf16)), dblk = (int) (kBS * a.d_o.sn * sizeof(bf16));
-    const int64_t qstep = 4 * a.q.sn * (int64_t) sizeof(bf16), dstep = 4 * a.d_o.sn * (int64_t) sizeof(bf16);
+    const int qstep = (int) (4 * a.q.sn * sizeof(bf16)), dstep = (int) (4 * a.d_o.sn * sizeof(bf16));
     auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.nq1 ? (int) a.nq1 - 1 : v); };
-    auto issue = [&](auto stage_tag, int qb) {
+    auto issue = [&](auto stage_tag, int qb_raw) {
+      const int qb = clampq(qb_raw);        // clamped here, an entry after the load: nothing waits for the index
       constexpr int SB = decltype(stage_tag)::value * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
       const char* qp = q_lane + (int64_t) qb * qblk;
       const char* dp = d_lane + (int64_t) qb * dblk;
@@ -886,10 +906,10 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
       cp_async16_sa<SB + TB + 512>(sa_cp1, dp + dstep);
       cp_async16_sa<SB + TB + 1024>(sa_cp0, dp + 2 * dstep);
       cp_async16_sa<SB + TB + 1536>(sa_cp1, dp + 3 * dstep);
-      if (lane < 8) cp_async16_sa<SB>(sa_stat, stat + (int64_t) qb * (kBS * (int) sizeof(float)));
+      if (lane < 8) cp_async16_sa<SB + 2 * TB>(sa_l16, stat + (int64_t) qb * (kBS * (int) sizeof(float)));
     };
-    int qb_nxt = rb + 1 < re ? clampq(fl[rb + 1]) : 0;
-    issue(std::integral_constant<int, 0>{}, clampq(fl[rb]));
+    int qb_nxt = rb + 1 < re ? __ldcg(fl + rb + 1) : 0;
+    issue(std::integral_constant<int, 0>{}, __ldcg(fl + rb));
     cp_async_commit();
     load_kv(j);
     prefetch_next(j);
@@ -916,20 +936,17 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
       }
       if (e + 1 < re) {
         issue(std::integral_constant<int, 1 - S>{}, qb_nxt);
-        qb_nxt = e + 2 < re ? clampq(fl[e + 2]) : 0;
+        qb_nxt = e + 2 < re ? __ldcg(fl + e + 2) : 0;
       }
       cp_async_commit();
       float s0[4], s1[4], e0[4], e1[4];
-      {
-        RowFrag x0, x1;
-        rowfrag_sa<SB>(x0, sa_f0, sa_f1);
-        rowfrag_sa<SB + 1024>(x1, sa_f0, sa_f1);
-        mma_rows_x_keys_z(s0, s1, ka, kb, x0, x1);
-        rowfrag_sa<SB + TB>(x0, sa_f0, sa_f1);
-        rowfrag_sa<SB + TB + 1024>(x1, sa_f0, sa_f1);
-        mma_rows_x_keys_z(e0, e1, va, vb, x0, x1);
-      }
-      const float2 la = lds64f<SB>(sa_st), lb = lds64f<SB + 32>(sa_st), da = lds64f<SB + 64>(sa_st), db = lds64f<SB + 96>(sa_st);
+      // S^T = K.Q^T and dP^T = V.dO^T, two k-steps (32 channels) per pair of 128-bit loads: eight fragment registers live at a time
+      half_rows_x_keys<SB, true>(s0, s1, ka, kb, sa_f0);
+      half_rows_x_keys<SB, false>(s0, s1, ka, kb, sa_f1);
+      half_rows_x_keys<SB + TB, true>(e0, e1, va, vb, sa_f0);
+      half_rows_x_keys<SB + TB, false>(e0, e1, va, vb, sa_f1);
+      const float2 la = lds64f<SB + 2 * TB>(sa_t8), lb = lds64f<SB + 2 * TB + 32>(sa_t8), da = lds64f<SB + 2 * TB + 64>(sa_t8),
+                   db = lds64f<SB + 2 * TB + 96>(sa_t8);
       uint32_t pa[4], ea[4];
       dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, 0.f, pa, ea);
 #pragma unroll
@@ -1060,7 +1077,7 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     float* partial = (float*) g->dkv_partial->ptr;
     const char* form = getenv("LLSA_B200_DKV_FINE");      // "regs": the two-CTA form that keeps the fragments in registers
     if (!(form && form[0] == 'r' && form[1] == 'e')) {
-      const size_t smem = (size_t) kFineWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;
+      const size_t smem = (size_t) kFineWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
       LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
       attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
       LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");

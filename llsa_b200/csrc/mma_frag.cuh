@@ -45,6 +45,13 @@ __device__ __forceinline__ void load_rowfrag(RowFrag& f, const bf16* row, int t)
                : "l"(row + 16 * t));
 }
 
+// The same load without an L1 allocation (L2 only): for kernels whose small L1 must keep other lines
+__device__ __forceinline__ void load_rowfrag_cg(RowFrag& f, const bf16* row, int t) {
+  asm volatile("ld.global.cg.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(f.r[0]), "=r"(f.r[1]), "=r"(f.r[2]), "=r"(f.r[3]), "=r"(f.r[4]), "=r"(f.r[5]), "=r"(f.r[6]), "=r"(f.r[7])
+               : "l"(row + 16 * t));
+}
+
 // The same fragment from a shared-memory tile (rows padded to kSmemPitch elements).
 constexpr int kSmemPitch = 72;   // 144 bytes: consecutive rows shift by 4 banks -> conflict-free 128-bit reads
 __device__ __forceinline__ void load_rowfrag_smem(RowFrag& f, const bf16* row, int t) {
