@@ -624,71 +624,6 @@ constexpr int kRingFineStages = 2;
 constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16) + 128;   // Q tile, dO tile, 16 lse, 16 delta
 constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
 
-// Shared-memory accesses as [32-bit shared address + compile-time offset]: the per-lane part of every address is computed
-// once per kernel, the stage / tile / row part is an immediate, and the entry loop spends no integer instruction on them.
-template <int IMM>
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t sa) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(sa), "n"(IMM));
-}
-template <int IMM>
-__device__ __forceinline__ void lds128(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t sa) {
-  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(sa), "n"(IMM));
-}
-template <int IMM>
-__device__ __forceinline__ float2 lds64f(uint32_t sa) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(sa), "n"(IMM));
-  return v;
-}
-template <int IMM>
-__device__ __forceinline__ void cp_async16_sa(uint32_t sa, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0+%1], [%2], 16;" ::"r"(sa), "n"(IMM), "l"(gsrc) : "memory");
-}
-// RowFrag of tile row (g or g+8: ROWOFF) from a swizzled ring tile: chunks 2t and 2t+1 of the row sit at sa0 / sa1
-template <int IMM>
-__device__ __forceinline__ void rowfrag_sa(RowFrag& f, uint32_t sa0, uint32_t sa1) {
-  lds128<IMM>(f.r[0], f.r[1], f.r[2], f.r[3], sa0);
-  lds128<IMM>(f.r[4], f.r[5], f.r[6], f.r[7], sa1);
-}
-// (see half_rows_x_keys below)
-// D = A.B (no accumulator input: the zero is the hardware zero register, not sixteen moves per entry)
-__device__ __forceinline__ void mma_bf16_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
-// Half of mma_rows_x_keys straight from a ring tile at byte offset IMM: the 128-bit chunk at `sa` (row g) and at sa + 1024 (row g + 8)
-// carries k-steps 0, 1 (FIRST, which also initialises the accumulators) or 2, 3 of the channel contraction.
-template <int IMM, bool FIRST>
-__device__ __forceinline__ void half_rows_x_keys(float (&s0)[4], float (&s1)[4], const RowFrag& alo, const RowFrag& ahi, uint32_t sa) {
-  uint32_t x0[4], x1[4];
-  lds128<IMM>(x0[0], x0[1], x0[2], x0[3], sa);
-  lds128<IMM + 1024>(x1[0], x1[1], x1[2], x1[3], sa);
-  constexpr int o = FIRST ? 0 : 4;
-  if (FIRST) {
-    mma_bf16_16816_z(s0, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], x0[0], x0[1]);
-    mma_bf16_16816_z(s1, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], x1[0], x1[1]);
-  } else {
-    mma_bf16_16816(s0, alo.r[o], ahi.r[o], alo.r[o + 1], ahi.r[o + 1], x0[0], x0[1]);
-    mma_bf16_16816(s1, alo.r[o], ahi.r[o], alo.r[o + 1], ahi.r[o + 1], x1[0], x1[1]);
-  }
-  mma_bf16_16816(s0, alo.r[o + 2], ahi.r[o + 2], alo.r[o + 3], ahi.r[o + 3], x0[2], x0[3]);
-  mma_bf16_16816(s1, alo.r[o + 2], ahi.r[o + 2], alo.r[o + 3], ahi.r[o + 3], x1[2], x1[3]);
-}
-
-__device__ __forceinline__ void mma_rows_x_keys_z(float (&s0)[4], float (&s1)[4], const RowFrag& alo, const RowFrag& ahi, const RowFrag& k0,
-                                                  const RowFrag& k1) {
-  mma_bf16_16816_z(s0, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], k0.r[0], k0.r[1]);
-  mma_bf16_16816_z(s1, alo.r[0], ahi.r[0], alo.r[1], ahi.r[1], k1.r[0], k1.r[1]);
-#pragma unroll
-  for (int s = 1; s < 4; ++s) {
-    mma_bf16_16816(s0, alo.r[2 * s], ahi.r[2 * s], alo.r[2 * s + 1], ahi.r[2 * s + 1], k0.r[2 * s], k0.r[2 * s + 1]);
-    mma_bf16_16816(s1, alo.r[2 * s], ahi.r[2 * s], alo.r[2 * s + 1], ahi.r[2 * s + 1], k1.r[2 * s], k1.r[2 * s + 1]);
-  }
-}
-
 // Pooling-backward fold and scale for the ldmatrix accumulator layout: afterwards dk / dv hold the final fp32 values.
 __device__ __forceinline__ void dkv_fine_fold_ld(const AttnP<bf16>& a, int64_t bh, int64_t j, float (&dk)[8][4], float (&dv)[8][4], int t) {
   if (a.fold) {
@@ -766,11 +701,6 @@ __device__ __forceinline__ void dkv_fine_store_ld(const AttnP<bf16>& a, int64_t 
     *reinterpret_cast<uint32_t*>(v0 + 8 * u) = pack_bf16(dv[u][0], dv[u][1]);
     *reinterpret_cast<uint32_t*>(v1 + 8 * u) = pack_bf16(dv[u][2], dv[u][3]);
   }
-}
-
-template <int IMM>
-__device__ __forceinline__ void stsm_x4(uint32_t sa, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
-  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0+%1], {%2,%3,%4,%5};" ::"r"(sa), "n"(IMM), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
 
 // Store of a finished tile through a free ring stage at byte offset SB: stmatrix writes the bf16 tile in the ring's swizzled row

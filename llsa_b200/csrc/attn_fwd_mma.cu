@@ -18,6 +18,8 @@
 // `l += l_ij * W; acc += P.V * W` in the reference amounts to.
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "attn.cuh"
 #include "mma_frag.cuh"
 
@@ -259,6 +261,140 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine_kernel(AttnP<bf16> a
   }
 }
 
+// ---- eight fine blocks, second form ----------------------------------------------------------------
+// The kernel above spends most of its issue slots around the MMAs: an online-softmax update (maximum, rescale of the 16x64
+// output) per 16-key block, byte permutes for the V operand, run-time ring addresses.  This form, for top-8, takes the blocks in
+// two halves of four: the four S tiles of a half are computed first, the softmax statistics are updated once per half, and P.V
+// follows with V read by ldmatrix.trans.  The sixteen K / V tiles go through a per-warp ring of six 2 KB stages in the order
+// K0..K3 V0..V3 K4..K7 V4..V7, five tiles ahead; the loop is unrolled over the tiles so that every shared-memory offset is an
+// immediate.  The output leaves through stmatrix into a free stage and 128-bit row stores.
+constexpr int kF8Stages = 6;
+constexpr int kF8TileBytes = kRingTileElems * (int) sizeof(bf16);
+
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine8_kernel(AttnP<bf16> a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // the swizzle arithmetic works on absolute shared addresses: start at a 128-byte boundary (the launch adds 128 bytes)
+  const uint32_t smem_sa = ((uint32_t) __cvta_generic_to_shared(smem_raw) + 127u) & ~127u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t ring_sa = smem_sa + warp * (kF8Stages * kF8TileBytes);
+  const uint32_t sa_cp0 = ring_sa + (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4), sa_cp1 = sa_cp0 ^ 64;
+  const uint32_t sa_f0 = ring_sa + g * 128 + (((2 * t) ^ g) << 4), sa_f1 = sa_f0 ^ 16;
+  const uint32_t sa_m = ring_sa + ((lane & 7) + ((lane >> 3) & 1) * 8) * 128 + (((lane >> 4) ^ (lane & 7)) << 4);
+  const int64_t qb = (int64_t) blockIdx.x * NW + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  const int my_fine = lane < 8 ? (int) fine_block(a, bh, qb, lane) : 0;
+  const float sl2 = a.scale * 1.4426950408889634f;
+  const char* k_lane = reinterpret_cast<const char*>(a.k.row(b, h, lane >> 3) + (lane & 7) * 8);
+  const char* v_lane = reinterpret_cast<const char*>(a.v.row(b, h, lane >> 3) + (lane & 7) * 8);
+  const int kblk = (int) (kBS * a.k.sn * sizeof(bf16)), vblk = (int) (kBS * a.v.sn * sizeof(bf16));
+  // tile s of the sequence K0..K3 V0..V3 K4..K7 V4..V7
+  auto issue = [&](auto s_tag) {
+    constexpr int s = decltype(s_tag)::value, blk = (s / 8) * 4 + s % 4, ST = (s % kF8Stages) * kF8TileBytes;
+    constexpr bool is_v = (s % 8) >= 4;
+    const int j = __shfl_sync(0xffffffffu, my_fine, blk);
+    const int blkb = is_v ? vblk : kblk;
+    const char* p = (is_v ? v_lane : k_lane) + (int64_t) j * blkb;
+    cp_async16_sa<ST>(sa_cp0, p);
+    cp_async16_sa<ST + 512>(sa_cp1, p + (blkb >> 2));
+    cp_async16_sa<ST + 1024>(sa_cp0, p + (blkb >> 1));
+    cp_async16_sa<ST + 1536>(sa_cp1, p + 3 * (blkb >> 2));
+  };
+  static_for<0, kF8Stages - 1>([&](auto s_tag) {
+    issue(s_tag);
+    cp_async_commit();
+  });
+  RowFrag qlo, qhi;
+  load_rowfrag(qlo, a.q.row(b, h, qb * kBS + g), t);
+  load_rowfrag(qhi, a.q.row(b, h, qb * kBS + g + 8), t);
+  float o[8][4], sc[4][2][4];
+  uint32_t pa[4][4];
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  static_for<0, 16>([&](auto s_tag) {
+    constexpr int s = decltype(s_tag)::value, half = s / 8, i = s % 4, ST = (s % kF8Stages) * kF8TileBytes;
+    constexpr bool is_v = (s % 8) >= 4;
+    cp_async_wait_group<kF8Stages - 2>();       // tile s has landed (this lane's chunks) ...
+    __syncwarp();                               // ... and everybody else's; the stage read last time is free
+    if constexpr (s + kF8Stages - 1 < 16) issue(std::integral_constant<int, s + kF8Stages - 1>{});
+    cp_async_commit();
+    if constexpr (!is_v) {
+      half_rows_x_keys<ST, true>(sc[i][0], sc[i][1], qlo, qhi, sa_f0);
+      half_rows_x_keys<ST, false>(sc[i][0], sc[i][1], qlo, qhi, sa_f1);
+      if constexpr (i == 3) {                   // the half's four S tiles are complete: one softmax update for 64 keys
+        float x0 = -INFINITY, x1 = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int n = 0; n < 2; ++n) {
+            x0 = fmaxf(x0, fmaxf(sc[u][n][0], sc[u][n][1]));
+            x1 = fmaxf(x1, fmaxf(sc[u][n][2], sc[u][n][3]));
+          }
+        const float mn0 = fmaxf(m0, quad_max(x0) * sl2), mn1 = fmaxf(m1, quad_max(x1) * sl2);
+        if constexpr (half > 0) {
+          const float al0 = fast_exp2(m0 - mn0), al1 = fast_exp2(m1 - mn1);
+          l0 *= al0; l1 *= al1;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { o[u][0] *= al0; o[u][1] *= al0; o[u][2] *= al1; o[u][3] *= al1; }
+        }
+        m0 = mn0; m1 = mn1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int n = 0; n < 2; ++n) {
+            sc[u][n][0] = fast_exp2(fmaf(sc[u][n][0], sl2, -mn0)); sc[u][n][1] = fast_exp2(fmaf(sc[u][n][1], sl2, -mn0));
+            sc[u][n][2] = fast_exp2(fmaf(sc[u][n][2], sl2, -mn1)); sc[u][n][3] = fast_exp2(fmaf(sc[u][n][3], sl2, -mn1));
+            l0 += sc[u][n][0] + sc[u][n][1];    // per-lane partial sums; reduced over the quad at the end
+            l1 += sc[u][n][2] + sc[u][n][3];
+          }
+          // the two C tiles of S are the k16 halves of the A operand
+          pa[u][0] = pack_bf16(sc[u][0][0], sc[u][0][1]); pa[u][1] = pack_bf16(sc[u][0][2], sc[u][0][3]);
+          pa[u][2] = pack_bf16(sc[u][1][0], sc[u][1][1]); pa[u][3] = pack_bf16(sc[u][1][2], sc[u][1][3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans<ST>(r0, r1, r2, r3, sa_m ^ (c << 5));
+        if constexpr (s == 4) {                 // first product: no accumulator input
+          mma_bf16_16816_z(o[2 * c], pa[i][0], pa[i][1], pa[i][2], pa[i][3], r0, r1);
+          mma_bf16_16816_z(o[2 * c + 1], pa[i][0], pa[i][1], pa[i][2], pa[i][3], r2, r3);
+        } else {
+          mma_bf16_16816(o[2 * c], pa[i][0], pa[i][1], pa[i][2], pa[i][3], r0, r1);
+          mma_bf16_16816(o[2 * c + 1], pa[i][0], pa[i][1], pa[i][2], pa[i][3], r2, r3);
+        }
+      }
+    }
+  });
+  l0 = quad_sum(l0); l1 = quad_sum(l1);
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
+  if (t == 0) {
+    a.lse[bh * a.Nq + qb * kBS + g] = (m0 + log2f(l0)) * 0.6931471805599453f;
+    a.lse[bh * a.Nq + qb * kBS + g + 8] = (m1 + log2f(l1)) * 0.6931471805599453f;
+  }
+  // accumulator tile u holds channels 8u + 2t, 8u + 2t + 1 of rows g (c0, c1) and g + 8 (c2, c3): through stage 0 to whole rows
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    stsm_x4<0>(sa_m ^ (c << 5), pack_bf16(o[2 * c][0] * i0, o[2 * c][1] * i0), pack_bf16(o[2 * c][2] * i1, o[2 * c][3] * i1),
+               pack_bf16(o[2 * c + 1][0] * i0, o[2 * c + 1][1] * i0), pack_bf16(o[2 * c + 1][2] * i1, o[2 * c + 1][3] * i1));
+  __syncwarp();
+  bf16* op = a.o.row(b, h, qb * kBS + (lane >> 3)) + (lane & 7) * 8;
+  const int64_t os = 4 * a.o.sn;
+  uint4 x;
+  lds128<0>(x.x, x.y, x.z, x.w, sa_cp0);    *reinterpret_cast<uint4*>(op) = x;
+  lds128<512>(x.x, x.y, x.z, x.w, sa_cp1);  *reinterpret_cast<uint4*>(op + os) = x;
+  lds128<1024>(x.x, x.y, x.z, x.w, sa_cp0); *reinterpret_cast<uint4*>(op + 2 * os) = x;
+  lds128<1536>(x.x, x.y, x.z, x.w, sa_cp1); *reinterpret_cast<uint4*>(op + 3 * os) = x;
+}
+
 bool mma_path_ok(const LlsaAttnArgs* g, bool bwd) {
   if (g->topk > 32 || (g->pk2 && g->topk_p > 32)) return false;
   // 256-bit fragment loads need 32-byte aligned rows
@@ -284,10 +420,18 @@ int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   const bool loop_tc = pooled_loop_tc_keys(a) > 0;
   if ((pooled_tc_keys(a) || loop_tc) && !(tc_env && tc_env[0] == '0')) {
     // fine blocks on mma.sync (o and lse of the fine part alone), pooled keys on tcgen05, merged there
-    const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
-    LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
-    attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
-    LLSA_LAUNCH_OK("attn_fwd_fine_kernel");
+    const char* form = getenv("LLSA_B200_FWD_FINE");     // "online": the per-block online-softmax form for any top-k
+    if (a.topk == 8 && !(form && form[0] == 'o')) {
+      const size_t ring = (size_t) NW * kF8Stages * kF8TileBytes + 128;
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine8_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+      attn_fwd_fine8_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
+      LLSA_LAUNCH_OK("attn_fwd_fine8_kernel");
+    } else {
+      const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
+      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+      attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
+      LLSA_LAUNCH_OK("attn_fwd_fine_kernel");
+    }
     return loop_tc ? launch_attn_fwd_pooled_loop_tc(g, a, BH, st) : launch_attn_fwd_pooled_tc(g, a, BH, st);
   }
   const int n_smem = pooled_smem_tiles(a.p1_blocks + a.p2_blocks);
