@@ -36,9 +36,9 @@ METRIC = "llsa_l2 fwd+bwd tokens/sec @N=16384,B*H=48,D=64"
 
 
 # this library's kernels launched by one llsa_l2 forward + backward (torch's own zero fills are not counted)
-KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_mma_kernel", "refine_topk_kernel", "attn_fwd_fine_kernel", "attn_fwd_pooled_tc_kernel",
+KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_mma_kernel", "refine_topk_kernel", "attn_fwd_fine8_kernel", "attn_fwd_pooled_tc_kernel",
                     "transpose_kernel", "attn_bwd_pooled_tc_kernel",
-                    "attn_dq_fine_kernel", "attn_dkv_fine_kernel", "attn_dkv_finish_kernel")
+                    "attn_dq_fine_kernel", "attn_dkv_fine_ring_kernel", "attn_dkv_finish_ld_kernel")
 
 
 # DRAM read + write bytes of one launch on 12 (b,h) slices of the config-3 shape, from the ncu capture summarised in

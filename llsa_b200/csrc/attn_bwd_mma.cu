@@ -685,33 +685,11 @@ __device__ __forceinline__ void dkv_fine_fold_smem(const AttnP<bf16>& a, uint32_
   }
 }
 
-// Direct store of a finished tile from the ldmatrix layout: a lane owns two channels per 8-channel group, so these are
-// 4-byte stores (the finish kernel's rare path; the main kernel goes through stmatrix below).
-__device__ __forceinline__ void dkv_fine_store_ld(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t j, float (&dk)[8][4],
-                                                  float (&dv)[8][4], int g, int t) {
-  dkv_fine_fold_ld(a, bh, j, dk, dv, t);
-  bf16* k0 = a.dk.row(b, h, j * kBS + g) + 2 * t;
-  bf16* k1 = a.dk.row(b, h, j * kBS + g + 8) + 2 * t;
-  bf16* v0 = a.dv.row(b, h, j * kBS + g) + 2 * t;
-  bf16* v1 = a.dv.row(b, h, j * kBS + g + 8) + 2 * t;
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    *reinterpret_cast<uint32_t*>(k0 + 8 * u) = pack_bf16(dk[u][0], dk[u][1]);
-    *reinterpret_cast<uint32_t*>(k1 + 8 * u) = pack_bf16(dk[u][2], dk[u][3]);
-    *reinterpret_cast<uint32_t*>(v0 + 8 * u) = pack_bf16(dv[u][0], dv[u][1]);
-    *reinterpret_cast<uint32_t*>(v1 + 8 * u) = pack_bf16(dv[u][2], dv[u][3]);
-  }
-}
-
-// Store of a finished tile through a free ring stage at byte offset SB: stmatrix writes the bf16 tile in the ring's swizzled row
-// layout (the ldmatrix addresses sa_m), every lane reads back four 16-byte chunks per tensor (the cp.async addresses sa_cp0 /
-// sa_cp1) and eight lanes write one whole 128-byte row: full sectors, 8 store instructions instead of 32.
+// The staging half of the store below: dk / dv already hold the final fp32 values.
 template <int SB>
-__device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t j, float (&dk)[8][4],
-                                                      float (&dv)[8][4], const uint32_t (&sa_m)[4], uint32_t sa_cp0, uint32_t sa_cp1,
-                                                      uint32_t sa_fold, int lane) {
+__device__ __forceinline__ void dkv_tile_store_staged(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t j, float (&dk)[8][4], float (&dv)[8][4],
+                                                      const uint32_t (&sa_m)[4], uint32_t sa_cp0, uint32_t sa_cp1, int lane) {
   constexpr int TB = kRingTileElems * (int) sizeof(bf16);
-  dkv_fine_fold_smem(a, sa_fold, dk, dv);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     stsm_x4<SB>(sa_m[c], pack_bf16(dk[2 * c][0], dk[2 * c][1]), pack_bf16(dk[2 * c][2], dk[2 * c][3]),
@@ -735,6 +713,17 @@ __device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int6
   __syncwarp();
 }
 
+
+// Store of a finished tile through a free ring stage at byte offset SB: stmatrix writes the bf16 tile in the ring's swizzled row
+// layout (the ldmatrix addresses sa_m), every lane reads back four 16-byte chunks per tensor (the cp.async addresses sa_cp0 /
+// sa_cp1) and eight lanes write one whole 128-byte row: full sectors, 8 store instructions instead of 32.
+template <int SB>
+__device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t j, float (&dk)[8][4],
+                                                      float (&dv)[8][4], const uint32_t (&sa_m)[4], uint32_t sa_cp0, uint32_t sa_cp1,
+                                                      uint32_t sa_fold, int lane) {
+  dkv_fine_fold_smem(a, sa_fold, dk, dv);
+  dkv_tile_store_staged<SB>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
+}
 __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // the swizzle arithmetic below works on absolute shared addresses: start at a 128-byte boundary (the launch adds 128 bytes)
@@ -927,20 +916,42 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
   }
 }
 
-template <bool LD>
+constexpr int kFinishPerWarp = 8;
 __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, const float* __restrict__ partial, int n_windows) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int64_t j = (int64_t) blockIdx.x * 4 + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  if (j >= a.n1) return;
-  const int bo = (int) csr_off(a, bh, j), be = (int) csr_off(a, bh, j + 1);
-  const int c_first = bo / kFineWindow, c_last = (be - 1) / kFineWindow;
-  if (be > bo && c_first == c_last) return;          // finished inside one window
-  float dk[8][4], dv[8][4];
-  tile_zero(dk, dv);
-  if (be > bo)
-    for (int c = c_first; c <= c_last; ++c)
-      tile_add_mem(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
-  dkv_fine_store_ld(a, b, h, bh, j, dk, dv, g, t);
+  __shared__ __align__(1024) unsigned char s_stage[4][2 * kRingTileElems * sizeof(bf16)];      // per warp: a dK and a dV tile on their way out
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
+  const int64_t j0 = ((int64_t) blockIdx.x * 4 + warp) * kFinishPerWarp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+  if (j0 >= a.n1) return;
+  // a warp looks at eight consecutive buckets at once (lane i: offsets of bucket j0 + i) and works only on those that need it:
+  // most buckets were finished inside one window of the main kernel
+  const int64_t jl = j0 + lane < a.n1 ? j0 + lane : a.n1 - 1;
+  const int my_bo = lane < kFinishPerWarp ? (int) csr_off(a, bh, jl) : 0, my_be = lane < kFinishPerWarp ? (int) csr_off(a, bh, jl + 1) : 1;
+  const bool need = lane < kFinishPerWarp && j0 + lane < a.n1 && (my_be == my_bo || my_bo / kFineWindow != (my_be - 1) / kFineWindow);
+  unsigned todo = __ballot_sync(0xffffffffu, need);
+  if (!todo) return;
+  const uint32_t st_sa = (uint32_t) __cvta_generic_to_shared(s_stage[warp]);
+  const uint32_t sa_cp0 = st_sa + (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4), sa_cp1 = sa_cp0 ^ 64;
+  uint32_t sa_m[4];
+  {
+    const uint32_t base = st_sa + ((lane & 7) + ((lane >> 3) & 1) * 8) * 128 + (((lane >> 4) ^ (lane & 7)) << 4);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) sa_m[c] = base ^ (c << 5);
+  }
+  while (todo) {
+    const int l = __ffs((int) todo) - 1;
+    todo &= todo - 1;
+    const int bo = __shfl_sync(0xffffffffu, my_bo, l), be = __shfl_sync(0xffffffffu, my_be, l);
+    const int64_t j = j0 + l;
+    float dk[8][4], dv[8][4];
+    tile_zero(dk, dv);
+    if (be > bo) {
+      const int c_first = bo / kFineWindow, c_last = (be - 1) / kFineWindow;
+      for (int c = c_first; c <= c_last; ++c)
+        tile_add_mem(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
+    }
+    dkv_fine_fold_ld(a, bh, j, dk, dv, t);
+    dkv_tile_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
+  }
 }
 
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st);
@@ -1011,7 +1022,7 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
       LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
       attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
       LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");
-      attn_dkv_finish_ld_kernel<true><<<dim3((unsigned) ((a.n1 + 3) / 4), BH), 128, 0, st>>>(a, partial, n_windows);
+      attn_dkv_finish_ld_kernel<<<dim3((unsigned) ((a.n1 + 4 * kFinishPerWarp - 1) / (4 * kFinishPerWarp)), BH), 128, 0, st>>>(a, partial, n_windows);
       LLSA_LAUNCH_OK("attn_dkv_finish_ld_kernel");
     } else {
       const size_t smem = (size_t) kFineWarps * 2 * kTileFloats * sizeof(float);
