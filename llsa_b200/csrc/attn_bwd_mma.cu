@@ -444,13 +444,14 @@ __device__ __forceinline__ void dkv_fine_store(const AttnP<bf16>& a, int64_t b, 
 // those (in CTA order) for the buckets that straddle windows.  No atomics: bit-reproducible.
 constexpr int kFineWarps = 4;
 constexpr int kFineWindow = 128;                // entries per CTA
-constexpr int kTileFloats = 64 * 32;            // a dK + dV tile pair as [64 accumulators][32 lanes]
+constexpr int kTileFloats = 64 * 32;            // a parked dK + dV tile pair: 64 accumulators x 32 lanes
 
 __device__ __forceinline__ int64_t csr_off(const AttnP<bf16>& a, int64_t bh, int64_t j) {
   const int64_t o = bh * (a.n1 + 1) + j;
   return a.off64 ? reinterpret_cast<const int64_t*>(a.offsets)[o] : (int64_t) reinterpret_cast<const int32_t*>(a.offsets)[o];
 }
 
+// A parked dK + dV tile pair is [64 accumulators][32 lanes] fp32: every access of a warp is one contiguous 128-byte row.
 __device__ __forceinline__ void tile_to_mem(float* s, const float (&dk)[8][4], const float (&dv)[8][4], int lane) {
 #pragma unroll
   for (int u = 0; u < 8; ++u)
@@ -468,6 +469,17 @@ __device__ __forceinline__ void tile_add_mem(const float* s, float (&dk)[8][4], 
       dk[u][c] += s[(u * 4 + c) * 32 + lane];
       dv[u][c] += s[(32 + u * 4 + c) * 32 + lane];
     }
+}
+// The same from global memory with all 64 loads in flight before the first add (64 more registers): for the finish kernels, whose
+// warps do little else than wait for these loads.
+__device__ __forceinline__ void tile_add_mem_batched(const float* s, float (&dk)[8][4], float (&dv)[8][4], int lane) {
+  float x[32], y[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { x[i] = __ldcg(s + i * 32 + lane); y[i] = __ldcg(s + (32 + i) * 32 + lane); }
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) { dk[u][c] += x[u * 4 + c]; dv[u][c] += y[u * 4 + c]; }
 }
 __device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) {
 #pragma unroll
@@ -607,7 +619,7 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_kernel(AttnP<bf16> a, con
   tile_zero(dk, dv);
   if (be > bo)
     for (int c = c_first; c <= c_last; ++c)
-      tile_add_mem(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
+      tile_add_mem_batched(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
   dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);
 }
 
@@ -947,7 +959,7 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
     if (be > bo) {
       const int c_first = bo / kFineWindow, c_last = (be - 1) / kFineWindow;
       for (int c = c_first; c <= c_last; ++c)
-        tile_add_mem(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
+        tile_add_mem_batched(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
     }
     dkv_fine_fold_ld(a, bh, j, dk, dv, t);
     dkv_tile_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
