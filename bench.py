@@ -44,8 +44,8 @@ KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_mma_kernel", "refine_top
 # DRAM read + write bytes of one launch on 12 (b,h) slices of the config-3 shape, from the ncu capture summarised in
 # profiles/attention_kernels_llsa_l2_batch2.md (dram__bytes_read.sum + dram__bytes_write.sum); traffic grows in
 # proportion to the slices (every slice is independent), so a full launch is scaled by B*H / 12.
-NCU_DRAM_BYTES_12_SLICES = dict(attn_fwd=(49.4 + 2.1 + 54.0 + 0.4) * 1e6, attn_bwd_dq=(100.6 + 11.8) * 1e6,
-                                attn_bwd_dkv_pooled=(85.6 + 4.9) * 1e6, attn_bwd_dkv_fine=(79.2 + 13.2 + 15.7 + 0.0) * 1e6)
+NCU_DRAM_BYTES_12_SLICES = dict(attn_fwd=(49.5 + 2.7 + 54.0 + 0.2) * 1e6, attn_bwd_dq=(100.6 + 11.1) * 1e6,
+                                attn_bwd_dkv_pooled=(85.7 + 4.2) * 1e6, attn_bwd_dkv_fine=(89.1 + 12.5 + 15.7 + 0.0) * 1e6)
 
 
 def parse():
