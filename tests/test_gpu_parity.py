@@ -324,6 +324,31 @@ def test_pooled_key_loop_on_tcgen05_matches_mma_path(levels, N, monkeypatch):
     assert_bf16_close(dva, dvb.float(), "dv")
 
 
+def test_fine_kernel_forms_agree(monkeypatch):
+    """The top-8 fine forward (softmax statistics per four blocks) and the three-CTA fine dK/dV kernel against the forms they
+    replaced (per-block online softmax; fragments in registers), on correlated inputs with empty and very long buckets."""
+    L = _ops()
+    q, k, v, do = [t.to(DEV) for t in synth.correlated_qkv(49, 2, 3, 16384, 64, dtype=torch.bfloat16)]
+
+    def run():
+        qg, kg, vg = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        d = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
+        d["o"].backward(do)
+        return d, qg.grad, kg.grad, vg.grad
+
+    a, dqa, dka, dva = run()
+    monkeypatch.setenv("LLSA_B200_FWD_FINE", "online")
+    monkeypatch.setenv("LLSA_B200_DKV_FINE", "regs")
+    b, dqb, dkb, dvb = run()
+    assert torch.equal(a["indices"], b["indices"])
+    assert_bf16_close(a["o"].detach(), b["o"].detach().float(), "o")
+    assert max_abs(a["lse"], b["lse"]) < 2e-3
+    assert_bf16_close(dqa, dqb.float(), "dq")
+    assert rel_l2(dka, dkb) < 2e-3 and rel_l2(dva, dvb) < 2e-3
+    assert_bf16_close(dka, dkb.float(), "dk")
+    assert_bf16_close(dva, dvb.float(), "dv")
+
+
 @pytest.mark.parametrize("levels,N", [(1, 256), (1, 1024), (1, 2048), (2, 4096), (2, 8192)])
 def test_small_shapes_bf16_vs_oracle(levels, N):
     """Sizes around the dispatch edges: pooled stages that are skipped (fewer than 64 pooled keys: llsa_l1 at N=256, llsa_l2 below
