@@ -32,23 +32,37 @@ __all__ = ["llsa_l2_seq_parallel", "llsa_l1_seq_parallel", "CudaBackend", "gathe
 _PER_SLICE_MAX = 16     # up to this many (b,h) slices the exchange runs per slice, straight into / out of place
 
 
-def gather_seq(x: torch.Tensor, group=None) -> torch.Tensor:
-    """[B,H,n_local,D] on every rank -> [B,H,W*n_local,D], ranks in order along dim 2."""
+def gather_seq_start(x: torch.Tensor, group=None):
+    """Starts the all-gather of [B,H,n_local,D] along dim 2 and returns a handle for gather_seq_finish: the collectives run on
+    the communicator's own stream, so kernels enqueued before the finish overlap with them."""
     world = dist.get_world_size(group)
     if world == 1:
-        return x
+        return x, [], None
     x = x.contiguous()
     B, H, n, D = x.shape
     if B * H <= _PER_SLICE_MAX:
         # a slice's full sequence [W*n, D] is the rank-major concatenation of the ranks' [n, D]: gather in place
         out = x.new_empty((B, H, world * n, D))
         works = [dist.all_gather_into_tensor(out[b, h], x[b, h], group=group, async_op=True) for b in range(B) for h in range(H)]
-        for w in works:
-            w.wait()
-        return out
+        return out, works, None
     out = x.new_empty((world * B, H, n, D))           # rank-major concatenation along dim 0, then one transposing copy
-    dist.all_gather_into_tensor(out, x, group=group)
+    work = dist.all_gather_into_tensor(out, x, group=group, async_op=True)
+    return out, [work], (world, B, H, n, D)
+
+
+def gather_seq_finish(handle) -> torch.Tensor:
+    out, works, shape = handle
+    for w in works:
+        w.wait()
+    if shape is None:
+        return out
+    world, B, H, n, D = shape
     return out.view(world, B, H, n, D).permute(1, 2, 0, 3, 4).reshape(B, H, world * n, D)
+
+
+def gather_seq(x: torch.Tensor, group=None) -> torch.Tensor:
+    """[B,H,n_local,D] on every rank -> [B,H,W*n_local,D], ranks in order along dim 2."""
+    return gather_seq_finish(gather_seq_start(x, group))
 
 
 def reduce_scatter_seq(x: torch.Tensor, group=None) -> torch.Tensor:
@@ -101,19 +115,22 @@ class CudaBackend:
         return dq, dk, dv
 
 
-def local_forward(backend, q, kf, vf, pq_levels, pk, pv, pk2, pv2, topk1, topk2, block_size):
-    """Selection and attention of LOCAL query rows q [B,H,Nq,D] (pooled levels pq_levels) against the
-    full-length keys kf, vf and their pooled levels.  Returns (o, lse, indices, p_indices, w1, w2)."""
+def local_select(backend, pq_levels, pk, pk2, topk1, topk2, block_size):
+    """Block selection of LOCAL query rows (pooled levels pq_levels) against the full-length pooled keys.
+    Returns (indices, p_indices, w1, w2, topk_p)."""
     bs = block_size
     if pk2 is not None:
         p_indices = backend.coarse_topk(pq_levels[1], pk2, topk2)
         indices = backend.refine_topk(pq_levels[0], pk, p_indices, topk1, p_indices.shape[-1], bs)
-        w1, w2, topk_p = float(bs), float(bs * bs), p_indices.shape[-1]
-    else:
-        p_indices, topk_p = None, 0
-        indices = backend.coarse_topk(pq_levels[0], pk, topk1)
-        w1, w2 = float(bs), 1.0
-    o, lse = backend.attn_fwd(q, kf, vf, pk, pv, pk2, pv2, indices, p_indices, indices.shape[-1], topk_p, bs, w1, w2)
+        return indices, p_indices, float(bs), float(bs * bs), p_indices.shape[-1]
+    return backend.coarse_topk(pq_levels[0], pk, topk1), None, float(bs), 1.0, 0
+
+
+def local_forward(backend, q, kf, vf, pq_levels, pk, pv, pk2, pv2, topk1, topk2, block_size):
+    """Selection and attention of LOCAL query rows q [B,H,Nq,D] (pooled levels pq_levels) against the
+    full-length keys kf, vf and their pooled levels.  Returns (o, lse, indices, p_indices, w1, w2)."""
+    indices, p_indices, w1, w2, topk_p = local_select(backend, pq_levels, pk, pk2, topk1, topk2, block_size)
+    o, lse = backend.attn_fwd(q, kf, vf, pk, pv, pk2, pv2, indices, p_indices, indices.shape[-1], topk_p, block_size, w1, w2)
     return o, lse, indices, p_indices, w1, w2
 
 
@@ -130,11 +147,16 @@ class _SeqParallel(torch.autograd.Function):
             raise ValueError("the local sequence length %d must be a multiple of block_size**2" % q.shape[2])
         pyr = backend.pool_pyramid([q.detach(), k.detach(), v.detach()], bs, levels)
         _mark("all_gather")
-        kf, vf = gather_seq(k.detach(), group), gather_seq(v.detach(), group)
-        pk, pv = gather_seq(pyr[0][1], group), gather_seq(pyr[0][2], group)
-        pk2, pv2 = (gather_seq(pyr[1][1], group), gather_seq(pyr[1][2], group)) if levels == 2 else (None, None)
-        o, lse, indices, p_indices, w1, w2 = local_forward(backend, q.detach(), kf, vf, [lv[0] for lv in pyr[:levels]], pk, pv, pk2, pv2,
-                                                           topk1, topk2, bs)
+        # the pooled levels go first (the selection needs only them); k and v follow on the communicator's stream while the
+        # selection kernels run, and are waited for right before the attention kernel
+        small = [gather_seq_start(t, group) for t in ([pyr[0][1], pyr[0][2]] + ([pyr[1][1], pyr[1][2]] if levels == 2 else []))]
+        big = [gather_seq_start(k.detach(), group), gather_seq_start(v.detach(), group)]
+        pk, pv = gather_seq_finish(small[0]), gather_seq_finish(small[1])
+        pk2, pv2 = (gather_seq_finish(small[2]), gather_seq_finish(small[3])) if levels == 2 else (None, None)
+        indices, p_indices, w1, w2, topk_p = local_select(backend, [lv[0] for lv in pyr[:levels]], pk, pk2, topk1, topk2, bs)
+        _mark("all_gather_wait")
+        kf, vf = gather_seq_finish(big[0]), gather_seq_finish(big[1])
+        o, lse = backend.attn_fwd(q.detach(), kf, vf, pk, pv, pk2, pv2, indices, p_indices, indices.shape[-1], topk_p, bs, w1, w2)
         ctx.save_for_backward(q, kf, vf, o, lse, indices, pk, pv, *([p_indices, pk2, pv2] if levels == 2 else []))
         ctx.cfg = (bs, w1, w2, levels, group, backend)
         return o
