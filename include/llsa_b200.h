@@ -192,6 +192,13 @@ int llsa_attn_bwd(const LlsaAttnArgs* args, void* stream);
  * shape with at least this many elements is accepted).  The library itself never allocates device memory. */
 int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk);
 
+/* Measurement aid, no counterpart in the reference: issue rate of mma.sync.m16n8k16 (bf16 in, fp32 out), the tensor
+ * instruction of the fine-block kernels.  Launches n_sms CTAs of warps_per_sm warps; every warp issues `ilp` (1, 2, 4 or 8)
+ * independent accumulator chains `iters` times.  `sink` (device, n_sms * warps_per_sm * 32 floats) receives the accumulators,
+ * `cycles` (device, one int64) the clock64 cycles CTA 0 spent in the loop.  Cycles per instruction per SM sub-partition =
+ * cycles / (iters * ilp * max(warps_per_sm, 4) / 4). */
+int llsa_probe_mma_rate(int warps_per_sm, int ilp, int iters, int n_sms, float* sink, long long* cycles, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

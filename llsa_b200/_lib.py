@@ -43,6 +43,7 @@ EXPORTS = [
     "llsa_rope_pool_pyramid_fwd",
     "llsa_rope_fwd", "llsa_rope_bwd", "llsa_coarse_topk", "llsa_refine_topk", "llsa_transpose_scratch_bytes",
     "llsa_transpose_indices", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd", "llsa_attn_bwd_partial_elems",
+    "llsa_probe_mma_rate",
 ]
 
 _lib: Optional[C.CDLL] = None
@@ -67,6 +68,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.llsa_transpose_indices_noalloc.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_void_p]
     lib.llsa_attn_bwd_partial_elems.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32]
     lib.llsa_attn_bwd_partial_elems.restype = C.c_int64
+    lib.llsa_probe_mma_rate.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.llsa_attn_fwd.argtypes = [C.POINTER(LlsaAttnArgs), C.c_void_p]
     lib.llsa_attn_bwd.argtypes = [C.POINTER(LlsaAttnArgs), C.c_void_p]
     for name in EXPORTS:

@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libllsa_b200.so")
 SOURCES = ["capi.cu", "pool.cu", "rope.cu", "topk.cu", "transpose.cu", "attn.cu", "attn_generic.cu",
-           "attn_fwd_mma.cu", "attn_bwd_mma.cu", "attn_pooled_tc.cu", "attn_pooled_bwd_tc.cu", "attn_pooled_loop_tc.cu", "attn_pooled_bwd_loop_tc.cu", "attn_pooled_dkv_loop_tc.cu"]
+           "attn_fwd_mma.cu", "attn_bwd_mma.cu", "attn_pooled_tc.cu", "attn_pooled_bwd_tc.cu", "attn_pooled_loop_tc.cu", "attn_pooled_bwd_loop_tc.cu", "attn_pooled_dkv_loop_tc.cu", "probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

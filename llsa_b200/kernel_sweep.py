@@ -6,6 +6,7 @@ quantiles of CUDA-event times like triton.testing.do_bench, plus tokens/s and th
 (4 FLOP per query row, attended key and channel forward, 14 forward + backward).
 
     python -m llsa_b200.kernel_sweep [--sizes 128 256 512] [--reps 30] [--json]
+    python -m llsa_b200.kernel_sweep --mma-rate      # issue rate of mma.sync.m16n8k16, the ceiling of the fine-block kernels
 """
 import argparse
 import json
@@ -40,13 +41,49 @@ def time_call(fn, reps: int, flush: torch.Tensor):
     return q(0.5), q(0.2), q(0.8)
 
 
+def mma_rate(dev) -> list:
+    """Cycles per mma.sync.m16n8k16 (bf16) per SM sub-partition for 1..32 warps per SM and 1..8 independent chains, and the
+    whole-GPU rate that the best of them implies at the current SM clock."""
+    import ctypes as C
+
+    from . import _lib
+    props = torch.cuda.get_device_properties(dev)
+    sms = props.multi_processor_count
+    sink = torch.empty(sms * 1024, dtype=torch.float32, device=dev)
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    iters, rows = 2000, []
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    for warps in (1, 4, 8, 12, 16, 32):
+        for ilp in (1, 2, 4, 8):
+            for _ in range(2):
+                _lib.check(_lib.lib().llsa_probe_mma_rate(warps, ilp, iters, sms, C.c_void_p(sink.data_ptr()), C.c_void_p(cyc.data_ptr()), stream),
+                           "probe_mma_rate")
+            torch.cuda.synchronize(dev)
+            per_smsp = float(cyc.item()) / (iters * ilp * max(warps, 4) / 4)
+            rows.append(dict(warps_per_sm=warps, ilp=ilp, cycles_per_mma_per_subpartition=per_smsp))
+    best = min(r["cycles_per_mma_per_subpartition"] for r in rows)
+    try:
+        mhz = int(torch.cuda.clock_rate(dev))           # current SM clock (NVML); 0 if it cannot be read
+    except Exception:
+        mhz = 0
+    for r in rows:
+        r["gpu_tflops_at_sm_clock"] = sms * 4 * (2 * 16 * 8 * 16) / r["cycles_per_mma_per_subpartition"] * mhz * 1e6 / 1e12 if mhz else None
+    rows.append(dict(best_cycles=best, sms=sms, sm_mhz=mhz))
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--mma-rate", action="store_true", help="measure the issue rate of mma.sync.m16n8k16 instead of the operator sweep")
     ap.add_argument("--sizes", type=int, nargs="+", default=[128, 256, 512])
     ap.add_argument("--reps", type=int, default=30)
     ap.add_argument("--json", action="store_true")
     args = ap.parse_args()
     dev = torch.device("cuda", torch.cuda.current_device())
+    if args.mma_rate:
+        for r in mma_rate(dev):
+            print(json.dumps(r))
+        return
     B, H, D = 2, 4, 64
     flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=dev)
     rows = []

@@ -324,6 +324,15 @@ def test_pooled_key_loop_on_tcgen05_matches_mma_path(levels, N, monkeypatch):
     assert_bf16_close(dva, dvb.float(), "dv")
 
 
+def test_mma_rate_probe_runs():
+    """The issue-rate probe of the harness: at 16 warps per SM the tensor pipe, not latency, bounds mma.sync.m16n8k16."""
+    from llsa_b200 import kernel_sweep
+    rows = kernel_sweep.mma_rate(torch.device(DEV))
+    sat = [r for r in rows if r.get("warps_per_sm") == 16 and r.get("ilp") == 4][0]["cycles_per_mma_per_subpartition"]
+    one = [r for r in rows if r.get("warps_per_sm") == 1 and r.get("ilp") == 1][0]["cycles_per_mma_per_subpartition"]
+    assert 2.0 < sat < 32.0 and one >= sat
+
+
 def test_fine_kernel_forms_agree(monkeypatch):
     """The top-8 fine forward (softmax statistics per four blocks) and the three-CTA fine dK/dV kernel against the forms they
     replaced (per-block online softmax; fragments in registers), on correlated inputs with empty and very long buckets."""
