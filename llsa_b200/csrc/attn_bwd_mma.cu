@@ -632,6 +632,7 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_kernel(AttnP<bf16> a, con
 // bucket it shares with EARLIER warps; the tile it shares with later warps stays in its accumulators
 // until the CTA has synchronised and is then completed from the later warps' parked tiles.
 // Accumulator layout (ldmatrix): tile u holds channels 8u + 2t, 8u + 2t + 1 of keys g (c0, c1) and g + 8 (c2, c3).
+constexpr int kRingWarps = 2;                   // warps per CTA of the ring form: 64 entries each, six CTAs per SM
 constexpr int kRingFineStages = 2;
 constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16) + 128;   // Q tile, dO tile, 16 lse, 16 delta
 constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
@@ -736,24 +737,24 @@ __device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int6
   dkv_fine_fold_smem(a, sa_fold, dk, dv);
   dkv_tile_store_staged<SB>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
 }
-__global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
+__global__ void __launch_bounds__(kRingWarps * 32, 12 / kRingWarps) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // the swizzle arithmetic below works on absolute shared addresses: start at a 128-byte boundary (the launch adds 128 bytes)
   unsigned char* smem = smem_raw + ((128u - ((uint32_t) __cvta_generic_to_shared(smem_raw) & 127u)) & 127u);
-  float* slots = reinterpret_cast<float*>(smem);            // [kFineWarps][kTileFloats]: tile of the bucket a warp shares with earlier warps
-  __shared__ int s_head_bucket[kFineWarps];
+  float* slots = reinterpret_cast<float*>(smem);            // [kRingWarps][kTileFloats]: tile of the bucket a warp shares with earlier warps
+  __shared__ int s_head_bucket[kRingWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   // per warp: the ring stages, then its copy of the pooled-gradient rows the current bucket folds in (4 rows x 256 bytes)
   constexpr int kWarpBytes = kRingFineStages * kRingFineStageBytes + kRingFoldBytes;
-  unsigned char* ring = smem + kFineWarps * kTileFloats * sizeof(float) + warp * kWarpBytes;
+  unsigned char* ring = smem + kRingWarps * kTileFloats * sizeof(float) + warp * kWarpBytes;
   const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const float sl2 = a.scale * kLog2e;
   const int E = (int) (a.nq1 * a.topk);
   const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E);
-  constexpr int L = kFineWindow / kFineWarps;
+  constexpr int L = kFineWindow / kRingWarps;
   const int rb = cb + warp * L, re = min(rb + L, ce);
   const int32_t* fl = a.flat + bh * (int64_t) E;
-  if (threadIdx.x < kFineWarps) s_head_bucket[threadIdx.x] = -1;
+  if (threadIdx.x < kRingWarps) s_head_bucket[threadIdx.x] = -1;
   __syncthreads();
 
   // Per-lane shared addresses, computed once (the ring is 128-byte aligned, so the chunk index of an address is its bits 4..6
@@ -913,7 +914,7 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
   }
   __syncthreads();
   if (tail_j >= 0) {
-    for (int w = warp + 1; w < kFineWarps && s_head_bucket[w] == tail_j; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
+    for (int w = warp + 1; w < kRingWarps && s_head_bucket[w] == tail_j; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
     if ((int) csr_off(a, bh, tail_j + 1) <= ce) {
       dkv_fine_store_staged<0>(a, b, h, tail_j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
     } else {                                // runs on into the next window: this window's tail slot
@@ -923,7 +924,7 @@ __global__ void __launch_bounds__(kFineWarps * 32, 3) attn_dkv_fine_ring_kernel(
   if (warp == 0 && s_head_bucket[0] >= 0) { // began in an earlier window: this window's head slot
     const int j0 = s_head_bucket[0];
     tile_zero(dk, dv);
-    for (int w = 0; w < kFineWarps && s_head_bucket[w] == j0; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
+    for (int w = 0; w < kRingWarps && s_head_bucket[w] == j0; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
     tile_to_mem(partial + ((bh * gridDim.x + blockIdx.x) * 2 + 0) * (int64_t) kTileFloats, dk, dv, lane);
   }
 }
@@ -1030,9 +1031,9 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     float* partial = (float*) g->dkv_partial->ptr;
     const char* form = getenv("LLSA_B200_DKV_FINE");      // "regs": the two-CTA form that keeps the fragments in registers
     if (!(form && form[0] == 'r' && form[1] == 'e')) {
-      const size_t smem = (size_t) kFineWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
+      const size_t smem = (size_t) kRingWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
       LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-      attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
+      attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kRingWarps * 32, smem, st>>>(a, partial);
       LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");
       attn_dkv_finish_ld_kernel<<<dim3((unsigned) ((a.n1 + 4 * kFinishPerWarp - 1) / (4 * kFinishPerWarp)), BH), 128, 0, st>>>(a, partial, n_windows);
       LLSA_LAUNCH_OK("attn_dkv_finish_ld_kernel");
