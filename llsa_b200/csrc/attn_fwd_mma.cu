@@ -333,8 +333,8 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine8_kernel(AttnP<bf16> 
         for (int u = 0; u < 4; ++u)
 #pragma unroll
           for (int n = 0; n < 2; ++n) {
-            x0 = fmaxf(x0, fmaxf(sc[u][n][0], sc[u][n][1]));
-            x1 = fmaxf(x1, fmaxf(sc[u][n][2], sc[u][n][3]));
+            x0 = fmax3(x0, sc[u][n][0], sc[u][n][1]);
+            x1 = fmax3(x1, sc[u][n][2], sc[u][n][3]);
           }
         const float mn0 = fmaxf(m0, quad_max(x0) * sl2), mn1 = fmaxf(m1, quad_max(x1) * sl2);
         if constexpr (half > 0) {

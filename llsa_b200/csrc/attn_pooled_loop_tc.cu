@@ -264,7 +264,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
             tc::tmem_ld32_async(t_s + 32 * q4, va);
             tc::tmem_ld_wait(va);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) m = fmaxf(m, va[e]);
+            for (int e = 0; e < 32; e += 2) m = fmax3(m, va[e], va[e + 1]);
           }
           mx = fmaxf(mx, fmaf(m, sl2, lw));
         } else {

@@ -171,9 +171,9 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       if (ok) {
         float m1 = -INFINITY, m2 = -INFINITY;
         auto chunk_max = [&](const float (&v)[32], int c0) {
-          float m = v[0];
+          float m = fmaxf(v[0], v[1]);
 #pragma unroll
-          for (int j = 1; j < 32; ++j) m = fmaxf(m, v[j]);
+          for (int j = 2; j < 32; j += 2) m = fmax3(m, v[j], v[j + 1]);
           if (c0 < p1_keys) m1 = fmaxf(m1, m); else m2 = fmaxf(m2, m);
         };
         tc::tmem_ld32_async(t_s, va);

@@ -265,6 +265,13 @@ __device__ __forceinline__ void store_acc_row_t(bf16* row, const float (&acc)[8]
   *reinterpret_cast<uint4*>(row + 16 * t + 8) = y;
 }
 
+// max of three in one instruction (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
