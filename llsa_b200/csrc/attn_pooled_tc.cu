@@ -38,7 +38,7 @@ namespace llsa {
 
 constexpr int kTcRows = 128;
 constexpr int kTcStages = 3;
-constexpr int kTcThreads = 320;       // 2 x 4 softmax warps + producer warp + MMA warp
+constexpr int kTcThreads = 352;       // 2 x 4 softmax warps + Q/key producer warp + MMA warp + value producer warp
 
 struct TcMaps {
   CUtensorMap q;      // [B,H,N,64] 4-D, box 128 rows
@@ -49,7 +49,9 @@ struct TcMaps {
 };
 
 struct TcBars {
-  uint64_t full[kTcStages], empty[kTcStages], s_ready[2], p_ready[2], o_ready[2];
+  // a stage's [Q | pooled keys] part and its [pooled values] part fill and drain separately: Q and the keys are free again as soon
+  // as S = Q.PK^T has executed, two tiles before the values (free after O = P.PV), so their refill runs that much further ahead
+  uint64_t full_k[kTcStages], empty_k[kTcStages], full_v[kTcStages], empty_v[kTcStages], s_ready[2], p_ready[2], o_ready[2];
 };
 
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -75,8 +77,10 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < kTcStages; ++i) {
-      tc::mbar_init(&bars.full[i], 1);
-      tc::mbar_init(&bars.empty[i], 1);
+      tc::mbar_init(&bars.full_k[i], 1);
+      tc::mbar_init(&bars.empty_k[i], 1);
+      tc::mbar_init(&bars.full_v[i], 1);
+      tc::mbar_init(&bars.empty_v[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.s_ready[i], 1);
@@ -92,30 +96,27 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
   const uint32_t tmem = s_tmem;
   const int n_my = (n_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x;
 
-  if (warp == 8) {
-    // ---------------------------------------------------------------- TMA producer
+  if (warp == 8 || warp == 10) {
+    // ---------------------------------------------------------------- TMA producers: warp 8 Q + pooled keys, warp 10 pooled values
     if (lane == 0) {
-      const uint32_t bytes = (uint32_t) stage_elems * 2;
+      const bool vals = warp == 10;
+      const uint32_t bytes = (uint32_t) (vals ? np * 64 : kTcRows * 64 + np * 64) * 2;
+      const CUtensorMap* m1 = vals ? &maps.pv1 : &maps.pk1;
+      const CUtensorMap* m2 = vals ? &maps.pv2 : &maps.pk2;
       for (int i = 0; i < n_my; ++i) {
         const int tile = blockIdx.x + i * gridDim.x, s = i % kTcStages, u = i / kTcStages;
         const int64_t bh = tile / tiles_per_head, row0 = (int64_t) (tile % tiles_per_head) * kTcRows;
-        if (!tc_wait(&bars.empty[s], (u & 1) ^ 1, abort_flag)) break;
+        uint64_t* full = vals ? &bars.full_v[s] : &bars.full_k[s];
+        if (!tc_wait(vals ? &bars.empty_v[s] : &bars.empty_k[s], (u & 1) ^ 1, abort_flag)) break;
         bf16* sQ = base + s * stage_elems;
-        bf16* sK = sQ + kTcRows * 64;
-        bf16* sV = sK + np * 64;
-        tma::expect_tx(&bars.full[s], bytes);
-        tma::load_4d(sQ, &maps.q, &bars.full[s], 0, (int) row0, (int) (bh % a.H), (int) (bh / a.H));
+        bf16* dst = sQ + kTcRows * 64 + (vals ? np * 64 : 0);
+        tma::expect_tx(full, bytes);
+        if (!vals) tma::load_4d(sQ, &maps.q, full, 0, (int) row0, (int) (bh % a.H), (int) (bh / a.H));
         const int n_p1 = p1_keys / kBS;
-        for (int j = 0; j < n_p1; ++j) {
-          const int r = (int) (bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS);
-          tma::load_2d(sK + j * kBS * 64, &maps.pk1, &bars.full[s], 0, r);
-          tma::load_2d(sV + j * kBS * 64, &maps.pv1, &bars.full[s], 0, r);
-        }
-        for (int j = 0; j < (np - p1_keys) / 64; ++j) {
-          const int r = (int) (bh * a.n2 + j * 64);
-          tma::load_2d(sK + (p1_keys + j * 64) * 64, &maps.pk2, &bars.full[s], 0, r);
-          tma::load_2d(sV + (p1_keys + j * 64) * 64, &maps.pv2, &bars.full[s], 0, r);
-        }
+        for (int j = 0; j < n_p1; ++j)
+          tma::load_2d(dst + j * kBS * 64, m1, full, 0, (int) (bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS));
+        for (int j = 0; j < (np - p1_keys) / 64; ++j)
+          tma::load_2d(dst + (p1_keys + j * 64) * 64, m2, full, 0, (int) (bh * a.n2 + j * 64));
       }
     }
   } else if (warp == 9) {
@@ -124,13 +125,14 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       const uint32_t idesc_s = tc::instr_desc(kTcRows, np, 0, 0), idesc_o = tc::instr_desc(kTcRows, 64, 0, 1);
       auto issue_s = [&](int i) -> bool {          // S(i) = Q.PK^T into TMEM buffer i & 1
         const int s = i % kTcStages, u = i / kTcStages, b = i & 1;
-        if (!tc_wait(&bars.full[s], u & 1, abort_flag)) return false;
+        if (!tc_wait(&bars.full_k[s], u & 1, abort_flag)) return false;
         tc::fence_after_sync();
         const uint32_t qa = tc::smem_u32(base + s * stage_elems), ka = qa + kTcRows * 128;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           tc::umma_ss(tmem + b * 256, tc::smem_desc(qa + ks * 32, 16, 1024), tc::smem_desc(ka + ks * 32, 16, 1024), idesc_s, ks > 0);
         tc::umma_commit(&bars.s_ready[b]);
+        tc::umma_commit(&bars.empty_k[s]);          // Q and the keys of this stage are free once S has executed
         return true;
       };
       bool ok = n_my > 0 && issue_s(0);
@@ -138,12 +140,13 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       for (int i = 0; ok && i < n_my; ++i) {
         const int s = i % kTcStages, b = i & 1;
         if (!tc_wait(&bars.p_ready[b], (i >> 1) & 1, abort_flag)) break;
+        if (!tc_wait(&bars.full_v[s], (i / kTcStages) & 1, abort_flag)) break;
         tc::fence_after_sync();
         const uint32_t va = tc::smem_u32(base + s * stage_elems) + (kTcRows + np) * 128;
         for (int ks = 0; ks < np / 16; ++ks)       // P: 16 keys = 8 packed columns per k-step; PV: 16 key rows = 2048 bytes
           tc::umma_ts(tmem + b * 256 + np, tmem + b * 256 + ks * 8, tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
         tc::umma_commit(&bars.o_ready[b]);
-        tc::umma_commit(&bars.empty[s]);
+        tc::umma_commit(&bars.empty_v[s]);
         if (i + 2 < n_my && !issue_s(i + 2)) break;
       }
     }
