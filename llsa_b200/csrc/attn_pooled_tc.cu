@@ -98,26 +98,36 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
 
   if (warp == 8 || warp == 10) {
     // ---------------------------------------------------------------- TMA producers: warp 8 Q + pooled keys, warp 10 pooled values
-    if (lane == 0) {
-      const bool vals = warp == 10;
-      const uint32_t bytes = (uint32_t) (vals ? np * 64 : kTcRows * 64 + np * 64) * 2;
-      const CUtensorMap* m1 = vals ? &maps.pv1 : &maps.pk1;
-      const CUtensorMap* m2 = vals ? &maps.pv2 : &maps.pk2;
-      for (int i = 0; i < n_my; ++i) {
-        const int tile = blockIdx.x + i * gridDim.x, s = i % kTcStages, u = i / kTcStages;
-        const int64_t bh = tile / tiles_per_head, row0 = (int64_t) (tile % tiles_per_head) * kTcRows;
-        uint64_t* full = vals ? &bars.full_v[s] : &bars.full_k[s];
-        if (!tc_wait(vals ? &bars.empty_v[s] : &bars.empty_k[s], (u & 1) ^ 1, abort_flag)) break;
-        bf16* sQ = base + s * stage_elems;
-        bf16* dst = sQ + kTcRows * 64 + (vals ? np * 64 : 0);
-        tma::expect_tx(full, bytes);
-        if (!vals) tma::load_4d(sQ, &maps.q, full, 0, (int) row0, (int) (bh % a.H), (int) (bh / a.H));
-        const int n_p1 = p1_keys / kBS;
-        for (int j = 0; j < n_p1; ++j)
-          tma::load_2d(dst + j * kBS * 64, m1, full, 0, (int) (bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS));
-        for (int j = 0; j < (np - p1_keys) / 64; ++j)
-          tma::load_2d(dst + (p1_keys + j * 64) * 64, m2, full, 0, (int) (bh * a.n2 + j * 64));
+    // One lane per copy: lane j < n_p1 fetches its block index and issues the copy of level-1 block j, the next lanes the 64-row
+    // level-2 boxes, lane 31 the Q tile.  A single lane doing all of them pays one index round trip per block, back to back
+    // (the copies' asm statements order memory accesses), which is longer than the tile period.
+    const bool vals = warp == 10;
+    const uint32_t bytes = (uint32_t) (vals ? np * 64 : kTcRows * 64 + np * 64) * 2;
+    const CUtensorMap* m1 = vals ? &maps.pv1 : &maps.pk1;
+    const CUtensorMap* m2 = vals ? &maps.pv2 : &maps.pk2;
+    const int n_p1 = p1_keys / kBS, n_p2 = (np - p1_keys) / 64;
+    for (int i = 0; i < n_my; ++i) {
+      const int tile = blockIdx.x + i * gridDim.x, s = i % kTcStages, u = i / kTcStages;
+      const int64_t bh = tile / tiles_per_head, row0 = (int64_t) (tile % tiles_per_head) * kTcRows;
+      uint64_t* full = vals ? &bars.full_v[s] : &bars.full_k[s];
+      int ok = 1;
+      if (lane == 0) {
+        ok = tc_wait(vals ? &bars.empty_v[s] : &bars.empty_k[s], (u & 1) ^ 1, abort_flag) ? 1 : 0;
+        if (ok) tma::expect_tx(full, bytes);
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      bf16* sQ = base + s * stage_elems;
+      bf16* dst = sQ + kTcRows * 64 + (vals ? np * 64 : 0);
+      if (lane < n_p1) {
+        tma::load_2d(dst + lane * kBS * 64, m1, full, 0, (int) (bh * a.n1 + p1_block(a, bh, row0 / kBS, lane) * kBS));
+      } else if (lane < n_p1 + n_p2) {
+        const int j = lane - n_p1;
+        tma::load_2d(dst + (p1_keys + j * 64) * 64, m2, full, 0, (int) (bh * a.n2 + j * 64));
+      } else if (lane == 31 && !vals) {
+        tma::load_4d(sQ, &maps.q, full, 0, (int) row0, (int) (bh % a.H), (int) (bh / a.H));
+      }
+      __syncwarp();
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
