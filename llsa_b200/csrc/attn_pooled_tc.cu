@@ -51,7 +51,7 @@ struct TcMaps {
 struct TcBars {
   // a stage's [Q | pooled keys] part and its [pooled values] part fill and drain separately: Q and the keys are free again as soon
   // as S = Q.PK^T has executed, two tiles before the values (free after O = P.PV), so their refill runs that much further ahead
-  uint64_t full_k[kTcStages], empty_k[kTcStages], full_v[kTcStages], empty_v[kTcStages], s_ready[2], p_ready[2], o_ready[2];
+  uint64_t full_k[kTcStages], empty_k[kTcStages], full_v[kTcStages], empty_v[kTcStages], s_ready[2], p_head[2], p_ready[2], o_ready[2];
 };
 
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -86,6 +86,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       tc::mbar_init(&bars.s_ready[i], 1);
       tc::mbar_init(&bars.o_ready[i], 1);
       tc::mbar_init(&bars.p_ready[i], 4);       // one arrival per softmax warp
+      tc::mbar_init(&bars.p_head[i], 4);        // P of all but the last 64 keys is written (np > 64)
     }
     tc::fence_mbar_init();
   }
@@ -149,11 +150,17 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       if (ok && n_my > 1) ok = issue_s(1);
       for (int i = 0; ok && i < n_my; ++i) {
         const int s = i % kTcStages, b = i & 1;
-        if (!tc_wait(&bars.p_ready[b], (i >> 1) & 1, abort_flag)) break;
+        // O = P.PV starts on the keys whose P is already written while the softmax warps finish the last 64
+        const int ks_head = np > 64 ? (np - 64) / 16 : 0;
+        if (ks_head && !tc_wait(&bars.p_head[b], (i >> 1) & 1, abort_flag)) break;
         if (!tc_wait(&bars.full_v[s], (i / kTcStages) & 1, abort_flag)) break;
         tc::fence_after_sync();
         const uint32_t va = tc::smem_u32(base + s * stage_elems) + (kTcRows + np) * 128;
-        for (int ks = 0; ks < np / 16; ++ks)       // P: 16 keys = 8 packed columns per k-step; PV: 16 key rows = 2048 bytes
+        for (int ks = 0; ks < ks_head; ++ks)       // P: 16 keys = 8 packed columns per k-step; PV: 16 key rows = 2048 bytes
+          tc::umma_ts(tmem + b * 256 + np, tmem + b * 256 + ks * 8, tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
+        if (!tc_wait(&bars.p_ready[b], (i >> 1) & 1, abort_flag)) break;
+        tc::fence_after_sync();
+        for (int ks = ks_head; ks < np / 16; ++ks)
           tc::umma_ts(tmem + b * 256 + np, tmem + b * 256 + ks * 8, tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
         tc::umma_commit(&bars.o_ready[b]);
         tc::umma_commit(&bars.empty_v[s]);
@@ -220,6 +227,12 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
           if (c0 + 64 < np) tc::tmem_ld32_async(t_s + c0 + 64, va);
           chunk_exp(vb, c0 + 32);
           if (c0 + 64 < np) tc::tmem_ld_wait(va);
+          if (c0 + 128 == np) {                     // everything but the last 64 keys: the MMA warp may start O = P.PV
+            tc::tmem_st_wait();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(&bars.p_head[wg]);
+          }
         }
         tc::tmem_st_wait();
         tc::fence_before_sync();
