@@ -45,7 +45,7 @@ KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_mma_kernel", "refine_top
 # profiles/attention_kernels_llsa_l2_batch2.md (dram__bytes_read.sum + dram__bytes_write.sum); traffic grows in
 # proportion to the slices (every slice is independent), so a full launch is scaled by B*H / 12.
 NCU_DRAM_BYTES_12_SLICES = dict(attn_fwd=(49.5 + 2.7 + 54.0 + 0.2) * 1e6, attn_bwd_dq=(100.6 + 11.1) * 1e6,
-                                attn_bwd_dkv_pooled=(85.7 + 4.2) * 1e6, attn_bwd_dkv_fine=(89.1 + 12.5 + 15.7 + 0.0) * 1e6)
+                                attn_bwd_dkv_pooled=(85.6 + 4.4) * 1e6, attn_bwd_dkv_fine=(89.1 + 14.7 + 15.7 + 0.1) * 1e6)
 
 
 def parse():
