@@ -50,7 +50,9 @@ class HostPipeline:
         torch.cuda.synchronize(self.dev)
         q.grad = k.grad = v.grad = None
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=self.s_comp):
+        # thread-local error mode: other threads of the process (a communicator's watchdog polling its events, for one) may keep
+        # calling the CUDA API while this thread captures
+        with torch.cuda.graph(g, stream=self.s_comp, capture_error_mode="thread_local"):
             o = self.call(q, k, v)
             o.backward(slot[3])
         return g, (o.detach(), q.grad, k.grad, v.grad)
