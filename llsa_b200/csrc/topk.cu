@@ -284,6 +284,44 @@ __device__ __forceinline__ void refine_select_regs(const float* sc, const int* c
   }
 }
 
+// The same selection for at most 128 candidates and top-k <= 32 with fewer instructions per round: a lane sorts its four
+// candidates once (descending score image, ascending block index among equals), so its best is always slot 0; a round is two warp
+// reductions, the winner's lane shifts its list up by one, and winner t stays in lane t until one store writes the row's list.
+__device__ __forceinline__ void refine_select_sorted4(const float* sc, const int* cand, int C, int bs, int topk, void* idx_out, int idx64,
+                                                      int64_t out_row0, int warp, int lane, int nwarps) {
+  for (int r = warp; r < bs; r += nwarps) {
+    const float* s = sc + r * C;
+    uint32_t key[4], blk[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = lane + 32 * u;
+      key[u] = j < C ? orderable(s[j]) : 0u;            // 0 is below every real score's image
+      blk[u] = j < C ? (uint32_t) cand[j] : 0xFFFFFFFFu;
+    }
+    auto order = [&](int x, int y) {                     // afterwards slot x is not worse than slot y
+      const bool sw = key[y] > key[x] || (key[y] == key[x] && blk[y] < blk[x]);
+      const uint32_t kx = sw ? key[y] : key[x], ky = sw ? key[x] : key[y], bx = sw ? blk[y] : blk[x], by = sw ? blk[x] : blk[y];
+      key[x] = kx; key[y] = ky; blk[x] = bx; blk[y] = by;
+    };
+    order(0, 1); order(2, 3); order(0, 2); order(1, 3); order(1, 2);
+    uint32_t mine = 0;                                   // winner number `lane` of this row
+    for (int t = 0; t < topk; ++t) {
+      const uint32_t mk = __reduce_max_sync(0xffffffffu, key[0]);
+      const uint32_t mb = __reduce_min_sync(0xffffffffu, key[0] == mk ? blk[0] : 0xFFFFFFFFu);
+      if (key[0] == mk && blk[0] == mb) {               // candidates are distinct blocks: one owner
+        key[0] = key[1]; blk[0] = blk[1]; key[1] = key[2]; blk[1] = blk[2]; key[2] = key[3]; blk[2] = blk[3];
+        key[3] = 0u; blk[3] = 0xFFFFFFFFu;
+      }
+      if (lane == t) mine = mb;
+    }
+    if (lane < topk) {
+      const int64_t o = (out_row0 + r) * topk + lane;
+      if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = (int64_t) mine;
+      else reinterpret_cast<int32_t*>(idx_out)[o] = (int32_t) mine;
+    }
+  }
+}
+
 template <typename T, bool MMA>
 __global__ void __launch_bounds__(128)
 refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
@@ -296,7 +334,8 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   const int64_t bh = blockIdx.y, P = blockIdx.x, n2q = M / bs, n2 = Mk / bs;
   const T* q0 = pq1 + (bh * M + P * bs) * D;
   const T* k0 = pk1 + bh * Mk * D;
-  for (int i = threadIdx.x; i < bs * D; i += blockDim.x) qs[i] = to_f32<T>(q0[i]);
+  if constexpr (!MMA)                                    // the tensor-core path takes its query fragments straight from global memory
+    for (int i = threadIdx.x; i < bs * D; i += blockDim.x) qs[i] = to_f32<T>(q0[i]);
   for (int j = threadIdx.x; j < C; j += blockDim.x) {
     int64_t p = p_idx.at((bh * n2q + P) * p_topk + j / bs);
     p = p < 0 ? 0 : (p >= n2 ? n2 - 1 : p);      // never read outside the tensor
@@ -358,7 +397,8 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   if (C <= 32 * kRefineSlots) {
-    if (C <= 128) refine_select_regs<4>(sc, cand, C, bs, topk, idx_out, idx64, bh * M + P * bs, warp, lane, nwarps);
+    if (C <= 128 && topk <= 32) refine_select_sorted4(sc, cand, C, bs, topk, idx_out, idx64, bh * M + P * bs, warp, lane, nwarps);
+    else if (C <= 128) refine_select_regs<4>(sc, cand, C, bs, topk, idx_out, idx64, bh * M + P * bs, warp, lane, nwarps);
     else refine_select_regs<kRefineSlots>(sc, cand, C, bs, topk, idx_out, idx64, bh * M + P * bs, warp, lane, nwarps);
     return;
   }
