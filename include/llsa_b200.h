@@ -40,7 +40,17 @@ enum LlsaStatus {
   LLSA_ERR_ARG = 5,         /* bad scalar argument (topk, block size, ...)        */
   LLSA_ERR_WORKSPACE = 6,   /* scratch buffer missing or too small                */
   LLSA_ERR_CUDA = 7,        /* a CUDA runtime call or kernel launch failed        */
-  LLSA_ERR_DEVICE_CHECK = 8 /* a kernel recorded an out-of-range index            */
+  LLSA_ERR_DEVICE_CHECK = 8 /* a kernel set the caller's device status word: an out-of-range
+                               index, or a bounded wait inside a kernel that ran out      */
+};
+
+/* Bits a kernel may set in a device status word (LlsaAttnArgs.status, the `status`
+ * argument of the transpose).  The host reads the word after synchronising;
+ * llsa_status_check() turns it into a return code. */
+enum LlsaDeviceStatus {
+  LLSA_DEV_BAD_INDEX = 1,    /* a block index outside [0, n) was met (and skipped or clamped) */
+  LLSA_DEV_WAIT_EXPIRED = 2  /* a bounded wait on an mbarrier gave up; the CTA left its tiles
+                                unfinished and the call's outputs are not valid               */
 };
 
 typedef struct LlsaTensor {
@@ -53,6 +63,9 @@ typedef struct LlsaTensor {
 
 int llsa_version(void);
 const char* llsa_last_error_string(void);
+/* LLSA_OK for a status word of 0, else LLSA_ERR_DEVICE_CHECK with the error string naming the bits
+ * (`status_word` is the value the caller copied back from the device). */
+int llsa_status_check(int32_t status_word);
 
 /* ---- pooling: src/llsa/kernel/triton/mean_pool.py --------------------------
  * y[b,h,s,:] = (sum_{t<k} x[b,h,s*k+t,:]) / k with the sum accumulated
@@ -107,6 +120,12 @@ int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTen
 size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t T, int64_t n_kv);
 int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
                            void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+/* The same transpose with a second list: pairs [B,H,M*T] (I32) holds, in the order of `flat`, the position
+ * m*T + t of each entry inside its head's idx (flat = pairs / T).  llsa_attn_bwd uses it to find what the
+ * query-major stage left for each (query block, selected block) pair (LlsaAttnArgs.flat_pairs).  The reference
+ * has the plain list only (indices_transpose.py:70-78). */
+int llsa_transpose_indices_pairs(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs,
+                                 int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
 
 /* The same transpose for hosts that cannot provide device scratch.  This entry
  * point has no counterpart in the reference: it exists for callers that never
@@ -175,6 +194,21 @@ typedef struct LlsaAttnArgs {
                                   [B,H,ceil(N/16*topk/128),4096] for dK/dV tiles of KV blocks whose
                                   list of query blocks straddles two work windows (not read before
                                   it is written; may be NULL for f32 tensors) */
+  const LlsaTensor* fine_pds;  /* backward, bf16 tensors only: F32-typed scratch of
+                                  llsa_attn_bwd_pds_elems() elements.  The dQ stage (stage_mask 1)
+                                  leaves P and dS (bf16) of every (query block, selected block) pair
+                                  here and the dK/dV stage (stage_mask 4) reads them instead of
+                                  recomputing both from q, k, v, lse and delta */
+  const LlsaTensor* flat_pairs;/* backward, bf16 tensors only: I32 [B,H,N/16*topk], the `pairs` list of
+                                  llsa_transpose_indices_pairs for the same CSR as offsets / flat */
+  int32_t no_tcgen05;          /* 1: keep the pooled-key stages on the mma.sync kernels (the form used
+                                  for shapes the tcgen05 kernels do not cover); for cross-checks */
+  int32_t wait_limit;          /* 0: default.  Otherwise the number of polls after which a bounded
+                                  mbarrier wait inside the tcgen05 kernels gives up (tests use a tiny
+                                  value to exercise the give-up path; the kernel then returns
+                                  normally with LLSA_DEV_WAIT_EXPIRED in *status) */
+  int32_t* status;             /* device int32 or NULL: kernels OR LlsaDeviceStatus bits into it; the
+                                  caller zeroes it, and reads it back after synchronising */
 } LlsaAttnArgs;
 
 /* Forward: o, lse.  One level (pk2 == NULL) replaces sparse_indices_attn_res_fwd
@@ -191,13 +225,8 @@ int llsa_attn_bwd(const LlsaAttnArgs* args, void* stream);
  * Nq query rows per (b,h) and `topk` selected blocks per query block (the caller allocates it; any 4-D contiguous
  * shape with at least this many elements is accepted).  The library itself never allocates device memory. */
 int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk);
-
-/* Measurement aid, no counterpart in the reference: issue rate of mma.sync.m16n8k16 (bf16 in, fp32 out), the tensor
- * instruction of the fine-block kernels.  Launches n_sms CTAs of warps_per_sm warps; every warp issues `ilp` (1, 2, 4 or 8)
- * independent accumulator chains `iters` times.  `sink` (device, n_sms * warps_per_sm * 32 floats) receives the accumulators,
- * `cycles` (device, one int64) the clock64 cycles CTA 0 spent in the loop.  Cycles per instruction per SM sub-partition =
- * cycles / (iters * ilp * max(warps_per_sm, 4) / 4). */
-int llsa_probe_mma_rate(int warps_per_sm, int ilp, int iters, int n_sms, float* sink, long long* cycles, void* stream);
+/* Element count (4-byte elements) of LlsaAttnArgs.fine_pds: 1 KB per (query block, selected block) pair. */
+int64_t llsa_attn_bwd_pds_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk);
 
 #ifdef __cplusplus
 }

@@ -35,6 +35,7 @@ class LlsaAttnArgs(C.Structure):
         ("dpk_acc", _P), ("dpv_acc", _P), ("dpk2_acc", _P), ("dpv2_acc", _P),
         ("fold_pool_bwd", C.c_int32), ("kv_weight", C.c_float), ("kv_weight_2", C.c_float),
         ("force_generic", C.c_int32), ("stage_mask", C.c_int32), ("dkv_partial", _P),
+        ("fine_pds", _P), ("flat_pairs", _P), ("no_tcgen05", C.c_int32), ("wait_limit", C.c_int32), ("status", C.c_void_p),
     ]
 
 
@@ -42,8 +43,8 @@ EXPORTS = [
     "llsa_version", "llsa_last_error_string", "llsa_mean_pool_fwd", "llsa_mean_pool_bwd", "llsa_pool_pyramid_fwd",
     "llsa_rope_pool_pyramid_fwd",
     "llsa_rope_fwd", "llsa_rope_bwd", "llsa_coarse_topk", "llsa_refine_topk", "llsa_transpose_scratch_bytes",
-    "llsa_transpose_indices", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd", "llsa_attn_bwd_partial_elems",
-    "llsa_probe_mma_rate",
+    "llsa_transpose_indices", "llsa_transpose_indices_pairs", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd",
+    "llsa_attn_bwd_partial_elems", "llsa_attn_bwd_pds_elems", "llsa_status_check",
 ]
 
 _lib: Optional[C.CDLL] = None
@@ -68,12 +69,15 @@ def _declare(lib: C.CDLL) -> None:
     lib.llsa_transpose_indices_noalloc.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_void_p]
     lib.llsa_attn_bwd_partial_elems.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32]
     lib.llsa_attn_bwd_partial_elems.restype = C.c_int64
-    lib.llsa_probe_mma_rate.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.llsa_transpose_indices_pairs.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+    lib.llsa_attn_bwd_pds_elems.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32]
+    lib.llsa_attn_bwd_pds_elems.restype = C.c_int64
+    lib.llsa_status_check.argtypes = [C.c_int32]
     lib.llsa_attn_fwd.argtypes = [C.POINTER(LlsaAttnArgs), C.c_void_p]
     lib.llsa_attn_bwd.argtypes = [C.POINTER(LlsaAttnArgs), C.c_void_p]
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("llsa_last_error_string", "llsa_transpose_scratch_bytes", "llsa_attn_bwd_partial_elems"):
+        if name not in ("llsa_last_error_string", "llsa_transpose_scratch_bytes", "llsa_attn_bwd_partial_elems", "llsa_attn_bwd_pds_elems"):
             fn.restype = C.c_int
 
 

@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libllsa_b200.so")
 SOURCES = ["capi.cu", "pool.cu", "rope.cu", "topk.cu", "transpose.cu", "attn.cu", "attn_generic.cu",
-           "attn_fwd_mma.cu", "attn_bwd_mma.cu", "attn_pooled_tc.cu", "attn_pooled_bwd_tc.cu", "attn_pooled_loop_tc.cu", "attn_pooled_bwd_loop_tc.cu", "attn_pooled_dkv_loop_tc.cu", "probe.cu"]
+           "attn_fwd_mma.cu", "attn_bwd_mma.cu", "attn_pooled_tc.cu", "attn_pooled_bwd_tc.cu", "attn_pooled_loop_tc.cu", "attn_pooled_bwd_loop_tc.cu", "attn_pooled_dkv_loop_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
@@ -45,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         sp = os.path.join(CSRC, src)
         if not os.path.exists(sp):
-            continue
+            raise FileNotFoundError("listed source %s is missing" % sp)
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", sp, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

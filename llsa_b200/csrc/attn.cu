@@ -67,6 +67,18 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
                        g->dkv_partial->shape[0] * g->dkv_partial->shape[1] * g->dkv_partial->shape[2] * g->dkv_partial->shape[3] >= need,
                    LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial must be a contiguous F32 tensor of at least %lld elements", (long long) need);
     }
+    if (dt == LLSA_BF16 && !g->force_generic) {
+      // P / dS hand-over between the dQ stage and the dK/dV stage of the tensor-core path
+      const int64_t need = B * H * nq1 * g->topk * 256;
+      LLSA_REQUIRE(g->fine_pds && g->fine_pds->ptr && g->fine_pds->dtype == LLSA_F32 && is_contiguous(g->fine_pds), LLSA_ERR_WORKSPACE,
+                   "attn_bwd: fine_pds scratch missing (a contiguous F32 tensor of llsa_attn_bwd_pds_elems() elements)");
+      int64_t have = 1;
+      for (int i = 0; i < g->fine_pds->ndim; ++i) have *= g->fine_pds->shape[i];
+      LLSA_REQUIRE(have >= need && ((uintptr_t) g->fine_pds->ptr % 16) == 0, LLSA_ERR_WORKSPACE,
+                   "attn_bwd: fine_pds holds %lld elements, %lld needed", (long long) have, (long long) need);
+      LLSA_REQUIRE(g->flat_pairs, LLSA_ERR_WORKSPACE, "attn_bwd: flat_pairs missing (llsa_transpose_indices_pairs)");
+      if ((rc = check_contig(g->flat_pairs, "flat_pairs", LLSA_I32, 3, sf))) return rc;
+    }
     if (two) {
       LLSA_REQUIRE(g->dpk2_acc && g->dpv2_acc, LLSA_ERR_NULL, "attn_bwd: dpk2_acc / dpv2_acc missing");
       if ((rc = check_contig(g->dpk2_acc, "dpk2_acc", LLSA_F32, 4, s2))) return rc;
@@ -83,6 +95,11 @@ using namespace llsa;
 extern "C" int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {
   if (B <= 0 || H <= 0 || Nq <= 0 || topk <= 0) return 0;
   return B * H * ((Nq / kBS * topk + 127) / 128) * 4096;
+}
+
+extern "C" int64_t llsa_attn_bwd_pds_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {
+  if (B <= 0 || H <= 0 || Nq <= 0 || topk <= 0) return 0;
+  return B * H * (Nq / kBS) * topk * 256;
 }
 
 extern "C" int llsa_attn_fwd(const LlsaAttnArgs* args, void* stream) {

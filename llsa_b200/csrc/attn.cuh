@@ -35,6 +35,11 @@ struct AttnP {
   const void* offsets;  // CSR of idx: [BH, n1+1]
   int off64;
   const int32_t* flat;  // [BH, nq1*topk]
+  const int32_t* pairs; // [BH, nq1*topk]: position qb*topk + slot of each CSR entry inside the head's index list, or nullptr
+  uint4* pds;           // [BH*nq1*topk][2][32]: P^T and dS^T (bf16) of every (query block, selected block) pair as the
+                        // A-operand registers of the dK/dV products, one uint4 per lane; nullptr: not handed over
+  int32_t* status;      // device status word (LlsaDeviceStatus bits) or nullptr
+  int wait_limit;       // polls before a bounded mbarrier wait gives up (0: the kernels' default)
   int H;
   int64_t N, n1, n2;      // KEY side: tokens, 16-token blocks, 256-token blocks of k / v
   int64_t Nq, nq1, nq2;   // QUERY side: the same counts for q (equal to the key side unless q is a shard of the sequence)
@@ -68,6 +73,7 @@ int build_attn_params_check(const LlsaAttnArgs* g, bool bwd);
 template <typename T>
 AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd);
 
+void note_scalar_path();                             // leaves a note in the thread's error string: bf16 operands on the scalar kernels
 bool mma_path_ok(const LlsaAttnArgs* g, bool bwd);   // operands meet the tensor-core kernels' alignment / top-k limits
 int pooled_smem_tiles(int n_pooled);                 // pooled key tiles a CTA keeps in shared memory
 int pooled_tc_keys(const AttnP<__nv_bfloat16>& a);   // pooled keys per row if the tcgen05 pooled kernels apply, else 0
@@ -114,6 +120,8 @@ inline AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd) {
   a.w1 = g->token_weight;
   a.w2 = g->token_weight_2;
   a.scale = 0.125f;
+  a.status = g->status;
+  a.wait_limit = g->wait_limit;
   if (a.two_level) {
     a.p1_blocks = a.topk_p;
     a.p2_blocks = a.n2 >= 64 ? (int) (a.n2 / kBS) : 0;
@@ -139,6 +147,8 @@ inline AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd) {
     a.offsets = g->offsets->ptr;
     a.off64 = g->offsets->dtype == LLSA_I64;
     a.flat = (const int32_t*) g->flat->ptr;
+    a.pairs = g->flat_pairs ? (const int32_t*) g->flat_pairs->ptr : nullptr;
+    a.pds = g->fine_pds ? (uint4*) g->fine_pds->ptr : nullptr;
     a.kvw1 = g->kv_weight;
     a.kvw2 = g->kv_weight_2;
     a.fold = g->fold_pool_bwd;

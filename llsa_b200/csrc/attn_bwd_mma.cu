@@ -15,17 +15,19 @@
 //                          products S^T, dP^T, dV += P^T.dO, dK += dS^T.Q over the
 //                          16 query blocks and add the 16x64 results into fp32
 //                          accumulators (one red.add per element and group).
-//   attn_dkv_fine_kernel   the CSR of a head is cut into equal windows of 128 entries
-//                          (one CTA, 32 entries per warp) so every warp runs the
-//                          same number of steps however skewed the fan-in is;
-//                          tiles of buckets that straddle a range meet in shared
-//                          memory / a global partial tensor (no atomics), and
-//   attn_dkv_finish_kernel sums the window partials; every store folds in the pooling
+//   attn_dq_fine_kernel    the same for the fine blocks alone (the pooled keys then run on
+//                          tcgen05); both dQ kernels leave P and dS of every (query block,
+//                          selected block) pair in a scratch tensor for the next kernel.
+//   attn_dkv_fine_ring_kernel  the CSR of a head is cut into equal windows of 128 entries
+//                          (one CTA, 32 entries per warp) so every warp runs the same
+//                          number of steps however skewed the fan-in is; an entry is
+//                          dV += P^T.dO, dK += dS^T.Q with P, dS read back; tiles of
+//                          buckets that straddle a range meet in shared memory / a
+//                          global partial tensor (no atomics), and
+//   attn_dkv_finish_ld_kernel sums the window partials; every store folds in the pooling
 //                          backward (dk += (dpk[j] + dpk2[j/16]/16)/16), one bf16 store.
 // The reference multiplies k by scale into new tensors first (res_1.py:420-422);
 // here scale rides in the exp2 argument and in the epilogues.
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "attn.cuh"
@@ -62,6 +64,34 @@ __device__ __forceinline__ void dq_ds(float (&s0)[4], float (&s1)[4], const floa
   s1[2] = fast_exp2(fmaf(s1[2], sl2, lw - r.L1)) * (p1[2] - r.delta1);
   s1[3] = fast_exp2(fmaf(s1[3], sl2, lw - r.L1)) * (p1[3] - r.delta1);
   da[0] = pack_bf16(s0[0], s0[1]); da[1] = pack_bf16(s0[2], s0[3]); da[2] = pack_bf16(s1[0], s1[1]); da[3] = pack_bf16(s1[2], s1[3]);
+}
+
+// The same for a fine block (weight 1), returning P (bf16) as well: both go to the dK/dV stage.
+__device__ __forceinline__ void dq_p_ds(float (&s0)[4], float (&s1)[4], const float (&p0)[4], const float (&p1)[4], const DqRow& r, float sl2,
+                                        uint32_t (&pa)[4], uint32_t (&da)[4]) {
+  s0[0] = fast_exp2(fmaf(s0[0], sl2, -r.L0)); s0[1] = fast_exp2(fmaf(s0[1], sl2, -r.L0));
+  s0[2] = fast_exp2(fmaf(s0[2], sl2, -r.L1)); s0[3] = fast_exp2(fmaf(s0[3], sl2, -r.L1));
+  s1[0] = fast_exp2(fmaf(s1[0], sl2, -r.L0)); s1[1] = fast_exp2(fmaf(s1[1], sl2, -r.L0));
+  s1[2] = fast_exp2(fmaf(s1[2], sl2, -r.L1)); s1[3] = fast_exp2(fmaf(s1[3], sl2, -r.L1));
+  pa[0] = pack_bf16(s0[0], s0[1]); pa[1] = pack_bf16(s0[2], s0[3]); pa[2] = pack_bf16(s1[0], s1[1]); pa[3] = pack_bf16(s1[2], s1[3]);
+  da[0] = pack_bf16(s0[0] * (p0[0] - r.delta0), s0[1] * (p0[1] - r.delta0));
+  da[1] = pack_bf16(s0[2] * (p0[2] - r.delta1), s0[3] * (p0[3] - r.delta1));
+  da[2] = pack_bf16(s1[0] * (p1[0] - r.delta0), s1[1] * (p1[1] - r.delta0));
+  da[3] = pack_bf16(s1[2] * (p1[2] - r.delta1), s1[3] * (p1[3] - r.delta1));
+}
+
+// Hands P and dS of a (query block, selected block) pair to the dK/dV stage.  That stage multiplies their transposes
+// (rows = keys) from the left: dV += P^T.dO, dK += dS^T.Q.  The A operand of those products holds, in lane (g,t),
+// (key g, queries 2t,2t+1), (key g+8, same), (key g, queries 8+2t,9+2t), (key g+8, same); the registers here hold
+// (query g, keys 2t,2t+1), (query g+8, ..), (query g, keys 8+2t,..), (query g+8, ..): each is an 8x8 matrix spread over
+// the warp, and transposing the four (movmatrix) and swapping the middle two gives exactly the A operand.  One uint4 per
+// lane and matrix: 1 KB per pair, written and later read in full 512-byte rows.
+__device__ __forceinline__ void store_pds(uint4* dst, const uint32_t (&pa)[4], const uint32_t (&da)[4], int lane) {
+  uint4 p, d;
+  p.x = movmatrix_trans(pa[0]); p.y = movmatrix_trans(pa[2]); p.z = movmatrix_trans(pa[1]); p.w = movmatrix_trans(pa[3]);
+  d.x = movmatrix_trans(da[0]); d.y = movmatrix_trans(da[2]); d.z = movmatrix_trans(da[1]); d.w = movmatrix_trans(da[3]);
+  dst[lane] = p;
+  dst[32 + lane] = d;
 }
 
 struct GlobalKV {
@@ -169,7 +199,13 @@ __global__ void __launch_bounds__(NW * 32, 4) attn_dq_mma_kernel(AttnP<bf16> a, 
         load_rowfrag(v1, r.v + (int64_t) (g + 8) * r.vs, t);
       }
       uint32_t da[4];
-      dq_ds(s0, s1, p0, p1, row, sl2, lw, da);
+      if (gi < a.topk && a.pds) {           // a fine block: P and dS also go to the dK/dV stage
+        uint32_t pa[4];
+        dq_p_ds(s0, s1, p0, p1, row, sl2, pa, da);
+        store_pds(a.pds + ((bh * a.nq1 + qb) * a.topk + gi) * 64, pa, da, lane);
+      } else {
+        dq_ds(s0, s1, p0, p1, row, sl2, lw, da);
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) mma_bf16_16816(dq[i], da[0], da[1], da[2], da[3], tk0[i], tk1[i]);
     }
@@ -271,7 +307,13 @@ __global__ void __launch_bounds__(NW * 32, 4) attn_dq_fine_kernel(AttnP<bf16> a)
     mma_rows_x_keys(s0, s1, qlo, qhi, k0, k1);
     mma_rows_x_keys(p0, p1, dlo, dhi, v0, v1);
     uint32_t da[4];
-    dq_ds(s0, s1, p0, p1, row, sl2, 0.f, da);
+    if (a.pds) {                            // P and dS also go to the dK/dV stage
+      uint32_t pa[4];
+      dq_p_ds(s0, s1, p0, p1, row, sl2, pa, da);
+      store_pds(a.pds + ((bh * a.nq1 + qb) * a.topk + gi) * 64, pa, da, lane);
+    } else {
+      dq_ds(s0, s1, p0, p1, row, sl2, 0.f, da);
+    }
     mma_x_rowfrag_t(dq, da[0], da[1], da[2], da[3], k0, k1);      // K transposed in registers (movmatrix)
   }
   store_acc_row_t<0>(a.dq.row(b, h, qb * kBS + g), dq, t, a.scale);
@@ -292,35 +334,6 @@ __device__ __forceinline__ void dkv_p_ds(float (&s0)[4], float (&s1)[4], float (
   e1[0] = s1[0] * (e1[0] - db.x); e1[1] = s1[1] * (e1[1] - db.y); e1[2] = s1[2] * (e1[2] - db.x); e1[3] = s1[3] * (e1[3] - db.y);
   pa[0] = pack_bf16(s0[0], s0[1]); pa[1] = pack_bf16(s0[2], s0[3]); pa[2] = pack_bf16(s1[0], s1[1]); pa[3] = pack_bf16(s1[2], s1[3]);
   ea[0] = pack_bf16(e0[0], e0[1]); ea[1] = pack_bf16(e0[2], e0[3]); ea[2] = pack_bf16(e1[0], e1[1]); ea[3] = pack_bf16(e1[2], e1[3]);
-}
-
-// One (key tile) x (query block) step of the dK/dV side with Q and dO read from global memory.
-// ka/kb, va/vb: the key tile's rows g / g+8 as the A operand.  dV += P^T.dO, dK += dS^T.Q (unscaled).
-__device__ __forceinline__ void dkv_step(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t qb, const RowFrag& ka, const RowFrag& kb,
-                                         const RowFrag& va, const RowFrag& vb, float lw, float sl2, int g, int t, float (&dk)[8][4],
-                                         float (&dv)[8][4]) {
-  const bf16* qp = a.q.row(b, h, qb * kBS);
-  const bf16* dp = a.d_o.row(b, h, qb * kBS);
-  RowFrag q0, q1, d0, d1;
-  load_rowfrag(q0, qp + (int64_t) g * a.q.sn, t);
-  load_rowfrag(q1, qp + (int64_t) (g + 8) * a.q.sn, t);
-  load_rowfrag(d0, dp + (int64_t) g * a.d_o.sn, t);
-  load_rowfrag(d1, dp + (int64_t) (g + 8) * a.d_o.sn, t);
-  ColFrag qc, dc;
-  load_colfrag(dc, dp, a.d_o.sn, g, t);
-  load_colfrag(qc, qp, a.q.sn, g, t);
-  const int64_t rbase = bh * a.Nq + qb * kBS;
-  const float2 la = *reinterpret_cast<const float2*>(a.lse + rbase + 2 * t);        // query rows 2t, 2t+1
-  const float2 lb = *reinterpret_cast<const float2*>(a.lse + rbase + 8 + 2 * t);    // query rows 8+2t, 9+2t
-  const float2 da = *reinterpret_cast<const float2*>(a.delta + rbase + 2 * t);
-  const float2 db = *reinterpret_cast<const float2*>(a.delta + rbase + 8 + 2 * t);
-  float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
-  mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
-  mma_rows_x_keys(e0, e1, va, vb, d0, d1);
-  uint32_t pa[4], ea[4];
-  dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, lw, pa, ea);
-  mma_x_cols(dv, pa[0], pa[1], pa[2], pa[3], dc);
-  mma_x_cols(dk, ea[0], ea[1], ea[2], ea[3], qc);
 }
 
 template <int NW>
@@ -396,53 +409,11 @@ __global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16>
   }
 }
 
-// Adds the pooling-backward term to a finished 16x64 dK/dV tile of KV block j and stores it (bf16).
-__device__ __forceinline__ void dkv_fine_store(const AttnP<bf16>& a, int64_t b, int64_t h, int64_t bh, int64_t j, float (&dk)[8][4],
-                                               float (&dv)[8][4], int g, int t) {
-  // the tiles come from mma_x_rowfrag_t-style products: acc[u][e] is channel 16t + 2u + e
-  float ek[2][8], ev[2][8];   // pooling-backward term: [e][u] for channel 16t + 2u + e
-#pragma unroll
-  for (int u = 0; u < 8; ++u) ek[0][u] = ek[1][u] = ev[0][u] = ev[1][u] = 0.f;
-  if (a.fold) {
-    const float* g1k = a.dpk + (bh * a.n1 + j) * kD + 16 * t;
-    const float* g1v = a.dpv + (bh * a.n1 + j) * kD + 16 * t;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) { ek[0][u] = g1k[2 * u]; ek[1][u] = g1k[2 * u + 1]; ev[0][u] = g1v[2 * u]; ev[1][u] = g1v[2 * u + 1]; }
-    if (a.two_level) {
-      const float* g2k = a.dpk2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
-      const float* g2v = a.dpv2 + (bh * a.n2 + j / kBS) * kD + 16 * t;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        ek[0][u] += g2k[2 * u] * (1.f / kBS); ek[1][u] += g2k[2 * u + 1] * (1.f / kBS);
-        ev[0][u] += g2v[2 * u] * (1.f / kBS); ev[1][u] += g2v[2 * u + 1] * (1.f / kBS);
-      }
-    }
-  }
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    dk[u][0] = dk[u][0] * a.scale + ek[0][u] * (1.f / kBS); dk[u][1] = dk[u][1] * a.scale + ek[1][u] * (1.f / kBS);
-    dk[u][2] = dk[u][2] * a.scale + ek[0][u] * (1.f / kBS); dk[u][3] = dk[u][3] * a.scale + ek[1][u] * (1.f / kBS);
-    dv[u][0] += ev[0][u] * (1.f / kBS); dv[u][1] += ev[1][u] * (1.f / kBS);
-    dv[u][2] += ev[0][u] * (1.f / kBS); dv[u][3] += ev[1][u] * (1.f / kBS);
-  }
-  store_acc_row_t<0>(a.dk.row(b, h, j * kBS + g), dk, t, 1.f);
-  store_acc_row_t<1>(a.dk.row(b, h, j * kBS + g + 8), dk, t, 1.f);
-  store_acc_row_t<0>(a.dv.row(b, h, j * kBS + g), dv, t, 1.f);
-  store_acc_row_t<1>(a.dv.row(b, h, j * kBS + g + 8), dv, t, 1.f);
-}
-
 // ---- fine dK/dV: equal windows of the CSR, whatever the fan-in ---------------------------------
-// The CSR of a head lists, bucket after bucket (KV block after KV block), the query blocks that
-// selected each KV block.  Fan-in is very uneven (0 ... >150 on correlated inputs), so the work
-// is cut by ENTRIES, not by buckets: a CTA owns a window of kFineWindow consecutive entries of
-// `flat`, each of its warps a contiguous quarter.  A warp walks its range in order, keeps the
-// dK/dV tile of the current bucket in registers and, when the bucket changes, either stores
-// the tile (bucket wholly inside its range) or parks it in one of its two shared-memory slots
-// (bucket shared with a neighbour warp).  After a barrier every shared bucket is summed in slot
-// order; if it lies inside the CTA's window it is stored, otherwise the CTA-level partial goes
-// to one of the CTA's two slots in a global scratch tensor, and attn_dkv_finish_kernel sums
-// those (in CTA order) for the buckets that straddle windows.  No atomics: bit-reproducible.
-constexpr int kFineWarps = 4;
+// The CSR of a head lists, bucket after bucket (KV block after KV block), the query blocks that selected each KV
+// block.  Fan-in is very uneven (0 ... >150 on correlated inputs), so the work is cut by ENTRIES, not by buckets: a
+// CTA owns a window of kFineWindow consecutive entries, each of its warps a contiguous quarter.  No atomics: the
+// result is bit-reproducible.
 constexpr int kFineWindow = 128;                // entries per CTA
 constexpr int kTileFloats = 64 * 32;            // a parked dK + dV tile pair: 64 accumulators x 32 lanes
 
@@ -486,155 +457,25 @@ __device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) 
   for (int u = 0; u < 8; ++u) dk[u][0] = dk[u][1] = dk[u][2] = dk[u][3] = dv[u][0] = dv[u][1] = dv[u][2] = dv[u][3] = 0.f;
 }
 
-__global__ void __launch_bounds__(kFineWarps * 32, 2) attn_dkv_fine_kernel(AttnP<bf16> a, float* __restrict__ partial) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* slots = reinterpret_cast<float*>(smem_raw);        // [kFineWarps*2][kTileFloats]
-  __shared__ int s_slot_bucket[kFineWarps * 2];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  const float sl2 = a.scale * kLog2e;
-  const int E = (int) (a.nq1 * a.topk);
-  const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E);
-  constexpr int L = kFineWindow / kFineWarps;
-  const int rb = cb + warp * L, re = min(rb + L, ce);
-  const int32_t* fl = a.flat + bh * (int64_t) E;
-  if (threadIdx.x < kFineWarps * 2) s_slot_bucket[threadIdx.x] = -1;
-  __syncthreads();
-
-  float dk[8][4], dv[8][4];
-  if (rb < re) {
-    // bucket of entry rb: the j with off[j] <= rb < off[j+1]
-    int lo = 0, hi = (int) a.n1;          // invariant: off[lo] <= rb < off[hi]
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (csr_off(a, bh, mid) <= rb) lo = mid; else hi = mid;
-    }
-    int j = lo;
-    int bo = (int) csr_off(a, bh, j), nxt = (int) csr_off(a, bh, j + 1);
-    RowFrag ka, kb, va, vb;
-    auto load_kv = [&](int jj) {
-      const bf16* kp = a.k.row(b, h, (int64_t) jj * kBS);
-      const bf16* vp = a.v.row(b, h, (int64_t) jj * kBS);
-      load_rowfrag(ka, kp + (int64_t) g * a.k.sn, t);
-      load_rowfrag(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
-      load_rowfrag(va, vp + (int64_t) g * a.v.sn, t);
-      load_rowfrag(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
-    };
-    auto flush = [&]() {
-      if (bo >= rb && nxt <= re) {
-        dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);              // the bucket is wholly this warp's
-      } else {
-        const int slot = warp * 2 + (bo < rb ? 0 : 1);              // shared with an earlier / a later warp
-        tile_to_mem(slots + slot * kTileFloats, dk, dv, lane);
-        if (lane == 0) s_slot_bucket[slot] = j;
-      }
-    };
-    auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.nq1 ? (int) a.nq1 - 1 : v); };
-    RowFrag q0, q1, d0, d1;
-    float2 la, lb, da, db;
-    auto load_rows = [&](int qb) {
-      const bf16* qp = a.q.row(b, h, (int64_t) qb * kBS);
-      const bf16* dp = a.d_o.row(b, h, (int64_t) qb * kBS);
-      load_rowfrag(q0, qp + (int64_t) g * a.q.sn, t);
-      load_rowfrag(q1, qp + (int64_t) (g + 8) * a.q.sn, t);
-      load_rowfrag(d0, dp + (int64_t) g * a.d_o.sn, t);
-      load_rowfrag(d1, dp + (int64_t) (g + 8) * a.d_o.sn, t);
-      const int64_t rbase = bh * a.Nq + (int64_t) qb * kBS;
-      la = *reinterpret_cast<const float2*>(a.lse + rbase + 2 * t);          // query rows 2t, 2t+1
-      lb = *reinterpret_cast<const float2*>(a.lse + rbase + 8 + 2 * t);      // query rows 8+2t, 9+2t
-      da = *reinterpret_cast<const float2*>(a.delta + rbase + 2 * t);
-      db = *reinterpret_cast<const float2*>(a.delta + rbase + 8 + 2 * t);
-    };
-    // software pipeline: the row fragments (and lse/delta) of entry e+1 are requested as soon as the
-    // S^T / dP^T products of entry e have consumed the registers; the query-block index runs two
-    // entries ahead so that no load waits for an index
-    int qb_cur = clampq(fl[rb]);
-    int qb_nxt = rb + 1 < re ? clampq(fl[rb + 1]) : 0;
-    load_kv(j);
-    load_rows(qb_cur);
-    tile_zero(dk, dv);
-    for (int e = rb; e < re; ++e) {
-      if (e >= nxt) {                     // next non-empty bucket
-        flush();
-        do { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); } while (nxt <= e);
-        load_kv(j);
-        tile_zero(dk, dv);
-      }
-      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
-      mma_rows_x_keys(s0, s1, ka, kb, q0, q1);
-      mma_rows_x_keys(e0, e1, va, vb, d0, d1);
-      const float2 cla = la, clb = lb, cda = da, cdb = db;
-      // the same Q / dO tiles, transposed in registers, are the B operands of dK / dV: no second load
-      uint32_t tq0[8], tq1[8], td0[8], td1[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        tq0[i] = movmatrix_trans(q0.r[i]); tq1[i] = movmatrix_trans(q1.r[i]);
-        td0[i] = movmatrix_trans(d0.r[i]); td1[i] = movmatrix_trans(d1.r[i]);
-      }
-      if (e + 1 < re) {
-        qb_cur = qb_nxt;
-        qb_nxt = e + 2 < re ? clampq(fl[e + 2]) : 0;
-        load_rows(qb_cur);
-      }
-      uint32_t pa[4], ea[4];
-      dkv_p_ds(s0, s1, e0, e1, cla, clb, cda, cdb, sl2, 0.f, pa, ea);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mma_bf16_16816(dv[i], pa[0], pa[1], pa[2], pa[3], td0[i], td1[i]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mma_bf16_16816(dk[i], ea[0], ea[1], ea[2], ea[3], tq0[i], tq1[i]);
-    }
-    flush();
-  }
-  __syncthreads();
-  // buckets shared between warps: the first slot that names a bucket sums the later ones
-  for (int s = warp; s < kFineWarps * 2; s += kFineWarps) {
-    const int j = s_slot_bucket[s];
-    if (j < 0) continue;
-    bool leader = true;
-    for (int p = 0; p < s; ++p) leader = leader && (s_slot_bucket[p] != j);
-    if (!leader) continue;
-    tile_zero(dk, dv);
-    for (int p = s; p < kFineWarps * 2; ++p)
-      if (s_slot_bucket[p] == j) tile_add_mem(slots + p * kTileFloats, dk, dv, lane);
-    const int bo = (int) csr_off(a, bh, j), be = (int) csr_off(a, bh, j + 1);
-    if (bo >= cb && be <= ce) {
-      dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);
-    } else {                              // straddles windows: head slot if it began in an earlier window
-      float* dst = partial + ((bh * gridDim.x + blockIdx.x) * 2 + (bo < cb ? 0 : 1)) * (int64_t) kTileFloats;
-      tile_to_mem(dst, dk, dv, lane);
-    }
-  }
-}
-
-// One warp per KV block: blocks nobody selected get their pooling-backward term, blocks whose bucket
-// straddles windows of attn_dkv_fine_kernel get the sum of the windows' partial tiles (window order).
-__global__ void __launch_bounds__(128) attn_dkv_finish_kernel(AttnP<bf16> a, const float* __restrict__ partial, int n_windows) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int64_t j = (int64_t) blockIdx.x * 4 + warp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  if (j >= a.n1) return;
-  const int bo = (int) csr_off(a, bh, j), be = (int) csr_off(a, bh, j + 1);
-  const int c_first = bo / kFineWindow, c_last = (be - 1) / kFineWindow;
-  if (be > bo && c_first == c_last) return;          // finished inside one window
-  float dk[8][4], dv[8][4];
-  tile_zero(dk, dv);
-  if (be > bo)
-    for (int c = c_first; c <= c_last; ++c)
-      tile_add_mem_batched(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
-  dkv_fine_store(a, b, h, bh, j, dk, dv, g, t);
-}
-
-// ---- fine dK/dV, second form: three CTAs per SM --------------------------------------------------
-// The kernel above is bound by latency at two CTAs (eight warps) per SM: 240 registers and 64 KB of
-// slots per CTA.  This form fits three: the Q / dO blocks of an entry (with their lse and delta) come
-// through a two-stage per-warp cp.async ring and are read as mma operands straight from shared memory
-// (128-bit loads for the channel contraction, ldmatrix.trans for the row contraction, so no fragment
-// is held across the entry and none is transposed in registers), and a warp parks only the tile of the
-// bucket it shares with EARLIER warps; the tile it shares with later warps stays in its accumulators
-// until the CTA has synchronised and is then completed from the later warps' parked tiles.
+// ---- fine dK/dV kernel ------------------------------------------------------------------------------
+// dV_j += P^T.dO and dK_j += dS^T.Q over the query blocks that selected KV block j (reference:
+// sparse_attention_res_2.py:371-415, the dK/dV half of _attn_bwd_res_dqkv).  P and dS are NOT recomputed here: the dQ
+// stage has left them, already transposed into A-operand registers, in `pds` (store_pds), so an entry costs two
+// 512-byte loads, the Q and dO tiles of its query block and 16 MMAs; K, V, lse and delta are not touched.
+//   * The Q / dO tiles come through a per-warp cp.async ring of kRingFineStages stages, three entries ahead, and are
+//     read with ldmatrix.trans (the B operand of a contraction over the tile's 16 rows).
+//   * The P^T / dS^T registers of the entry three ahead are requested with plain 128-bit loads into a rotating set
+//     of register buffers (two CTAs of four warps per SM leave 255 registers per thread).
+//   * A warp parks only the tile of the bucket it shares with EARLIER warps; the tile it shares with later warps
+//     stays in its accumulators until the CTA has synchronised and is then completed from their parked tiles;
+//     buckets that straddle windows go to the `partial` scratch and attn_dkv_finish_ld_kernel adds them in window
+//     order.
+//   * The pooled-gradient rows a finished tile folds in (the pooling backward) are requested into registers when
+//     the bucket begins and parked in shared memory right before the store.
 // Accumulator layout (ldmatrix): tile u holds channels 8u + 2t, 8u + 2t + 1 of keys g (c0, c1) and g + 8 (c2, c3).
-constexpr int kRingWarps = 4;                   // warps per CTA of the ring form: 32 entries each, three CTAs per SM (2 x 64 entries measured 4 % slower)
-constexpr int kRingFineStages = 2;
-constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16) + 128;   // Q tile, dO tile, 16 lse, 16 delta
+constexpr int kRingWarps = 4;                   // warps per CTA: 32 entries each, two CTAs per SM
+constexpr int kRingFineStages = 4;
+constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16);           // Q tile, dO tile
 constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
 
 // Pooling-backward fold and scale for the ldmatrix accumulator layout: afterwards dk / dv hold the final fp32 values.
@@ -737,37 +578,39 @@ __device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int6
   dkv_fine_fold_smem(a, sa_fold, dk, dv);
   dkv_tile_store_staged<SB>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
 }
-__global__ void __launch_bounds__(kRingWarps * 32, 12 / kRingWarps) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
+__global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // the swizzle arithmetic below works on absolute shared addresses: start at a 128-byte boundary (the launch adds 128 bytes)
   unsigned char* smem = smem_raw + ((128u - ((uint32_t) __cvta_generic_to_shared(smem_raw) & 127u)) & 127u);
   float* slots = reinterpret_cast<float*>(smem);            // [kRingWarps][kTileFloats]: tile of the bucket a warp shares with earlier warps
   __shared__ int s_head_bucket[kRingWarps];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
   // per warp: the ring stages, then its copy of the pooled-gradient rows the current bucket folds in (4 rows x 256 bytes)
   constexpr int kWarpBytes = kRingFineStages * kRingFineStageBytes + kRingFoldBytes;
+  constexpr int kFoldOff = kRingFineStages * kRingFineStageBytes;
   unsigned char* ring = smem + kRingWarps * kTileFloats * sizeof(float) + warp * kWarpBytes;
   const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  const float sl2 = a.scale * kLog2e;
   const int E = (int) (a.nq1 * a.topk);
-  const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E);
+  // entries the CSR really holds: fewer than E when the transpose dropped out-of-range indices; offsets handed in by a
+  // caller are not trusted further than this clamp and the bounds on the bucket walk below
+  const int E_used = (int) min((int64_t) E, max((int64_t) 0, csr_off(a, bh, a.n1)));
+  const int cb = blockIdx.x * kFineWindow, ce = min(cb + kFineWindow, E_used);
   constexpr int L = kFineWindow / kRingWarps;
+  static_assert(L == 32, "one lane per entry of a warp's range");
   const int rb = cb + warp * L, re = min(rb + L, ce);
   const int32_t* fl = a.flat + bh * (int64_t) E;
+  const int32_t* pr = a.pairs + bh * (int64_t) E;
   if (threadIdx.x < kRingWarps) s_head_bucket[threadIdx.x] = -1;
   __syncthreads();
 
   // Per-lane shared addresses, computed once (the ring is 128-byte aligned, so the chunk index of an address is its bits 4..6
   // and a swizzle partner is one XOR away):
   //   sa_cp0 / sa_cp1  where this lane's cp.async chunks of tile rows (lane/8) + {0, 8} / + {4, 12} land
-  //   sa_f0 / sa_f1    chunks 2t / 2t+1 of tile row g (row g+8: +1024), the channel-contraction fragments
   //   sa_m[c]          ldmatrix.trans row address for output channels 16c..16c+15
-  //   sa_st            lse / delta of query rows 2t, 2t+1
   const uint32_t ring_sa = (uint32_t) __cvta_generic_to_shared(ring);
-  const uint32_t sa_t8 = ring_sa + 8 * t, sa_l16 = ring_sa + lane * 16;      // + immediates: lse / delta / gradient rows
-  const uint32_t sa_fold = sa_t8 + kRingFineStages * kRingFineStageBytes;
+  const uint32_t sa_t8 = ring_sa + 8 * t, sa_l16 = ring_sa + lane * 16;      // + immediates: gradient rows
+  const uint32_t sa_fold = sa_t8 + kFoldOff;
   const uint32_t sa_cp0 = ring_sa + (lane >> 3) * 128 + (((lane & 7) ^ (lane >> 3)) << 4), sa_cp1 = sa_cp0 ^ 64;
-  const uint32_t sa_f0 = ring_sa + g * 128 + (((2 * t) ^ g) << 4), sa_f1 = sa_f0 ^ 16;
   uint32_t sa_m[4];
   {
     const int lr = (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -778,56 +621,58 @@ __global__ void __launch_bounds__(kRingWarps * 32, 12 / kRingWarps) attn_dkv_fin
   float dk[8][4], dv[8][4];
   int tail_j = -1;                          // bucket whose tile is still in dk / dv after the loop
   if (rb < re) {
+    const int n = re - rb;                  // entries of this warp, one per lane
+    const int n1 = (int) a.n1;
     // bucket of entry rb (off[j] <= rb < off[j+1]) by a 32-way search: every round the lanes probe 32 evenly spaced offsets,
     // so n1 = 1024 costs two dependent loads instead of ten
-    int lo = 0, span = (int) a.n1;          // invariant: off[lo] <= rb < off[lo + span]
+    int lo = 0, span = n1;                  // invariant: off[lo] <= rb < off[lo + span]
     while (span > 1) {
       const int step = (span + 31) >> 5;
       const int probe = lo + lane * step;
       const bool le = probe < lo + span && (int) csr_off(a, bh, probe) <= rb;
-      const int last = 31 - __clz((int) __ballot_sync(0xffffffffu, le));     // lane 0 always qualifies
+      const int last = 31 - __clz((int) (__ballot_sync(0xffffffffu, le) | 1u));     // lane 0 qualifies for a well-formed CSR
       const int nlo = lo + last * step;
       span = min(step, lo + span - nlo);
       lo = nlo;
     }
     int j = lo;
     int bo = (int) csr_off(a, bh, j), nxt = (int) csr_off(a, bh, j + 1);
-    int nxt2 = j + 2 <= (int) a.n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;      // one bucket ahead: no load to wait for at a switch
-    RowFrag ka, kb, va, vb;
-    auto load_kv = [&](int jj) {
-      const bf16* kp = a.k.row(b, h, (int64_t) jj * kBS);
-      const bf16* vp = a.v.row(b, h, (int64_t) jj * kBS);
-      load_rowfrag_cg(ka, kp + (int64_t) g * a.k.sn, t);
-      load_rowfrag_cg(kb, kp + (int64_t) (g + 8) * a.k.sn, t);
-      load_rowfrag_cg(va, vp + (int64_t) g * a.v.sn, t);
-      load_rowfrag_cg(vb, vp + (int64_t) (g + 8) * a.v.sn, t);
+    int nxt2 = j + 2 <= n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;      // one bucket ahead: no load to wait for at a switch
+    // the pooled-gradient rows the bucket's store folds in: lanes 0..15 hold the dpk row, lanes 16..31 the dpv row (16 bytes each)
+    uint4 f1 = make_uint4(0u, 0u, 0u, 0u), f2 = make_uint4(0u, 0u, 0u, 0u);
+    auto load_fold = [&](int jj) {
+      if (a.fold) {
+        f1 = __ldcg(reinterpret_cast<const uint4*>((lane < 16 ? a.dpk : a.dpv) + (bh * a.n1 + jj) * kD + (lane & 15) * 4));
+        if (a.two_level) f2 = __ldcg(reinterpret_cast<const uint4*>((lane < 16 ? a.dpk2 : a.dpv2) + (bh * a.n2 + jj / kBS) * kD + (lane & 15) * 4));
+      }
     };
-    // what the NEXT bucket switch will wait for, pulled towards the SM while this bucket is being worked on: the K / V rows of the
-    // following KV block (one 128-byte row per lane) and the pooled-gradient rows that this bucket's store folds in
-    auto prefetch_next = [&](int jj) {
-      if (jj + 1 < (int) a.n1) {
-        const bf16* row = lane < 16 ? a.k.row(b, h, (int64_t) (jj + 1) * kBS + lane) : a.v.row(b, h, (int64_t) (jj + 1) * kBS + lane - 16);
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(row));
+    auto park_fold = [&]() {
+      if (a.fold) {
+        sts128<kFoldOff>(sa_l16, f1);
+        if (a.two_level) sts128<kFoldOff + 512>(sa_l16, f2);
       }
-      if (a.fold) {     // lands with the entry group that is committed next; the bucket's store comes at least an entry later
-        const float* l1 = (lane < 16 ? a.dpk : a.dpv) + (bh * a.n1 + jj) * kD + (lane & 15) * 4;
-        cp_async16_sa<kRingFineStages * kRingFineStageBytes>(sa_l16, l1);
-        if (a.two_level) {
-          const float* l2 = (lane < 16 ? a.dpk2 : a.dpv2) + (bh * a.n2 + jj / kBS) * kD + (lane & 15) * 4;
-          cp_async16_sa<kRingFineStages * kRingFineStageBytes + 512>(sa_l16, l2);
-        }
-      }
+      __syncwarp();
     };
     // global side: row (lane/8), chunk (lane%8) of block 0; a block is qblk / dblk bytes further, four rows qstep / dstep bytes
     const char* q_lane = reinterpret_cast<const char*>(a.q.row(b, h, lane >> 3) + (lane & 7) * 8);
     const char* d_lane = reinterpret_cast<const char*>(a.d_o.row(b, h, lane >> 3) + (lane & 7) * 8);
-    const char* stat = reinterpret_cast<const char*>((lane < 4 ? a.lse : a.delta) + bh * a.Nq + (lane & 3) * 4);
     const int qblk = (int) (kBS * a.q.sn * sizeof(bf16)), dblk = (int) (kBS * a.d_o.sn * sizeof(bf16));
     const int qstep = (int) (4 * a.q.sn * sizeof(bf16)), dstep = (int) (4 * a.d_o.sn * sizeof(bf16));
-    auto clampq = [&](int v) { return v < 0 ? 0 : (v >= (int) a.nq1 ? (int) a.nq1 - 1 : v); };
-    auto issue = [&](auto stage_tag, int qb_raw) {
-      const int qb = clampq(qb_raw);        // clamped here, an entry after the load: nothing waits for the index
-      constexpr int SB = decltype(stage_tag)::value * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
+    // lane i: query block and pair number of entry rb + i (clamped: nothing is read outside the tensors)
+    int my_qb = 0, my_pair = 0;
+    if (lane < n) {
+      my_qb = __ldcg(fl + rb + lane);
+      my_pair = __ldcg(pr + rb + lane);
+      my_qb = my_qb < 0 ? 0 : (my_qb >= (int) a.nq1 ? (int) a.nq1 - 1 : my_qb);
+      my_pair = my_pair < 0 ? 0 : (my_pair >= E ? E - 1 : my_pair);
+    }
+    const uint4* pds_lane = a.pds + bh * (int64_t) E * 64 + lane;
+    uint4 pP[kRingFineStages], pD[kRingFineStages];       // P^T / dS^T registers of the entries in flight
+    auto issue = [&](auto stage_tag, int i) {
+      constexpr int ST = decltype(stage_tag)::value;
+      constexpr int SB = ST * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
+      const int qb = __shfl_sync(0xffffffffu, my_qb, i);
+      const int pair = __shfl_sync(0xffffffffu, my_pair, i);
       const char* qp = q_lane + (int64_t) qb * qblk;
       const char* dp = d_lane + (int64_t) qb * dblk;
       cp_async16_sa<SB>(sa_cp0, qp);
@@ -838,70 +683,66 @@ __global__ void __launch_bounds__(kRingWarps * 32, 12 / kRingWarps) attn_dkv_fin
       cp_async16_sa<SB + TB + 512>(sa_cp1, dp + dstep);
       cp_async16_sa<SB + TB + 1024>(sa_cp0, dp + 2 * dstep);
       cp_async16_sa<SB + TB + 1536>(sa_cp1, dp + 3 * dstep);
-      if (lane < 8) cp_async16_sa<SB + 2 * TB>(sa_l16, stat + (int64_t) qb * (kBS * (int) sizeof(float)));
+      const uint4* pp = pds_lane + (int64_t) pair * 64;
+      pP[ST] = __ldcg(pp);
+      pD[ST] = __ldcg(pp + 32);
     };
-    int qb_nxt = rb + 1 < re ? __ldcg(fl + rb + 1) : 0;
-    issue(std::integral_constant<int, 0>{}, __ldcg(fl + rb));
+    if (0 < n) issue(std::integral_constant<int, 0>{}, 0);
     cp_async_commit();
-    load_kv(j);
-    prefetch_next(j);
+    if (1 < n) issue(std::integral_constant<int, 1>{}, 1);
+    cp_async_commit();
+    if (2 < n) issue(std::integral_constant<int, 2>{}, 2);
+    cp_async_commit();
+    load_fold(j);
     tile_zero(dk, dv);
     // one entry; the ring stage is a template argument so that every shared-memory offset below is an immediate
-    auto entry = [&](auto stage_tag, int e) {
-      constexpr int S = decltype(stage_tag)::value;
+    auto entry = [&](auto stage_tag, int i) {
+      constexpr int S = decltype(stage_tag)::value, SF = (S + kRingFineStages - 1) % kRingFineStages;    // SF: the stage read an entry ago
       constexpr int SB = S * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
-      cp_async_wait_all();                  // entry e has landed (this lane's chunks) ...
-      __syncwarp();                         // ... and everybody else's; the other stage was read an entry ago
-      if (e >= nxt) {                       // next non-empty bucket; the other stage is free until the copies below: it stages the store
+      const int e = rb + i;
+      cp_async_wait_group<kRingFineStages - 2>();     // entry i has landed (this lane's chunks) ...
+      __syncwarp();                                   // ... and everybody else's; stage SF is free
+      if (e >= nxt && j + 1 < n1) {                   // next non-empty bucket; stage SF stages the store before it is refilled
         if (bo >= rb) {
-          dkv_fine_store_staged<(1 - S) * kRingFineStageBytes>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+          park_fold();
+          dkv_fine_store_staged<SF * kRingFineStageBytes>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
         } else {
           tile_to_mem(slots + warp * kTileFloats, dk, dv, lane);   // began in an earlier warp's range
           if (lane == 0) s_head_bucket[warp] = j;
         }
         ++j; bo = nxt; nxt = nxt2;
-        while (nxt <= e) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }      // empty buckets
-        nxt2 = j + 2 <= (int) a.n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;
-        load_kv(j);
-        prefetch_next(j);
+        while (nxt <= e && j + 1 < n1) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }      // empty buckets
+        nxt2 = j + 2 <= n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;
+        load_fold(j);
         tile_zero(dk, dv);
       }
-      if (e + 1 < re) {
-        issue(std::integral_constant<int, 1 - S>{}, qb_nxt);
-        qb_nxt = e + 2 < re ? __ldcg(fl + e + 2) : 0;
-      }
+      const uint4 P = pP[S], D = pD[S];
+      if (i + kRingFineStages - 1 < n) issue(std::integral_constant<int, SF>{}, i + kRingFineStages - 1);
       cp_async_commit();
-      float s0[4], s1[4], e0[4], e1[4];
-      // S^T = K.Q^T and dP^T = V.dO^T, two k-steps (32 channels) per pair of 128-bit loads: eight fragment registers live at a time
-      half_rows_x_keys<SB, true>(s0, s1, ka, kb, sa_f0);
-      half_rows_x_keys<SB, false>(s0, s1, ka, kb, sa_f1);
-      half_rows_x_keys<SB + TB, true>(e0, e1, va, vb, sa_f0);
-      half_rows_x_keys<SB + TB, false>(e0, e1, va, vb, sa_f1);
-      const float2 la = lds64f<SB + 2 * TB>(sa_t8), lb = lds64f<SB + 2 * TB + 32>(sa_t8), da = lds64f<SB + 2 * TB + 64>(sa_t8),
-                   db = lds64f<SB + 2 * TB + 96>(sa_t8);
-      uint32_t pa[4], ea[4];
-      dkv_p_ds(s0, s1, e0, e1, la, lb, da, db, sl2, 0.f, pa, ea);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r0, r1, r2, r3;
         ldsm_x4_trans<SB + TB>(r0, r1, r2, r3, sa_m[c]);
-        mma_bf16_16816(dv[2 * c], pa[0], pa[1], pa[2], pa[3], r0, r1);
-        mma_bf16_16816(dv[2 * c + 1], pa[0], pa[1], pa[2], pa[3], r2, r3);
+        mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, r0, r1);
+        mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, r2, r3);
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r0, r1, r2, r3;
         ldsm_x4_trans<SB>(r0, r1, r2, r3, sa_m[c]);
-        mma_bf16_16816(dk[2 * c], ea[0], ea[1], ea[2], ea[3], r0, r1);
-        mma_bf16_16816(dk[2 * c + 1], ea[0], ea[1], ea[2], ea[3], r2, r3);
+        mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, r0, r1);
+        mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, r2, r3);
       }
     };
-    for (int e = rb; e < re; e += 2) {
-      entry(std::integral_constant<int, 0>{}, e);
-      if (e + 1 < re) entry(std::integral_constant<int, 1>{}, e + 1);
+    for (int i = 0; i < n; i += 4) {
+      entry(std::integral_constant<int, 0>{}, i);
+      if (i + 1 < n) entry(std::integral_constant<int, 1>{}, i + 1);
+      if (i + 2 < n) entry(std::integral_constant<int, 2>{}, i + 2);
+      if (i + 3 < n) entry(std::integral_constant<int, 3>{}, i + 3);
     }
-    cp_async_wait_all();                    // the last bucket's gradient rows
+    cp_async_wait_all();
     __syncwarp();
+    park_fold();                            // the last bucket's gradient rows, for whichever path below stores it
     // the last bucket of the range (the ring is idle by now)
     if (bo >= rb && nxt <= re) {
       dkv_fine_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
@@ -938,7 +779,10 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
   // a warp looks at eight consecutive buckets at once (lane i: offsets of bucket j0 + i) and works only on those that need it:
   // most buckets were finished inside one window of the main kernel
   const int64_t jl = j0 + lane < a.n1 ? j0 + lane : a.n1 - 1;
-  const int my_bo = lane < kFinishPerWarp ? (int) csr_off(a, bh, jl) : 0, my_be = lane < kFinishPerWarp ? (int) csr_off(a, bh, jl + 1) : 1;
+  // offsets are clamped to [0, E] and to each other: a malformed CSR cannot send the window arithmetic below outside `partial`
+  const int64_t E = a.nq1 * a.topk;
+  const int my_bo = lane < kFinishPerWarp ? (int) min(E, max((int64_t) 0, csr_off(a, bh, jl))) : 0;
+  const int my_be = lane < kFinishPerWarp ? (int) min(E, max((int64_t) my_bo, csr_off(a, bh, jl + 1))) : 1;
   const bool need = lane < kFinishPerWarp && j0 + lane < a.n1 && (my_be == my_bo || my_bo / kFineWindow != (my_be - 1) / kFineWindow);
   unsigned todo = __ballot_sync(0xffffffffu, need);
   if (!todo) return;
@@ -970,16 +814,18 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
 int zero_pooled_acc(const LlsaAttnArgs* g, cudaStream_t st);
 
 int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
-  if (!mma_path_ok(g, true)) return launch_attn_bwd_generic(g, st);
+  if (!mma_path_ok(g, true)) {
+    note_scalar_path();
+    return launch_attn_bwd_generic(g, st);
+  }
   AttnP<bf16> a = build_attn_params<bf16>(g, true);
   const unsigned BH = (unsigned) (g->q->shape[0] * a.H);
   const int mask = g->stage_mask ? g->stage_mask : 7;
   // pooled keys on tcgen05 (attn_pooled_bwd_tc.cu): the dQ kernel then covers the fine blocks only and the
   // tensor-core kernel adds the pooled part of dq and produces the pooled-key gradients
-  const char* tc_env = getenv("LLSA_B200_TC");
-  const bool tc = pooled_bwd_tc_ok(a) && !(tc_env && tc_env[0] == '0');
+  const bool tc = pooled_bwd_tc_ok(a) && !g->no_tcgen05;
   // long pooled key lists: the pooled part of dQ on the key-loop tcgen05 kernel (the pooled dK/dV stay on mma.sync)
-  const bool loop_dq = !tc && pooled_dq_loop_tc_keys(a) > 0 && !(tc_env && tc_env[0] == '0');
+  const bool loop_dq = !tc && pooled_dq_loop_tc_keys(a) > 0 && !g->no_tcgen05;
   if (mask & 1) {
     int rc = zero_pooled_acc(g, st);
     if (rc) return rc;
@@ -991,11 +837,11 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
     if (n_all == 0) {
       const size_t ring = (size_t) NWQ * kDqStages * 2 * kRingTileElems * sizeof(bf16);
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_fine_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+      LLSA_SMEM_LIMIT((attn_dq_fine_kernel<NWQ>), ring);
       attn_dq_fine_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, ring, st>>>(aq);
       LLSA_LAUNCH_OK("attn_dq_fine_kernel");
     } else {
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_mma_kernel<NWQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      LLSA_SMEM_LIMIT((attn_dq_mma_kernel<NWQ>), smem);
       attn_dq_mma_kernel<NWQ><<<dim3((unsigned) (a.nq1 / NWQ), BH), NWQ * 32, smem, st>>>(aq, n_smem);
       LLSA_LAUNCH_OK("attn_dq_mma_kernel");
     }
@@ -1020,7 +866,7 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     if (ap.p1_blocks + ap.p2_blocks > 0) {
       constexpr int NWP = 8;
       const size_t smem = (size_t) 2 * kBS * kBS * kSmemPitch * sizeof(bf16) + 2 * kBS * kBS * sizeof(float);
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_kernel<NWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      LLSA_SMEM_LIMIT((attn_dkv_pooled_kernel<NWP>), smem);
       attn_dkv_pooled_kernel<NWP><<<dim3((unsigned) (a.nq1 / kBS), BH), NWP * 32, smem, st>>>(ap);
       LLSA_LAUNCH_OK("attn_dkv_pooled_kernel");
     }
@@ -1029,22 +875,12 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
     const int64_t E = a.nq1 * a.topk;
     const int n_windows = (int) ((E + kFineWindow - 1) / kFineWindow);
     float* partial = (float*) g->dkv_partial->ptr;
-    const char* form = getenv("LLSA_B200_DKV_FINE");      // "regs": the two-CTA form that keeps the fragments in registers
-    if (!(form && form[0] == 'r' && form[1] == 'e')) {
-      const size_t smem = (size_t) kRingWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-      attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kRingWarps * 32, smem, st>>>(a, partial);
-      LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");
-      attn_dkv_finish_ld_kernel<<<dim3((unsigned) ((a.n1 + 4 * kFinishPerWarp - 1) / (4 * kFinishPerWarp)), BH), 128, 0, st>>>(a, partial, n_windows);
-      LLSA_LAUNCH_OK("attn_dkv_finish_ld_kernel");
-    } else {
-      const size_t smem = (size_t) kFineWarps * 2 * kTileFloats * sizeof(float);
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_fine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-      attn_dkv_fine_kernel<<<dim3((unsigned) n_windows, BH), kFineWarps * 32, smem, st>>>(a, partial);
-      LLSA_LAUNCH_OK("attn_dkv_fine_kernel");
-      attn_dkv_finish_kernel<<<dim3((unsigned) ((a.n1 + 3) / 4), BH), 128, 0, st>>>(a, partial, n_windows);
-      LLSA_LAUNCH_OK("attn_dkv_finish_kernel");
-    }
+    const size_t smem = (size_t) kRingWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
+    LLSA_SMEM_LIMIT((attn_dkv_fine_ring_kernel), smem);
+    attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kRingWarps * 32, smem, st>>>(a, partial);
+    LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");
+    attn_dkv_finish_ld_kernel<<<dim3((unsigned) ((a.n1 + 4 * kFinishPerWarp - 1) / (4 * kFinishPerWarp)), BH), 128, 0, st>>>(a, partial, n_windows);
+    LLSA_LAUNCH_OK("attn_dkv_finish_ld_kernel");
   }
   return LLSA_OK;
 }

@@ -16,8 +16,6 @@
 // The softmax runs online, one 16-key block at a time, in the exp2 domain; a
 // pooled key's weight enters as +log2(weight) on its logit, which is what
 // `l += l_ij * W; acc += P.V * W` in the reference amounts to.
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "attn.cuh"
@@ -395,6 +393,13 @@ __global__ void __launch_bounds__(NW * 32, 2) attn_fwd_fine8_kernel(AttnP<bf16> 
   lds128<1536>(x.x, x.y, x.z, x.w, sa_cp1); *reinterpret_cast<uint4*>(op + 3 * os) = x;
 }
 
+// A bf16 call whose operands miss the tensor-core kernels' limits still runs, on the scalar kernels and many times
+// slower: the call succeeds, and the thread's error string says why so that a caller who wonders can find out.
+void note_scalar_path() {
+  set_error("note: bf16 operands ran on the scalar kernels (the tensor-core kernels need 32-byte aligned rows, "
+            "batch/head/token strides that are multiples of 16 elements, and top-k <= 32)");
+}
+
 bool mma_path_ok(const LlsaAttnArgs* g, bool bwd) {
   if (g->topk > 32 || (g->pk2 && g->topk_p > 32)) return false;
   // 256-bit fragment loads need 32-byte aligned rows
@@ -412,23 +417,24 @@ bool mma_path_ok(const LlsaAttnArgs* g, bool bwd) {
 int pooled_smem_tiles(int n_pooled) { return n_pooled < 20 ? n_pooled : 20; }   // 20 tiles = 90 KB of K+V, two CTAs per SM
 
 int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
-  if (!mma_path_ok(g, false)) return launch_attn_fwd_generic(g, st);
+  if (!mma_path_ok(g, false)) {
+    note_scalar_path();
+    return launch_attn_fwd_generic(g, st);
+  }
   AttnP<bf16> a = build_attn_params<bf16>(g, false);
   constexpr int NW = 8;
   const int64_t BH = g->q->shape[0] * a.H;
-  const char* tc_env = getenv("LLSA_B200_TC");      // "0" keeps the pooled stages on mma.sync (cross-check)
   const bool loop_tc = pooled_loop_tc_keys(a) > 0;
-  if ((pooled_tc_keys(a) || loop_tc) && !(tc_env && tc_env[0] == '0')) {
+  if ((pooled_tc_keys(a) || loop_tc) && !g->no_tcgen05) {
     // fine blocks on mma.sync (o and lse of the fine part alone), pooled keys on tcgen05, merged there
-    const char* form = getenv("LLSA_B200_FWD_FINE");     // "online": the per-block online-softmax form for any top-k
-    if (a.topk == 8 && !(form && form[0] == 'o')) {
+    if (a.topk == 8) {
       const size_t ring = (size_t) NW * kF8Stages * kF8TileBytes + 128;
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine8_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+      LLSA_SMEM_LIMIT((attn_fwd_fine8_kernel<NW>), ring);
       attn_fwd_fine8_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
       LLSA_LAUNCH_OK("attn_fwd_fine8_kernel");
     } else {
       const size_t ring = (size_t) NW * kFineStages * 2 * kRingTileElems * sizeof(bf16);
-      LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_fine_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ring));
+      LLSA_SMEM_LIMIT((attn_fwd_fine_kernel<NW>), ring);
       attn_fwd_fine_kernel<NW><<<dim3((unsigned) (a.nq1 / NW), (unsigned) BH), NW * 32, ring, st>>>(a);
       LLSA_LAUNCH_OK("attn_fwd_fine_kernel");
     }
@@ -436,7 +442,7 @@ int launch_attn_fwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   }
   const int n_smem = pooled_smem_tiles(a.p1_blocks + a.p2_blocks);
   const size_t smem = (size_t) n_smem * kBS * kSmemPitch * sizeof(bf16) * 2;
-  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_mma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((attn_fwd_mma_kernel<NW>), smem);
   dim3 grid((unsigned) (a.nq1 / NW), (unsigned) (g->q->shape[0] * a.H));
   attn_fwd_mma_kernel<NW><<<grid, NW * 32, smem, st>>>(a, n_smem);
   LLSA_LAUNCH_OK("attn_fwd_mma_kernel");

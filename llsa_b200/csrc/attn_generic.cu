@@ -188,6 +188,10 @@ __global__ void __launch_bounds__(128) attn_dkv_generic(AttnP<T> a) {
       list0 = reinterpret_cast<const int32_t*>(a.offsets)[bh * (a.n1 + 1) + j];
       list1 = reinterpret_cast<const int32_t*>(a.offsets)[bh * (a.n1 + 1) + j + 1];
     }
+    // offsets and list entries handed in by a caller are clamped: nothing is read outside the tensors
+    const int64_t E = a.nq1 * a.topk;
+    list0 = list0 < 0 ? 0 : (list0 > E ? E : list0);
+    list1 = list1 < list0 ? list0 : (list1 > E ? E : list1);
   } else {
     grp = blockIdx.z;
     const int i = blockIdx.x;  // pooled tile of this group: [pooled-1 | pooled-2]
@@ -204,7 +208,8 @@ __global__ void __launch_bounds__(128) attn_dkv_generic(AttnP<T> a) {
 #pragma unroll
   for (int d = 0; d < 8; ++d) dk[d] = dv[d] = 0.f;
   for (int64_t it = list0; it < list1; ++it) {
-    const int64_t qb = MODE == 0 ? (int64_t) a.flat[bh * a.nq1 * a.topk + it] : grp * kBS + it;
+    int64_t qb = MODE == 0 ? (int64_t) a.flat[bh * a.nq1 * a.topk + it] : grp * kBS + it;
+    qb = qb < 0 ? 0 : (qb >= a.nq1 ? a.nq1 - 1 : qb);
     __syncthreads();
     load_block_smem<T>(qs, a.q.row(b, h, qb * kBS), a.q.sn, 1.f, false);
     load_block_smem<T>(dos, a.d_o.row(b, h, qb * kBS), a.d_o.sn, 1.f, false);

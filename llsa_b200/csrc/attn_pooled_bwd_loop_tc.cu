@@ -46,15 +46,6 @@ struct DqBars {
   uint64_t sdp_ready[2], ds_ready[2], dq_ready, dq_free;
 };
 
-__device__ __forceinline__ bool dl_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 400000; ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 // jobs: 64-key chunks per tile (even); gathered: number of leading chunks that are gathered level-1 blocks (0 or 2);
 // n_c: rows per head of the contiguous pooled tensor.
 __global__ void __launch_bounds__(kThreads, 1)
@@ -63,17 +54,18 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
   extern __shared__ unsigned char smem_dyn[];
   __shared__ DqBars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
+  __shared__ tc::WaitCtl s_ctl;
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   bf16* sQ = base;                          // [2][128][64]
   bf16* sDO = sQ + 2 * kTile;               // [2][128][64]
   bf16* sK = sDO + 2 * kTile;               // [kStages][64][64]
   bf16* sV = sK + kStages * kChunkElems;    // [kStages][64][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  volatile int* abort_flag = &s_abort;
+  volatile tc::WaitCtl* abort_flag = &s_ctl;
 
   if (tid == 0) {
-    s_abort = 0;
+    s_ctl.abort = 0;
+    s_ctl.limit = a.wait_limit > 0 ? a.wait_limit : tc::kWaitPolls;
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.q_full[i], 1);
       tc::mbar_init(&bars.q_empty[i], 1);
@@ -102,7 +94,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
       for (int i = 0; i < n_my; ++i) {
         const int tile = blockIdx.x + i * gridDim.x, qs = i & 1;
         const int bh = tile / tiles_per_head, row0 = (tile % tiles_per_head) * kRows;
-        if (!dl_wait(&bars.q_empty[qs], ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.q_empty[qs], ((i >> 1) & 1) ^ 1, abort_flag)) break;
         tma::expect_tx(&bars.q_full[qs], 2 * kTile * 2);
         tma::load_4d(sQ + qs * kTile, &maps.q, &bars.q_full[qs], 0, row0, bh % a.H, bh / a.H);
         tma::load_4d(sDO + qs * kTile, &maps.d_o, &bars.q_full[qs], 0, row0, bh % a.H, bh / a.H);
@@ -116,7 +108,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
           const int st = cj % kStages;
           const uint32_t par = ((cj / kStages) & 1) ^ 1;
           const int crow = (int) ((int64_t) bh * n_c + (int64_t) (j - gathered) * kCk);
-          if (!(ok = dl_wait(&bars.k_empty[st], par, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.k_empty[st], par, abort_flag))) break;
           tma::expect_tx(&bars.k_full[st], kChunkElems * 2);
           if (j < gathered) {
 #pragma unroll
@@ -125,7 +117,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
           } else {
             tma::load_2d(sK + st * kChunkElems, &maps.kc, &bars.k_full[st], 0, crow);
           }
-          if (!(ok = dl_wait(&bars.v_empty[st], par, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.v_empty[st], par, abort_flag))) break;
           tma::expect_tx(&bars.v_full[st], kChunkElems * 2);
           if (j < gathered) {
 #pragma unroll
@@ -151,14 +143,14 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
       bool ok = true;
       for (int i = 0; ok && i < n_my; ++i) {
         const int qs = i & 1;
-        if (!(ok = dl_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
+        if (!(ok = tc::bounded_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
         tc::fence_after_sync();
         const int cj0 = cj;                          // ring position of this tile's chunk 0
         auto issue_sdp = [&](int j) -> bool {        // S and dP of chunk j into buffer j & 1
           const int st = cj % kStages;
           const uint32_t par = (cj / kStages) & 1;
-          if (!dl_wait(&bars.k_full[st], par, abort_flag)) return false;
-          if (!dl_wait(&bars.v_full[st], par, abort_flag)) return false;
+          if (!tc::bounded_wait(&bars.k_full[st], par, abort_flag)) return false;
+          if (!tc::bounded_wait(&bars.v_full[st], par, abort_flag)) return false;
           tc::fence_after_sync();
           const uint32_t d = tmem + (j & 1) * 128;
           const uint32_t q_ = lQ + qs * kQStage, o_ = lDO + qs * kQStage, k_ = lK + st * kCStage, v_ = lV + st * kCStage;
@@ -176,7 +168,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
         };
         auto issue_dq = [&](int j) -> bool {         // dQ (+)= dS(chunk j, TMEM) . K chunk (16 key rows = 2048 bytes per k-step)
           const int st = (cj0 + j) % kStages;
-          if (j == 0 && i > 0 && !dl_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) return false;     // previous tile's dQ has been read
+          if (j == 0 && i > 0 && !tc::bounded_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) return false;     // previous tile's dQ has been read
           tc::fence_after_sync();
           const uint64_t kdesc = ((uint64_t) hi << 32) | (uint64_t) (lKm + st * kCStage);
 #pragma unroll
@@ -188,7 +180,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
         for (int j = 0; ok && j < jobs; ++j) {
           if (j >= 2) {
             const int64_t Jp = J + j - 2;            // buffer j & 1 was used by chunk j - 2: its dS feeds dQ, then the buffer is free
-            if (!(ok = dl_wait(&bars.ds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+            if (!(ok = tc::bounded_wait(&bars.ds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
             tc::fence_after_sync();
             if (!(ok = issue_dq(j - 2))) break;
           }
@@ -197,7 +189,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
         if (!ok) break;
         for (int j = jobs - 2; ok && j < jobs; ++j) {
           const int64_t Jp = J + j;
-          if (!(ok = dl_wait(&bars.ds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.ds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
           tc::fence_after_sync();
           ok = issue_dq(j);
         }
@@ -228,7 +220,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
       bool ok = true;
       for (int j = wg; j < jobs; j += 2) {
         const float off = ((gathered ? (j < gathered) : !a.two_level) ? lw1 : lw2) - L;
-        ok = __all_sync(0xffffffffu, dl_wait(&bars.sdp_ready[wg], (uint32_t) (Jw & 1), abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.sdp_ready[wg], (uint32_t) (Jw & 1), abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
 #pragma unroll
@@ -252,7 +244,7 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
         ++Jw;
       }
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, dl_wait(&bars.dq_ready, (uint32_t) (i & 1), abort_flag));
+      ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.dq_ready, (uint32_t) (i & 1), abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
       tc::tmem_ld32_async(t_dq, vs);
@@ -272,8 +264,10 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
       if (lane == 0) tma::mbar_arrive(&bars.dq_free);
     }
   }
+  if (abort_flag->abort) tc::abort_drain();
   tc::fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && abort_flag->abort && a.status) atomicOr(a.status, (int) LLSA_DEV_WAIT_EXPIRED);
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
 }
 
@@ -308,7 +302,7 @@ int launch_attn_dq_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, i
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = n_tiles < sms ? n_tiles : sms;
   const size_t smem = 1024 + (size_t) (4 * kTile + 2 * kStages * kChunkElems) * sizeof(bf16);
-  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dq_pooled_loop_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((attn_dq_pooled_loop_tc_kernel), smem);
   attn_dq_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, np / kCk, gathered, n_c, n_tiles, tiles_per_head);
   LLSA_LAUNCH_OK("attn_dq_pooled_loop_tc_kernel");
   return LLSA_OK;

@@ -66,21 +66,12 @@ struct BwdBars {
   uint64_t full[2], mma_done[2], v_free[2], s_ready, s_consumed, dp_ready, pds_ready, out_ready, dq_free, acc_free;
 };
 
-__device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 400000; ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
-attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, int n_tiles, int tiles_per_head, int* __restrict__ status) {
+attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, int n_tiles, int tiles_per_head) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ BwdBars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
+  __shared__ tc::WaitCtl s_ctl;
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   bf16* sQ = base;                      // [2][128][64]
   bf16* sDO = sQ + 2 * kTile;           // [2][128][64]
@@ -90,10 +81,11 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
   bf16* sV2 = sV1 + kTile;              // [64][64] level-2 values: 192 contiguous rows
   bf16* sP = sV2 + kTile / 2;           // P tiles 0, 1, 2, then dS tiles 2, 0, 1 (tile = [128 rows][64 keys])
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  volatile int* abort_flag = &s_abort;
+  volatile tc::WaitCtl* abort_flag = &s_ctl;
 
   if (tid == 0) {
-    s_abort = 0;
+    s_ctl.abort = 0;
+    s_ctl.limit = a.wait_limit > 0 ? a.wait_limit : tc::kWaitPolls;
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.full[i], 1);
       tc::mbar_init(&bars.mma_done[i], 1);
@@ -131,9 +123,9 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
           for (int j = 0; j < 8; ++j) krow[j] = (int) ((int64_t) bh * a.n1 + p1_block(a, bh, row0 / kBS, j) * kBS);
         }
         // stage s (and the level-1 key buffer of the parent two back) is free once every product of tile i - 2 has completed
-        if (i >= 2 && !bw_wait(&bars.mma_done[s], ((i - 2) >> 1) & 1, abort_flag)) break;
+        if (i >= 2 && !tc::bounded_wait(&bars.mma_done[s], ((i - 2) >> 1) & 1, abort_flag)) break;
         // the level-2 buffers are free once every product of the previous tile has completed
-        if (i >= 1 && new_head && !bw_wait(&bars.mma_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;
+        if (i >= 1 && new_head && !tc::bounded_wait(&bars.mma_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;
         tma::expect_tx(&bars.full[s], 2u * kTile * 2 + (new_parent ? 2u * kTile * 2 : 0u) + (new_head ? (uint32_t) kTile * 2 : 0u));
         tma::load_4d(sQ + s * kTile, &maps.q, &bars.full[s], 0, row0, bh % a.H, bh / a.H);
         tma::load_4d(sDO + s * kTile, &maps.d_o, &bars.full[s], 0, row0, bh % a.H, bh / a.H);
@@ -147,7 +139,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
           for (int j = 0; j < 8; ++j) tma::load_2d(k1 + j * kBS * 64, &maps.pk1, &bars.full[s], 0, krow[j]);
           // the level-1 values are last read by dP of the previous tile.  New parents come every other tile, so one of
           // the two v_free barriers is waited on at each of its phases and the other never.
-          if (i >= 1 && !bw_wait(&bars.v_free[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;
+          if (i >= 1 && !tc::bounded_wait(&bars.v_free[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) break;
 #pragma unroll
           for (int j = 0; j < 8; ++j) tma::load_2d(sV1 + j * kBS * 64, &maps.pv1, &bars.full[s], 0, krow[j]);
         }
@@ -175,7 +167,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       const uint32_t lK1_k0 = lo(sK1, 16), lK1_m0 = lo(sK1, 1024);
       auto issue_s = [&](int i) -> bool {          // S(i) = Q . [PK1 ; PK2]^T into columns [0,192)
         const int s = i & 1;
-        if (!bw_wait(&bars.full[s], (i >> 1) & 1, abort_flag)) return false;
+        if (!tc::bounded_wait(&bars.full[s], (i >> 1) & 1, abort_flag)) return false;
         tc::fence_after_sync();
         const uint32_t q_ = lQ_k0 + s * kStage, k1_ = lK1_k0 + (((t_begin + i) >> 1) & 1) * kStage;
         tc::umma_ss_lh<0>(tmem, q_, hi, k1_, hi, id_s128);
@@ -193,7 +185,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       for (int i = 0; ok && i < n_my; ++i) {
         const int s = i & 1, tile = t_begin + i;
         // dP(i) = dO . [PV1 ; PV2]^T over the columns of S once every softmax warp has read S
-        if (!bw_wait(&bars.s_consumed, i & 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.s_consumed, i & 1, abort_flag)) break;
         tc::fence_after_sync();
         {
           const uint32_t d_ = lDO_k0 + s * kStage;
@@ -203,7 +195,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         }
         tc::umma_commit(&bars.dp_ready);
         tc::umma_commit(&bars.v_free[s]);
-        if (!bw_wait(&bars.pds_ready, i & 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.pds_ready, i & 1, abort_flag)) break;
         tc::fence_after_sync();
         // The next tile's S goes ahead of this tile's output products, unless it belongs to a new head: the level-2
         // buffers are reloaded only after these products have completed.
@@ -211,7 +203,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         if (next_early && !issue_s(i + 1)) break;
         // dQ = dS . [PK1 ; PK2]: 12 k-steps of 16 keys, dS tile ks / 4; its columns are free once the drain warps have read
         // the previous tile's dQ
-        if (i > 0 && !bw_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) break;
+        if (i > 0 && !tc::bounded_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) break;
         tc::fence_after_sync();
         {
           const uint32_t k1_ = lK1_m0 + ((tile >> 1) & 1) * kStage;
@@ -228,7 +220,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         // the previous parent's results.
         const uint32_t acc1 = (i > 0 && (tile & 1)) ? 1u : 0u;
         const uint32_t acc2 = (i > 0 && (tile % tiles_per_head) != 0) ? 1u : 0u;
-        if (!acc1 && parents_done > 0 && !bw_wait(&bars.acc_free, (parents_done - 1) & 1, abort_flag)) break;
+        if (!acc1 && parents_done > 0 && !tc::bounded_wait(&bars.acc_free, (parents_done - 1) & 1, abort_flag)) break;
         tc::fence_after_sync();
         {
           const uint32_t do_ = lDO_m0 + s * kStage, q_ = lQ_m0 + s * kStage, qdo_ = lQDO_m0 + s * kStage;
@@ -272,7 +264,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
 #pragma unroll
       for (int q = 0; q < 8; ++q) old[q] = *reinterpret_cast<const uint4*>(dqrow + 8 * q);
       const int64_t key = parent_end ? p1_block(a, bh, row0 / kBS, r >> 4) * kBS + (r & 15) : 0;
-      const bool ok = __all_sync(0xffffffffu, bw_wait(&bars.out_ready, i & 1, abort_flag));
+      const bool ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.out_ready, i & 1, abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
 #pragma unroll
@@ -326,7 +318,7 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       const int tile = t_begin + i;
       const float off = lw - lse_n * kLog2eF;
       const float dls = delta_n * a.scale;
-      ok = __all_sync(0xffffffffu, bw_wait(&bars.s_ready, i & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.s_ready, i & 1, abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
       uint32_t pk[32];          // this row's 64 probabilities, bf16 pairs, kept for dS
@@ -342,14 +334,14 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       if (lane == 0) tma::mbar_arrive(&bars.s_consumed);
       if (i > 0) {
         // the previous tile's products read its P / dS tiles: wait for them before overwriting
-        ok = __all_sync(0xffffffffu, bw_wait(&bars.out_ready, (i - 1) & 1, abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.out_ready, (i - 1) & 1, abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
       }
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         *reinterpret_cast<uint4*>(myP + tc::swz(r, q)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-      ok = __all_sync(0xffffffffu, bw_wait(&bars.dp_ready, i & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.dp_ready, i & 1, abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
       if (i + 1 < n_my) {        // next tile's log-sum-exp and delta: in flight during the dS arithmetic
@@ -379,9 +371,10 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       if (lane == 0) tma::mbar_arrive(&bars.pds_ready);
     }
   }
+  if (abort_flag->abort) tc::abort_drain();
   tc::fence_before_sync();
   __syncthreads();
-  if (tid == 0 && s_abort && status) *status = 1;
+  if (threadIdx.x == 0 && abort_flag->abort && a.status) atomicOr(a.status, (int) LLSA_DEV_WAIT_EXPIRED);
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
 }
 
@@ -409,8 +402,8 @@ int launch_attn_bwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = n_tiles < sms ? n_tiles : sms;
   const size_t smem = 1024 + (size_t) 14 * kTile * sizeof(bf16);     // Q, dO x 2, K1 x 2, V1, K2 + V2, P x 3, dS x 3
-  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_bwd_pooled_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-  attn_bwd_pooled_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, n_tiles, tiles_per_head, nullptr);
+  LLSA_SMEM_LIMIT((attn_bwd_pooled_tc_kernel), smem);
+  attn_bwd_pooled_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, n_tiles, tiles_per_head);
   LLSA_LAUNCH_OK("attn_bwd_pooled_tc_kernel");
   return LLSA_OK;
 }

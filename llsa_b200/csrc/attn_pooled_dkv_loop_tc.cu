@@ -46,15 +46,6 @@ struct KvBars {
   uint64_t kv_full, kv_empty, q_full[kStages], q_empty[kStages], sdp_ready[2], pds_ready[2], acc_ready, acc_free;
 };
 
-__device__ __forceinline__ bool kl_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 400000; ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 // n_keys: pooled keys per head (a multiple of 128); jobs: 64-row query jobs per unit (even); splits: units per (head, key chunk),
 // each walking its own range of the queries (with more than one, the results are added with reductions instead of stored);
 // units = BH * n_keys / 128 * splits.
@@ -64,7 +55,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
   extern __shared__ unsigned char smem_dyn[];
   __shared__ KvBars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
+  __shared__ tc::WaitCtl s_ctl;
   __shared__ __align__(16) float s_lse[kStages][kQ], s_delta[kStages][kQ];
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   bf16* sK = base;                           // [128][64]
@@ -72,10 +63,11 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
   bf16* sQ = sV + kKeyTile;                  // [kStages][64][64]
   bf16* sDO = sQ + kStages * kQTile;         // [kStages][64][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  volatile int* abort_flag = &s_abort;
+  volatile tc::WaitCtl* abort_flag = &s_ctl;
 
   if (tid == 0) {
-    s_abort = 0;
+    s_ctl.abort = 0;
+    s_ctl.limit = a.wait_limit > 0 ? a.wait_limit : tc::kWaitPolls;
     tc::mbar_init(&bars.kv_full, 1);
     tc::mbar_init(&bars.kv_empty, 1);
     for (int i = 0; i < kStages; ++i) { tc::mbar_init(&bars.q_full[i], 1); tc::mbar_init(&bars.q_empty[i], 1); }
@@ -99,14 +91,14 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
       for (int i = 0; i < n_my; ++i) {
         const int unit = blockIdx.x + i * gridDim.x, sp = unit % splits;
         const int bh = unit / splits / chunks_per_head, c = unit / splits % chunks_per_head;
-        if (!kl_wait(&bars.kv_empty, (i & 1) ^ 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.kv_empty, (i & 1) ^ 1, abort_flag)) break;
         tma::expect_tx(&bars.kv_full, 2 * kKeyTile * 2);
         tma::load_2d(sK, &maps.k, &bars.kv_full, 0, (int) ((int64_t) bh * n_keys + (int64_t) c * kKeys));
         tma::load_2d(sV, &maps.v, &bars.kv_full, 0, (int) ((int64_t) bh * n_keys + (int64_t) c * kKeys));
         bool ok = true;
         for (int j = 0; ok && j < jobs; ++j, ++cj) {
           const int st = cj % kStages;
-          if (!(ok = kl_wait(&bars.q_empty[st], ((cj / kStages) & 1) ^ 1, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.q_empty[st], ((cj / kStages) & 1) ^ 1, abort_flag))) break;
           tma::expect_tx(&bars.q_full[st], 2 * kQTile * 2 + 2 * kQ * 4);
           const int qrow = (sp * jobs + j) * kQ;
           tma::load_4d(sQ + st * kQTile, &maps.q, &bars.q_full[st], 0, qrow, bh % a.H, bh / a.H);
@@ -129,12 +121,12 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
       int64_t J = 0;
       bool ok = true;
       for (int i = 0; ok && i < n_my; ++i) {
-        if (!(ok = kl_wait(&bars.kv_full, i & 1, abort_flag))) break;
+        if (!(ok = tc::bounded_wait(&bars.kv_full, i & 1, abort_flag))) break;
         tc::fence_after_sync();
         const int cj0 = cj;
         auto issue_sdp = [&](int j) -> bool {        // S^T and dP^T of job j into buffer j & 1
           const int st = cj % kStages;
-          if (!kl_wait(&bars.q_full[st], (cj / kStages) & 1, abort_flag)) return false;
+          if (!tc::bounded_wait(&bars.q_full[st], (cj / kStages) & 1, abort_flag)) return false;
           tc::fence_after_sync();
           const uint32_t d = tmem + (j & 1) * 128, q_ = lQ + st * kQStage, o_ = lDO + st * kQStage;
           tc::umma_ss_lh<0>(d, lK, hi, q_, hi, id_s);
@@ -150,7 +142,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
         };
         auto issue_out = [&](int j) -> bool {        // dV (+)= P^T . dO_t, dK (+)= dS^T . Q_t: 4 k-steps of 16 query rows (2048 bytes)
           const int st = (cj0 + j) % kStages;
-          if (j == 0 && i > 0 && !kl_wait(&bars.acc_free, (i - 1) & 1, abort_flag)) return false;    // previous unit's results have been read
+          if (j == 0 && i > 0 && !tc::bounded_wait(&bars.acc_free, (i - 1) & 1, abort_flag)) return false;    // previous unit's results have been read
           tc::fence_after_sync();
           const uint64_t dodesc = ((uint64_t) hi << 32) | (uint64_t) (lDOm + st * kQStage), qdesc = ((uint64_t) hi << 32) | (uint64_t) (lQm + st * kQStage);
           const uint32_t b = tmem + (j & 1) * 128;
@@ -166,7 +158,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
         for (int j = 0; ok && j < jobs; ++j) {
           if (j >= 2) {
             const int64_t Jp = J + j - 2;
-            if (!(ok = kl_wait(&bars.pds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+            if (!(ok = tc::bounded_wait(&bars.pds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
             tc::fence_after_sync();
             if (!(ok = issue_out(j - 2))) break;
           }
@@ -175,7 +167,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
         if (!ok) break;
         for (int j = jobs - 2; ok && j < jobs; ++j) {
           const int64_t Jp = J + j;
-          if (!(ok = kl_wait(&bars.pds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.pds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
           tc::fence_after_sync();
           ok = issue_out(j);
         }
@@ -200,7 +192,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
       bool ok = true;
       for (int j = wg; j < jobs; j += 2, cj += 2) {
         const int st = cj % kStages;
-        ok = __all_sync(0xffffffffu, kl_wait(&bars.sdp_ready[wg], (uint32_t) (Jw & 1), abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.sdp_ready[wg], (uint32_t) (Jw & 1), abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
 #pragma unroll
@@ -233,7 +225,7 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
         ++Jw;
       }
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, kl_wait(&bars.acc_ready, (uint32_t) (i & 1), abort_flag));
+      ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.acc_ready, (uint32_t) (i & 1), abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
       float* dst = (wg == 0 ? dpv : dpk) + ((int64_t) bh * n_keys + (int64_t) c * kKeys + r) * kD;
@@ -256,8 +248,10 @@ attn_dkv_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ KvMaps map
       if (lane == 0) tma::mbar_arrive(&bars.acc_free);
     }
   }
+  if (abort_flag->abort) tc::abort_drain();
   tc::fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && abort_flag->abort && a.status) atomicOr(a.status, (int) LLSA_DEV_WAIT_EXPIRED);
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
 }
 
@@ -292,7 +286,7 @@ int launch_attn_dkv_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, 
   const int n_units = base_units * splits, jobs = jobs_all / splits;
   const int grid = n_units < sms ? n_units : sms;
   const size_t smem = 1024 + (size_t) (2 * kKeyTile + 2 * kStages * kQTile) * sizeof(bf16);
-  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_dkv_pooled_loop_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((attn_dkv_pooled_loop_tc_kernel), smem);
   if (level == 1)
     attn_dkv_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, a.dpk, a.dpv, n_keys, jobs, splits, n_units, log2f(a.w1),
                                                                  a.kvw1 / a.w1);

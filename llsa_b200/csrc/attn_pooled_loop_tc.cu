@@ -51,15 +51,6 @@ struct LoopBars {
   uint64_t s_ready[2], wg_done[2], o_ready, o_free, xchg;
 };
 
-__device__ __forceinline__ bool lp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 400000; ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 // n_chunks: chunks per tile; gathered: chunk 0 is the gathered level-1 set (two levels); n_c: rows per head of the
 // contiguous pooled tensor.
 __global__ void __launch_bounds__(kThreads, 1)
@@ -68,17 +59,18 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
   extern __shared__ unsigned char smem_dyn[];
   __shared__ LoopBars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
+  __shared__ tc::WaitCtl s_ctl;
   __shared__ float s_part[2][2][kRows];     // [exchange parity][group][row]: row maxima, then row sums
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   bf16* sQ = base;                          // [2][128][64]
   bf16* sK = sQ + 2 * kTile;                // [kKStages][128][64]
   bf16* sV = sK + kKStages * kTile;         // [kVStages][128][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  volatile int* abort_flag = &s_abort;
+  volatile tc::WaitCtl* abort_flag = &s_ctl;
 
   if (tid == 0) {
-    s_abort = 0;
+    s_ctl.abort = 0;
+    s_ctl.limit = a.wait_limit > 0 ? a.wait_limit : tc::kWaitPolls;
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.q_full[i], 1);
       tc::mbar_init(&bars.q_empty[i], 1);
@@ -107,7 +99,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
       for (int i = 0; i < n_my; ++i) {
         const int tile = blockIdx.x + i * gridDim.x, qs = i & 1;
         const int bh = tile / tiles_per_head, row0 = (tile % tiles_per_head) * kRows;
-        if (!lp_wait(&bars.q_empty[qs], ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.q_empty[qs], ((i >> 1) & 1) ^ 1, abort_flag)) break;
         tma::expect_tx(&bars.q_full[qs], kTile * 2);
         tma::load_4d(sQ + qs * kTile, &maps.q, &bars.q_full[qs], 0, row0, bh % a.H, bh / a.H);
         int krow[8];
@@ -120,7 +112,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
           const int c = j % n_chunks, pass = j / n_chunks;
           const int crow = (int) ((int64_t) bh * n_c + (int64_t) (c - gathered) * kChunk);      // contiguous chunk
           const int ks = kjob % kKStages;
-          if (!(ok = lp_wait(&bars.k_empty[ks], ((kjob / kKStages) & 1) ^ 1, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.k_empty[ks], ((kjob / kKStages) & 1) ^ 1, abort_flag))) break;
           tma::expect_tx(&bars.k_full[ks], kTile * 2);
           if (gathered && c == 0) {
 #pragma unroll
@@ -131,7 +123,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
           ++kjob;
           if (pass == 1) {
             const int vs = vjob % kVStages;
-            if (!(ok = lp_wait(&bars.v_empty[vs], ((vjob / kVStages) & 1) ^ 1, abort_flag))) break;
+            if (!(ok = tc::bounded_wait(&bars.v_empty[vs], ((vjob / kVStages) & 1) ^ 1, abort_flag))) break;
             tma::expect_tx(&bars.v_full[vs], kTile * 2);
             if (gathered && c == 0) {
 #pragma unroll
@@ -158,11 +150,11 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
       bool ok = true;
       for (int i = 0; ok && i < n_my; ++i) {
         const int qs = i & 1;
-        if (!(ok = lp_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
+        if (!(ok = tc::bounded_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
         tc::fence_after_sync();
         auto issue_s = [&](int j) -> bool {             // S of job j into buffer j & 1
           const int ks = kjob % kKStages;
-          if (!lp_wait(&bars.k_full[ks], (kjob / kKStages) & 1, abort_flag)) return false;
+          if (!tc::bounded_wait(&bars.k_full[ks], (kjob / kKStages) & 1, abort_flag)) return false;
           tc::fence_after_sync();
           const uint32_t q_ = lQ + qs * kStage, k_ = lK + ks * kStage, d = tmem + (j & 1) * kChunk;
           tc::umma_ss_lh<0>(d, q_, hi, k_, hi, id_s);
@@ -175,8 +167,8 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         };
         auto issue_pv = [&](int j) -> bool {            // O (+)= P(job j, TMEM) . V chunk
           const int vs = vjob % kVStages, c = j - n_chunks;
-          if (!lp_wait(&bars.v_full[vs], (vjob / kVStages) & 1, abort_flag)) return false;
-          if (c == 0 && i > 0 && !lp_wait(&bars.o_free, (i - 1) & 1, abort_flag)) return false;      // previous tile's O has been read
+          if (!tc::bounded_wait(&bars.v_full[vs], (vjob / kVStages) & 1, abort_flag)) return false;
+          if (c == 0 && i > 0 && !tc::bounded_wait(&bars.o_free, (i - 1) & 1, abort_flag)) return false;      // previous tile's O has been read
           tc::fence_after_sync();
           const uint64_t vdesc = ((uint64_t) hi << 32) | (uint64_t) (lV + vs * kStage);
 #pragma unroll
@@ -191,7 +183,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
             // buffer j & 1 was used by job j - 2: wait until its group is done with it; a pass-2 job then feeds P.V,
             // which precedes the new S in issue order
             const int64_t Jp = J + j - 2;
-            if (!(ok = lp_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+            if (!(ok = tc::bounded_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
             tc::fence_after_sync();
             if (j - 2 >= n_chunks && !(ok = issue_pv(j - 2))) break;
           } else if (J > 0) {
@@ -203,7 +195,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         if (!ok) break;
         for (int j = jobs - 2; ok && j < jobs; ++j) {   // the last two jobs' P.V
           const int64_t Jp = J + j;
-          if (!(ok = lp_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
           tc::fence_after_sync();
           ok = issue_pv(j);
         }
@@ -229,7 +221,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
       s_part[n_x & 1][wg][r] = mine;
       __syncwarp();
       if (lane == 0) tma::mbar_arrive(&bars.xchg);
-      const bool ok_ = __all_sync(0xffffffffu, lp_wait(&bars.xchg, n_x & 1, abort_flag));
+      const bool ok_ = __all_sync(0xffffffffu, tc::bounded_wait(&bars.xchg, n_x & 1, abort_flag));
       other = s_part[n_x & 1][wg ^ 1][r];
       ++n_x;
       return ok_;
@@ -254,7 +246,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
           if (!(ok = exchange(mx, other))) break;
           mx = fmaxf(mx, other);
         }
-        ok = __all_sync(0xffffffffu, lp_wait(&bars.s_ready[wg], (uint32_t) (Jw & 1), abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.s_ready[wg], (uint32_t) (Jw & 1), abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
         if (pass == 0) {
@@ -296,7 +288,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         lsum = wg == 0 ? lsum + other : other + lsum;          // the same order in both groups: identical bits
       }
       if (ok) {
-        ok = __all_sync(0xffffffffu, lp_wait(&bars.o_ready, (uint32_t) (i & 1), abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.o_ready, (uint32_t) (i & 1), abort_flag));
         tc::fence_after_sync();
       }
       if (ok) {
@@ -328,8 +320,10 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
       if (!ok) break;
     }
   }
+  if (abort_flag->abort) tc::abort_drain();
   tc::fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && abort_flag->abort && a.status) atomicOr(a.status, (int) LLSA_DEV_WAIT_EXPIRED);
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
 }
 
@@ -365,7 +359,7 @@ int launch_attn_fwd_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, 
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = n_tiles < sms ? n_tiles : sms;
   const size_t smem = 1024 + (size_t) (2 + kKStages + kVStages) * kTile * sizeof(bf16);
-  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_pooled_loop_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((attn_fwd_pooled_loop_tc_kernel), smem);
   attn_fwd_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, np / kChunk, gathered, n_c, n_tiles, tiles_per_head);
   LLSA_LAUNCH_OK("attn_fwd_pooled_loop_tc_kernel");
   return LLSA_OK;

@@ -54,28 +54,20 @@ struct TcBars {
   uint64_t full_k[kTcStages], empty_k[kTcStages], full_v[kTcStages], empty_v[kTcStages], s_ready[2], p_head[2], p_ready[2], o_ready[2];
 };
 
-__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 400000; ++i) {
-    if (tc::mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, int p1_keys, int np, int n_tiles, int tiles_per_head) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ TcBars bars;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_abort;
+  __shared__ tc::WaitCtl s_ctl;
   bf16* base = reinterpret_cast<bf16*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int stage_elems = kTcRows * 64 + 2 * np * 64;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  volatile int* abort_flag = &s_abort;
+  volatile tc::WaitCtl* abort_flag = &s_ctl;
 
   if (tid == 0) {
-    s_abort = 0;
+    s_ctl.abort = 0;
+    s_ctl.limit = a.wait_limit > 0 ? a.wait_limit : tc::kWaitPolls;
     for (int i = 0; i < kTcStages; ++i) {
       tc::mbar_init(&bars.full_k[i], 1);
       tc::mbar_init(&bars.empty_k[i], 1);
@@ -113,7 +105,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       uint64_t* full = vals ? &bars.full_v[s] : &bars.full_k[s];
       int ok = 1;
       if (lane == 0) {
-        ok = tc_wait(vals ? &bars.empty_v[s] : &bars.empty_k[s], (u & 1) ^ 1, abort_flag) ? 1 : 0;
+        ok = tc::bounded_wait(vals ? &bars.empty_v[s] : &bars.empty_k[s], (u & 1) ^ 1, abort_flag) ? 1 : 0;
         if (ok) tma::expect_tx(full, bytes);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -136,7 +128,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       const uint32_t idesc_s = tc::instr_desc(kTcRows, np, 0, 0), idesc_o = tc::instr_desc(kTcRows, 64, 0, 1);
       auto issue_s = [&](int i) -> bool {          // S(i) = Q.PK^T into TMEM buffer i & 1
         const int s = i % kTcStages, u = i / kTcStages, b = i & 1;
-        if (!tc_wait(&bars.full_k[s], u & 1, abort_flag)) return false;
+        if (!tc::bounded_wait(&bars.full_k[s], u & 1, abort_flag)) return false;
         tc::fence_after_sync();
         const uint32_t qa = tc::smem_u32(base + s * stage_elems), ka = qa + kTcRows * 128;
 #pragma unroll
@@ -152,13 +144,13 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
         const int s = i % kTcStages, b = i & 1;
         // O = P.PV starts on the keys whose P is already written while the softmax warps finish the last 64
         const int ks_head = np > 64 ? (np - 64) / 16 : 0;
-        if (ks_head && !tc_wait(&bars.p_head[b], (i >> 1) & 1, abort_flag)) break;
-        if (!tc_wait(&bars.full_v[s], (i / kTcStages) & 1, abort_flag)) break;
+        if (ks_head && !tc::bounded_wait(&bars.p_head[b], (i >> 1) & 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.full_v[s], (i / kTcStages) & 1, abort_flag)) break;
         tc::fence_after_sync();
         const uint32_t va = tc::smem_u32(base + s * stage_elems) + (kTcRows + np) * 128;
         for (int ks = 0; ks < ks_head; ++ks)       // P: 16 keys = 8 packed columns per k-step; PV: 16 key rows = 2048 bytes
           tc::umma_ts(tmem + b * 256 + np, tmem + b * 256 + ks * 8, tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
-        if (!tc_wait(&bars.p_ready[b], (i >> 1) & 1, abort_flag)) break;
+        if (!tc::bounded_wait(&bars.p_ready[b], (i >> 1) & 1, abort_flag)) break;
         tc::fence_after_sync();
         for (int ks = ks_head; ks < np / 16; ++ks)
           tc::umma_ts(tmem + b * 256 + np, tmem + b * 256 + ks * 8, tc::smem_desc(va + ks * 2048, 1024, 1024), idesc_o, ks > 0);
@@ -184,7 +176,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       for (int q = 0; q < 8; ++q) of[q] = *reinterpret_cast<const uint4*>(orow + 8 * q);
       const float lse_f = a.lse[bh * a.Nq + row];
       // `ok` is kept warp-uniform: the TMEM accesses below are warp-wide instructions
-      bool ok = __all_sync(0xffffffffu, tc_wait(&bars.s_ready[wg], u & 1, abort_flag));
+      bool ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.s_ready[wg], u & 1, abort_flag));
       tc::fence_after_sync();
       float mx = 0.f, lsum = 0.f;
       float va[32], vb[32];
@@ -238,7 +230,7 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
         tc::fence_before_sync();
         __syncwarp();
         if (lane == 0) tma::mbar_arrive(&bars.p_ready[wg]);
-        ok = __all_sync(0xffffffffu, tc_wait(&bars.o_ready[wg], u & 1, abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.o_ready[wg], u & 1, abort_flag));
         tc::fence_after_sync();
       }
       float lse_out = __int_as_float(0x7fc00000);               // NaN unless everything completed
@@ -273,8 +265,10 @@ attn_fwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ TcMaps maps, in
       if (!ok) break;
     }
   }
+  if (abort_flag->abort) tc::abort_drain();
   tc::fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && abort_flag->abort && a.status) atomicOr(a.status, (int) LLSA_DEV_WAIT_EXPIRED);
   if (warp == 0) tc::tmem_dealloc(tmem, 512);
 }
 
@@ -304,7 +298,7 @@ int launch_attn_fwd_pooled_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, int64
   LLSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = n_tiles < sms ? n_tiles : sms;
   const size_t smem = 1024 + (size_t) kTcStages * (kTcRows * 64 + 2 * np * 64) * sizeof(bf16);
-  LLSA_CUDA_OK(cudaFuncSetAttribute(attn_fwd_pooled_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((attn_fwd_pooled_tc_kernel), smem);
   attn_fwd_pooled_tc_kernel<<<grid, kTcThreads, smem, st>>>(a, maps, p1_keys, np, n_tiles, tiles_per_head);
   LLSA_LAUNCH_OK("attn_fwd_pooled_tc_kernel");
   return LLSA_OK;

@@ -2,6 +2,10 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "common.cuh"
 
 namespace llsa {
@@ -42,7 +46,30 @@ int check_contig(const LlsaTensor* t, const char* name, int dtype, int ndim, con
   return LLSA_OK;
 }
 
+// The dynamic shared-memory limit is an attribute of the kernel, not of a launch: it is only ever raised, under a lock,
+// and remembered per (kernel, device), so launches of different sizes from different host threads cannot lower each
+// other's limit between the attribute call and the launch.
+int raise_smem_limit(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, size_t> limit;
+  int dev = 0;
+  LLSA_CUDA_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& cur = limit[std::make_pair(kernel, dev)];
+  if (bytes > cur) {
+    LLSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) bytes));
+    cur = bytes;
+  }
+  return LLSA_OK;
+}
+
 }  // namespace llsa
 
-extern "C" int llsa_version(void) { return 100; }
+extern "C" int llsa_version(void) { return 101; }
+extern "C" int llsa_status_check(int32_t w) {
+  LLSA_REQUIRE(w == 0, LLSA_ERR_DEVICE_CHECK, "device status 0x%x:%s%s", (unsigned) w,
+               (w & LLSA_DEV_BAD_INDEX) ? " a block index outside its range was met;" : "",
+               (w & LLSA_DEV_WAIT_EXPIRED) ? " a bounded wait inside a kernel ran out (outputs invalid);" : "");
+  return LLSA_OK;
+}
 extern "C" const char* llsa_last_error_string(void) { return llsa::g_err; }

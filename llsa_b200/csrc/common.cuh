@@ -38,6 +38,14 @@ void set_error(const char* fmt, ...);
     }                                                                                   \
   } while (0)
 
+// Raises (never lowers) a kernel's dynamic shared-memory limit on the current device; thread-safe.
+int raise_smem_limit(const void* kernel, size_t bytes);
+#define LLSA_SMEM_LIMIT(kernel, bytes)                                              \
+  do {                                                                              \
+    int rc__ = ::llsa::raise_smem_limit((const void*) (kernel), (size_t) (bytes));  \
+    if (rc__) return rc__;                                                          \
+  } while (0)
+
 inline size_t dtype_size(int dt) {
   switch (dt) {
     case LLSA_F32: return 4;

@@ -138,6 +138,10 @@ __device__ __forceinline__ void lds128(uint32_t& r0, uint32_t& r1, uint32_t& r2,
   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(sa), "n"(IMM));
 }
 template <int IMM>
+__device__ __forceinline__ void sts128(uint32_t sa, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0+%1], {%2,%3,%4,%5};" ::"r"(sa), "n"(IMM), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+template <int IMM>
 __device__ __forceinline__ float2 lds64f(uint32_t sa) {
   float2 v;
   asm volatile("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(sa), "n"(IMM));

@@ -45,6 +45,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// ---- bounded waits of the warp-specialised kernels -------------------------------------------------
+// One WaitCtl per CTA (shared memory).  A wait polls at most `limit` times; the first wait that runs out raises
+// `abort`, which every other wait of the CTA notices within a thousand polls, so all roles leave their loops, the
+// kernel ORs LLSA_DEV_WAIT_EXPIRED into the caller's status word, lets what it still has in flight finish
+// (abort_drain), frees its tensor memory and returns normally: the context stays usable and the host can tell.
+struct WaitCtl {
+  int abort;
+  int limit;
+};
+constexpr int kWaitPolls = 400000;
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile WaitCtl* c) {
+  const int limit = c->limit;
+  for (int i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && c->abort) return false;
+  }
+  c->abort = 1;
+  return false;
+}
+// After an abort: a fixed, bounded pause (about 60 microseconds) in which bulk copies and tensor-core instructions
+// this CTA has already issued complete, before its shared and tensor memory are given back.
+__device__ __forceinline__ void abort_drain() {
+  for (int i = 0; i < 64; ++i) __nanosleep(1000);
+}
+
 // Bounded wait: returns false if the phase did not complete within `spins` polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int spins = 2000000) {
   for (int i = 0; i < spins; ++i)

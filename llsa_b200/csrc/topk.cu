@@ -27,6 +27,11 @@ struct Cand {
 
 __device__ __forceinline__ bool better(float v2, int64_t i2, float v, int64_t i) { return v2 > v || (v2 == v && i2 < i); }
 
+// Scores as the selection sees them: a NaN score ranks as the largest value (torch.topk's order, so a row of
+// NaNs still yields topk distinct in-range columns); NaN is thereby free to mark "retired / unused" entries,
+// which `better` never prefers.
+__device__ __forceinline__ float nan_first(float v) { return v != v ? CUDART_INF_F : v; }
+
 __device__ __forceinline__ Cand warp_argmax(Cand c) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -80,7 +85,7 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
   const T* q0 = pq + (bh * M + row0) * D;
   const T* k0 = pk + bh * n * D;
   for (int i = threadIdx.x; i < kCoarseRows * D; i += blockDim.x) qs[i] = (i / D) < nrows ? to_f32<T>(q0[i]) : 0.f;
-  for (int i = threadIdx.x; i < kCoarseRows * kMaxTopk; i += blockDim.x) { cv[i] = -CUDART_INF_F; ci[i] = INT64_MAX; }
+  for (int i = threadIdx.x; i < kCoarseRows * kMaxTopk; i += blockDim.x) { cv[i] = CUDART_NAN_F; ci[i] = INT64_MAX; }
   __syncthreads();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -89,7 +94,7 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
     for (int j = threadIdx.x; j < cn; j += blockDim.x) {
       const T* kr = k0 + (base + j) * D;
 #pragma unroll
-      for (int r = 0; r < kCoarseRows; ++r) sc[r * kCoarseChunk + j] = round_to<T>(dot_row<T>(qs + r * D, kr, D));
+      for (int r = 0; r < kCoarseRows; ++r) sc[r * kCoarseChunk + j] = nan_first(round_to<T>(dot_row<T>(qs + r * D, kr, D)));
     }
     __syncthreads();
     for (int r = warp; r < nrows; r += nwarps) {
@@ -114,10 +119,10 @@ coarse_topk_kernel(const T* __restrict__ pq, const T* __restrict__ pk, void* __r
         if (lane == 0) { nv[r * kMaxTopk + t] = best.v; ni[r * kMaxTopk + t] = best.i; }
         // retire the winner from whichever set holds it
         if (best.i >= base && best.i < base + cn) {
-          if (lane == 0) s[best.i - base] = -CUDART_INF_F;
+          if (lane == 0) s[best.i - base] = CUDART_NAN_F;
         } else {
           for (int u = lane; u < topk; u += 32)
-            if (ci[r * kMaxTopk + u] == best.i) cv[r * kMaxTopk + u] = -CUDART_INF_F;
+            if (ci[r * kMaxTopk + u] == best.i) cv[r * kMaxTopk + u] = CUDART_NAN_F;
         }
         __syncwarp();
       }
@@ -153,6 +158,9 @@ constexpr int kCmRows = 64, kCmKeys = 64, kCmTop = 8;
 __device__ __forceinline__ uint32_t orderable(float v);
 
 __device__ __forceinline__ void top8_insert(float (&val)[kCmTop], int (&idx)[kCmTop], float v, int i) {
+  // NaN ranks first (torch.topk); -inf is lifted above the lists' initial -inf so that every column can enter:
+  // a lane always ends with eight real columns, whatever the scores are
+  v = v != v ? CUDART_INF_F : fmaxf(v, -3.0e38f);
   if (!(v > val[kCmTop - 1])) return;
   val[kCmTop - 1] = v;
   idx[kCmTop - 1] = i;
@@ -247,6 +255,7 @@ constexpr int kRefineSlots = 8;        // register path of the refine selection:
 __device__ __forceinline__ uint32_t orderable(float v) {
   uint32_t u = __float_as_uint(v);
   if (u == 0x80000000u) u = 0u;
+  if (v != v) u = 0x7FC00000u;           // any NaN ranks above +inf, as in torch.topk
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
@@ -262,7 +271,7 @@ __device__ __forceinline__ void refine_select_regs(const float* sc, const int* c
 #pragma unroll
     for (int u = 0; u < SLOTS; ++u) {
       const int j = lane + 32 * u;
-      key[u] = j < C ? orderable(s[j]) : 0u;            // 0 is below every real score's image
+      key[u] = (j < C && cand[j] >= 0) ? orderable(s[j]) : 0u;            // 0 is below every real score's image
       blk[u] = j < C ? (uint32_t) cand[j] : 0xFFFFFFFFu;
     }
     for (int t = 0; t < topk; ++t) {
@@ -295,7 +304,7 @@ __device__ __forceinline__ void refine_select_sorted4(const float* sc, const int
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int j = lane + 32 * u;
-      key[u] = j < C ? orderable(s[j]) : 0u;            // 0 is below every real score's image
+      key[u] = (j < C && cand[j] >= 0) ? orderable(s[j]) : 0u;            // 0 is below every real score's image
       blk[u] = j < C ? (uint32_t) cand[j] : 0xFFFFFFFFu;
     }
     auto order = [&](int x, int y) {                     // afterwards slot x is not worse than slot y
@@ -339,7 +348,15 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   for (int j = threadIdx.x; j < C; j += blockDim.x) {
     int64_t p = p_idx.at((bh * n2q + P) * p_topk + j / bs);
     p = p < 0 ? 0 : (p >= n2 ? n2 - 1 : p);      // never read outside the tensor
-    cand[j] = (int) (p * bs + j % bs);
+    // a parent listed twice (possible only in a caller-made p_idx) contributes its children once: the selection
+    // below relies on distinct candidate blocks; the repeats are marked unused (-1)
+    bool repeat = false;
+    for (int u = 0; u < j / bs; ++u) {
+      int64_t pu = p_idx.at((bh * n2q + P) * p_topk + u);
+      pu = pu < 0 ? 0 : (pu >= n2 ? n2 - 1 : pu);
+      repeat = repeat || pu == p;
+    }
+    cand[j] = repeat ? -1 : (int) (p * bs + j % bs);
   }
   __syncthreads();
   if constexpr (MMA) {
@@ -350,8 +367,8 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
       load_rowfrag(qhi, reinterpret_cast<const bf16*>(q0) + (g + 8) * D, t);
       for (int tile = warp_ * 2; tile < C / 8; tile += 8) {      // two 8-candidate n-tiles per step and warp
         RowFrag ka, kb;
-        load_rowfrag(ka, reinterpret_cast<const bf16*>(k0) + (int64_t) cand[tile * 8 + g] * D, t);
-        load_rowfrag(kb, reinterpret_cast<const bf16*>(k0) + (int64_t) cand[tile * 8 + 8 + g] * D, t);
+        load_rowfrag(ka, reinterpret_cast<const bf16*>(k0) + (int64_t) max(cand[tile * 8 + g], 0) * D, t);
+        load_rowfrag(kb, reinterpret_cast<const bf16*>(k0) + (int64_t) max(cand[tile * 8 + 8 + g], 0) * D, t);
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
         mma_rows_x_keys(s0, s1, qlo, qhi, ka, kb);
         // C fragment: rows g / g+8, candidates tile*8 + 2t, +1 (and +8 for the second tile)
@@ -365,7 +382,7 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   // each thread owns a candidate: its key row is read once per group of 16 query rows and
   // meets the rows (broadcast from shared memory) in 16 independent accumulators
   for (int j = threadIdx.x; j < C; j += blockDim.x) {
-    const T* kr = k0 + (int64_t) cand[j] * D;
+    const T* kr = k0 + (int64_t) max(cand[j], 0) * D;
     for (int r0 = 0; r0 < bs; r0 += 16) {
       float acc[16];
 #pragma unroll
@@ -404,15 +421,17 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   }
   for (int r = warp; r < bs; r += nwarps) {
     float* s = sc + r * C;
+    for (int j = lane; j < C; j += 32) s[j] = cand[j] < 0 ? CUDART_NAN_F : nan_first(s[j]);
+    __syncwarp();
     for (int t = 0; t < topk; ++t) {
       Cand best{-CUDART_INF_F, INT64_MAX};
       int bj = -1;
       for (int j = lane; j < C; j += 32) {
-        const float v = s[j];
+        const float v = s[j];           // NaN here = retired or a repeated parent's candidate
         if (better(v, cand[j], best.v, best.i)) { best.v = v; best.i = cand[j]; bj = j; }
       }
       const Cand w = warp_argmax(best);
-      if (bj >= 0 && w.i == best.i && w.v == best.v) s[bj] = -CUDART_INF_F;  // candidates are distinct blocks: one owner
+      if (bj >= 0 && w.i == best.i && w.v == best.v) s[bj] = CUDART_NAN_F;  // candidates are distinct blocks: one owner
       if (lane == 0) {
         const int64_t o = (bh * M + P * bs + r) * topk + t;
         if (idx64) reinterpret_cast<int64_t*>(idx_out)[o] = w.i;
@@ -445,7 +464,7 @@ extern "C" int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, cons
   dim3 grid((unsigned) ((M + kCoarseRows - 1) / kCoarseRows), (unsigned) (B * H));
   cudaStream_t st = (cudaStream_t) stream;
   if (pq->dtype == LLSA_F32) {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(coarse_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    LLSA_SMEM_LIMIT((coarse_topk_kernel<float>), smem);
     coarse_topk_kernel<float><<<grid, kCoarseThreads, smem, st>>>((const float*) pq->ptr, (const float*) pk->ptr, idx->ptr,
                                                                    idx->dtype == LLSA_I64, M, n, (int) D, topk);
   } else if (D == 64 && topk <= kCmTop && n % kCmKeys == 0 && n >= topk && ((uintptr_t) pq->ptr % 32) == 0 && ((uintptr_t) pk->ptr % 16) == 0 &&
@@ -453,7 +472,7 @@ extern "C" int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, cons
     coarse_topk_mma_kernel<<<dim3((unsigned) ((M + kCmRows - 1) / kCmRows), (unsigned) (B * H)), 128, 0, st>>>(
         (const __nv_bfloat16*) pq->ptr, (const __nv_bfloat16*) pk->ptr, idx->ptr, idx->dtype == LLSA_I64, M, n, topk);
   } else {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(coarse_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    LLSA_SMEM_LIMIT((coarse_topk_kernel<__nv_bfloat16>), smem);
     coarse_topk_kernel<__nv_bfloat16><<<grid, kCoarseThreads, smem, st>>>((const __nv_bfloat16*) pq->ptr, (const __nv_bfloat16*) pk->ptr,
                                                                            idx->ptr, idx->dtype == LLSA_I64, M, n, (int) D, topk);
   }
@@ -485,15 +504,15 @@ extern "C" int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, co
   dim3 grid((unsigned) (M / bs), (unsigned) (B * H));
   cudaStream_t st = (cudaStream_t) stream;
   if (pq1->dtype == LLSA_F32) {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    LLSA_SMEM_LIMIT((refine_topk_kernel<float, false>), smem);
     refine_topk_kernel<float, false><<<grid, 128, smem, st>>>((const float*) pq1->ptr, (const float*) pk1->ptr, make_idx(p_idx), idx->ptr,
                                                               idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
   } else if (D == 64 && bs == 16 && p_topk % 2 == 0 && ((uintptr_t) pq1->ptr % 32) == 0 && ((uintptr_t) pk1->ptr % 32) == 0) {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    LLSA_SMEM_LIMIT((refine_topk_kernel<__nv_bfloat16, true>), smem);
     refine_topk_kernel<__nv_bfloat16, true><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
                                                                      make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
   } else {
-    LLSA_CUDA_OK(cudaFuncSetAttribute(refine_topk_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    LLSA_SMEM_LIMIT((refine_topk_kernel<__nv_bfloat16, false>), smem);
     refine_topk_kernel<__nv_bfloat16, false><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
                                                                       make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
   }

@@ -27,6 +27,7 @@ struct TransposeArgs {
   void* offsets;    // [BH, n_kv+1]
   int off64;
   int32_t* flat;    // [BH, M*T]
+  int32_t* pairs;   // [BH, M*T] or nullptr: entry position m*T + t in the order of `flat`
   int64_t E;        // entries per head
   int T;
   int64_t n_kv;
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
     bool valid = e < seg1;
     int64_t key = valid ? a.idx.at(bh * E + e) : -1;
     if (valid && (key < 0 || key >= n)) {
-      if (a.status) *a.status = 1;
+      if (a.status) atomicOr(a.status, (int) LLSA_DEV_BAD_INDEX);
       valid = false;
     }
     const unsigned act = __ballot_sync(0xffffffffu, valid);
@@ -107,6 +108,9 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
         tab[(int64_t) s * n + j] = (uint16_t) run;
         run += c;
       }
+      // the prefixes are 16-bit: a key listed more than 65535 times in one head (possible only when rows repeat a key)
+      // cannot be placed; the fill below then skips what would fall outside and the status word says so
+      if (run > 65535 && a.status) atomicOr(a.status, (int) LLSA_DEV_BAD_INDEX);
     }
     int total;
     const int excl = block_exclusive_scan(run, warp_sums, total);
@@ -136,7 +140,10 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
       peers = __match_any_sync(act, (int) key);
       seen = mytab[key];
       const int pos = base[key] + seen + __popc(peers & lt_mask);
-      a.flat[bh * E + pos] = (int32_t) (e / a.T);
+      if (pos < E) {
+        a.flat[bh * E + pos] = (int32_t) (e / a.T);
+        if (a.pairs) a.pairs[bh * E + pos] = (int32_t) e;
+      }
     }
     __syncwarp();
     if (valid && (peers & lt_mask) == 0) mytab[key] = (uint16_t) (seen + __popc(peers));
@@ -173,8 +180,8 @@ extern "C" size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, 
   return global ? (size_t) B * H * 32 * n_kv * 2 : 0;
 }
 
-extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
-                                      void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs, int64_t n_kv,
+                          void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
   LLSA_REQUIRE(idx && offsets && flat && idx->ptr && offsets->ptr && flat->ptr, LLSA_ERR_NULL, "transpose_indices: null tensor");
   LLSA_REQUIRE(idx->ndim == 4, LLSA_ERR_SHAPE, "transpose_indices: idx must be [B,H,M,T]");
   const int64_t B = idx->shape[0], H = idx->shape[1], M = idx->shape[2], T = idx->shape[3];
@@ -188,6 +195,9 @@ extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* o
   if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
   if ((rc = check_contig(offsets, "offsets", offsets->dtype, 3, so))) return rc;
   if ((rc = check_contig(flat, "flat", LLSA_I32, 3, sf))) return rc;
+  if (pairs && (rc = check_contig(pairs, "pairs", LLSA_I32, 3, sf))) return rc;
+  // the per-key prefixes over the segments are 16-bit: with distinct keys inside a row a key occurs at most M times per head
+  LLSA_REQUIRE(M <= 65535, LLSA_ERR_SHAPE, "transpose_indices: M=%lld query blocks per head exceed the supported 65535", (long long) M);
   if (B * H == 0) return LLSA_OK;
   size_t smem;
   bool global;
@@ -198,6 +208,7 @@ extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* o
   a.offsets = offsets->ptr;
   a.off64 = offsets->dtype == LLSA_I64;
   a.flat = (int32_t*) flat->ptr;
+  a.pairs = pairs ? (int32_t*) pairs->ptr : nullptr;
   a.E = E;
   a.T = (int) T;
   a.n_kv = n_kv;
@@ -209,10 +220,21 @@ extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* o
     a.gtab = (uint16_t*) scratch;
   }
   // a segment holds at most 65535 entries, so the 16-bit counters cannot overflow
-  LLSA_CUDA_OK(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((transpose_kernel), smem);
   transpose_kernel<<<(unsigned) (B * H), W * 32, smem, (cudaStream_t) stream>>>(a);
   LLSA_LAUNCH_OK("transpose_kernel");
   return LLSA_OK;
+}
+
+extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
+                                      void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+  return transpose_impl(idx, offsets, flat, nullptr, n_kv, scratch, scratch_bytes, status, stream);
+}
+
+extern "C" int llsa_transpose_indices_pairs(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs,
+                                            int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+  LLSA_REQUIRE(pairs && pairs->ptr, LLSA_ERR_NULL, "transpose_indices_pairs: null pairs tensor");
+  return transpose_impl(idx, offsets, flat, pairs, n_kv, scratch, scratch_bytes, status, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -283,6 +305,7 @@ extern "C" int llsa_transpose_indices_noalloc(const LlsaTensor* idx, const LlsaT
                "(use llsa_transpose_indices with caller scratch)", (long long) (B * H * n_kv), need, (size_t) kNoAllocScratchBytes);
   const size_t smem = (size_t) n_kv * 4;   // per-key bases stay in shared memory
   LLSA_REQUIRE(smem <= 200 * 1024, LLSA_ERR_SHAPE, "transpose_indices_noalloc: n_kv=%lld too large", (long long) n_kv);
+  LLSA_REQUIRE(M <= 65535, LLSA_ERR_SHAPE, "transpose_indices_noalloc: M=%lld query blocks per head exceed the supported 65535", (long long) M);
   if (B * H == 0) return LLSA_OK;
   void* tab = nullptr;
   if ((rc = noalloc_scratch(&tab))) return rc;
@@ -291,12 +314,13 @@ extern "C" int llsa_transpose_indices_noalloc(const LlsaTensor* idx, const LlsaT
   a.offsets = offsets->ptr;
   a.off64 = offsets->dtype == LLSA_I64;
   a.flat = (int32_t*) flat->ptr;
+  a.pairs = nullptr;
   a.E = E;
   a.T = (int) T;
   a.n_kv = n_kv;
   a.gtab = (uint16_t*) tab;     // the kernel zero-fills the part of the table it uses before counting
   a.status = status;
-  LLSA_CUDA_OK(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  LLSA_SMEM_LIMIT((transpose_kernel), smem);
   transpose_kernel<<<(unsigned) (B * H), 32 * 32, smem, (cudaStream_t) stream>>>(a);
   LLSA_LAUNCH_OK("transpose_kernel");
   return LLSA_OK;

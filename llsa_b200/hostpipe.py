@@ -20,6 +20,30 @@ some twenty kernel launches plus autograd bookkeeping per chunk, which is what l
 import torch
 
 
+def capture_fwd_bwd(call, q, k, v, do, stream=None):
+    """One forward + backward of `call(q, k, v)` against the upstream gradient `do`, captured as a CUDA graph on static
+    device tensors: returns (graph, (o, dq, dk, dv)); graph.replay() recomputes the four results in place from whatever
+    q, k, v, do hold by then.  A step then costs the host one graph launch instead of some fifteen kernel launches, the
+    operator dispatch and the autograd bookkeeping, which is what bounds small problems (a few (b,h) slices per GPU)."""
+    dev = q.device
+    stream = stream or torch.cuda.Stream(dev)
+    ql, kl, vl = [t.detach().requires_grad_(True) for t in (q, k, v)]
+    stream.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(stream):                       # warm-up outside the capture: lazy initialisation, kernel attributes
+        for _ in range(2):
+            ql.grad = kl.grad = vl.grad = None
+            call(ql, kl, vl).backward(do)
+    torch.cuda.synchronize(dev)
+    ql.grad = kl.grad = vl.grad = None
+    g = torch.cuda.CUDAGraph()
+    # thread-local error mode: other threads of the process (a communicator's watchdog polling its events, for one) may keep
+    # calling the CUDA API while this thread captures
+    with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+        o = call(ql, kl, vl)
+        o.backward(do)
+    return g, (o.detach(), ql.grad, kl.grad, vl.grad)
+
+
 class HostPipeline:
     def __init__(self, call, shape, dtype, device, chunk_batch=1, chunk_heads=None, depth=3, graphs=False):
         """call(q, k, v) -> o on device tensors; shape = (B, H, N, D) of the full host operands.

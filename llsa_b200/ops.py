@@ -34,6 +34,7 @@ __all__ = [
     "sparse_indices_attn_res_2_2_fwd", "sparse_indices_attn_res_scatter_2_2_bwd_v2",
     "flash_sparse_residual_attention_l1_op", "flash_sparse_residual_attention_l2_op",
     "llsa_l1", "llsa_l2", "llsa_l1_rope", "llsa_l2_rope", "pool_pyramid", "rope_pool_pyramid", "set_exact_pooled_grad",
+    "set_device_checks",
 ]
 
 _FLOAT = (torch.float32, torch.bfloat16)
@@ -47,6 +48,30 @@ _exact_pooled_grad = os.environ.get("LLSA_B200_EXACT_POOLED_GRAD", "0") == "1"
 _stage_hook = None
 _overlap_transpose = os.environ.get("LLSA_B200_OVERLAP_TRANSPOSE", "1") != "0"
 _side_streams = {}
+# Cross-check switch: keep the pooled-key stages on the mma.sync kernels (the form other shapes use).
+_no_tcgen05 = False
+# Test hook: polls after which a bounded wait inside the tcgen05 kernels gives up (0 = the kernels' default).
+_wait_limit = 0
+# Device-side checks.  The kernels OR bits into a status word when they meet an out-of-range block index or when a
+# bounded wait runs out.  Reading the word back costs a host synchronisation, which the reference's operators never do,
+# so it is off by default; with it on, every operator synchronises and raises (LLSA_ERR_DEVICE_CHECK) on a set bit.
+_device_checks = os.environ.get("LLSA_B200_DEVICE_CHECKS", "0") == "1"
+
+
+def set_device_checks(flag: bool) -> None:
+    """Debug mode: read the kernels' device status word back after every operator (a host sync) and raise if a kernel
+    met an out-of-range block index or gave up a bounded wait."""
+    global _device_checks
+    _device_checks = bool(flag)
+
+
+def _new_status(device):
+    return torch.zeros(1, dtype=torch.int32, device=device) if _device_checks else None
+
+
+def _check_status(status, what: str) -> None:
+    if status is not None:
+        _lib.check(_lib.lib().llsa_status_check(int(status.item())), what)
 
 
 def _side_stream(device) -> "torch.cuda.Stream":
@@ -80,13 +105,6 @@ def _need_cuda(*ts: torch.Tensor) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:
             raise RuntimeError("llsa_b200 runs on CUDA tensors only (got a %s tensor); there is no CPU path" % t.device.type)
-
-
-def _rows_ok(t: torch.Tensor) -> bool:
-    per16 = 16 // t.element_size()
-    if t.stride(-1) != 1 or t.data_ptr() % 16:
-        return False
-    return all(t.shape[i] == 1 or t.stride(i) % per16 == 0 for i in range(t.dim() - 1))
 
 
 def _prep(t: torch.Tensor) -> torch.Tensor:
@@ -319,26 +337,38 @@ def compute_topk_indices_sparse(pq, pk, p_indices, topk=8, p_topk=8, block_size=
     return _refine_topk(pq.detach(), pk.detach(), p_indices, topk, p_topk, block_size)
 
 
-def transpose_indices(q_topk_indices: torch.Tensor, k_ntx: Optional[int] = None, offsets_dtype=torch.int64):
-    """Query-major top-k lists -> (offsets [B,H,k_ntx+1], flat [B,H,M*T]) with every
-    bucket in ascending query order.  Mirrors transpose_indices
-    (triton/indices_transpose.py:104-109); `flat` is int32 (the reference's
-    uint32 holds the same values)."""
-    _need_cuda(q_topk_indices)
-    idx = q_topk_indices.contiguous()
+def _transpose(idx: torch.Tensor, k_ntx: int, offsets_dtype, want_pairs: bool):
     B, H, M, T = idx.shape
-    if k_ntx is None:
-        k_ntx = M
     offsets = torch.empty((B, H, k_ntx + 1), device=idx.device, dtype=offsets_dtype)
-    flat = torch.empty((B, H, M * T), device=idx.device, dtype=torch.int32)
+    lists = torch.empty((2 if want_pairs else 1, B, H, M * T), device=idx.device, dtype=torch.int32)
+    flat, pairs = lists[0], (lists[1] if want_pairs else None)
+    status = _new_status(idx.device)
     _mark("transpose_indices")
     with torch.cuda.device(idx.device):
         L = _lib.lib()
         nbytes = L.llsa_transpose_scratch_bytes(B, H, M, T, k_ntx)
-        scratch = torch.empty((max(nbytes, 1),), device=idx.device, dtype=torch.uint8) if nbytes else None
+        scratch = torch.empty((nbytes,), device=idx.device, dtype=torch.uint8) if nbytes else None
+        sp = C.c_void_p(scratch.data_ptr() if nbytes else 0)
+        st = C.c_void_p(status.data_ptr()) if status is not None else None
         a, b, c = desc(idx), desc(offsets), desc(flat)
-        _lib.check(L.llsa_transpose_indices(ref(a), ref(b), ref(c), k_ntx, C.c_void_p(scratch.data_ptr() if nbytes else 0), nbytes, None,
-                                            _stream(idx)), "transpose_indices")
+        if want_pairs:
+            d = desc(pairs)
+            _lib.check(L.llsa_transpose_indices_pairs(ref(a), ref(b), ref(c), ref(d), k_ntx, sp, nbytes, st, _stream(idx)), "transpose_indices")
+        else:
+            _lib.check(L.llsa_transpose_indices(ref(a), ref(b), ref(c), k_ntx, sp, nbytes, st, _stream(idx)), "transpose_indices")
+    return offsets, flat, pairs, status
+
+
+def transpose_indices(q_topk_indices: torch.Tensor, k_ntx: Optional[int] = None, offsets_dtype=torch.int64):
+    """Query-major top-k lists -> (offsets [B,H,k_ntx+1], flat [B,H,M*T]) with every
+    bucket in ascending query order.  Mirrors transpose_indices
+    (triton/indices_transpose.py:104-109); `flat` is int32 (the reference's
+    uint32 holds the same values).  Indices outside [0, k_ntx) are left out of the
+    lists (offsets[..., -1] is then below M*T); with set_device_checks(True) they raise."""
+    _need_cuda(q_topk_indices)
+    idx = q_topk_indices.contiguous()
+    offsets, flat, _, status = _transpose(idx, idx.shape[2] if k_ntx is None else k_ntx, offsets_dtype, False)
+    _check_status(status, "transpose_indices")
     return offsets, flat
 
 
@@ -352,6 +382,8 @@ def _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk
     a.topk, a.topk_p, a.block_size = int(topk), int(topk_p), int(block_size)
     a.token_weight, a.token_weight_2 = float(w1), float(w2)
     a.force_generic = 1 if _force_generic else 0
+    a.no_tcgen05 = 1 if _no_tcgen05 else 0
+    a.wait_limit = int(_wait_limit)
     return a, keep
 
 
@@ -366,11 +398,38 @@ def _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk_p, block
     o = torch.empty_like(q)
     lse = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
     a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
+    status = _new_status(q.device)
+    a.status = status.data_ptr() if status is not None else None
     _mark("attn_fwd")
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().llsa_attn_fwd(C.byref(a), _stream(q)), "attn_fwd")
     _mark("end")
+    _check_status(status, "attn_fwd")
     return o, lse
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    """Unit channel stride; bf16 rows on 32-byte boundaries (what the tensor-core kernels load with one 256-bit
+    instruction per lane), fp32 rows on 16-byte boundaries."""
+    align = 32 if t.dtype == torch.bfloat16 else 16
+    per = align // t.element_size()
+    if t.stride(-1) != 1 or t.data_ptr() % align:
+        return False
+    return all(t.shape[i] == 1 or t.stride(i) % per == 0 for i in range(t.dim() - 1))
+
+
+def _carve(buf: torch.Tensor, specs):
+    """Views into one byte buffer: specs = [(name, dtype, shape)], every view 256-byte aligned."""
+    out, off = {}, 0
+    for name, dtype, shape in specs:
+        n = int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
+        out[name] = buf[off:off + n].view(dtype).view(shape)
+        off += (n + 255) // 256 * 256
+    return out
+
+
+def _carve_bytes(specs) -> int:
+    return sum((int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256 for _, dtype, shape in specs)
 
 
 def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, topk_p, block_size, w1, w2, kvw1, kvw2, fold):
@@ -381,50 +440,68 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
         pk2, pv2, p_indices = pk2.contiguous(), pv2.contiguous(), p_indices.contiguous()
     indices = indices.contiguous()
     lse = lse.contiguous()
+    B, H, Nq, T = q.shape[0], q.shape[1], q.shape[2], indices.shape[3]
+    tensor_core = q.dtype == torch.bfloat16 and not _force_generic
     # The index transpose (one CTA per (b,h): a latency-bound kernel that leaves most SMs idle) is needed only by the fine
     # dK/dV stage, so it runs on a side stream next to the dQ and pooled stages.
     cur = torch.cuda.current_stream(q.device)
     side = _side_stream(q.device) if _overlap_transpose else None
+    n_kv = k.shape[2] // block_size                       # buckets = KEY blocks
     if side is not None:
         side.wait_stream(cur)
         with torch.cuda.stream(side):
-            offsets, flat = transpose_indices(indices, k_ntx=k.shape[2] // block_size, offsets_dtype=torch.int32)   # buckets = KEY blocks
+            offsets, flat, pairs, t_status = _transpose(indices, n_kv, torch.int32, tensor_core)
     else:
-        offsets, flat = transpose_indices(indices, k_ntx=k.shape[2] // block_size, offsets_dtype=torch.int32)
+        offsets, flat, pairs, t_status = _transpose(indices, n_kv, torch.int32, tensor_core)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    delta = torch.empty_like(lse)
-    f32 = dict(device=q.device, dtype=torch.float32)
-    # the fp32 pooled-gradient accumulators sit back to back in one allocation: the library clears them with one memset
-    shapes = [pk.shape, pv.shape] + ([pk2.shape, pv2.shape] if pk2 is not None else [])
-    sizes = [int(torch.Size(s_).numel()) for s_ in shapes]
-    acc = torch.empty(sum(sizes), **f32)
-    views = [acc[sum(sizes[:i]):sum(sizes[:i + 1])].view(shapes[i]) for i in range(len(shapes))]
-    dpk, dpv = views[0], views[1]
-    dpk2, dpv2 = (views[2], views[3]) if pk2 is not None else (None, None)
+    # every scratch tensor of the call comes out of ONE allocation; the fp32 pooled-gradient accumulators sit back to back in
+    # it (the library clears them with one memset)
+    f32 = torch.float32
+    specs = [("delta", f32, lse.shape), ("dpk", f32, pk.shape), ("dpv", f32, pv.shape)]
+    if pk2 is not None:
+        specs += [("dpk2", f32, pk2.shape), ("dpv2", f32, pv2.shape)]
+    if tensor_core:     # window partials of the fine dK/dV kernel and the P / dS hand-over (csrc/attn_bwd_mma.cu)
+        L = _lib.lib()
+        specs += [("partial", f32, (B, H, L.llsa_attn_bwd_partial_elems(B, H, Nq, T) // (B * H * 4096), 4096)),
+                  ("pds", f32, (L.llsa_attn_bwd_pds_elems(B, H, Nq, T),))]
+    ws = _carve(torch.empty(_carve_bytes(specs), device=q.device, dtype=torch.uint8), specs)
+    delta, dpk, dpv = ws["delta"], ws["dpk"], ws["dpv"]
+    dpk2, dpv2 = ws.get("dpk2"), ws.get("dpv2")
     a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
-    partial = None
-    if q.dtype == torch.bfloat16:     # window partials of the fine dK/dV kernel (csrc/attn_bwd_mma.cu)
-        n_elems = _lib.lib().llsa_attn_bwd_partial_elems(q.shape[0], q.shape[1], q.shape[2], indices.shape[3])
-        partial = torch.empty((q.shape[0], q.shape[1], n_elems // (q.shape[0] * q.shape[1] * 4096), 4096), **f32)
+    status = _new_status(q.device)
+    a.status = status.data_ptr() if status is not None else None
     extra = dict(d_o=desc(do), dq=desc(dq), dk=desc(dk), dv=desc(dv), offsets=desc(offsets), flat=desc(flat), delta=desc(delta),
-                 dpk_acc=desc(dpk), dpv_acc=desc(dpv), dpk2_acc=desc(dpk2), dpv2_acc=desc(dpv2), dkv_partial=desc(partial))
+                 dpk_acc=desc(dpk), dpv_acc=desc(dpv), dpk2_acc=desc(dpk2), dpv2_acc=desc(dpv2), dkv_partial=desc(ws.get("partial")),
+                 fine_pds=desc(ws.get("pds")), flat_pairs=desc(pairs))
     for name, d in extra.items():
         setattr(a, name, ptr(d))
     a.fold_pool_bwd = 1 if fold else 0
     a.kv_weight, a.kv_weight_2 = float(kvw1), float(kvw2)
+
+    def join_side():
+        cur.wait_stream(side)                 # the CSR is ready; its memory now also belongs to this stream
+        for t in (offsets, flat) + ((pairs,) if pairs is not None else ()):
+            t.record_stream(cur)
+
     with torch.cuda.device(q.device):
         if _stage_hook is None and side is None:
+            _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), "attn_bwd")
+        elif _stage_hook is None:             # dQ and pooled stages, then the CSR's stream joins, then dK/dV
+            a.stage_mask = 3
+            _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), "attn_bwd")
+            join_side()
+            a.stage_mask = 4
             _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), "attn_bwd")
         else:
             for mask, name in ((1, "attn_bwd_dq"), (2, "attn_bwd_dkv_pooled"), (4, "attn_bwd_dkv_fine")):
                 if mask == 4 and side is not None:
-                    cur.wait_stream(side)                 # the CSR is ready; its memory now also belongs to this stream
-                    offsets.record_stream(cur)
-                    flat.record_stream(cur)
+                    join_side()
                 _mark(name)
                 a.stage_mask = mask
                 _lib.check(_lib.lib().llsa_attn_bwd(C.byref(a), _stream(q)), name)
             _mark("end")
+    _check_status(t_status, "transpose_indices")
+    _check_status(status, "attn_bwd")
     return dq, dk, dv, dpk, dpv, dpk2, dpv2
 
 

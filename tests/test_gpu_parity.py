@@ -245,7 +245,7 @@ def test_llsa_l2_bf16_vs_oracle(path, monkeypatch):
     L = _ops()
     from llsa_b200 import ops
     monkeypatch.setattr(ops, "_force_generic", path == "generic")
-    monkeypatch.setenv("LLSA_B200_TC", "1" if path == "tcgen05" else "0")
+    monkeypatch.setattr(ops, "_no_tcgen05", path != "tcgen05")
     q, k, v, do = _bf16_case("l2", 1, 2, 16384, 41)
     qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
     dbg = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
@@ -298,64 +298,204 @@ def test_llsa_l1_bf16_rope_vs_oracle(force_generic, monkeypatch):
     assert_bf16_close(vg.grad, dv + O.mean_pool1d_bwd(dpv, 16), "dv")
 
 
-@pytest.mark.parametrize("levels,N", [(1, 16384), (2, 65536)])
-def test_pooled_key_loop_on_tcgen05_matches_mma_path(levels, N, monkeypatch):
-    """Long pooled key lists (1024 level-1 keys; 128 gathered + 256 level-2 keys) go through the key-loop tcgen05 kernels
-    (forward, pooled part of dQ); the mma.sync kernels (validated against the oracle above) are the reference here."""
+def _gpu_l2(L, q, k, v, do, topk1=8, topk2=8):
+    """llsa_l2 forward + backward on the GPU (default kernels); everything the comparisons need, on the host."""
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    dbg = L.llsa_l2_debug(qg, kg, vg, topk1, topk2, 16)
+    dbg["o"].backward(do.to(DEV))
+    got = {n: dbg[n].detach().cpu() for n in ("o", "lse", "indices", "p_indices", "pk", "pv", "pk2", "pv2")}
+    got.update(dq=qg.grad.cpu(), dk=kg.grad.cpu(), dv=vg.grad.cpu())
+    return got
+
+
+def _oracle_l2_compare(q, k, v, do, got, topk1=8, topk2=8, rows=None, label=""):
+    """GPU results `got` against the oracle: pooled tensors bit-exact, both selections against the dtype-faithful oracle
+    with the tie-aware comparator (stage isolation: the refine step is fed the GPU's parents), o / lse / dq / dk / dv
+    against the fp32 evaluation on the same inputs and the GPU's indices.  `rows` = (r0, r1), whole 256-row parents:
+    o, lse and dq only on those query rows (the oracle's rectangular form: q a shard, k / v full) and dk / dv through
+    identities that hold at any size -- for sequences whose full fp32 evaluation would not fit the host.
+    Returns the number of rows whose ordered index lists differed (all within the tie margin)."""
+    pk, pv, pk2, pv2 = got["pk"], got["pv"], got["pk2"], got["pv2"]
+    assert torch.equal(pk, O.mean_pool1d(k, 16)) and torch.equal(pv, O.mean_pool1d(v, 16)), label
+    assert torch.equal(pk2, O.mean_pool1d(pk, 16)) and torch.equal(pv2, O.mean_pool1d(pv, 16)), label
+    pq = O.mean_pool1d(q, 16)
+    pq2 = O.mean_pool1d(pq, 16)
+    want_p = O.gen_sparse_indices(pq2, pk2, topk2)
+    differ2 = int((got["p_indices"].long() != want_p.long()).any(-1).sum())
+    if differ2:
+        s2 = (pq2.float() @ pk2.float().transpose(-1, -2)).to(q.dtype).float()
+        differ2, bad2 = topk_mismatch_rows(got["p_indices"], want_p, s2, margin=2.0 ** -7)
+        assert bad2 == 0, label
+    pidx = got["p_indices"].long()
+    want_idx = O.compute_topk_indices_sparse(pq, pk, pidx, topk1, topk2, 16)
+    differ1 = int((got["indices"].long() != want_idx.long()).any(-1).sum())
+    if differ1:
+        s1 = pq.float() @ pk.float().transpose(-1, -2)
+        differ1, bad1 = topk_mismatch_rows(got["indices"], want_idx, s1, margin=1e-6)
+        assert bad1 == 0, label
+    idx = got["indices"]
+    if rows is None:
+        o_ref, lse_ref = O.attn_fwd_l2(q, k, v, pk, pv, pk2, pv2, idx, pidx, topk1, topk2, faithful=False)
+        assert_bf16_close(got["o"], o_ref, label + " o")
+        assert max_abs(got["lse"], lse_ref) < 2e-2, label
+        dq, dk, dv, dpk, dpv, dpk2, dpv2 = O.attn_bwd_l2(do, q, k, v, pk, pv, pk2, pv2, o_ref.float(), lse_ref, idx, pidx, topk1, topk2,
+                                                         faithful=False)
+        dk = dk + O.mean_pool1d_bwd(dpk + O.mean_pool1d_bwd(dpk2, 16), 16)
+        dv = dv + O.mean_pool1d_bwd(dpv + O.mean_pool1d_bwd(dpv2, 16), 16)
+        assert_bf16_close(got["dq"], dq, label + " dq")
+        assert_bf16_close(got["dk"], dk, label + " dk")
+        assert_bf16_close(got["dv"], dv, label + " dv")
+    else:
+        r0, r1 = rows
+        sl = slice(r0, r1)
+        o_ref, lse_ref = O.attn_fwd_l2(q[:, :, sl], k, v, pk, pv, pk2, pv2, idx[:, :, r0 // 16:r1 // 16], pidx[:, :, r0 // 256:r1 // 256],
+                                       topk1, topk2, faithful=False)
+        assert_bf16_close(got["o"][:, :, sl], o_ref, label + " o")
+        assert max_abs(got["lse"][:, :, sl], lse_ref) < 2e-2, label
+        dq = O.attn_bwd_l2(do[:, :, sl], q[:, :, sl], k, v, pk, pv, pk2, pv2, o_ref.float(), lse_ref, idx[:, :, r0 // 16:r1 // 16],
+                           pidx[:, :, r0 // 256:r1 // 256], topk1, topk2, faithful=False)[0]
+        assert_bf16_close(got["dq"][:, :, sl], dq, label + " dq")
+        assert rel_l2(got["dv"].float().sum(2), do.float().sum(2)) < 5e-3, label       # attention weights of a row sum to one
+        a = (got["dq"].float() * q.float()).sum((2, 3))
+        b = (got["dk"].float() * k.float()).sum((2, 3))
+        assert rel_l2(a, b) < 2e-2, label                      # softmax shift invariance: sum dq.q == sum dk.k
+    return differ2 + differ1
+
+
+def _oracle_l2_check(L, q, k, v, do, topk1=8, topk2=8, rows=None, label=""):
+    return _oracle_l2_compare(q, k, v, do, _gpu_l2(L, q, k, v, do, topk1, topk2), topk1, topk2, rows, label)
+
+
+@pytest.mark.parametrize("N", [32768, 65536])
+def test_llsa_l2_long_pooled_lists_vs_oracle(N):
+    """More than 64 level-2 keys: the gathered chunk + dense level-2 loop of the key-loop tcgen05 kernels (forward, pooled
+    dQ, level-2 pooled dK/dV) and the level-1 remainder on the mma.sync kernel, default dispatch, against the oracle
+    (semantics: sparse_attention_res_2.py:94-149 forward, :323-366 and :451-575 backward)."""
     L = _ops()
-    q, k, v, do = [t.to(DEV) for t in synth.correlated_qkv(48, 1, 2, N, 64, dtype=torch.bfloat16)]
-
-    def run():
-        qg, kg, vg = [t.clone().requires_grad_(True) for t in (q, k, v)]
-        d = L.llsa_l1_debug(qg, kg, vg, 8, 16) if levels == 1 else L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
-        d["o"].backward(do)
-        return d, qg.grad, kg.grad, vg.grad
-
-    monkeypatch.setenv("LLSA_B200_TC", "1")
-    a, dqa, dka, dva = run()
-    monkeypatch.setenv("LLSA_B200_TC", "0")
-    b, dqb, dkb, dvb = run()
-    assert torch.equal(a["indices"], b["indices"])
-    assert not torch.isnan(a["lse"]).any()
-    assert_bf16_close(a["o"].detach(), b["o"].detach().float(), "o")
-    assert max_abs(a["lse"], b["lse"]) < 2e-3
-    assert_bf16_close(dqa, dqb.float(), "dq")
-    assert_bf16_close(dka, dkb.float(), "dk")
-    assert_bf16_close(dva, dvb.float(), "dv")
+    q, k, v, do = synth.correlated_qkv(48, 1, 1, N, 64, dtype=torch.bfloat16)
+    _oracle_l2_check(L, q, k, v, do, label="N=%d" % N)
 
 
-def test_mma_rate_probe_runs():
-    """The issue-rate probe of the harness: at 16 warps per SM the tensor pipe, not latency, bounds mma.sync.m16n8k16."""
-    from llsa_b200 import kernel_sweep
-    rows = kernel_sweep.mma_rate(torch.device(DEV))
-    sat = [r for r in rows if r.get("warps_per_sm") == 16 and r.get("ilp") == 4][0]["cycles_per_mma_per_subpartition"]
-    one = [r for r in rows if r.get("warps_per_sm") == 1 and r.get("ilp") == 1][0]["cycles_per_mma_per_subpartition"]
-    assert 2.0 < sat < 32.0 and one >= sat
-
-
-def test_fine_kernel_forms_agree(monkeypatch):
-    """The top-8 fine forward (softmax statistics per four blocks) and the three-CTA fine dK/dV kernel against the forms they
-    replaced (per-block online softmax; fragments in registers), on correlated inputs with empty and very long buckets."""
+def test_llsa_l1_long_pooled_list_vs_oracle():
+    """llsa_l1 at N=16384: 1024 level-1 pooled keys per row through the key-loop tcgen05 kernels, against the oracle."""
     L = _ops()
-    q, k, v, do = [t.to(DEV) for t in synth.correlated_qkv(49, 2, 3, 16384, 64, dtype=torch.bfloat16)]
+    q, k, v, do = synth.correlated_qkv(49, 1, 1, 16384, 64, dtype=torch.bfloat16)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    dbg = L.llsa_l1_debug(qg, kg, vg, 8, 16)
+    idx = dbg["indices"].cpu()
+    pk, pv = dbg["pk"].detach().cpu(), dbg["pv"].detach().cpu()
+    o_ref, lse_ref = O.attn_fwd_l1(q, k, v, pk, pv, idx, faithful=False)
+    assert_bf16_close(dbg["o"].detach(), o_ref, "o")
+    assert max_abs(dbg["lse"], lse_ref) < 2e-2
+    dbg["o"].backward(do.to(DEV))
+    dq, dk, dv, dpk, dpv = O.attn_bwd_l1(do, q, k, v, pk, pv, o_ref.float(), lse_ref, idx, faithful=False)
+    assert_bf16_close(qg.grad, dq, "dq")
+    assert_bf16_close(kg.grad, dk + O.mean_pool1d_bwd(dpk, 16), "dk")
+    assert_bf16_close(vg.grad, dv + O.mean_pool1d_bwd(dpv, 16), "dv")
 
-    def run():
-        qg, kg, vg = [t.clone().requires_grad_(True) for t in (q, k, v)]
-        d = L.llsa_l2_debug(qg, kg, vg, 8, 8, 16)
-        d["o"].backward(do)
-        return d, qg.grad, kg.grad, vg.grad
 
-    a, dqa, dka, dva = run()
-    monkeypatch.setenv("LLSA_B200_FWD_FINE", "online")
-    monkeypatch.setenv("LLSA_B200_DKV_FINE", "regs")
-    b, dqb, dkb, dvb = run()
-    assert torch.equal(a["indices"], b["indices"])
-    assert_bf16_close(a["o"].detach(), b["o"].detach().float(), "o")
-    assert max_abs(a["lse"], b["lse"]) < 2e-3
-    assert_bf16_close(dqa, dqb.float(), "dq")
-    assert rel_l2(dka, dkb) < 2e-3 and rel_l2(dva, dvb) < 2e-3
-    assert_bf16_close(dka, dkb.float(), "dk")
-    assert_bf16_close(dva, dvb.float(), "dv")
+def test_llsa_l2_cfg5_shape_vs_oracle():
+    """BASELINE config 5's sequence length (N=262144: 1024 level-2 keys per row), one (b,h) slice.  Pooling and both
+    selections are compared in full; o, lse and dq on two ranges of 1024 query rows (the oracle's fp32 evaluation of all
+    262144 rows against the dense 1024-key tail would need several GB); dk / dv through the size-independent identities."""
+    L = _ops()
+    q, k, v, do = synth.correlated_qkv(5, 1, 1, 262144, 64, dtype=torch.bfloat16)
+    got = _gpu_l2(L, q, k, v, do)
+    _oracle_l2_compare(q, k, v, do, got, rows=(0, 1024), label="cfg5 first rows")
+    _oracle_l2_compare(q, k, v, do, got, rows=(200704, 201728), label="cfg5 middle rows")
+
+
+@pytest.mark.parametrize("topk", [4, 16])
+def test_llsa_l2_other_topk_vs_oracle(topk):
+    """Top-k values other than 8 take the per-block online-softmax fine forward (attn_fwd_fine_kernel) and the generic
+    selection widths; against the oracle like the top-8 case."""
+    L = _ops()
+    q, k, v, do = synth.correlated_qkv(52, 1, 2, 16384, 64, dtype=torch.bfloat16)
+    _oracle_l2_check(L, q, k, v, do, topk1=topk, topk2=8, label="topk=%d" % topk)
+
+
+def test_l1_op_with_explicit_pooled_inputs_vs_oracle():
+    """flash_sparse_residual_attention_l1_op (torch_op/flash_sparse_attention_res_1.py:38) called the way the reference's
+    benchmark does (test_kernel.py:9-13): 9 positional arguments, pooled tensors made by mean_pool1d; the pooled-key
+    gradients flow back through the pooling operators' own backward."""
+    L = _ops()
+    q, k, v, do = synth.gaussian_qkv(53, 1, 2, 2048, 64, dtype=torch.float32)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    pq, pk, pv = L.mean_pool1d(qg, 16), L.mean_pool1d(kg, 16), L.mean_pool1d(vg, 16)
+    o = L.flash_sparse_residual_attention_l1_op(qg, kg, vg, pq, pk, pv, 8, 16, 16)
+    o.backward(do.to(DEV))
+    r = O.llsa_l1_fwd_bwd(q, k, v, do, faithful=False)
+    assert rel_l2(o.detach(), r["o"]) < 2e-5
+    assert rel_l2(qg.grad, r["dq"]) < 2e-5 and rel_l2(kg.grad, r["dk"]) < 2e-5 and rel_l2(vg.grad, r["dv"]) < 2e-5
+
+
+def test_nan_rows_still_select_valid_blocks():
+    """A query row of NaNs: torch.topk ranks NaN first, so the reference still returns topk in-range, distinct indices
+    (topk.py:6-9).  The selection kernels must do the same, and the transposed lists must stay complete."""
+    L = _ops()
+    for dtype in (torch.bfloat16, torch.float32):
+        pq, pk = synth.gaussian_qkv(54, 1, 2, 256, 64, n_tensors=2, dtype=dtype)
+        pq[0, 0, 3] = float("nan")
+        pq[0, 1, 100, 7] = float("nan")
+        got = L.gen_sparse_indices(pq.to(DEV), pk.to(DEV), 8).cpu()
+        assert int(got.min()) >= 0 and int(got.max()) < 256
+        assert (got.sort(-1).values.diff(dim=-1) > 0).all(), "repeated block in a row"
+        off, flat = L.transpose_indices(got.to(DEV))
+        assert int(off[..., -1].min()) == 256 * 8
+        # rows without NaN are unaffected
+        want = O.gen_sparse_indices(pq, pk, 8)
+        ok = torch.ones(1, 2, 256, dtype=torch.bool)
+        ok[0, 0, 3] = ok[0, 1, 100] = False
+        sc = (pq.float() @ pk.float().transpose(-1, -2)).to(dtype).float()
+        sc = torch.nan_to_num(sc, nan=0.0)
+        differ, bad = topk_mismatch_rows(got[ok], want[ok], sc[ok], margin=2.0 ** -7 if dtype == torch.bfloat16 else 1e-6)
+        assert bad == 0
+    # refine: a NaN level-1 query row and a parent listed twice
+    pq, pk = synth.gaussian_qkv(55, 1, 1, 1024, 64, n_tensors=2, dtype=torch.bfloat16)
+    pq[0, 0, 5] = float("nan")
+    pidx = O.gen_sparse_indices(O.mean_pool1d(pq.nan_to_num(0.0), 16), O.mean_pool1d(pk, 16), 8)
+    pidx[0, 0, 2, 1] = pidx[0, 0, 2, 0]
+    got = L.compute_topk_indices_sparse(pq.to(DEV), pk.to(DEV), pidx.to(DEV), 8, 8, 16).cpu().long()
+    assert int(got.min()) >= 0 and int(got.max()) < 1024
+    assert (got.sort(-1).values.diff(dim=-1) > 0).all(), "repeated block in a row"
+
+
+def test_out_of_range_index_is_reported_not_followed():
+    """An index outside [0, n) handed to the transpose is left out of the lists and raises under set_device_checks."""
+    L = _ops()
+    idx = torch.arange(8, dtype=torch.int32).repeat(1, 1, 64, 1)
+    idx[0, 0, 5, 3] = 9999
+    off, flat = L.transpose_indices(idx.to(DEV))
+    assert int(off[0, 0, -1]) == 64 * 8 - 1
+    L.set_device_checks(True)
+    try:
+        with pytest.raises(RuntimeError, match="outside its range"):
+            L.transpose_indices(idx.to(DEV))
+    finally:
+        L.set_device_checks(False)
+
+
+def test_bounded_wait_expiry_is_reported(monkeypatch):
+    """A bounded mbarrier wait that runs out (forced here by a poll limit of one) must not hang or trap: the kernel
+    returns, the status word carries LLSA_DEV_WAIT_EXPIRED, the operator raises under set_device_checks, and the next
+    ordinary call on the same context is correct."""
+    L = _ops()
+    from llsa_b200 import ops
+    q, k, v, do = _bf16_case("l2", 1, 1, 16384, 56)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    want = L.llsa_l2(qd, kd, vd, 8, 8, 16)
+    torch.cuda.synchronize()
+    L.set_device_checks(True)
+    monkeypatch.setattr(ops, "_wait_limit", 1)
+    try:
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            L.llsa_l2(qd, kd, vd, 8, 8, 16)
+    finally:
+        monkeypatch.setattr(ops, "_wait_limit", 0)
+        L.set_device_checks(False)
+    torch.cuda.synchronize()
+    again = L.llsa_l2(qd, kd, vd, 8, 8, 16)
+    assert torch.equal(again, want)
 
 
 @pytest.mark.parametrize("levels,N", [(1, 256), (1, 1024), (1, 2048), (2, 4096), (2, 8192)])
@@ -407,7 +547,8 @@ def test_strided_bnhd_inputs_match_contiguous(tc, monkeypatch):
     """[B,H,N,D] views of [B,N,H,D] storage (what the model passes) give the same bits; o keeps q's strides.
     tc="1": the forward's pooled stages go through the 4-D tensor map of the strided q."""
     L = _ops()
-    monkeypatch.setenv("LLSA_B200_TC", tc)
+    from llsa_b200 import ops
+    monkeypatch.setattr(ops, "_no_tcgen05", tc == "0")
     q, k, v, do = _bf16_case("l2", 2, 3, 16384, 44)
     to_view = lambda t: t.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)
     qc, kc, vc = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
@@ -523,3 +664,19 @@ def test_cfg3_full_size_properties():
     # (5) the same call twice gives the same forward bits and indices
     dbg2 = L.llsa_l2_debug(qg.detach(), kg.detach(), ones, 8, 8, 16)
     assert torch.equal(dbg2["indices"], idx) and torch.equal(dbg2["o"], dbg["o"])
+
+
+def test_cfg3_full_size_vs_oracle():
+    """BASELINE config 3 at full size (B=8, H=6, N=16384: the benchmark's launch) against the oracle, one batch element
+    of the oracle at a time: pooled tensors bit-exact, block indices bit-exact as ordered lists except rows inside the
+    tie margin (counted and printed), o / dq / dk / dv within max-abs 2e-2 and rel-L2 1e-2 of the fp32 evaluation."""
+    L = _ops()
+    q, k, v, do, _ = synth.make_config_inputs("cfg3")
+    got = _gpu_l2(L, q, k, v, do)
+    tie_rows = 0
+    for b in range(q.shape[0]):
+        sl = slice(b, b + 1)
+        tie_rows += _oracle_l2_compare(q[sl], k[sl], v[sl], do[sl], {n: t[sl] for n, t in got.items()}, label="cfg3 b=%d" % b)
+    rows = q.shape[0] * q.shape[1] * (q.shape[2] // 16 + q.shape[2] // 256)
+    print("cfg3 full size: %d of %d index rows differ from the oracle's ordered lists, all inside the tie margin" % (tie_rows, rows))
+    assert tie_rows <= rows // 1000

@@ -17,6 +17,7 @@ import pytest
 import torch
 
 from llsa_b200 import _lib
+from oracle import llsa_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -69,6 +70,10 @@ def test_noalloc_transpose_equals_regular_on_two_calls_in_a_row():
         assert torch.equal(off, want_off)
         assert torch.equal(flat, want_flat)
         assert int(off[..., -1].min()) == n_kv * 8
+        # ... and the CPU oracle's lists (indices_transpose.py:104-109, buckets ascending), so that the entry point is pinned to the
+        # reference's semantics and not only to its sibling
+        o_off, o_flat = O.transpose_indices(idx.cpu())
+        assert torch.equal(off.cpu(), o_off) and torch.equal(flat.cpu().long(), o_flat)
     # the same input again, after the other case dirtied the scratch: identical bits
     off2, flat2 = torch.empty_like(outs[0][0]), torch.empty_like(outs[0][1])
     assert _noalloc(cases[0], n_kv, off2, flat2) == 0
