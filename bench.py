@@ -259,6 +259,10 @@ def main():
     B, H, N, D = args.batch or cfg["B"], cfg["H"], cfg["N"], cfg["D"]
     fn = llsa_b200.llsa_l2 if cfg["op"] == "llsa_l2" else llsa_b200.llsa_l1
     call = (lambda q, k, v: fn(q, k, v, 8, 8, 16)) if cfg["op"] == "llsa_l2" else (lambda q, k, v: fn(q, k, v, 8, 16))
+    if cfg["rope"]:      # the model's 2-D RoPE on q and k, fused into the pooling pass (rope_dit_transformer_2d.py:232-241)
+        import math
+        table = synth.rope_table_2d(int(round(math.sqrt(N))), dtype=cfg["dtype"]).to(dev)
+        call = lambda q, k, v: llsa_b200.llsa_l1_rope(q, k, v, table, 8, 16)
 
     seq_parallel = B * H < world or args.seq_parallel          # too few (b,h) slices to go round: shard the sequence
     full = synth.correlated_qkv(cfg["seed"], B, H, N, D, dtype=cfg["dtype"])          # the ONE workload, the same on every rank
@@ -329,10 +333,13 @@ def main():
             per[name] = per.get(name, 0.0) + ev.elapsed_time(nxt)
     per = {kname: max(tms, 0.0) / args.steps for kname, tms in per.items()}    # a stage moved to a side stream shows ~0 here
     units = n_slices * (N // world if seq_parallel else N) * D      # query rows x channels on this rank
-    keys = dict(fine=128, p1=128, p2=N // 256 if N // 256 >= 64 else 0)
+    if cfg["op"] == "llsa_l2":
+        keys = dict(fine=128, p1=128, p2=N // 256 if N // 256 >= 64 else 0)
+    else:
+        keys = dict(fine=128, p1=N // 16 if N // 16 >= 64 else 0, p2=0)
     ktot = sum(keys.values())
     pooled = keys["p1"] + keys["p2"]
-    if N // 256 == 64:      # tcgen05 pooled backward: S, dP, dQ, dPK, dPV of the pooled keys in one kernel; the dQ kernel is fine-only
+    if cfg["op"] == "llsa_l2" and N // 256 == 64:      # tcgen05 pooled backward: S, dP, dQ, dPK, dPV of the pooled keys in one kernel; the dQ kernel is fine-only
         flops = dict(attn_fwd=4 * units * ktot, attn_bwd_dq=6 * units * keys["fine"], attn_bwd_dkv_fine=4 * units * keys["fine"],
                      attn_bwd_dkv_pooled=10 * units * pooled)
     else:
@@ -361,9 +368,9 @@ def main():
                                 frac_of_hbm_peak=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9 / peaks["hbm_gbs"])
                     for kname in alg_bytes if per.get(kname, 0.0) > 1e-4}
 
-    out = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+    out = dict(metric=METRIC if args.config == "cfg3" else "%s fwd+bwd tokens/sec (%s)" % (cfg["op"], args.config), value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
-               config=dict(workload="%s: %s fwd+bwd bf16 B=%d H=%d N=%d D=%d block=16 topk=8/8, ONE problem split over %d GPU(s)" % (
+               config=dict(workload="%s: %s fwd+bwd bf16 B=%d H=%d N=%d D=%d block=16 topk=8, ONE problem split over %d GPU(s)" % (
                                args.config, cfg["op"], B, H, N, D, world),
                            inputs="N(0,1) + 0.5*low-frequency 2-D field, Morton order, seed %d" % cfg["seed"],
                            slices_per_gpu=n_slices,

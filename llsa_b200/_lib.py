@@ -35,7 +35,7 @@ class LlsaAttnArgs(C.Structure):
         ("dpk_acc", _P), ("dpv_acc", _P), ("dpk2_acc", _P), ("dpv2_acc", _P),
         ("fold_pool_bwd", C.c_int32), ("kv_weight", C.c_float), ("kv_weight_2", C.c_float),
         ("force_generic", C.c_int32), ("stage_mask", C.c_int32), ("dkv_partial", _P),
-        ("fine_pds", _P), ("flat_pairs", _P), ("no_tcgen05", C.c_int32), ("wait_limit", C.c_int32), ("status", C.c_void_p),
+        ("fine_pds", _P), ("flat_pairs", _P), ("flat_ranges", _P), ("no_tcgen05", C.c_int32), ("wait_limit", C.c_int32), ("status", C.c_void_p),
     ]
 
 
@@ -69,7 +69,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.llsa_transpose_indices_noalloc.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_void_p]
     lib.llsa_attn_bwd_partial_elems.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32]
     lib.llsa_attn_bwd_partial_elems.restype = C.c_int64
-    lib.llsa_transpose_indices_pairs.argtypes = [TP, TP, TP, TP, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+    lib.llsa_transpose_indices_pairs.argtypes = [TP, TP, TP, TP, TP, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     lib.llsa_attn_bwd_pds_elems.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int32]
     lib.llsa_attn_bwd_pds_elems.restype = C.c_int64
     lib.llsa_status_check.argtypes = [C.c_int32]

@@ -62,7 +62,7 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
     if ((rc = check_contig(g->dpv_acc, "dpv_acc", LLSA_F32, 4, s1))) return rc;
     if (dt == LLSA_BF16 && !g->force_generic) {
       LLSA_REQUIRE(g->dkv_partial, LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial scratch missing");
-      const int64_t need = B * H * ((nq1 * g->topk + 127) / 128) * 4096;
+      const int64_t need = B * H * ((nq1 * g->topk + kRangeEntries - 1) / kRangeEntries) * 4096;
       LLSA_REQUIRE(g->dkv_partial->ptr && g->dkv_partial->dtype == LLSA_F32 && g->dkv_partial->ndim == 4 && is_contiguous(g->dkv_partial) &&
                        g->dkv_partial->shape[0] * g->dkv_partial->shape[1] * g->dkv_partial->shape[2] * g->dkv_partial->shape[3] >= need,
                    LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial must be a contiguous F32 tensor of at least %lld elements", (long long) need);
@@ -76,8 +76,10 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
       for (int i = 0; i < g->fine_pds->ndim; ++i) have *= g->fine_pds->shape[i];
       LLSA_REQUIRE(have >= need && ((uintptr_t) g->fine_pds->ptr % 16) == 0, LLSA_ERR_WORKSPACE,
                    "attn_bwd: fine_pds holds %lld elements, %lld needed", (long long) have, (long long) need);
-      LLSA_REQUIRE(g->flat_pairs, LLSA_ERR_WORKSPACE, "attn_bwd: flat_pairs missing (llsa_transpose_indices_pairs)");
+      LLSA_REQUIRE(g->flat_pairs && g->flat_ranges, LLSA_ERR_WORKSPACE, "attn_bwd: flat_pairs / flat_ranges missing (llsa_transpose_indices_pairs)");
       if ((rc = check_contig(g->flat_pairs, "flat_pairs", LLSA_I32, 3, sf))) return rc;
+      const int64_t sr[4] = {B, H, (nq1 * g->topk + kRangeEntries - 1) / kRangeEntries, 2};
+      if ((rc = check_contig(g->flat_ranges, "flat_ranges", LLSA_I32, 4, sr))) return rc;
     }
     if (two) {
       LLSA_REQUIRE(g->dpk2_acc && g->dpv2_acc, LLSA_ERR_NULL, "attn_bwd: dpk2_acc / dpv2_acc missing");
@@ -94,7 +96,7 @@ using namespace llsa;
 
 extern "C" int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {
   if (B <= 0 || H <= 0 || Nq <= 0 || topk <= 0) return 0;
-  return B * H * ((Nq / kBS * topk + 127) / 128) * 4096;
+  return B * H * ((Nq / kBS * topk + kRangeEntries - 1) / kRangeEntries) * 4096;
 }
 
 extern "C" int64_t llsa_attn_bwd_pds_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {

@@ -28,6 +28,7 @@ struct TransposeArgs {
   int off64;
   int32_t* flat;    // [BH, M*T]
   int32_t* pairs;   // [BH, M*T] or nullptr: entry position m*T + t in the order of `flat`
+  int2* ranges;     // [BH, ceil(M*T / 32)] or nullptr: (first entry, its bucket) of the work ranges cut for the dK/dV kernel
   int64_t E;        // entries per head
   int T;
   int64_t n_kv;
@@ -126,8 +127,15 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
     else reinterpret_cast<int32_t*>(a.offsets)[bh * (n + 1) + n] = carry;
   }
   __syncthreads();
+  // ranges that lie wholly behind the last entry (entries were dropped, or E is not a multiple of 32) are empty
+  if (a.ranges) {
+    const int64_t R = (E + kRangeEntries - 1) / kRangeEntries;
+    for (int64_t r = threadIdx.x; r < R; r += blockDim.x)
+      if (r * kRangeEntries >= carry) a.ranges[bh * R + r] = make_int2(carry, (int) n - 1);
+  }
 
   // ---- 3: stable fill
+  const int total_entries = carry;          // every thread ran the same scan: entries that were kept
   for (int64_t e0 = seg0; e0 < seg1; e0 += 32) {
     const int64_t e = e0 + lane;
     bool valid = e < seg1;
@@ -143,6 +151,14 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
       if (pos < E) {
         a.flat[bh * E + pos] = (int32_t) (e / a.T);
         if (a.pairs) a.pairs[bh * E + pos] = (int32_t) e;
+        // Work ranges of the dK/dV kernel: nominally 32 entries each, but a bucket of at most 32 entries is never cut --
+        // the range that would begin inside it begins at the bucket's first entry instead (ranges then hold 1..63
+        // entries); only longer buckets are cut, at multiples of 32.  The entry that lands on a multiple of 32 knows
+        // its bucket and that bucket's extent.
+        if (a.ranges && pos % kRangeEntries == 0) {
+          const int b0 = base[key], b1 = key + 1 < n ? base[key + 1] : total_entries;
+          a.ranges[bh * ((E + kRangeEntries - 1) / kRangeEntries) + pos / kRangeEntries] = make_int2(b1 - b0 <= kRangeEntries ? b0 : pos, (int) key);
+        }
       }
     }
     __syncwarp();
@@ -180,8 +196,8 @@ extern "C" size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, 
   return global ? (size_t) B * H * 32 * n_kv * 2 : 0;
 }
 
-static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs, int64_t n_kv,
-                          void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs,
+                          const LlsaTensor* ranges, int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
   LLSA_REQUIRE(idx && offsets && flat && idx->ptr && offsets->ptr && flat->ptr, LLSA_ERR_NULL, "transpose_indices: null tensor");
   LLSA_REQUIRE(idx->ndim == 4, LLSA_ERR_SHAPE, "transpose_indices: idx must be [B,H,M,T]");
   const int64_t B = idx->shape[0], H = idx->shape[1], M = idx->shape[2], T = idx->shape[3];
@@ -196,6 +212,8 @@ static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, cons
   if ((rc = check_contig(offsets, "offsets", offsets->dtype, 3, so))) return rc;
   if ((rc = check_contig(flat, "flat", LLSA_I32, 3, sf))) return rc;
   if (pairs && (rc = check_contig(pairs, "pairs", LLSA_I32, 3, sf))) return rc;
+  const int64_t sr[4] = {B, H, (E + kRangeEntries - 1) / kRangeEntries, 2};
+  if (ranges && (rc = check_contig(ranges, "ranges", LLSA_I32, 4, sr))) return rc;
   // the per-key prefixes over the segments are 16-bit: with distinct keys inside a row a key occurs at most M times per head
   LLSA_REQUIRE(M <= 65535, LLSA_ERR_SHAPE, "transpose_indices: M=%lld query blocks per head exceed the supported 65535", (long long) M);
   if (B * H == 0) return LLSA_OK;
@@ -209,6 +227,7 @@ static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, cons
   a.off64 = offsets->dtype == LLSA_I64;
   a.flat = (int32_t*) flat->ptr;
   a.pairs = pairs ? (int32_t*) pairs->ptr : nullptr;
+  a.ranges = ranges ? (int2*) ranges->ptr : nullptr;
   a.E = E;
   a.T = (int) T;
   a.n_kv = n_kv;
@@ -228,13 +247,14 @@ static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, cons
 
 extern "C" int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, int64_t n_kv,
                                       void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
-  return transpose_impl(idx, offsets, flat, nullptr, n_kv, scratch, scratch_bytes, status, stream);
+  return transpose_impl(idx, offsets, flat, nullptr, nullptr, n_kv, scratch, scratch_bytes, status, stream);
 }
 
 extern "C" int llsa_transpose_indices_pairs(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs,
-                                            int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
-  LLSA_REQUIRE(pairs && pairs->ptr, LLSA_ERR_NULL, "transpose_indices_pairs: null pairs tensor");
-  return transpose_impl(idx, offsets, flat, pairs, n_kv, scratch, scratch_bytes, status, stream);
+                                            const LlsaTensor* ranges, int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status,
+                                            void* stream) {
+  LLSA_REQUIRE(pairs && pairs->ptr && ranges && ranges->ptr, LLSA_ERR_NULL, "transpose_indices_pairs: null pairs / ranges tensor");
+  return transpose_impl(idx, offsets, flat, pairs, ranges, n_kv, scratch, scratch_bytes, status, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -315,6 +335,7 @@ extern "C" int llsa_transpose_indices_noalloc(const LlsaTensor* idx, const LlsaT
   a.off64 = offsets->dtype == LLSA_I64;
   a.flat = (int32_t*) flat->ptr;
   a.pairs = nullptr;
+  a.ranges = nullptr;
   a.E = E;
   a.T = (int) T;
   a.n_kv = n_kv;

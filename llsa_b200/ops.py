@@ -342,6 +342,7 @@ def _transpose(idx: torch.Tensor, k_ntx: int, offsets_dtype, want_pairs: bool):
     offsets = torch.empty((B, H, k_ntx + 1), device=idx.device, dtype=offsets_dtype)
     lists = torch.empty((2 if want_pairs else 1, B, H, M * T), device=idx.device, dtype=torch.int32)
     flat, pairs = lists[0], (lists[1] if want_pairs else None)
+    ranges = torch.empty((B, H, (M * T + 31) // 32, 2), device=idx.device, dtype=torch.int32) if want_pairs else None
     status = _new_status(idx.device)
     _mark("transpose_indices")
     with torch.cuda.device(idx.device):
@@ -352,11 +353,11 @@ def _transpose(idx: torch.Tensor, k_ntx: int, offsets_dtype, want_pairs: bool):
         st = C.c_void_p(status.data_ptr()) if status is not None else None
         a, b, c = desc(idx), desc(offsets), desc(flat)
         if want_pairs:
-            d = desc(pairs)
-            _lib.check(L.llsa_transpose_indices_pairs(ref(a), ref(b), ref(c), ref(d), k_ntx, sp, nbytes, st, _stream(idx)), "transpose_indices")
+            d, e = desc(pairs), desc(ranges)
+            _lib.check(L.llsa_transpose_indices_pairs(ref(a), ref(b), ref(c), ref(d), ref(e), k_ntx, sp, nbytes, st, _stream(idx)), "transpose_indices")
         else:
             _lib.check(L.llsa_transpose_indices(ref(a), ref(b), ref(c), k_ntx, sp, nbytes, st, _stream(idx)), "transpose_indices")
-    return offsets, flat, pairs, status
+    return offsets, flat, (pairs, ranges), status
 
 
 def transpose_indices(q_topk_indices: torch.Tensor, k_ntx: Optional[int] = None, offsets_dtype=torch.int64):
@@ -450,9 +451,9 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
     if side is not None:
         side.wait_stream(cur)
         with torch.cuda.stream(side):
-            offsets, flat, pairs, t_status = _transpose(indices, n_kv, torch.int32, tensor_core)
+            offsets, flat, (pairs, ranges), t_status = _transpose(indices, n_kv, torch.int32, tensor_core)
     else:
-        offsets, flat, pairs, t_status = _transpose(indices, n_kv, torch.int32, tensor_core)
+        offsets, flat, (pairs, ranges), t_status = _transpose(indices, n_kv, torch.int32, tensor_core)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     # every scratch tensor of the call comes out of ONE allocation; the fp32 pooled-gradient accumulators sit back to back in
     # it (the library clears them with one memset)
@@ -472,7 +473,7 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
     a.status = status.data_ptr() if status is not None else None
     extra = dict(d_o=desc(do), dq=desc(dq), dk=desc(dk), dv=desc(dv), offsets=desc(offsets), flat=desc(flat), delta=desc(delta),
                  dpk_acc=desc(dpk), dpv_acc=desc(dpv), dpk2_acc=desc(dpk2), dpv2_acc=desc(dpv2), dkv_partial=desc(ws.get("partial")),
-                 fine_pds=desc(ws.get("pds")), flat_pairs=desc(pairs))
+                 fine_pds=desc(ws.get("pds")), flat_pairs=desc(pairs), flat_ranges=desc(ranges))
     for name, d in extra.items():
         setattr(a, name, ptr(d))
     a.fold_pool_bwd = 1 if fold else 0
@@ -480,7 +481,7 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
 
     def join_side():
         cur.wait_stream(side)                 # the CSR is ready; its memory now also belongs to this stream
-        for t in (offsets, flat) + ((pairs,) if pairs is not None else ()):
+        for t in (offsets, flat) + ((pairs, ranges) if pairs is not None else ()):
             t.record_stream(cur)
 
     with torch.cuda.device(q.device):
