@@ -124,10 +124,11 @@ int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, con
  * indices_transpose.py:70-78):
  *   pairs  [B,H,M*T] (I32): in the order of `flat`, the position m*T + t of each entry inside its head's idx
  *          (flat = pairs / T); finds what the query-major stage left for each (query block, selected block) pair;
- *   ranges [B,H,ceil(M*T/32),2] (I32): the entry list cut into the work ranges of the dK/dV kernel, (first entry,
- *          bucket of that entry) per range.  Range r nominally starts at entry 32 r; where that entry lies inside a
- *          bucket of at most 32 entries the range starts at the bucket's first entry instead, so that only longer
- *          buckets are ever split (at multiples of 32).  Range r ends where range r+1 starts. */
+ *   ranges [B,H,ceil(M*T/S),2] (I32), S = llsa_transpose_range_entries(): the entry list cut into the work ranges of
+ *          the dK/dV kernel, (first entry, bucket of that entry) per range.  Range r nominally starts at entry S r;
+ *          where that entry lies inside a bucket of at most S entries the range starts at the bucket's first entry
+ *          instead, so that only longer buckets are ever split (at multiples of S).  Range r ends where r+1 starts. */
+int llsa_transpose_range_entries(void);
 int llsa_transpose_indices_pairs(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs,
                                  const LlsaTensor* ranges, int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status,
                                  void* stream);
@@ -196,9 +197,9 @@ typedef struct LlsaAttnArgs {
                                   (lets a caller time the kernels separately, or build the CSR
                                   on another stream while 1 and 2 run) */
   const LlsaTensor* dkv_partial; /* backward, bf16 tensors only: F32 scratch
-                                  [B,H,ceil(N/16*topk/32),4096] for dK/dV tiles of KV blocks whose
-                                  list of query blocks is split over several work ranges (not read
-                                  before it is written; may be NULL for f32 tensors) */
+                                  of llsa_attn_bwd_partial_elems() elements for dK/dV tiles of KV
+                                  blocks whose list of query blocks is split over several CTAs (not
+                                  read before it is written; may be NULL for f32 tensors) */
   const LlsaTensor* fine_pds;  /* backward, bf16 tensors only: F32-typed scratch of
                                   llsa_attn_bwd_pds_elems() elements.  The dQ stage (stage_mask 1)
                                   leaves P and dS (bf16) of every (query block, selected block) pair
@@ -206,7 +207,7 @@ typedef struct LlsaAttnArgs {
                                   recomputing both from q, k, v, lse and delta */
   const LlsaTensor* flat_pairs;/* backward, bf16 tensors only: I32 [B,H,N/16*topk], the `pairs` list of
                                   llsa_transpose_indices_pairs for the same CSR as offsets / flat */
-  const LlsaTensor* flat_ranges;/* backward, bf16 tensors only: I32 [B,H,ceil(N/16*topk/32),2], the `ranges`
+  const LlsaTensor* flat_ranges;/* backward, bf16 tensors only: I32 [B,H,ceil(N/16*topk/S),2], the `ranges`
                                   list of the same call */
   int32_t no_tcgen05;          /* 1: keep the pooled-key stages on the mma.sync kernels (the form used
                                   for shapes the tcgen05 kernels do not cover); for cross-checks */

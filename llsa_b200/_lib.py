@@ -43,7 +43,7 @@ EXPORTS = [
     "llsa_version", "llsa_last_error_string", "llsa_mean_pool_fwd", "llsa_mean_pool_bwd", "llsa_pool_pyramid_fwd",
     "llsa_rope_pool_pyramid_fwd",
     "llsa_rope_fwd", "llsa_rope_bwd", "llsa_coarse_topk", "llsa_refine_topk", "llsa_transpose_scratch_bytes",
-    "llsa_transpose_indices", "llsa_transpose_indices_pairs", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd",
+    "llsa_transpose_indices", "llsa_transpose_indices_pairs", "llsa_transpose_range_entries", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd",
     "llsa_attn_bwd_partial_elems", "llsa_attn_bwd_pds_elems", "llsa_status_check",
 ]
 

@@ -62,7 +62,7 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
     if ((rc = check_contig(g->dpv_acc, "dpv_acc", LLSA_F32, 4, s1))) return rc;
     if (dt == LLSA_BF16 && !g->force_generic) {
       LLSA_REQUIRE(g->dkv_partial, LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial scratch missing");
-      const int64_t need = B * H * ((nq1 * g->topk + kRangeEntries - 1) / kRangeEntries) * 4096;
+      const int64_t need = llsa_attn_bwd_partial_elems(B, H, Nq, g->topk);
       LLSA_REQUIRE(g->dkv_partial->ptr && g->dkv_partial->dtype == LLSA_F32 && g->dkv_partial->ndim == 4 && is_contiguous(g->dkv_partial) &&
                        g->dkv_partial->shape[0] * g->dkv_partial->shape[1] * g->dkv_partial->shape[2] * g->dkv_partial->shape[3] >= need,
                    LLSA_ERR_WORKSPACE, "attn_bwd: dkv_partial must be a contiguous F32 tensor of at least %lld elements", (long long) need);
@@ -96,7 +96,8 @@ using namespace llsa;
 
 extern "C" int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {
   if (B <= 0 || H <= 0 || Nq <= 0 || topk <= 0) return 0;
-  return B * H * ((Nq / kBS * topk + kRangeEntries - 1) / kRangeEntries) * 4096;
+  const int64_t ranges = (Nq / kBS * topk + kRangeEntries - 1) / kRangeEntries;
+  return B * H * ((ranges + 3) / 4) * 4096;          // a head and a tail tile (2048 floats each) per CTA of four ranges
 }
 
 extern "C" int64_t llsa_attn_bwd_pds_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {

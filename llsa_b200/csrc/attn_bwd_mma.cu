@@ -412,10 +412,10 @@ __global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16>
 // ---- fine dK/dV: ranges of the CSR entry list, whatever the fan-in ------------------------------
 // The CSR of a head lists, bucket after bucket (KV block after KV block), the query blocks that selected each KV
 // block.  Fan-in is very uneven (0 ... >150 on correlated inputs), so the work is cut by ENTRIES, not by buckets: the
-// index transpose cuts the list into ranges of nominally 32 entries, one per warp, moving a cut that would fall inside
-// a bucket of at most 32 entries to that bucket's start.  Most buckets are therefore finished by one warp; a longer
-// bucket is cut at multiples of 32 and its pieces meet in the `partial` scratch, added in range order by the finish
-// kernel.  No atomics: the result is bit-reproducible; no warp waits for another.
+// index transpose cuts the list into ranges of nominally kRangeEntries entries, one per warp, moving a cut that would
+// fall inside a bucket of at most kRangeEntries entries to that bucket's start.  Most buckets are therefore finished
+// by one warp; longer ones are cut at multiples of kRangeEntries and their pieces meet in shared memory (same CTA) or
+// in the `partial` scratch (summed in window order by the finish kernel).  No atomics: bit-reproducible.
 constexpr int kTileFloats = 64 * 32;            // a parked dK + dV tile pair: 64 accumulators x 32 lanes
 
 __device__ __forceinline__ int64_t csr_off(const AttnP<bf16>& a, int64_t bh, int64_t j) {
@@ -463,19 +463,22 @@ __device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) 
 // sparse_attention_res_2.py:371-415, the dK/dV half of _attn_bwd_res_dqkv).  P and dS are NOT recomputed here: the dQ
 // stage has left them, already transposed into A-operand registers, in `pds` (store_pds), so an entry costs two
 // 512-byte loads, the Q and dO tiles of its query block and 16 MMAs; K, V, lse and delta are not touched.
-//   * The Q / dO tiles come through a per-warp cp.async ring of kRingFineStages stages, two entries ahead, and are
+//   * The Q / dO tiles come through a per-warp cp.async ring of kRingFineStages stages, three entries ahead, and are
 //     read with ldmatrix.trans (the B operand of a contraction over the tile's 16 rows).
-//   * The P^T / dS^T registers of the entry two ahead are requested with plain 128-bit loads into a rotating set
-//     of register buffers.  13 KB of shared memory per warp: sixteen warps per SM.
-//   * A warp owns one range of the entry list (cut by the index transpose so that buckets of up to 32 entries are
-//     never split) and waits for no other warp; the pieces of longer buckets go to the `partial` scratch and
-//     attn_dkv_finish_ld_kernel adds them in range order.
+//   * The P^T / dS^T registers of the entry three ahead are requested with plain 128-bit loads into a rotating set
+//     of register buffers (two CTAs of four warps per SM leave 255 registers per thread).
+//   * A warp owns one range of the entry list, a CTA four consecutive ranges (its window).  The index transpose cuts
+//     the ranges so that a bucket of up to kRangeEntries entries is never split and hands over each range's first
+//     bucket, so a warp starts without a search.  A longer bucket is cut at multiples of kRangeEntries: a warp parks
+//     the tile of a bucket it shares with EARLIER warps in its shared-memory slot; the tile it shares with later warps
+//     stays in its accumulators until the CTA has synchronised and is then completed from their slots; pieces of
+//     buckets that straddle windows go to the `partial` scratch and attn_dkv_finish_ld_kernel adds them in window order.
 //   * The pooled-gradient rows a finished tile folds in (the pooling backward) are requested into registers when
 //     the bucket begins and parked in shared memory right before the store.
 // Accumulator layout (ldmatrix): tile u holds channels 8u + 2t, 8u + 2t + 1 of keys g (c0, c1) and g + 8 (c2, c3).
-constexpr int kRingWarps = 4;                   // warps per CTA, each on its own range
-constexpr int kRingCtasPerSm = 4;               // 13 KB of shared memory per warp, at most 128 registers per thread
-constexpr int kRingFineStages = 3;
+constexpr int kRingWarps = 4;                   // warps per CTA, each on its own range; two CTAs per SM
+constexpr int kRingFineStages = 4;
+constexpr int kFineWindow = kRingWarps * kRangeEntries;      // nominal entries per CTA
 constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16);           // Q tile, dO tile
 constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
 
@@ -579,30 +582,31 @@ __device__ __forceinline__ void dkv_fine_store_staged(const AttnP<bf16>& a, int6
   dkv_fine_fold_smem(a, sa_fold, dk, dv);
   dkv_tile_store_staged<SB>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
 }
-__global__ void __launch_bounds__(kRingWarps * 32, kRingCtasPerSm) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
+__global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(AttnP<bf16> a, float* __restrict__ partial) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // the swizzle arithmetic below works on absolute shared addresses: start at a 128-byte boundary (the launch adds 128 bytes)
   unsigned char* smem = smem_raw + ((128u - ((uint32_t) __cvta_generic_to_shared(smem_raw) & 127u)) & 127u);
+  float* slots = reinterpret_cast<float*>(smem);            // [kRingWarps][kTileFloats]: tile of the bucket a warp shares with earlier warps
+  __shared__ int s_head_bucket[kRingWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
   // per warp: the ring stages, then its copy of the pooled-gradient rows the current bucket folds in (4 rows x 256 bytes)
   constexpr int kWarpBytes = kRingFineStages * kRingFineStageBytes + kRingFoldBytes;
   constexpr int kFoldOff = kRingFineStages * kRingFineStageBytes;
-  unsigned char* ring = smem + warp * kWarpBytes;
+  unsigned char* ring = smem + kRingWarps * kTileFloats * sizeof(float) + warp * kWarpBytes;
   const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const int E = (int) (a.nq1 * a.topk), n1 = (int) a.n1;
   const int R = (E + kRangeEntries - 1) / kRangeEntries;
-  const int r = blockIdx.x * kRingWarps + warp;           // this warp's range; warps never wait for one another
-  if (r >= R) return;
   // entries the CSR really holds: fewer than E when the transpose dropped out-of-range indices; ranges and offsets handed in
   // by a caller are not trusted further than these clamps and the bounds on the bucket walk below
   const int E_used = (int) min((int64_t) E, max((int64_t) 0, csr_off(a, bh, n1)));
-  const int2 r0 = __ldcg(a.ranges + bh * R + r);
-  const int rb = min(max(r0.x, 0), E_used);
-  const int re = r + 1 < R ? min(max(__ldcg(a.ranges + bh * R + r + 1).x, rb), E_used) : E_used;
-  const int n = min(re - rb, 2 * kRangeEntries);          // 1..63 entries for ranges cut by the transpose kernel
-  if (n <= 0) return;
+  auto cut = [&](int r) { return r < R ? min(max(__ldcg(&a.ranges[bh * R + r].x), 0), E_used) : E_used; };
+  const int r = blockIdx.x * kRingWarps + warp;           // this warp's range; the CTA's window is its four ranges
+  const int cb = cut(blockIdx.x * kRingWarps), ce = max(cut((blockIdx.x + 1) * kRingWarps), cb);
+  const int rb = min(max(cut(r), cb), ce), re = min(max(cut(r + 1), rb), ce);
   const int32_t* fl = a.flat + bh * (int64_t) E;
   const int32_t* pr = a.pairs + bh * (int64_t) E;
+  if (threadIdx.x < kRingWarps) s_head_bucket[threadIdx.x] = -1;
+  __syncthreads();
 
   // Per-lane shared addresses, computed once (the ring is 128-byte aligned, so the chunk index of an address is its bits 4..6
   // and a swizzle partner is one XOR away):
@@ -619,131 +623,159 @@ __global__ void __launch_bounds__(kRingWarps * 32, kRingCtasPerSm) attn_dkv_fine
 #pragma unroll
     for (int c = 0; c < 4; ++c) sa_m[c] = base ^ (c << 5);
   }
-  // first bucket of the range (handed over by the transpose kernel; clamped, and moved on if it does not hold rb)
-  int j = min(max(r0.y, 0), n1 - 1);
-  int bo = (int) csr_off(a, bh, j), nxt = (int) csr_off(a, bh, j + 1);
-  while (nxt <= rb && j + 1 < n1) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }
-  int nxt2 = j + 2 <= n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;      // one bucket ahead: no load to wait for at a switch
-  // the pooled-gradient rows the bucket's store folds in: lanes 0..15 hold the dpk row, lanes 16..31 the dpv row (16 bytes each)
-  uint4 f1 = make_uint4(0u, 0u, 0u, 0u), f2 = make_uint4(0u, 0u, 0u, 0u);
-  auto load_fold = [&](int jj) {
-    if (a.fold) {
-      f1 = __ldcg(reinterpret_cast<const uint4*>((lane < 16 ? a.dpk : a.dpv) + (bh * a.n1 + jj) * kD + (lane & 15) * 4));
-      if (a.two_level) f2 = __ldcg(reinterpret_cast<const uint4*>((lane < 16 ? a.dpk2 : a.dpv2) + (bh * a.n2 + jj / kBS) * kD + (lane & 15) * 4));
-    }
-  };
-  auto park_fold = [&]() {
-    if (a.fold) {
-      sts128<kFoldOff>(sa_l16, f1);
-      if (a.two_level) sts128<kFoldOff + 512>(sa_l16, f2);
-    }
-    __syncwarp();
-  };
-  // global side: row (lane/8), chunk (lane%8) of block 0; a block is qblk / dblk bytes further, four rows qstep / dstep bytes
-  const char* q_lane = reinterpret_cast<const char*>(a.q.row(b, h, lane >> 3) + (lane & 7) * 8);
-  const char* d_lane = reinterpret_cast<const char*>(a.d_o.row(b, h, lane >> 3) + (lane & 7) * 8);
-  const int qblk = (int) (kBS * a.q.sn * sizeof(bf16)), dblk = (int) (kBS * a.d_o.sn * sizeof(bf16));
-  const int qstep = (int) (4 * a.q.sn * sizeof(bf16)), dstep = (int) (4 * a.d_o.sn * sizeof(bf16));
-  // lane i: query block and pair number of entries rb + i and rb + 32 + i (clamped: nothing is read outside the tensors)
-  int my_qb[2] = {0, 0}, my_pair[2] = {0, 0};
-#pragma unroll
-  for (int u = 0; u < 2; ++u)
-    if (lane + 32 * u < n) {
-      int qb = __ldcg(fl + rb + 32 * u + lane), pair = __ldcg(pr + rb + 32 * u + lane);
-      my_qb[u] = qb < 0 ? 0 : (qb >= (int) a.nq1 ? (int) a.nq1 - 1 : qb);
-      my_pair[u] = pair < 0 ? 0 : (pair >= E ? E - 1 : pair);
-    }
-  const uint4* pds_lane = a.pds + bh * (int64_t) E * 64 + lane;
-  uint4 pP[kRingFineStages], pD[kRingFineStages];         // P^T / dS^T registers of the entries in flight
-  auto issue = [&](auto stage_tag, int i) {
-    constexpr int ST = decltype(stage_tag)::value;
-    constexpr int SB = ST * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
-    const int qb = __shfl_sync(0xffffffffu, i < 32 ? my_qb[0] : my_qb[1], i & 31);
-    const int pair = __shfl_sync(0xffffffffu, i < 32 ? my_pair[0] : my_pair[1], i & 31);
-    const char* qp = q_lane + (int64_t) qb * qblk;
-    const char* dp = d_lane + (int64_t) qb * dblk;
-    cp_async16_sa<SB>(sa_cp0, qp);
-    cp_async16_sa<SB + 512>(sa_cp1, qp + qstep);
-    cp_async16_sa<SB + 1024>(sa_cp0, qp + 2 * qstep);
-    cp_async16_sa<SB + 1536>(sa_cp1, qp + 3 * qstep);
-    cp_async16_sa<SB + TB>(sa_cp0, dp);
-    cp_async16_sa<SB + TB + 512>(sa_cp1, dp + dstep);
-    cp_async16_sa<SB + TB + 1024>(sa_cp0, dp + 2 * dstep);
-    cp_async16_sa<SB + TB + 1536>(sa_cp1, dp + 3 * dstep);
-    const uint4* pp = pds_lane + (int64_t) pair * 64;
-    pP[ST] = __ldcg(pp);
-    pD[ST] = __ldcg(pp + 32);
-  };
-  static_assert(kRingFineStages == 3, "the entry loop below is unrolled over three stages");
-  if (0 < n) issue(std::integral_constant<int, 0>{}, 0);
-  cp_async_commit();
-  if (1 < n) issue(std::integral_constant<int, 1>{}, 1);
-  cp_async_commit();
-  load_fold(j);
   float dk[8][4], dv[8][4];
-  tile_zero(dk, dv);
-  // Where a finished tile goes: a bucket wholly inside the range is folded and stored; a bucket that began before the range
-  // (`head`) or runs on behind it goes, unscaled and unfolded, to the range's head / tail slot of `partial`, and the finish
-  // kernel adds the pieces in range order.
-  float* my_partial = partial + ((bh * R + r) * 2) * (int64_t) kTileFloats;
-  // one entry; the ring stage is a template argument so that every shared-memory offset below is an immediate
-  auto entry = [&](auto stage_tag, int i) {
-    constexpr int S = decltype(stage_tag)::value, SF = (S + kRingFineStages - 1) % kRingFineStages;    // SF: the stage read an entry ago
-    constexpr int SB = S * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
-    const int e = rb + i;
-    cp_async_wait_group<kRingFineStages - 2>();     // entry i has landed (this lane's chunks) ...
-    __syncwarp();                                   // ... and everybody else's; stage SF is free
-    if (e >= nxt && j + 1 < n1) {                   // next non-empty bucket; stage SF stages the store before it is refilled
-      if (bo >= rb) {
-        park_fold();
-        dkv_fine_store_staged<SF * kRingFineStageBytes>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
-      } else {
-        tile_to_mem(my_partial, dk, dv, lane);      // began in an earlier range
+  int tail_j = -1;                          // bucket whose tile is still in dk / dv after the loop
+  if (rb < re) {
+    const int n = min(re - rb, 4 * 32);     // entries of this warp: 1..127 for ranges cut by the transpose kernel
+    // lane i: query block and pair number of entries rb + i, rb + 32 + i, ... (clamped: nothing is read outside the tensors);
+    // requested first, they arrive while the bucket offsets below are being fetched
+    int my_qb[4] = {0, 0, 0, 0}, my_pair[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (lane + 32 * u < n) {
+        my_qb[u] = __ldcg(fl + rb + 32 * u + lane);
+        my_pair[u] = __ldcg(pr + rb + 32 * u + lane);
       }
-      ++j; bo = nxt; nxt = nxt2;
-      while (nxt <= e && j + 1 < n1) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }      // empty buckets
-      nxt2 = j + 2 <= n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;
-      load_fold(j);
-      tile_zero(dk, dv);
+    // first bucket of the range (handed over by the transpose kernel; clamped, and moved on if it does not hold rb)
+    int j = min(max(__ldcg(&a.ranges[bh * R + r].y), 0), n1 - 1);
+    int bo = (int) csr_off(a, bh, j), nxt = (int) csr_off(a, bh, j + 1);
+    while (nxt <= rb && j + 1 < n1) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }
+    int nxt2 = j + 2 <= n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;      // one bucket ahead: no load to wait for at a switch
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      my_qb[u] = my_qb[u] < 0 ? 0 : (my_qb[u] >= (int) a.nq1 ? (int) a.nq1 - 1 : my_qb[u]);
+      my_pair[u] = my_pair[u] < 0 ? 0 : (my_pair[u] >= E ? E - 1 : my_pair[u]);
     }
-    const uint4 P = pP[S], D = pD[S];
-    if (i + kRingFineStages - 1 < n) issue(std::integral_constant<int, SF>{}, i + kRingFineStages - 1);
+    // the pooled-gradient rows the bucket's store folds in: lanes 0..15 hold the dpk row, lanes 16..31 the dpv row (16 bytes each)
+    uint4 f1 = make_uint4(0u, 0u, 0u, 0u), f2 = make_uint4(0u, 0u, 0u, 0u);
+    auto load_fold = [&](int jj) {
+      if (a.fold) {
+        f1 = __ldcg(reinterpret_cast<const uint4*>((lane < 16 ? a.dpk : a.dpv) + (bh * a.n1 + jj) * kD + (lane & 15) * 4));
+        if (a.two_level) f2 = __ldcg(reinterpret_cast<const uint4*>((lane < 16 ? a.dpk2 : a.dpv2) + (bh * a.n2 + jj / kBS) * kD + (lane & 15) * 4));
+      }
+    };
+    auto park_fold = [&]() {
+      if (a.fold) {
+        sts128<kFoldOff>(sa_l16, f1);
+        if (a.two_level) sts128<kFoldOff + 512>(sa_l16, f2);
+      }
+      __syncwarp();
+    };
+    // global side: row (lane/8), chunk (lane%8) of block 0; a block is qblk / dblk bytes further, four rows qstep / dstep bytes
+    const char* q_lane = reinterpret_cast<const char*>(a.q.row(b, h, lane >> 3) + (lane & 7) * 8);
+    const char* d_lane = reinterpret_cast<const char*>(a.d_o.row(b, h, lane >> 3) + (lane & 7) * 8);
+    const int qblk = (int) (kBS * a.q.sn * sizeof(bf16)), dblk = (int) (kBS * a.d_o.sn * sizeof(bf16));
+    const int qstep = (int) (4 * a.q.sn * sizeof(bf16)), dstep = (int) (4 * a.d_o.sn * sizeof(bf16));
+    const uint4* pds_lane = a.pds + bh * (int64_t) E * 64 + lane;
+    uint4 pP[kRingFineStages], pD[kRingFineStages];       // P^T / dS^T registers of the entries in flight
+    auto issue = [&](auto stage_tag, int i) {
+      constexpr int ST = decltype(stage_tag)::value;
+      constexpr int SB = ST * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
+      const int u = i >> 5;
+      const int qb = __shfl_sync(0xffffffffu, u == 0 ? my_qb[0] : (u == 1 ? my_qb[1] : (u == 2 ? my_qb[2] : my_qb[3])), i & 31);
+      const int pair = __shfl_sync(0xffffffffu, u == 0 ? my_pair[0] : (u == 1 ? my_pair[1] : (u == 2 ? my_pair[2] : my_pair[3])), i & 31);
+      const char* qp = q_lane + (int64_t) qb * qblk;
+      const char* dp = d_lane + (int64_t) qb * dblk;
+      cp_async16_sa<SB>(sa_cp0, qp);
+      cp_async16_sa<SB + 512>(sa_cp1, qp + qstep);
+      cp_async16_sa<SB + 1024>(sa_cp0, qp + 2 * qstep);
+      cp_async16_sa<SB + 1536>(sa_cp1, qp + 3 * qstep);
+      cp_async16_sa<SB + TB>(sa_cp0, dp);
+      cp_async16_sa<SB + TB + 512>(sa_cp1, dp + dstep);
+      cp_async16_sa<SB + TB + 1024>(sa_cp0, dp + 2 * dstep);
+      cp_async16_sa<SB + TB + 1536>(sa_cp1, dp + 3 * dstep);
+      const uint4* pp = pds_lane + (int64_t) pair * 64;
+      pP[ST] = __ldcg(pp);
+      pD[ST] = __ldcg(pp + 32);
+    };
+    static_assert(kRingFineStages == 4, "the entry loop below is unrolled over four stages");
+    if (0 < n) issue(std::integral_constant<int, 0>{}, 0);
     cp_async_commit();
+    if (1 < n) issue(std::integral_constant<int, 1>{}, 1);
+    cp_async_commit();
+    if (2 < n) issue(std::integral_constant<int, 2>{}, 2);
+    cp_async_commit();
+    load_fold(j);
+    tile_zero(dk, dv);
+    // one entry; the ring stage is a template argument so that every shared-memory offset below is an immediate
+    auto entry = [&](auto stage_tag, int i) {
+      constexpr int S = decltype(stage_tag)::value, SF = (S + kRingFineStages - 1) % kRingFineStages;    // SF: the stage read an entry ago
+      constexpr int SB = S * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
+      const int e = rb + i;
+      cp_async_wait_group<kRingFineStages - 2>();     // entry i has landed (this lane's chunks) ...
+      __syncwarp();                                   // ... and everybody else's; stage SF is free
+      if (e >= nxt && j + 1 < n1) {                   // next non-empty bucket; stage SF stages the store before it is refilled
+        if (bo >= rb) {
+          park_fold();
+          dkv_fine_store_staged<SF * kRingFineStageBytes>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+        } else {
+          tile_to_mem(slots + warp * kTileFloats, dk, dv, lane);   // began in an earlier warp's range
+          if (lane == 0) s_head_bucket[warp] = j;
+        }
+        ++j; bo = nxt; nxt = nxt2;
+        while (nxt <= e && j + 1 < n1) { ++j; bo = nxt; nxt = (int) csr_off(a, bh, j + 1); }      // empty buckets
+        nxt2 = j + 2 <= n1 ? (int) csr_off(a, bh, j + 2) : 0x7fffffff;
+        load_fold(j);
+        tile_zero(dk, dv);
+      }
+      const uint4 P = pP[S], D = pD[S];
+      if (i + kRingFineStages - 1 < n) issue(std::integral_constant<int, SF>{}, i + kRingFineStages - 1);
+      cp_async_commit();
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r0_, r1_, r2_, r3_;
-      ldsm_x4_trans<SB + TB>(r0_, r1_, r2_, r3_, sa_m[c]);
-      mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, r0_, r1_);
-      mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, r2_, r3_);
-    }
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans<SB + TB>(r0, r1, r2, r3, sa_m[c]);
+        mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, r0, r1);
+        mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, r2, r3);
+      }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r0_, r1_, r2_, r3_;
-      ldsm_x4_trans<SB>(r0_, r1_, r2_, r3_, sa_m[c]);
-      mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, r0_, r1_);
-      mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, r2_, r3_);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans<SB>(r0, r1, r2, r3, sa_m[c]);
+        mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, r0, r1);
+        mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, r2, r3);
+      }
+    };
+    for (int i = 0; i < n; i += 4) {
+      entry(std::integral_constant<int, 0>{}, i);
+      if (i + 1 < n) entry(std::integral_constant<int, 1>{}, i + 1);
+      if (i + 2 < n) entry(std::integral_constant<int, 2>{}, i + 2);
+      if (i + 3 < n) entry(std::integral_constant<int, 3>{}, i + 3);
     }
-  };
-  for (int i = 0; i < n; i += 3) {
-    entry(std::integral_constant<int, 0>{}, i);
-    if (i + 1 < n) entry(std::integral_constant<int, 1>{}, i + 1);
-    if (i + 2 < n) entry(std::integral_constant<int, 2>{}, i + 2);
+    cp_async_wait_all();
+    __syncwarp();
+    park_fold();                            // the last bucket's gradient rows, for whichever path below stores it
+    // the last bucket of the range (the ring is idle by now)
+    if (bo >= rb && nxt <= re) {
+      dkv_fine_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+    } else if (bo < rb) {                   // the whole range lies inside one bucket that began earlier
+      tile_to_mem(slots + warp * kTileFloats, dk, dv, lane);
+      if (lane == 0) s_head_bucket[warp] = j;
+    } else {
+      tail_j = j;                           // continues in later warps (or windows): completed below
+    }
   }
-  cp_async_wait_all();
-  __syncwarp();
-  // the last bucket of the range (the ring is idle by now)
-  if (bo >= rb && nxt <= re) {
-    park_fold();
-    dkv_fine_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
-  } else {
-    tile_to_mem(my_partial + (bo < rb ? 0 : 1) * (int64_t) kTileFloats, dk, dv, lane);     // head: began earlier; tail: runs on
+  __syncthreads();
+  if (tail_j >= 0) {
+    for (int w = warp + 1; w < kRingWarps && s_head_bucket[w] == tail_j; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
+    if ((int) csr_off(a, bh, tail_j + 1) <= ce) {
+      dkv_fine_store_staged<0>(a, b, h, tail_j, dk, dv, sa_m, sa_cp0, sa_cp1, sa_fold, lane);
+    } else {                                // runs on into the next window: this window's tail slot
+      tile_to_mem(partial + ((bh * gridDim.x + blockIdx.x) * 2 + 1) * (int64_t) kTileFloats, dk, dv, lane);
+    }
+  }
+  if (warp == 0 && s_head_bucket[0] >= 0) { // began in an earlier window: this window's head slot
+    const int j0 = s_head_bucket[0];
+    tile_zero(dk, dv);
+    for (int w = 0; w < kRingWarps && s_head_bucket[w] == j0; ++w) tile_add_mem(slots + w * kTileFloats, dk, dv, lane);
+    tile_to_mem(partial + ((bh * gridDim.x + blockIdx.x) * 2 + 0) * (int64_t) kTileFloats, dk, dv, lane);
   }
 }
 
 constexpr int kFinishPerWarp = 8;
 // One warp per eight KV blocks: blocks nobody selected get their pooling-backward term alone, blocks whose bucket was cut
-// (more than kRangeEntries entries: pieces at multiples of kRangeEntries) get the sum of their pieces, in range order.
-__global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, const float* __restrict__ partial, int n_ranges) {
+// across windows of the main kernel get the sum of their pieces, in window order.
+__global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, const float* __restrict__ partial, int n_windows) {
   __shared__ __align__(1024) unsigned char s_stage[4][2 * kRingTileElems * sizeof(bf16)];      // per warp: a dK and a dV tile on their way out
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
   const int64_t j0 = ((int64_t) blockIdx.x * 4 + warp) * kFinishPerWarp, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
@@ -755,7 +787,7 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
   const int64_t E = a.nq1 * a.topk;
   const int my_bo = lane < kFinishPerWarp ? (int) min(E, max((int64_t) 0, csr_off(a, bh, jl))) : 0;
   const int my_be = lane < kFinishPerWarp ? (int) min(E, max((int64_t) my_bo, csr_off(a, bh, jl + 1))) : 1;
-  const bool need = lane < kFinishPerWarp && j0 + lane < a.n1 && (my_be == my_bo || my_be - my_bo > kRangeEntries);
+  const bool need = lane < kFinishPerWarp && j0 + lane < a.n1 && (my_be == my_bo || (my_be - my_bo > kRangeEntries && my_bo / kFineWindow != (my_be - 1) / kFineWindow));
   unsigned todo = __ballot_sync(0xffffffffu, need);
   if (!todo) return;
   const uint32_t st_sa = (uint32_t) __cvta_generic_to_shared(s_stage[warp]);
@@ -774,10 +806,11 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
     float dk[8][4], dv[8][4];
     tile_zero(dk, dv);
     if (be > bo) {
-      // the first piece is the tail of the range that holds entry bo, every later piece the head of its range
-      const int c_first = bo / kRangeEntries, c_last = min((be - 1) / kRangeEntries, n_ranges - 1);
+      // a bucket of more than kRangeEntries entries is cut at multiples of kRangeEntries only, so its pieces by windows lie
+      // between multiples of kFineWindow: the first is the tail of the window that holds entry bo, every later one a head
+      const int c_first = bo / kFineWindow, c_last = min((be - 1) / kFineWindow, n_windows - 1);
       for (int c = c_first; c <= c_last; ++c)
-        tile_add_mem_batched(partial + ((bh * n_ranges + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
+        tile_add_mem_batched(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
     }
     dkv_fine_fold_ld(a, bh, j, dk, dv, t);
     dkv_tile_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
@@ -846,13 +879,13 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   }
   if (mask & 4) {
     const int64_t E = a.nq1 * a.topk;
-    const int n_ranges = (int) ((E + kRangeEntries - 1) / kRangeEntries);
+    const int n_ranges = (int) ((E + kRangeEntries - 1) / kRangeEntries), n_windows = (n_ranges + kRingWarps - 1) / kRingWarps;
     float* partial = (float*) g->dkv_partial->ptr;
-    const size_t smem = (size_t) kRingWarps * (kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: ring, gradient rows
+    const size_t smem = (size_t) kRingWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
     LLSA_SMEM_LIMIT((attn_dkv_fine_ring_kernel), smem);
-    attn_dkv_fine_ring_kernel<<<dim3((unsigned) ((n_ranges + kRingWarps - 1) / kRingWarps), BH), kRingWarps * 32, smem, st>>>(a, partial);
+    attn_dkv_fine_ring_kernel<<<dim3((unsigned) n_windows, BH), kRingWarps * 32, smem, st>>>(a, partial);
     LLSA_LAUNCH_OK("attn_dkv_fine_ring_kernel");
-    attn_dkv_finish_ld_kernel<<<dim3((unsigned) ((a.n1 + 4 * kFinishPerWarp - 1) / (4 * kFinishPerWarp)), BH), 128, 0, st>>>(a, partial, n_ranges);
+    attn_dkv_finish_ld_kernel<<<dim3((unsigned) ((a.n1 + 4 * kFinishPerWarp - 1) / (4 * kFinishPerWarp)), BH), 128, 0, st>>>(a, partial, n_windows);
     LLSA_LAUNCH_OK("attn_dkv_finish_ld_kernel");
   }
   return LLSA_OK;

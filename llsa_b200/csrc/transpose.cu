@@ -28,7 +28,7 @@ struct TransposeArgs {
   int off64;
   int32_t* flat;    // [BH, M*T]
   int32_t* pairs;   // [BH, M*T] or nullptr: entry position m*T + t in the order of `flat`
-  int2* ranges;     // [BH, ceil(M*T / 32)] or nullptr: (first entry, its bucket) of the work ranges cut for the dK/dV kernel
+  int2* ranges;     // [BH, ceil(M*T / kRangeEntries)] or nullptr: (first entry, its bucket) of the work ranges cut for the dK/dV kernel
   int64_t E;        // entries per head
   int T;
   int64_t n_kv;
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
     else reinterpret_cast<int32_t*>(a.offsets)[bh * (n + 1) + n] = carry;
   }
   __syncthreads();
-  // ranges that lie wholly behind the last entry (entries were dropped, or E is not a multiple of 32) are empty
+  // ranges that lie wholly behind the last entry (entries were dropped, or E is not a multiple of the range size) are empty
   if (a.ranges) {
     const int64_t R = (E + kRangeEntries - 1) / kRangeEntries;
     for (int64_t r = threadIdx.x; r < R; r += blockDim.x)
@@ -151,10 +151,10 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
       if (pos < E) {
         a.flat[bh * E + pos] = (int32_t) (e / a.T);
         if (a.pairs) a.pairs[bh * E + pos] = (int32_t) e;
-        // Work ranges of the dK/dV kernel: nominally 32 entries each, but a bucket of at most 32 entries is never cut --
-        // the range that would begin inside it begins at the bucket's first entry instead (ranges then hold 1..63
-        // entries); only longer buckets are cut, at multiples of 32.  The entry that lands on a multiple of 32 knows
-        // its bucket and that bucket's extent.
+        // Work ranges of the dK/dV kernel: nominally kRangeEntries entries each, but a bucket of at most that many entries is
+        // never cut -- the range that would begin inside it begins at the bucket's first entry instead (ranges then hold
+        // 1 .. 2 kRangeEntries - 1 entries); only longer buckets are cut, at multiples of kRangeEntries.  The entry that lands
+        // on such a multiple knows its bucket and that bucket's extent.
         if (a.ranges && pos % kRangeEntries == 0) {
           const int b0 = base[key], b1 = key + 1 < n ? base[key + 1] : total_entries;
           a.ranges[bh * ((E + kRangeEntries - 1) / kRangeEntries) + pos / kRangeEntries] = make_int2(b1 - b0 <= kRangeEntries ? b0 : pos, (int) key);
@@ -188,6 +188,8 @@ static int plan_transpose(int64_t n_kv, int64_t E, size_t* smem, bool* global) {
 }  // namespace llsa
 
 using namespace llsa;
+
+extern "C" int llsa_transpose_range_entries(void) { return kRangeEntries; }
 
 extern "C" size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t T, int64_t n_kv) {
   size_t smem;

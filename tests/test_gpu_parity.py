@@ -165,8 +165,9 @@ def test_transpose_indices(M, T, dtype):
 
 def test_transpose_pairs_and_work_ranges():
     """The two extra lists of llsa_transpose_indices_pairs: pairs names each entry's (query block, slot); ranges cuts the
-    entry list at multiples of 32, moved back to a bucket's start where the bucket holds at most 32 entries."""
-    from llsa_b200 import ops
+    entry list at multiples of the range size S, moved back to a bucket's start where the bucket holds at most S entries."""
+    from llsa_b200 import _lib, ops
+    S = _lib.lib().llsa_transpose_range_entries()
     gen = torch.Generator().manual_seed(7)
     M, T = 2048, 8
     hot = torch.randint(0, 24, (1, 3, M, T // 2), generator=gen)               # a few very long buckets
@@ -184,9 +185,9 @@ def test_transpose_pairs_and_work_ranges():
         size = off[0, h].diff()
         for r in range(cut.numel()):
             j = int(bucket[r])
-            assert int(off[0, h, j]) <= 32 * r < int(off[0, h, j + 1])                          # bucket of the nominal first entry
-            assert int(cut[r]) == (int(off[0, h, j]) if int(size[j]) <= 32 else 32 * r)
-        assert (cut.diff() > 0).all() and int(cut.diff().max()) <= 63
+            assert int(off[0, h, j]) <= S * r < int(off[0, h, j + 1])                           # bucket of the nominal first entry
+            assert int(cut[r]) == (int(off[0, h, j]) if int(size[j]) <= S else S * r)
+        assert (cut.diff() > 0).all() and int(cut.diff().max()) <= 2 * S - 1
 
 
 def test_transpose_matches_reference_golden():
