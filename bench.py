@@ -268,11 +268,17 @@ def main():
     full = synth.correlated_qkv(cfg["seed"], B, H, N, D, dtype=cfg["dtype"])          # the ONE workload, the same on every rank
     if seq_parallel:
         # rank r owns tokens [r*N/W, (r+1)*N/W) of q, k, v (llsa_b200/seqpar.py)
+        # (b,h) slices are split over groups of ranks first; inside a group rank r owns tokens [r*N/R, (r+1)*N/R)
         from llsa_b200 import seqpar
-        n_loc = N // world
-        hq, hk, hv, hdo = [t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous().pin_memory() for t in full]
-        call = lambda q, k, v: seqpar.llsa_l2_seq_parallel(q, k, v, 8, 8, 16)
-        n_slices = B * H
+        grp, rpg, sr, pg = seqpar.make_head_group(B * H, world, rank)
+        n_grp = B * H // (world // rpg)
+        n_loc = N // rpg
+        hq, hk, hv, hdo = [t.reshape(1, B * H, N, D)[:, grp * n_grp:(grp + 1) * n_grp, sr * n_loc:(sr + 1) * n_loc].contiguous().pin_memory()
+                           for t in full]
+        sp_group = pg if rpg > 1 else seqpar._ALONE
+        call = lambda q, k, v: seqpar.llsa_l2_seq_parallel(q, k, v, 8, 8, 16, group=sp_group)
+        n_slices = n_grp
+        seq_ranks = rpg
     else:
         # rank r owns a contiguous range of the flattened (batch, head) axis: [1, slices, N, D] (llsa_b200/shard.py)
         hq, hk, hv, hdo = [shard.take_slices(t, world, rank).contiguous().pin_memory() for t in full]
@@ -332,7 +338,9 @@ def main():
         if name != "end":
             per[name] = per.get(name, 0.0) + ev.elapsed_time(nxt)
     per = {kname: max(tms, 0.0) / args.steps for kname, tms in per.items()}    # a stage moved to a side stream shows ~0 here
-    units = n_slices * (N // world if seq_parallel else N) * D      # query rows x channels on this rank
+    if not seq_parallel:
+        seq_ranks = 1
+    units = n_slices * (N // seq_ranks) * D      # query rows x channels on this rank
     if cfg["op"] == "llsa_l2":
         keys = dict(fine=128, p1=128, p2=N // 256 if N // 256 >= 64 else 0)
     else:
@@ -359,7 +367,7 @@ def main():
     total_flops = 14 * B * H * N * D * ktot                    # the whole workload
     # memory-bound stages: algorithmic bytes per launch (this rank) against the measured copy bandwidth
     T = units * 2                                             # one [slices, N, D] bf16 tensor
-    nq1, n2k = n_slices * (N // world if seq_parallel else N) // 16, N // 256
+    nq1, n2k = n_slices * (N // seq_ranks) // 16, N // 256
     alg_bytes = dict(pool_pyramid=3 * T + 3 * T * (1 / 16 + 1 / 256),
                      coarse_topk=2 * n_slices * n2k * D * 2 + n_slices * n2k * 8 * 4,
                      refine_topk=nq1 * D * 2 + (nq1 // 16) * 128 * D * 2 + nq1 * 8 * 4,
@@ -381,7 +389,8 @@ def main():
                            l2_policy="no flush: a step streams %.0f MB per GPU (q, k, v, do in, o, dq, dk, dv out: 8 x %.1f MB; P / dS scratch %.0f MB), "
                                      "%s the 126 MB L2" % (8 * units * 2 / 1e6 + nq1 * 8 * 1024 / 1e6, units * 2 / 1e6, nq1 * 8 * 1024 / 1e6,
                                                            "more than" if 8 * units * 2 + nq1 * 8 * 1024 > 126e6 else "LESS than (reads may hit L2)"),
-                           parallelism=("%d rank(s), sequence sharded: all-gather of k, v and pooled levels, reduce-scatter of dk, dv" % world)
+                           parallelism=("%d rank(s): %d group(s) of (b,h) slices x %d rank(s) sharding the sequence (all-gather of k, v and pooled "
+                                        "levels, reduce-scatter of dk, dv inside a group)" % (world, world // seq_ranks, seq_ranks))
                            if seq_parallel else "%d rank(s), the 48 (batch, head) slices split contiguously, no collective" % world),
                windows=len(windows), eager_ms_per_step=eager_ms_step,
                effective_tflops=total_flops / (ms_step * 1e-3) / 1e12,

@@ -48,7 +48,7 @@ int raise_smem_limit(const void* kernel, size_t bytes);
 
 // Nominal entries per work range of the fine dK/dV kernel: the index transpose cuts the CSR entry list into ranges of this
 // many entries (transpose.cu), one warp of attn_dkv_fine_ring_kernel walks one range (attn_bwd_mma.cu).
-constexpr int kRangeEntries = 64;
+constexpr int kRangeEntries = 32;
 
 inline size_t dtype_size(int dt) {
   switch (dt) {

@@ -26,16 +26,53 @@ from typing import List, Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["llsa_l2_seq_parallel", "llsa_l1_seq_parallel", "CudaBackend", "gather_seq", "reduce_scatter_seq", "local_forward"]
+__all__ = ["llsa_l2_seq_parallel", "llsa_l1_seq_parallel", "CudaBackend", "gather_seq", "reduce_scatter_seq", "local_forward",
+           "head_groups", "make_head_group"]
 
 
 _PER_SLICE_MAX = 16     # up to this many (b,h) slices the exchange runs per slice, straight into / out of place
 
 
+def head_groups(n_slices: int, world: int) -> int:
+    """How many groups the ranks are cut into when a problem of n_slices (batch, head) slices is spread over `world`
+    ranks: the (b,h) slices are split over the groups first (no communication between groups: every stage of the
+    operator is independent per slice), and only inside a group is the SEQUENCE sharded.  The largest divisor of `world`
+    that also divides n_slices: 6 slices on 8 ranks -> 2 groups of 4 ranks with 3 slices each, so a rank exchanges k, v
+    and dk, dv of three heads with three peers instead of six heads with seven."""
+    g = 1
+    for d in range(1, world + 1):
+        if world % d == 0 and n_slices % d == 0:
+            g = d
+    return g
+
+
+def make_head_group(n_slices: int, world: Optional[int] = None, rank: Optional[int] = None):
+    """(group index, ranks per group, rank inside its group, process group of this rank's group).  Every rank of the
+    default group must call this (torch.distributed.new_group is collective)."""
+    world = dist.get_world_size() if world is None else world
+    rank = dist.get_rank() if rank is None else rank
+    g = head_groups(n_slices, world)
+    rpg = world // g
+    mine = None
+    for i in range(g):
+        ranks = list(range(i * rpg, (i + 1) * rpg))
+        pg = dist.new_group(ranks) if rpg > 1 else None
+        if rank in ranks:
+            mine = pg
+    return rank // rpg, rpg, rank % rpg, mine
+
+
+_ALONE = "alone"        # group argument of a rank that shares its slices' sequence with nobody: no exchange at all
+
+
+def _group_size(group) -> int:
+    return 1 if group is _ALONE else dist.get_world_size(group)
+
+
 def gather_seq_start(x: torch.Tensor, group=None):
     """Starts the all-gather of [B,H,n_local,D] along dim 2 and returns a handle for gather_seq_finish: the collectives run on
     the communicator's own stream, so kernels enqueued before the finish overlap with them."""
-    world = dist.get_world_size(group)
+    world = _group_size(group)
     if world == 1:
         return x, [], None
     x = x.contiguous()
@@ -67,7 +104,7 @@ def gather_seq(x: torch.Tensor, group=None) -> torch.Tensor:
 
 def reduce_scatter_seq(x: torch.Tensor, group=None) -> torch.Tensor:
     """Full-length partial sums [B,H,W*n_local,D] on every rank -> this rank's [B,H,n_local,D] of the total."""
-    world = dist.get_world_size(group)
+    world = _group_size(group)
     if world == 1:
         return x
     B, H, N, D = x.shape

@@ -164,3 +164,12 @@ def test_two_gpus_sequence_sharded_over_nccl(tmp_path):
     r = torch.load(out)
     assert torch.equal(r["got"][0], r["ref"][0]) and torch.equal(r["got"][1], r["ref"][1])
     assert rel_l2(r["got"][2], r["ref"][2]) < 4e-3 and rel_l2(r["got"][3], r["ref"][3]) < 4e-3
+
+
+def test_head_groups_split_slices_before_the_sequence():
+    """(b,h) slices are split over groups of ranks first, only the rest shards the sequence: 6 heads on 8 GPUs are two
+    groups of four ranks with three heads each."""
+    from llsa_b200 import seqpar
+    assert seqpar.head_groups(6, 8) == 2 and seqpar.head_groups(6, 4) == 2 and seqpar.head_groups(6, 2) == 2
+    assert seqpar.head_groups(48, 8) == 8 and seqpar.head_groups(6, 3) == 3 and seqpar.head_groups(5, 4) == 1
+    assert seqpar.head_groups(6, 1) == 1
