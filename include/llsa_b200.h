@@ -90,6 +90,20 @@ int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* 
 int llsa_rope_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr,
                                const LlsaTensor* y1, const LlsaTensor* y2, int block_size, void* stream);
 
+/* The same pass with the attention block's q / k RMSNorm fused in front of the rotation as well
+ * (models/rope_dit_transformer_2d.py:215-238: norm_q / norm_k, then my_rope_fn, then llsa_l1 / llsa_l2 pools): tensors
+ * whose bit is set in norm_mask are normalised over their C channels, y = T((x * rsqrt(mean(x^2) + eps)) * w) in fp32
+ * with w = norm_weight[i] (F32 [C]; a NULL entry means ones), then rotated if their rope_mask bit is set (freq may be
+ * NULL when rope_mask is 0), written to xr[i] and pooled.  One read of q and k instead of three.  The arithmetic is
+ * that of llsa_rms_norm_fwd followed by llsa_rope_fwd and llsa_pool_pyramid_fwd, bit for bit. */
+int llsa_rms_rope_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* const* norm_weight, int norm_mask, float eps,
+                                   const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr, const LlsaTensor* y1,
+                                   const LlsaTensor* y2, int block_size, void* stream);
+/* RMSNorm over the last dimension of a [B,H,S,C] tensor (any batch/head/token strides), the q / k normalisation of the
+ * reference's attention block (diffusers' RMSNorm as used at rope_dit_transformer_2d.py:215-218): fp32 sum of squares in
+ * a fixed order, y = T((x * rsqrt(mean + eps)) * weight).  weight: F32 [C] or NULL (ones). */
+int llsa_rms_norm_fwd(const LlsaTensor* x, const LlsaTensor* weight, float eps, const LlsaTensor* y, void* stream);
+
 /* ---- RoPE: src/llsa/kernel/triton/rope.py ---------------------------------
  * Interleaved-pair rotation by a [S,D] table whose even columns are sin and odd
  * columns cos (rope.py:28-50); y has x's shape, any strides.  Replaces

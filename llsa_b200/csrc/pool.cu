@@ -58,7 +58,26 @@ struct PyramidArgs {
   int64_t fs;      // table row stride in elements
   View<T> xr[3];
   int rope_mask;
+  // fused RMSNorm (NORM kernels only): tensors whose bit is set in norm_mask are normalised over their C channels before the
+  // rotation: y = T((x * rsqrt(mean(x^2) + eps)) * w), fp32 arithmetic, w an fp32 [C] weight (nullptr: ones)
+  const float* norm_w[3];
+  float eps;
+  int norm_mask;
 };
+
+// RMSNorm of one token row held by `lanes` neighbouring threads (VEC consecutive channels each; lanes a power of two, the
+// group aligned inside its warp): squares summed in channel order per thread, then a butterfly over the group.  The
+// stand-alone kernel and the fused pooling pass share this function, so their results are identical bit for bit.
+template <typename T, int VEC>
+__device__ __forceinline__ void rms_normalise(float (&v)[VEC], const float* w, int c, int lanes, int C, float eps) {
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) ss = __fmaf_rn(v[i], v[i], ss);
+  for (int o = 1; o < lanes; o <<= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+  const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float) C), eps));
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) v[i] = round_to<T>(__fmul_rn(__fmul_rn(v[i], rstd), w ? w[c + i] : 1.f));
+}
 
 // Interleaved-pair rotation of VEC channels of one token, every product and sum rounded to T separately
 // (rope.py:37-47 evaluated as an element-wise tensor program; the same arithmetic as rope_kernel in rope.cu).
@@ -73,7 +92,7 @@ __device__ __forceinline__ void rope_rotate(float (&v)[VEC], const float (&f)[VE
 }
 
 // blockDim.x = ROWS * (C / VEC); ROWS level-1 rows per CTA (== bs when LEVELS == 2).
-template <typename T, int LEVELS, bool ROPE = false>
+template <typename T, int LEVELS, bool ROPE = false, bool NORM = false>
 __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t ctas_per_head) {
   constexpr int VEC = Vec16<T>::N;
   extern __shared__ float smem[];  // LEVELS==2: [rows][C] level-1 results as fp32 images of T
@@ -84,12 +103,18 @@ __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t 
   const int lanes = a.C / VEC;
   const int r = threadIdx.x / lanes, c = (threadIdx.x % lanes) * VEC;
   const int64_t row1 = grp * rows_per_cta + r;  // level-1 row inside (b,h)
-  if (row1 < a.n1) {
-    const T* xp = a.x[ti].row(b, h, row1 * a.bs) + c;
+  // NORM: every thread of a warp takes part in the row reductions, so rows past the end are computed on the last row and dropped
+  const bool live = row1 < a.n1;
+  if (live || NORM) {
+    const int64_t row1c = live ? row1 : a.n1 - 1;
+    const T* xp = a.x[ti].row(b, h, row1c * a.bs) + c;
     const int64_t sn = a.x[ti].sn;
     const bool rope = ROPE && ((a.rope_mask >> ti) & 1);
-    T* rp = rope ? a.xr[ti].row(b, h, row1 * a.bs) + c : nullptr;
-    const T* fp = rope ? a.freq + row1 * a.bs * a.fs + c : nullptr;
+    const bool norm = NORM && ((a.norm_mask >> ti) & 1);
+    const bool writes = (rope || norm) && live;        // the transformed rows go to xr
+    T* rp = (rope || norm) ? a.xr[ti].row(b, h, row1c * a.bs) + c : nullptr;
+    const T* fp = rope ? a.freq + row1c * a.bs * a.fs + c : nullptr;
+    const float* nw = norm ? a.norm_w[ti] : nullptr;
     float acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
@@ -99,15 +124,20 @@ __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t 
       float v[8][VEC];
 #pragma unroll
       for (int u = 0; u < 8; ++u) Vec16<T>::load(xp + (int64_t) (t + u) * sn, v[u]);
+      if (NORM && norm) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) rms_normalise<T, VEC>(v[u], nw, c, lanes, a.C, a.eps);
+      }
       if (ROPE && rope) {
         float f[8][VEC];
 #pragma unroll
         for (int u = 0; u < 8; ++u) Vec16<T>::load(fp + (int64_t) (t + u) * a.fs, f[u]);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          rope_rotate<T, VEC>(v[u], f[u]);
-          Vec16<T>::store(rp + (int64_t) (t + u) * a.xr[ti].sn, v[u]);
-        }
+        for (int u = 0; u < 8; ++u) rope_rotate<T, VEC>(v[u], f[u]);
+      }
+      if ((ROPE || NORM) && writes) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) Vec16<T>::store(rp + (int64_t) (t + u) * a.xr[ti].sn, v[u]);
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u)
@@ -117,20 +147,21 @@ __global__ void pool_pyramid_kernel(PyramidArgs<T> a, int rows_per_cta, int64_t 
     for (; t < a.bs; ++t) {
       float v[VEC];
       Vec16<T>::load(xp + (int64_t) t * sn, v);
+      if (NORM && norm) rms_normalise<T, VEC>(v, nw, c, lanes, a.C, a.eps);
       if (ROPE && rope) {
         float f[VEC];
         Vec16<T>::load(fp + (int64_t) t * a.fs, f);
         rope_rotate<T, VEC>(v, f);
-        Vec16<T>::store(rp + (int64_t) t * a.xr[ti].sn, v);
       }
+      if ((ROPE || NORM) && writes) Vec16<T>::store(rp + (int64_t) t * a.xr[ti].sn, v);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[i] = round_to<T>(acc[i] + v[i]);
     }
     const float kf = (float) a.bs;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = round_to<T>(__fdiv_rn(acc[i], kf));
-    Vec16<T>::store(a.y1[ti] + (bh * a.n1 + row1) * a.C + c, acc);
-    if (LEVELS == 2) {
+    if (live) Vec16<T>::store(a.y1[ti] + (bh * a.n1 + row1) * a.C + c, acc);
+    if (LEVELS == 2 && live) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) smem[r * a.C + c + i] = acc[i];
     }
@@ -181,6 +212,22 @@ __global__ void mean_pool_bwd_kernel(View<const T> dy, View<T> dx, int H, int C,
     const float g = to_f32<T>(dy.row(bh / H, bh % H, sx / k)[c]);
     dx.row(bh / H, bh % H, sx)[c] = from_f32<T>(__fdiv_rn(g, (float) k));
   }
+}
+
+// Stand-alone RMSNorm over the channels of [B,H,S,C] (the q / k normalisation of the attention block): one thread per
+// 16-byte channel group, a row's C / VEC threads neighbours in a warp.  y has x's shape, any strides.
+template <typename T>
+__global__ void rms_norm_kernel(View<const T> x, View<T> y, const float* __restrict__ w, float eps, int H, int C, int64_t S, int64_t rows) {
+  constexpr int VEC = Vec16<T>::N;
+  const int lanes = C / VEC;
+  const int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x;
+  const int64_t row = min(i / lanes, rows - 1);          // rows past the end take part in the reductions and store nothing
+  const int c = (int) (i % lanes) * VEC;
+  const int64_t s = row % S, bh = row / S;
+  float v[VEC];
+  Vec16<T>::load(x.row(bh / H, bh % H, s) + c, v);
+  rms_normalise<T, VEC>(v, w, c, lanes, C, eps);
+  if (i / lanes < rows) Vec16<T>::store(y.row(bh / H, bh % H, s) + c, v);
 }
 
 static int grid_for(int64_t total, int block) {
@@ -247,19 +294,38 @@ extern "C" int llsa_mean_pool_bwd(const LlsaTensor* dy, const LlsaTensor* dx, in
   return LLSA_OK;
 }
 
+struct NormSpec {
+  int mask;
+  const float* w[3];
+  float eps;
+};
+
+template <typename T, int LEVELS>
+static void launch_pyramid_variant(const PyramidArgs<T>& a, dim3 grid, int threads, size_t smem, int rows, int64_t per_head, cudaStream_t st) {
+  if (a.rope_mask && a.norm_mask) pool_pyramid_kernel<T, LEVELS, true, true><<<grid, threads, smem, st>>>(a, rows, per_head);
+  else if (a.rope_mask) pool_pyramid_kernel<T, LEVELS, true, false><<<grid, threads, smem, st>>>(a, rows, per_head);
+  else if (a.norm_mask) pool_pyramid_kernel<T, LEVELS, false, true><<<grid, threads, smem, st>>>(a, rows, per_head);
+  else pool_pyramid_kernel<T, LEVELS, false, false><<<grid, threads, smem, st>>>(a, rows, per_head);
+}
+
 template <typename T>
 static int launch_pyramid(int n, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2, int bs, cudaStream_t st,
-                          const LlsaTensor* freq = nullptr, int rope_mask = 0, const LlsaTensor* xr = nullptr) {
+                          const LlsaTensor* freq = nullptr, int rope_mask = 0, const LlsaTensor* xr = nullptr, const NormSpec* norm = nullptr) {
   constexpr int VEC = Vec16<T>::N;
   PyramidArgs<T> a;
   memset(&a, 0, sizeof(a));
   a.rope_mask = freq ? rope_mask : 0;
+  a.norm_mask = norm ? norm->mask : 0;
   if (a.rope_mask) {
     a.freq = (const T*) freq->ptr;
     a.fs = freq->stride[0];
-    for (int i = 0; i < n; ++i)
-      if ((rope_mask >> i) & 1) a.xr[i] = make_view<T>(&xr[i]);
   }
+  if (a.norm_mask) {
+    a.eps = norm->eps;
+    for (int i = 0; i < n; ++i) a.norm_w[i] = norm->w[i];
+  }
+  for (int i = 0; i < n; ++i)
+    if (((a.rope_mask | a.norm_mask) >> i) & 1) a.xr[i] = make_view<T>(&xr[i]);
   const int64_t B = x[0].shape[0], H = x[0].shape[1], N = x[0].shape[2], C = x[0].shape[3];
   for (int i = 0; i < 3; ++i) {
     const int j = i < n ? i : 0;
@@ -272,21 +338,20 @@ static int launch_pyramid(int n, const LlsaTensor* x, const LlsaTensor* y1, cons
   if (y2) {
     const int64_t n2 = a.n1 / bs;
     dim3 grid((unsigned) (B * H * n2), n);
-    if (a.rope_mask) pool_pyramid_kernel<T, 2, true><<<grid, bs * lanes, bs * C * sizeof(float), st>>>(a, bs, n2);
-    else pool_pyramid_kernel<T, 2><<<grid, bs * lanes, bs * C * sizeof(float), st>>>(a, bs, n2);
+    launch_pyramid_variant<T, 2>(a, grid, bs * lanes, bs * C * sizeof(float), bs, n2, st);
   } else {
     const int rows = 16;
     const int64_t per_head = (a.n1 + rows - 1) / rows;
     dim3 grid((unsigned) (B * H * per_head), n);
-    if (a.rope_mask) pool_pyramid_kernel<T, 1, true><<<grid, rows * lanes, 0, st>>>(a, rows, per_head);
-    else pool_pyramid_kernel<T, 1><<<grid, rows * lanes, 0, st>>>(a, rows, per_head);
+    launch_pyramid_variant<T, 1>(a, grid, rows * lanes, 0, rows, per_head, st);
   }
   LLSA_LAUNCH_OK("pool_pyramid_kernel");
   return LLSA_OK;
 }
 
 static int pyramid_entry(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2, int block_size, void* stream,
-                         const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr) {
+                         const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr, const LlsaTensor* const* norm_w = nullptr, int norm_mask = 0,
+                         float eps = 0.f) {
   LLSA_REQUIRE(x && y1, LLSA_ERR_NULL, "pool_pyramid: null tensor list");
   LLSA_REQUIRE(n_tensors >= 1 && n_tensors <= 3, LLSA_ERR_ARG, "pool_pyramid: n_tensors must be 1..3");
   const int bs = block_size;
@@ -325,10 +390,36 @@ static int pyramid_entry(int n_tensors, const LlsaTensor* x, const LlsaTensor* y
       if (rc) return rc;
     }
   }
+  NormSpec ns;
+  memset(&ns, 0, sizeof(ns));
+  if (norm_mask) {
+    LLSA_REQUIRE(norm_mask > 0 && norm_mask < (1 << n_tensors) && xr, LLSA_ERR_ARG, "rms_rope_pool_pyramid: bad norm mask");
+    const int lanes = (int) (C / vec);
+    LLSA_REQUIRE(lanes <= 32 && (lanes & (lanes - 1)) == 0, LLSA_ERR_SHAPE, "rms_rope_pool_pyramid: channels=%lld unsupported for the fused norm",
+                 (long long) C);
+    LLSA_REQUIRE(eps >= 0.f, LLSA_ERR_ARG, "rms_rope_pool_pyramid: eps must not be negative");
+    ns.mask = norm_mask;
+    ns.eps = eps;
+    for (int i = 0; i < n_tensors; ++i) {
+      if (!((norm_mask >> i) & 1)) continue;
+      const LlsaTensor* w = norm_w ? norm_w[i] : nullptr;
+      if (w) {
+        const int64_t sw[1] = {C};
+        int rc = check_contig(w, "norm weight", LLSA_F32, 1, sw);
+        if (rc) return rc;
+        ns.w[i] = (const float*) w->ptr;
+      }
+      if (!((rope_mask >> i) & 1) || !freq) {
+        int rc = check_bhnd(&xr[i], "xr", dt, B, H, N, C);
+        if (rc) return rc;
+      }
+    }
+  }
   if (B * H * N * C == 0) return LLSA_OK;
   cudaStream_t st = (cudaStream_t) stream;
-  return dt == LLSA_F32 ? launch_pyramid<float>(n_tensors, x, y1, y2, bs, st, freq, rope_mask, xr)
-                        : launch_pyramid<__nv_bfloat16>(n_tensors, x, y1, y2, bs, st, freq, rope_mask, xr);
+  const int rc = dt == LLSA_F32 ? launch_pyramid<float>(n_tensors, x, y1, y2, bs, st, freq, rope_mask, xr, norm_mask ? &ns : nullptr)
+                                : launch_pyramid<__nv_bfloat16>(n_tensors, x, y1, y2, bs, st, freq, rope_mask, xr, norm_mask ? &ns : nullptr);
+  return rc;
 }
 
 extern "C" int llsa_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* y1, const LlsaTensor* y2,
@@ -340,4 +431,41 @@ extern "C" int llsa_rope_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, co
                                           const LlsaTensor* y1, const LlsaTensor* y2, int block_size, void* stream) {
   LLSA_REQUIRE(freq, LLSA_ERR_NULL, "rope_pool_pyramid: null table");
   return pyramid_entry(n_tensors, x, y1, y2, block_size, stream, freq, rope_mask, xr);
+}
+
+
+extern "C" int llsa_rms_rope_pool_pyramid_fwd(int n_tensors, const LlsaTensor* x, const LlsaTensor* const* norm_weight, int norm_mask, float eps,
+                                              const LlsaTensor* freq, int rope_mask, const LlsaTensor* xr, const LlsaTensor* y1,
+                                              const LlsaTensor* y2, int block_size, void* stream) {
+  return pyramid_entry(n_tensors, x, y1, y2, block_size, stream, freq, freq ? rope_mask : 0, xr, norm_weight, norm_mask, eps);
+}
+
+extern "C" int llsa_rms_norm_fwd(const LlsaTensor* x, const LlsaTensor* weight, float eps, const LlsaTensor* y, void* stream) {
+  LLSA_REQUIRE(x && y && x->ptr && y->ptr, LLSA_ERR_NULL, "rms_norm_fwd: null tensor");
+  LLSA_REQUIRE(x->ndim == 4 && is_float_dtype(x->dtype), LLSA_ERR_DTYPE, "rms_norm_fwd: x must be a [B,H,S,C] f32 or bf16 tensor");
+  const int64_t B = x->shape[0], H = x->shape[1], S = x->shape[2], C = x->shape[3];
+  const int vec = x->dtype == LLSA_F32 ? 4 : 8;
+  const int64_t lanes = C / vec;
+  LLSA_REQUIRE(C % vec == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0, LLSA_ERR_SHAPE, "rms_norm_fwd: channels=%lld unsupported", (long long) C);
+  LLSA_REQUIRE(eps >= 0.f, LLSA_ERR_ARG, "rms_norm_fwd: eps must not be negative");
+  int rc;
+  if ((rc = check_bhnd(x, "x", x->dtype, B, H, S, C))) return rc;
+  if ((rc = check_bhnd(y, "y", x->dtype, B, H, S, C))) return rc;
+  const float* w = nullptr;
+  if (weight) {
+    const int64_t sw[1] = {C};
+    if ((rc = check_contig(weight, "weight", LLSA_F32, 1, sw))) return rc;
+    w = (const float*) weight->ptr;
+  }
+  const int64_t rows = B * H * S;
+  if (rows == 0) return LLSA_OK;
+  const int64_t threads = rows * lanes;
+  cudaStream_t st = (cudaStream_t) stream;
+  const unsigned grid = (unsigned) ((threads + 255) / 256);
+  if (x->dtype == LLSA_F32)
+    rms_norm_kernel<float><<<grid, 256, 0, st>>>(make_view<const float>(x), make_view<float>(y), w, eps, (int) H, (int) C, S, rows);
+  else
+    rms_norm_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(make_view<const __nv_bfloat16>(x), make_view<__nv_bfloat16>(y), w, eps, (int) H, (int) C, S, rows);
+  LLSA_LAUNCH_OK("rms_norm_kernel");
+  return LLSA_OK;
 }

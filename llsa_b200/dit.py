@@ -85,9 +85,19 @@ class RopeAttention(nn.Module):
         k = self.to_k(x).view(B, N, self.heads, self.head_dim).transpose(1, 2)
         v = self.to_v(x).view(B, N, self.heads, self.head_dim).transpose(1, 2)
         dt = q.dtype
+        table = rope_table.to(dt)
+        if self.norm_q is not None and self.fused_rope and self.attn_type != "pixel" and q.is_cuda:
+            # q / k RMSNorm, rotation and pooling in one pass over q and k (rope_dit_transformer_2d.py:215-251)
+            from . import ops
+            bs, t = self.block_size, self.topk
+            if self.attn_type == "sparse_l1":
+                o = ops.llsa_l1_rms_rope(q, k, v, self.norm_q.weight, self.norm_k.weight, table, self.norm_q.eps, t, bs)
+            else:
+                o = ops.llsa_l2_rms_rope(q, k, v, self.norm_q.weight, self.norm_k.weight, table, self.norm_q.eps, t, t, bs)
+            o = o.transpose(1, 2).reshape(B, N, self.heads * self.head_dim).to(dt)
+            return self.to_out(o)
         if self.norm_q is not None:
             q, k = self.norm_q(q).to(dt), self.norm_k(k).to(dt)
-        table = rope_table.to(dt)
         if self.attn_type == "pixel":
             q, k = _rope_eager(q, table), _rope_eager(k, table)
             o = F.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=False)

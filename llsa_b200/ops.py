@@ -34,7 +34,7 @@ __all__ = [
     "sparse_indices_attn_res_2_2_fwd", "sparse_indices_attn_res_scatter_2_2_bwd_v2",
     "flash_sparse_residual_attention_l1_op", "flash_sparse_residual_attention_l2_op",
     "llsa_l1", "llsa_l2", "llsa_l1_rope", "llsa_l2_rope", "pool_pyramid", "rope_pool_pyramid", "set_exact_pooled_grad",
-    "set_device_checks",
+    "set_device_checks", "rms_norm", "rms_rope_pool_pyramid", "llsa_l1_rms_rope", "llsa_l2_rms_rope",
 ]
 
 _FLOAT = (torch.float32, torch.bfloat16)
@@ -240,6 +240,71 @@ def rope_pool_pyramid(xs: List[torch.Tensor], freq: torch.Tensor, rope: List[boo
         f = desc(freq)
         _lib.check(_lib.lib().llsa_rope_pool_pyramid_fwd(n, XA, ref(f), mask, XR, Y1, Y2, bs, _stream(xs[0])), "rope_pool_pyramid_fwd")
     return xr, y1, y2
+
+
+def rms_rope_pool_pyramid(xs: List[torch.Tensor], weights: List[Optional[torch.Tensor]], eps: float, freq: Optional[torch.Tensor],
+                          rope: List[bool], block_size: int, levels: int):
+    """RMSNorm (tensors with a weight entry that is not None... or True for an all-ones weight), RoPE (flagged tensors) and
+    every pyramid level in ONE pass over HBM: what the attention block does to q and k before llsa_l1 / llsa_l2
+    (models/rope_dit_transformer_2d.py:215-238).  Returns (transformed tensors, level-1 list, level-2 list or None); the
+    results carry the bits of rms_norm -> my_rope_fn -> mean_pool1d run one after the other."""
+    _need_cuda(*xs)
+    _check_float(*xs)
+    xs = [_prep(x) for x in xs]
+    B, H, N, D = xs[0].shape
+    bs = block_size
+    use_rope = freq is not None and any(rope)
+    if use_rope:
+        if freq.dtype != xs[0].dtype:
+            freq = freq.to(xs[0].dtype)
+        freq = freq if (freq.stride(-1) == 1 and freq.data_ptr() % 16 == 0 and (freq.stride(0) * freq.element_size()) % 16 == 0) else freq.contiguous()
+    normed = [w is not None for w in weights]
+    changed = [(r and use_rope) or nm for r, nm in zip(rope, normed)]
+    xr = [torch.empty_like(x) if c else x for x, c in zip(xs, changed)]
+    y1 = [torch.empty((B, H, N // bs, D), device=x.device, dtype=x.dtype) for x in xs]
+    y2 = [torch.empty((B, H, N // bs // bs, D), device=x.device, dtype=x.dtype) for x in xs] if levels == 2 else None
+    n = len(xs)
+    TP = C.POINTER(_lib.LlsaTensor)
+    XA = (_lib.LlsaTensor * n)(*[desc(x) for x in xs])
+    XR = (_lib.LlsaTensor * n)(*[desc(x) for x in xr])
+    Y1 = (_lib.LlsaTensor * n)(*[desc(y) for y in y1])
+    Y2 = (_lib.LlsaTensor * n)(*[desc(y) for y in y2]) if y2 is not None else None
+    keep = [w.detach().float().contiguous() if isinstance(w, torch.Tensor) else None for w in weights]
+    wdesc = [desc(k) for k in keep]
+    WP = (TP * n)(*[C.pointer(d) if d is not None else TP() for d in wdesc])
+    rmask = sum(1 << i for i, r in enumerate(rope) if r) if use_rope else 0
+    nmask = sum(1 << i for i, nm in enumerate(normed) if nm)
+    _mark("pool_pyramid")
+    with torch.cuda.device(xs[0].device):
+        f = desc(freq) if use_rope else None
+        _lib.check(_lib.lib().llsa_rms_rope_pool_pyramid_fwd(n, XA, WP, nmask, float(eps), ref(f), rmask, XR, Y1, Y2, bs, _stream(xs[0])),
+                   "rms_rope_pool_pyramid_fwd")
+    return xr, y1, y2
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
+    """RMSNorm over the last dimension of [B,H,S,C] with a fixed summation order (the stand-alone form of the
+    normalisation fused into rms_rope_pool_pyramid); not differentiable by itself."""
+    _need_cuda(x)
+    _check_float(x)
+    x = _prep(x)
+    y = torch.empty_like(x)
+    w = weight.detach().float().contiguous() if weight is not None else None
+    with torch.cuda.device(x.device):
+        a, b, wd = desc(x), desc(y), desc(w)
+        _lib.check(_lib.lib().llsa_rms_norm_fwd(ref(a), ref(wd), float(eps), ref(b), _stream(x)), "rms_norm_fwd")
+    return y
+
+
+def _rms_norm_bwd(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, dy: torch.Tensor):
+    """Gradient of y = (x * rsqrt(mean(x^2) + eps)) * w with respect to x and w (fp32 arithmetic, eager)."""
+    xf, g = x.float(), dy.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    xh = xf * rstd
+    gw = g * weight.float() if weight is not None else g
+    dx = rstd * (gw - xh * (gw * xh).mean(-1, keepdim=True))
+    dw = (g * xh).reshape(-1, x.shape[-1]).sum(0).to(weight.dtype) if weight is not None else None
+    return dx.to(x.dtype), dw
 
 
 # ----------------------------------------------------------------------------- RoPE
@@ -750,6 +815,57 @@ def llsa_l2_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, freq: torch.
     """llsa_l2(my_rope_fn(q, freq), my_rope_fn(k, freq), v, topk1, topk2, block_size)
     (models/rope_dit_transformer_2d.py:232-251) with the rotation fused into the pooling pass."""
     return _llsa_rope_fwd(q, k, v, freq, topk1, topk2, block_size, 2)[0]
+
+
+class _LlsaRmsRope(torch.autograd.Function):
+    """llsa_l1 / llsa_l2 on RMS-normalised, rotated q and k: normalisation, rotation and pooling in one pass forward; the
+    backward runs the operator's backward, then the rotation's and the normalisation's."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, wq, wk, freq, eps, topk1, topk2, block_size, levels):
+        bs = block_size
+        (qr, kr, _), l1, l2 = rms_rope_pool_pyramid([q.detach(), k.detach(), v.detach()], [wq, wk, None], eps, freq, [True, True, False], bs, levels)
+        pq, pk, pv = l1
+        vd = v.detach()
+        if levels == 2:
+            pq2, pk2, pv2 = l2
+            p_indices = _coarse_topk(pq2, pk2, topk2)
+            indices = _refine_topk(pq, pk, p_indices, topk1, p_indices.shape[-1], bs)
+            o, lse = _attn_fwd(qr, kr, vd, pk, pv, pk2, pv2, indices, p_indices, topk1, p_indices.shape[-1], bs, float(bs), float(bs * bs))
+            extra = [p_indices, pk2, pv2]
+        else:
+            indices = _coarse_topk(pq, pk, topk1)
+            o, lse = _attn_fwd(qr, kr, vd, pk, pv, None, None, indices, None, indices.shape[-1], 0, bs, float(bs), 1.0)
+            extra = []
+        ctx.save_for_backward(q, k, v, wq, wk, freq, o, lse, qr, kr, indices, pk, pv, *extra)
+        ctx.cfg = (float(eps), bs, levels)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        eps, bs, levels = ctx.cfg
+        q, k, v, wq, wk, freq, o, lse, qr, kr, indices, pk, pv = ctx.saved_tensors[:13]
+        if levels == 2:
+            p_indices, pk2, pv2 = ctx.saved_tensors[13:]
+            dqr, dkr, dv = _llsa_l2_bwd(do, qr, kr, v, o, lse, indices, p_indices, pk, pv, pk2, pv2, bs)
+        else:
+            dqr, dkr, dv = _llsa_l1_bwd(do, qr, kr, v, o, lse, indices, pk, pv, bs, _exact_pooled_grad)
+        dq, dwq = _rms_norm_bwd(q, wq, eps, _rope_bwd_op(dqr, freq))
+        dk, dwk = _rms_norm_bwd(k, wk, eps, _rope_bwd_op(dkr, freq))
+        return dq, dk, dv, dwq, dwk, None, None, None, None, None, None
+
+
+def llsa_l1_rms_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, freq: torch.Tensor,
+                     eps: float = 1e-5, topk: int = 8, block_size: int = 16) -> torch.Tensor:
+    """llsa_l1(my_rope_fn(norm_q(q)), my_rope_fn(norm_k(k)), v, topk, block_size): the whole q / k preparation of the attention
+    block (models/rope_dit_transformer_2d.py:215-241) fused into the pooling pass.  wq, wk: RMSNorm weights [D]."""
+    return _LlsaRmsRope.apply(q, k, v, wq, wk, freq, eps, topk, 0, block_size, 1)
+
+
+def llsa_l2_rms_rope(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, freq: torch.Tensor,
+                     eps: float = 1e-5, topk1: int = 8, topk2: int = 8, block_size: int = 16) -> torch.Tensor:
+    """llsa_l2 on RMS-normalised, rotated q and k (models/rope_dit_transformer_2d.py:215-251), q / k read once."""
+    return _LlsaRmsRope.apply(q, k, v, wq, wk, freq, eps, topk1, topk2, block_size, 2)
 
 
 def llsa_l1(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk: int = 8, block_size: int = 16) -> torch.Tensor:

@@ -634,6 +634,59 @@ def test_llsa_rope_operators_match_rope_then_llsa(levels):
     assert rel_l2(a[1].grad, b[1].grad) < 1e-3 and rel_l2(a[2].grad, b[2].grad) < 1e-3     # fp32 reductions: order may differ
 
 
+@pytest.mark.parametrize("dtype,levels", [(torch.bfloat16, 2), (torch.float32, 1)])
+def test_rms_rope_pool_pyramid_fused_is_bit_exact(dtype, levels):
+    """q / k RMSNorm + RoPE + every pyramid level in one pass == rms_norm, my_rope_fn and the pyramid run one after the other,
+    bit for bit (models/rope_dit_transformer_2d.py:215-251); the stand-alone rms_norm agrees with the eager fp32 formula
+    to the last bit of the output type."""
+    L = _ops()
+    N = 4096
+    q, k, v, _ = synth.gaussian_qkv(57, 2, 3, N, 64, dtype=dtype)
+    gen = torch.Generator().manual_seed(5)
+    wq, wk = (1 + 0.1 * torch.randn(64, generator=gen)).to(DEV), (1 + 0.1 * torch.randn(64, generator=gen)).to(DEV)
+    table = synth.rope_table_2d(int(math.isqrt(N)), dtype=dtype).to(DEV)
+    to_view = lambda t: t.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)       # [B,N,H,D] storage, as the model passes
+    xs = [to_view(q), to_view(k), v.to(DEV)]
+    xr, y1, y2 = L.rms_rope_pool_pyramid(xs, [wq, wk, None], 1e-5, table, [True, True, False], 16, levels)
+    qn, kn = L.rms_norm(xs[0], wq, 1e-5), L.rms_norm(xs[1], wk, 1e-5)
+    want = [L.my_rope_fn(qn, table), L.my_rope_fn(kn, table), xs[2]]
+    w1, w2 = L.pool_pyramid(want, 16, levels)
+    assert xr[0].stride() == xs[0].stride() and xr[2] is xs[2]
+    for a, b in zip(xr[:2], want[:2]):
+        assert torch.equal(a, b)
+    for a, b in zip(y1, w1):
+        assert torch.equal(a, b)
+    if levels == 2:
+        for a, b in zip(y2, w2):
+            assert torch.equal(a, b)
+    xf = xs[0].float()
+    ref = ((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)) * wq).to(dtype)
+    tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-6
+    assert float(((qn.float() - ref.float()).abs() / ref.float().abs().clamp_min(1e-3)).max()) <= tol
+
+
+def test_llsa_l2_rms_rope_operator_matches_the_unfused_chain():
+    """llsa_l2_rms_rope == llsa_l2_rope(rms_norm(q), rms_norm(k), v): same output bits; gradients of q, k, v and of the two
+    norm weights against autograd through an eager RMSNorm in front of llsa_l2_rope."""
+    L = _ops()
+    N = 16384
+    q, k, v, do = _bf16_case("l2", 1, 2, N, 58)
+    table = synth.rope_table_2d(int(math.isqrt(N)), dtype=torch.bfloat16).to(DEV)
+    a = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    b = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    wa = [torch.full((64,), 1.1, device=DEV, requires_grad=True), torch.full((64,), 0.9, device=DEV, requires_grad=True)]
+    wb = [w.detach().clone().requires_grad_(True) for w in wa]
+    o1 = L.llsa_l2_rms_rope(a[0], a[1], a[2], wa[0], wa[1], table, 1e-5, 8, 8, 16)
+    eager = lambda x, w: ((x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)) * w).to(x.dtype)
+    o2 = L.llsa_l2_rope(L.rms_norm(b[0], wb[0], 1e-5), L.rms_norm(b[1], wb[1], 1e-5), b[2], table, 8, 8, 16)
+    assert torch.equal(o1, o2)
+    o1.backward(do.to(DEV))
+    o3 = L.llsa_l2_rope(eager(b[0], wb[0]), eager(b[1], wb[1]), b[2], table, 8, 8, 16)
+    o3.backward(do.to(DEV))
+    for x, y in zip(a + wa, b + wb):
+        assert rel_l2(x.grad, y.grad) < 2e-2
+
+
 @pytest.mark.parametrize("chunk_heads,graphs", [(None, False), (1, False), (None, True), (1, True)])
 def test_host_pipeline_matches_direct_call(chunk_heads, graphs):
     """Pinned host operands through the three-stream chunk pipeline (eager launches or one CUDA graph per staging slot)
