@@ -40,24 +40,32 @@ def test_token_permutation_does_not_change_dense_attention():
 
 
 @pytest.mark.gpu
-def test_sparse_l2_dit_fused_rope_equals_unfused():
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_sparse_l2_dit_fused_rope_equals_unfused(qk_norm):
+    """The fused q / k preparation inside the model.  Without q/k RMSNorm (RoPE + pooling fused) the fused and the unfused
+    model agree bit for bit.  With it, the fused pass sums the squares in its own fixed order while the unfused model runs
+    the eager RMSNorm, so the normalised q, k can differ in the last bf16 bit: outputs and gradients agree like two bf16
+    evaluations of one model."""
     dev = "cuda:0"
     torch.manual_seed(1)
-    a = RopeDiT(layers=2, attn_type="sparse_l2", fused_rope=True).to(dev)
-    b = RopeDiT(layers=2, attn_type="sparse_l2", fused_rope=False).to(dev)
+    a = RopeDiT(layers=2, attn_type="sparse_l2", fused_rope=True, qk_norm=qk_norm).to(dev)
+    b = RopeDiT(layers=2, attn_type="sparse_l2", fused_rope=False, qk_norm=qk_norm).to(dev)
     b.load_state_dict(a.state_dict())
     x = torch.randn(1, 3, 128, 128, device=dev)
     t = torch.tensor([321], device=dev)
     with torch.autocast("cuda", dtype=torch.bfloat16):
         ya, yb = a(x, t), b(x, t)
     assert ya.shape == (1, 3, 128, 128) and torch.isfinite(ya).all()
-    assert torch.equal(ya, yb)
+    if qk_norm:
+        assert (ya.float() - yb.float()).norm() <= 3e-2 * yb.float().norm()
+    else:
+        assert torch.equal(ya, yb)
     ya.float().square().mean().backward()
     yb.float().square().mean().backward()
     for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
         assert torch.isfinite(p.grad).all(), n
         # dk / dv sum fp32 reductions in a run-dependent order and bf16 rounding follows: the two runs differ like two runs of one model
-        assert (p.grad - q.grad).norm() <= 5e-2 * (q.grad.norm() + 1e-12), n
+        assert (p.grad - q.grad).norm() <= (1e-1 if qk_norm else 5e-2) * (q.grad.norm() + 1e-12), n
 
 
 @pytest.mark.gpu
