@@ -39,7 +39,7 @@ sys.path.insert(0, ROOT)
 METRIC = "llsa_l2 fwd+bwd tokens/sec @N=16384,B*H=48,D=64"
 
 # this library's kernels launched by one llsa_l2 forward + backward (torch's own zero fills are not counted)
-KERNELS_PER_STEP = ("pool_pyramid_kernel", "coarse_topk_mma_kernel", "refine_topk_kernel", "attn_fwd_fine8_kernel", "attn_fwd_pooled_tc_kernel",
+KERNELS_PER_STEP = ("pool_pyramid_kernel", "refine_topk_kernel", "attn_fwd_fine8_kernel", "attn_fwd_pooled_tc_kernel",
                     "transpose_kernel", "attn_bwd_pooled_tc_kernel",
                     "attn_dq_fine_kernel", "attn_dkv_fine_ring_kernel", "attn_dkv_finish_ld_kernel")
 
@@ -371,6 +371,7 @@ def main():
     alg_bytes = dict(pool_pyramid=3 * T + 3 * T * (1 / 16 + 1 / 256),
                      coarse_topk=2 * n_slices * n2k * D * 2 + n_slices * n2k * 8 * 4,
                      refine_topk=nq1 * D * 2 + (nq1 // 16) * 128 * D * 2 + nq1 * 8 * 4,
+                     select_two_level=2 * n_slices * n2k * D * 2 + n_slices * n2k * 8 * 4 + nq1 * D * 2 + (nq1 // 16) * 128 * D * 2 + nq1 * 8 * 4,
                      transpose_indices=nq1 * 8 * 4 * 2 + n_slices * (N // 16 + 1) * 4)
     memory_bound = {kname: dict(bytes=int(alg_bytes[kname]), gbs=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9,
                                 frac_of_hbm_peak=alg_bytes[kname] / (per[kname] * 1e-3) / 1e9 / peaks["hbm_gbs"])

@@ -123,6 +123,15 @@ int llsa_coarse_topk(const LlsaTensor* pq, const LlsaTensor* pk, const LlsaTenso
 int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTensor* p_idx, const LlsaTensor* idx,
                      int topk, int p_topk, int block_size, void* stream);
 
+/* Both selections of the two-level operator in one launch where the shape allows it (bf16, D = 64, block 16, exactly 64
+ * level-2 keys, p_topk <= 8): every CTA of the refine kernel first selects its own level-2 query block's parents, with the
+ * arithmetic and tie rule of llsa_coarse_topk, writes them to p_idx and goes on to the refine step; otherwise the two
+ * entry points above are called one after the other.  Outputs are those of llsa_coarse_topk(pq2, pk2) followed by
+ * llsa_refine_topk, bit for bit.  Replaces gen_sparse_indices + compute_topk_indices_sparse as called at
+ * torch_op/flash_sparse_attention_res_2.py:14-16. */
+int llsa_select_two_level(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTensor* pq2, const LlsaTensor* pk2,
+                          const LlsaTensor* p_idx, const LlsaTensor* idx, int topk, int p_topk, int block_size, void* stream);
+
 /* ---- index transpose: src/llsa/kernel/triton/indices_transpose.py ---------
  * Query-major lists idx [B,H,M,T] (I32/I64, values in [0,n_kv)) -> KV-major CSR:
  * offsets [B,H,n_kv+1] (I32 or I64) and flat [B,H,M*T] (I32), each bucket in

@@ -42,7 +42,7 @@ class LlsaAttnArgs(C.Structure):
 EXPORTS = [
     "llsa_version", "llsa_last_error_string", "llsa_mean_pool_fwd", "llsa_mean_pool_bwd", "llsa_pool_pyramid_fwd",
     "llsa_rope_pool_pyramid_fwd", "llsa_rms_rope_pool_pyramid_fwd", "llsa_rms_norm_fwd",
-    "llsa_rope_fwd", "llsa_rope_bwd", "llsa_coarse_topk", "llsa_refine_topk", "llsa_transpose_scratch_bytes",
+    "llsa_rope_fwd", "llsa_rope_bwd", "llsa_coarse_topk", "llsa_refine_topk", "llsa_select_two_level", "llsa_transpose_scratch_bytes",
     "llsa_transpose_indices", "llsa_transpose_indices_pairs", "llsa_transpose_range_entries", "llsa_transpose_indices_noalloc", "llsa_attn_fwd", "llsa_attn_bwd",
     "llsa_attn_bwd_partial_elems", "llsa_attn_bwd_pds_elems", "llsa_status_check",
 ]
@@ -65,6 +65,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.llsa_rope_bwd.argtypes = [TP, TP, TP, C.c_void_p]
     lib.llsa_coarse_topk.argtypes = [TP, TP, TP, C.c_int, C.c_void_p]
     lib.llsa_refine_topk.argtypes = [TP, TP, TP, TP, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.llsa_select_two_level.argtypes = [TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.llsa_transpose_scratch_bytes.argtypes = [C.c_int64] * 5
     lib.llsa_transpose_scratch_bytes.restype = C.c_size_t
     lib.llsa_transpose_indices.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]

@@ -331,11 +331,70 @@ __device__ __forceinline__ void refine_select_sorted4(const float* sc, const int
   }
 }
 
-template <typename T, bool MMA>
+// Coarse selection of ONE level-2 query block against 64 level-2 keys, inside the refine kernel's CTA (four warps: 16 keys
+// each).  The scores are the ones coarse_topk_mma_kernel computes -- the same mma.sync k-steps in the same order on the same
+// operands (all 16 A rows hold the query block's row, so every row of the result is that row's), rounded to bf16, NaN first --
+// and the winners come out in the same order (descending score, ties to the smaller key), so the fused form returns the
+// bits of the two-kernel form while saving its launch and its 64 x 64-score CTAs.
+struct FusedCoarse {
+  const bf16* pq2;     // [BH, M / bs, 64]
+  const bf16* pk2;     // [BH, 64, 64]
+  void* pidx_out;      // [BH, M / bs, p_topk]
+  int pidx64;
+};
+
+__device__ __forceinline__ void coarse_row_64(const FusedCoarse& f, int64_t bh, int64_t P, int64_t n2q, int p_topk, float* sc2, int* s_pidx) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  RowFrag q2, ka, kb;
+  load_rowfrag(q2, f.pq2 + (bh * n2q + P) * 64, t);
+  const bf16* k0 = f.pk2 + bh * 64 * 64;
+  load_rowfrag(ka, k0 + (warp * 16 + g) * 64, t);
+  load_rowfrag(kb, k0 + (warp * 16 + 8 + g) * 64, t);
+  float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+  mma_rows_x_keys(s0, s1, q2, q2, ka, kb);
+  if (g == 0) {
+    const int c = warp * 16 + 2 * t;
+    sc2[c] = round_to<bf16>(s0[0]); sc2[c + 1] = round_to<bf16>(s0[1]);
+    sc2[c + 8] = round_to<bf16>(s1[0]); sc2[c + 9] = round_to<bf16>(s1[1]);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t key[2], blk[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      float v = sc2[lane + 32 * u];
+      v = v != v ? CUDART_INF_F : fmaxf(v, -3.0e38f);       // as top8_insert orders them
+      key[u] = orderable(v);
+      blk[u] = (uint32_t) (lane + 32 * u);
+    }
+    uint32_t mine = 0;
+    for (int tt = 0; tt < p_topk; ++tt) {
+      const uint32_t bk = key[1] > key[0] ? key[1] : key[0];
+      const uint32_t bb = key[1] > key[0] ? blk[1] : blk[0];      // equal scores: the smaller key (slot 0) wins
+      const uint32_t mk = __reduce_max_sync(0xffffffffu, bk);
+      const uint32_t mb = __reduce_min_sync(0xffffffffu, bk == mk ? bb : 0xFFFFFFFFu);
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        if (blk[u] == mb) { key[u] = 0u; blk[u] = 0xFFFFFFFFu; }
+      if (lane == tt) mine = mb;
+    }
+    if (lane < p_topk) {
+      s_pidx[lane] = (int) mine;
+      const int64_t o = (bh * n2q + P) * p_topk + lane;
+      if (f.pidx64) reinterpret_cast<int64_t*>(f.pidx_out)[o] = (int64_t) mine;
+      else reinterpret_cast<int32_t*>(f.pidx_out)[o] = (int32_t) mine;
+    }
+  }
+  __syncthreads();
+}
+
+template <typename T, bool MMA, bool FUSED = false>
 __global__ void __launch_bounds__(128)
 refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView p_idx, void* __restrict__ idx_out, int idx64, int64_t M,
-                   int64_t Mk, int D, int topk, int p_topk, int bs) {
+                   int64_t Mk, int D, int topk, int p_topk, int bs, FusedCoarse fused) {
   extern __shared__ float sm[];
+  __shared__ float s_sc2[64];
+  __shared__ int s_pidx[kMaxTopk];
   const int C = p_topk * bs;
   float* qs = sm;                 // [bs][D]
   float* sc = qs + bs * D;        // [bs][C]
@@ -345,14 +404,15 @@ refine_topk_kernel(const T* __restrict__ pq1, const T* __restrict__ pk1, IdxView
   const T* k0 = pk1 + bh * Mk * D;
   if constexpr (!MMA)                                    // the tensor-core path takes its query fragments straight from global memory
     for (int i = threadIdx.x; i < bs * D; i += blockDim.x) qs[i] = to_f32<T>(q0[i]);
+  if constexpr (FUSED) coarse_row_64(fused, bh, P, n2q, p_topk, s_sc2, s_pidx);
   for (int j = threadIdx.x; j < C; j += blockDim.x) {
-    int64_t p = p_idx.at((bh * n2q + P) * p_topk + j / bs);
+    int64_t p = FUSED ? (int64_t) s_pidx[j / bs] : p_idx.at((bh * n2q + P) * p_topk + j / bs);
     p = p < 0 ? 0 : (p >= n2 ? n2 - 1 : p);      // never read outside the tensor
     // a parent listed twice (possible only in a caller-made p_idx) contributes its children once: the selection
     // below relies on distinct candidate blocks; the repeats are marked unused (-1)
     bool repeat = false;
     for (int u = 0; u < j / bs; ++u) {
-      int64_t pu = p_idx.at((bh * n2q + P) * p_topk + u);
+      int64_t pu = FUSED ? (int64_t) s_pidx[u] : p_idx.at((bh * n2q + P) * p_topk + u);
       pu = pu < 0 ? 0 : (pu >= n2 ? n2 - 1 : pu);
       repeat = repeat || pu == p;
     }
@@ -506,16 +566,59 @@ extern "C" int llsa_refine_topk(const LlsaTensor* pq1, const LlsaTensor* pk1, co
   if (pq1->dtype == LLSA_F32) {
     LLSA_SMEM_LIMIT((refine_topk_kernel<float, false>), smem);
     refine_topk_kernel<float, false><<<grid, 128, smem, st>>>((const float*) pq1->ptr, (const float*) pk1->ptr, make_idx(p_idx), idx->ptr,
-                                                              idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
+                                                              idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs, FusedCoarse{});
   } else if (D == 64 && bs == 16 && p_topk % 2 == 0 && ((uintptr_t) pq1->ptr % 32) == 0 && ((uintptr_t) pk1->ptr % 32) == 0) {
     LLSA_SMEM_LIMIT((refine_topk_kernel<__nv_bfloat16, true>), smem);
     refine_topk_kernel<__nv_bfloat16, true><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
-                                                                     make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
+                                                                     make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs, FusedCoarse{});
   } else {
     LLSA_SMEM_LIMIT((refine_topk_kernel<__nv_bfloat16, false>), smem);
     refine_topk_kernel<__nv_bfloat16, false><<<grid, 128, smem, st>>>((const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr,
-                                                                      make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs);
+                                                                      make_idx(p_idx), idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk, p_topk, bs, FusedCoarse{});
   }
   LLSA_LAUNCH_OK("refine_topk_kernel");
+  return LLSA_OK;
+}
+
+extern "C" int llsa_select_two_level(const LlsaTensor* pq1, const LlsaTensor* pk1, const LlsaTensor* pq2, const LlsaTensor* pk2,
+                                     const LlsaTensor* p_idx, const LlsaTensor* idx, int topk, int p_topk, int block_size, void* stream) {
+  LLSA_REQUIRE(pq1 && pk1 && pq2 && pk2 && p_idx && idx, LLSA_ERR_NULL, "select_two_level: null tensor");
+  // the fused form covers the benchmark class: bf16, D = 64, block 16, exactly 64 level-2 keys, at most 8 parents per row
+  const bool fusable = pq1->ptr && pk1->ptr && pq2->ptr && pk2->ptr && p_idx->ptr && idx->ptr && pq1->dtype == LLSA_BF16 && pq1->ndim == 4 &&
+                       pk2->ndim == 4 && pq1->shape[3] == 64 && block_size == 16 && pk2->shape[2] == 64 && p_topk >= 2 && p_topk <= kCmTop &&
+                       p_topk % 2 == 0 && ((uintptr_t) pq1->ptr % 32) == 0 && ((uintptr_t) pk1->ptr % 32) == 0 &&
+                       ((uintptr_t) pq2->ptr % 32) == 0 && ((uintptr_t) pk2->ptr % 32) == 0;
+  if (!fusable) {
+    int rc = llsa_coarse_topk(pq2, pk2, p_idx, p_topk, stream);
+    if (rc) return rc;
+    return llsa_refine_topk(pq1, pk1, p_idx, idx, topk, p_topk, block_size, stream);
+  }
+  const int64_t B = pq1->shape[0], H = pq1->shape[1], M = pq1->shape[2], D = 64, Mk = pk1->shape[2];
+  const int bs = block_size;
+  LLSA_REQUIRE(pk1->dtype == LLSA_BF16 && pq2->dtype == LLSA_BF16 && pk2->dtype == LLSA_BF16, LLSA_ERR_DTYPE, "select_two_level: all pooled tensors must be bf16");
+  LLSA_REQUIRE(is_index_dtype(idx->dtype) && is_index_dtype(p_idx->dtype), LLSA_ERR_DTYPE, "select_two_level: index tensors must be i32 or i64");
+  LLSA_REQUIRE(M % bs == 0 && Mk == 64 * bs, LLSA_ERR_SHAPE, "select_two_level: M=%lld / Mk=%lld do not fit 64 level-2 keys", (long long) M, (long long) Mk);
+  LLSA_REQUIRE(topk >= 1 && topk <= p_topk * bs, LLSA_ERR_ARG, "select_two_level: bad topk=%d / p_topk=%d", topk, p_topk);
+  const int64_t sq[4] = {B, H, M, D}, sk[4] = {B, H, Mk, D}, sq2[4] = {B, H, M / bs, D}, sk2[4] = {B, H, 64, D}, sp[4] = {B, H, M / bs, p_topk},
+                si[4] = {B, H, M, topk};
+  int rc;
+  if ((rc = check_contig(pq1, "pq1", LLSA_BF16, 4, sq))) return rc;
+  if ((rc = check_contig(pk1, "pk1", LLSA_BF16, 4, sk))) return rc;
+  if ((rc = check_contig(pq2, "pq2", LLSA_BF16, 4, sq2))) return rc;
+  if ((rc = check_contig(pk2, "pk2", LLSA_BF16, 4, sk2))) return rc;
+  if ((rc = check_contig(p_idx, "p_idx", p_idx->dtype, 4, sp))) return rc;
+  if ((rc = check_contig(idx, "idx", idx->dtype, 4, si))) return rc;
+  if (B * H * M == 0) return LLSA_OK;
+  const size_t smem = ((size_t) bs * D + (size_t) bs * p_topk * bs + (size_t) p_topk * bs) * 4;
+  FusedCoarse f;
+  f.pq2 = (const __nv_bfloat16*) pq2->ptr;
+  f.pk2 = (const __nv_bfloat16*) pk2->ptr;
+  f.pidx_out = p_idx->ptr;
+  f.pidx64 = p_idx->dtype == LLSA_I64;
+  LLSA_SMEM_LIMIT((refine_topk_kernel<__nv_bfloat16, true, true>), smem);
+  refine_topk_kernel<__nv_bfloat16, true, true><<<dim3((unsigned) (M / bs), (unsigned) (B * H)), 128, smem, (cudaStream_t) stream>>>(
+      (const __nv_bfloat16*) pq1->ptr, (const __nv_bfloat16*) pk1->ptr, IdxView{nullptr, 0}, idx->ptr, idx->dtype == LLSA_I64, M, Mk, (int) D, topk,
+      p_topk, bs, f);
+  LLSA_LAUNCH_OK("refine_topk_kernel<fused>");
   return LLSA_OK;
 }

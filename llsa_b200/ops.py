@@ -396,6 +396,23 @@ def _refine_topk(pq, pk, p_indices, topk, p_topk, block_size) -> torch.Tensor:
     return idx
 
 
+def _select_two_level(pq, pk, pq2, pk2, topk, p_topk, block_size):
+    """(indices, p_indices) of the two-level operator: gen_sparse_indices on the level-2 pooled tensors followed by
+    compute_topk_indices_sparse (torch_op/flash_sparse_attention_res_2.py:14-16), one launch where the shape allows."""
+    _need_cuda(pq, pk, pq2, pk2)
+    _check_float(pq, pk, pq2, pk2)
+    pq, pk, pq2, pk2 = pq.contiguous(), pk.contiguous(), pq2.contiguous(), pk2.contiguous()
+    p_topk = min(p_topk, pk2.shape[2])
+    p_indices = torch.empty((*pq2.shape[:3], p_topk), device=pq.device, dtype=torch.int32)
+    indices = torch.empty((*pq.shape[:3], topk), device=pq.device, dtype=torch.int32)
+    _mark("select_two_level")
+    with torch.cuda.device(pq.device):
+        a, b, c, d, e, f = desc(pq), desc(pk), desc(pq2), desc(pk2), desc(p_indices), desc(indices)
+        _lib.check(_lib.lib().llsa_select_two_level(ref(a), ref(b), ref(c), ref(d), ref(e), ref(f), topk, p_topk, block_size, _stream(pq)),
+                   "select_two_level")
+    return indices, p_indices
+
+
 def compute_topk_indices_sparse(pq, pk, p_indices, topk=8, p_topk=8, block_size=16) -> torch.Tensor:
     """Fine top-k among the children of the selected parent blocks; int32
     [B,H,M,topk].  Mirrors compute_topk_indices_sparse (triton/topk.py:172-197)."""
@@ -629,8 +646,7 @@ class _FlashSparseResidualAttentionL2(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, pq, pk, pv, pq2, pk2, pv2, topk, topk2, token_weight=1, token_weight_2=1, block_size=16):
-        p_indices = _coarse_topk(pq2, pk2, topk2)
-        indices = _refine_topk(pq, pk, p_indices, topk, topk2, block_size)
+        indices, p_indices = _select_two_level(pq, pk, pq2, pk2, topk, topk2, block_size)
         o, m = _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk2, block_size, token_weight, token_weight_2)
         ctx.save_for_backward(q, k, v, pk, pv, pk2, pv2, o, m, indices, p_indices)
         ctx.cfg = (topk, topk2, block_size, token_weight, token_weight_2)
@@ -701,8 +717,7 @@ _llsa_l1_fwd.register_autograd(_l1_backward, setup_context=_l1_setup)
 @torch.library.custom_op("llsa_b200::llsa_l2_fwd", mutates_args=())
 def _llsa_l2_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, topk1: int, topk2: int, block_size: int) -> List[torch.Tensor]:
     (pq, pk, pv), (pq2, pk2, pv2) = pool_pyramid([q, k, v], block_size, 2)
-    p_indices = _coarse_topk(pq2, pk2, topk2)
-    indices = _refine_topk(pq, pk, p_indices, topk1, p_indices.shape[-1], block_size)
+    indices, p_indices = _select_two_level(pq, pk, pq2, pk2, topk1, topk2, block_size)
     o, lse = _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk1, p_indices.shape[-1], block_size,
                        float(block_size), float(block_size * block_size))
     return [o, lse, indices, p_indices, pk, pv, pk2, pv2]
@@ -761,8 +776,7 @@ def _llsa_rope_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, freq: torc
     bs = block_size
     if levels == 2:
         pq2, pk2, pv2 = l2
-        p_indices = _coarse_topk(pq2, pk2, topk2)
-        indices = _refine_topk(pq, pk, p_indices, topk1, p_indices.shape[-1], bs)
+        indices, p_indices = _select_two_level(pq, pk, pq2, pk2, topk1, topk2, bs)
         o, lse = _attn_fwd(qr, kr, v, pk, pv, pk2, pv2, indices, p_indices, topk1, p_indices.shape[-1], bs, float(bs), float(bs * bs))
         return [o, lse, qr, kr, indices, pk, pv, p_indices, pk2, pv2]
     indices = _coarse_topk(pq, pk, topk1)
@@ -829,8 +843,7 @@ class _LlsaRmsRope(torch.autograd.Function):
         vd = v.detach()
         if levels == 2:
             pq2, pk2, pv2 = l2
-            p_indices = _coarse_topk(pq2, pk2, topk2)
-            indices = _refine_topk(pq, pk, p_indices, topk1, p_indices.shape[-1], bs)
+            indices, p_indices = _select_two_level(pq, pk, pq2, pk2, topk1, topk2, bs)
             o, lse = _attn_fwd(qr, kr, vd, pk, pv, pk2, pv2, indices, p_indices, topk1, p_indices.shape[-1], bs, float(bs), float(bs * bs))
             extra = [p_indices, pk2, pv2]
         else:
