@@ -147,11 +147,12 @@ int llsa_transpose_indices(const LlsaTensor* idx, const LlsaTensor* offsets, con
  * indices_transpose.py:70-78):
  *   pairs  [B,H,M*T] (I32): in the order of `flat`, the position m*T + t of each entry inside its head's idx
  *          (flat = pairs / T); finds what the query-major stage left for each (query block, selected block) pair;
- *   ranges [B,H,ceil(M*T/S),2] (I32), S = llsa_transpose_range_entries(): the entry list cut into the work ranges of
+ *   ranges [B,H,ceil(M*T/S),2] (I32), S = llsa_transpose_range_entries(B,H,M,T) (32, or 16 for problems too small to fill
+ *          the GPU with 32; the tensor's length tells the library which): the entry list cut into the work ranges of
  *          the dK/dV kernel, (first entry, bucket of that entry) per range.  Range r nominally starts at entry S r;
  *          where that entry lies inside a bucket of at most S entries the range starts at the bucket's first entry
  *          instead, so that only longer buckets are ever split (at multiples of S).  Range r ends where r+1 starts. */
-int llsa_transpose_range_entries(void);
+int llsa_transpose_range_entries(int64_t B, int64_t H, int64_t M, int64_t T);
 int llsa_transpose_indices_pairs(const LlsaTensor* idx, const LlsaTensor* offsets, const LlsaTensor* flat, const LlsaTensor* pairs,
                                  const LlsaTensor* ranges, int64_t n_kv, void* scratch, size_t scratch_bytes, int32_t* status,
                                  void* stream);

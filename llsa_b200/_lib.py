@@ -66,6 +66,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.llsa_coarse_topk.argtypes = [TP, TP, TP, C.c_int, C.c_void_p]
     lib.llsa_refine_topk.argtypes = [TP, TP, TP, TP, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.llsa_select_two_level.argtypes = [TP, TP, TP, TP, TP, TP, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.llsa_transpose_range_entries.argtypes = [C.c_int64] * 4
     lib.llsa_transpose_scratch_bytes.argtypes = [C.c_int64] * 5
     lib.llsa_transpose_scratch_bytes.restype = C.c_size_t
     lib.llsa_transpose_indices.argtypes = [TP, TP, TP, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]

@@ -78,7 +78,9 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
                    "attn_bwd: fine_pds holds %lld elements, %lld needed", (long long) have, (long long) need);
       LLSA_REQUIRE(g->flat_pairs && g->flat_ranges, LLSA_ERR_WORKSPACE, "attn_bwd: flat_pairs / flat_ranges missing (llsa_transpose_indices_pairs)");
       if ((rc = check_contig(g->flat_pairs, "flat_pairs", LLSA_I32, 3, sf))) return rc;
-      const int64_t sr[4] = {B, H, (nq1 * g->topk + kRangeEntries - 1) / kRangeEntries, 2};
+      LLSA_REQUIRE(g->flat_ranges->ndim == 4 && range_entries_of(nq1 * g->topk, g->flat_ranges->shape[2]) > 0, LLSA_ERR_SHAPE,
+                   "attn_bwd: flat_ranges must be the [B,H,R,2] ranges tensor of llsa_transpose_indices_pairs");
+      const int64_t sr[4] = {B, H, g->flat_ranges->shape[2], 2};
       if ((rc = check_contig(g->flat_ranges, "flat_ranges", LLSA_I32, 4, sr))) return rc;
     }
     if (two) {
@@ -96,7 +98,7 @@ using namespace llsa;
 
 extern "C" int64_t llsa_attn_bwd_partial_elems(int64_t B, int64_t H, int64_t Nq, int32_t topk) {
   if (B <= 0 || H <= 0 || Nq <= 0 || topk <= 0) return 0;
-  const int64_t ranges = (Nq / kBS * topk + kRangeEntries - 1) / kRangeEntries;
+  const int64_t ranges = (Nq / kBS * topk + kRangeEntriesSmall - 1) / kRangeEntriesSmall;     // sized for the smaller of the two range sizes
   return B * H * ((ranges + 3) / 4) * 4096;          // a head and a tail tile (2048 floats each) per CTA of four ranges
 }
 

@@ -36,6 +36,7 @@ struct AttnP {
   int off64;
   const int32_t* flat;  // [BH, nq1*topk]
   const int32_t* pairs; // [BH, nq1*topk]: position qb*topk + slot of each CSR entry inside the head's index list, or nullptr
+  int range_entries;    // nominal entries per work range (32, or 16 for small problems)
   const int2* ranges;   // [BH, ceil(nq1*topk / 32)]: (first entry, its bucket) of every work range of the fine dK/dV kernel, or nullptr
   uint4* pds;           // [BH*nq1*topk][2][32]: P^T and dS^T (bf16) of every (query block, selected block) pair as the
                         // A-operand registers of the dK/dV products, one uint4 per lane; nullptr: not handed over
@@ -151,6 +152,7 @@ inline AttnP<T> build_attn_params(const LlsaAttnArgs* g, bool bwd) {
     a.pairs = g->flat_pairs ? (const int32_t*) g->flat_pairs->ptr : nullptr;
     a.pds = g->fine_pds ? (uint4*) g->fine_pds->ptr : nullptr;
     a.ranges = g->flat_ranges ? (const int2*) g->flat_ranges->ptr : nullptr;
+    a.range_entries = g->flat_ranges ? range_entries_of(a.nq1 * a.topk, g->flat_ranges->shape[2]) : kRangeEntries;
     a.kvw1 = g->kv_weight;
     a.kvw2 = g->kv_weight_2;
     a.fold = g->fold_pool_bwd;

@@ -478,7 +478,6 @@ __device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) 
 // Accumulator layout (ldmatrix): tile u holds channels 8u + 2t, 8u + 2t + 1 of keys g (c0, c1) and g + 8 (c2, c3).
 constexpr int kRingWarps = 4;                   // warps per CTA, each on its own range; two CTAs per SM
 constexpr int kRingFineStages = 4;
-constexpr int kFineWindow = kRingWarps * kRangeEntries;      // nominal entries per CTA
 constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16);           // Q tile, dO tile
 constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
 
@@ -595,7 +594,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(
   unsigned char* ring = smem + kRingWarps * kTileFloats * sizeof(float) + warp * kWarpBytes;
   const int64_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const int E = (int) (a.nq1 * a.topk), n1 = (int) a.n1;
-  const int R = (E + kRangeEntries - 1) / kRangeEntries;
+  const int R = (E + a.range_entries - 1) / a.range_entries;
   // entries the CSR really holds: fewer than E when the transpose dropped out-of-range indices; ranges and offsets handed in
   // by a caller are not trusted further than these clamps and the bounds on the bucket walk below
   const int E_used = (int) min((int64_t) E, max((int64_t) 0, csr_off(a, bh, n1)));
@@ -787,7 +786,8 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
   const int64_t E = a.nq1 * a.topk;
   const int my_bo = lane < kFinishPerWarp ? (int) min(E, max((int64_t) 0, csr_off(a, bh, jl))) : 0;
   const int my_be = lane < kFinishPerWarp ? (int) min(E, max((int64_t) my_bo, csr_off(a, bh, jl + 1))) : 1;
-  const bool need = lane < kFinishPerWarp && j0 + lane < a.n1 && (my_be == my_bo || (my_be - my_bo > kRangeEntries && my_bo / kFineWindow != (my_be - 1) / kFineWindow));
+  const int range = a.range_entries, window = kRingWarps * range;       // nominal entries per warp / per CTA of the main kernel
+  const bool need = lane < kFinishPerWarp && j0 + lane < a.n1 && (my_be == my_bo || (my_be - my_bo > range && my_bo / window != (my_be - 1) / window));
   unsigned todo = __ballot_sync(0xffffffffu, need);
   if (!todo) return;
   const uint32_t st_sa = (uint32_t) __cvta_generic_to_shared(s_stage[warp]);
@@ -806,9 +806,9 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
     float dk[8][4], dv[8][4];
     tile_zero(dk, dv);
     if (be > bo) {
-      // a bucket of more than kRangeEntries entries is cut at multiples of kRangeEntries only, so its pieces by windows lie
-      // between multiples of kFineWindow: the first is the tail of the window that holds entry bo, every later one a head
-      const int c_first = bo / kFineWindow, c_last = min((be - 1) / kFineWindow, n_windows - 1);
+      // a bucket of more than `range` entries is cut at multiples of `range` only, so its pieces by windows lie
+      // between multiples of `window`: the first is the tail of the window that holds entry bo, every later one a head
+      const int c_first = bo / window, c_last = min((be - 1) / window, n_windows - 1);
       for (int c = c_first; c <= c_last; ++c)
         tile_add_mem_batched(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
     }
@@ -879,7 +879,7 @@ int launch_attn_bwd_mma(const LlsaAttnArgs* g, cudaStream_t st) {
   }
   if (mask & 4) {
     const int64_t E = a.nq1 * a.topk;
-    const int n_ranges = (int) ((E + kRangeEntries - 1) / kRangeEntries), n_windows = (n_ranges + kRingWarps - 1) / kRingWarps;
+    const int n_ranges = (int) ((E + a.range_entries - 1) / a.range_entries), n_windows = (n_ranges + kRingWarps - 1) / kRingWarps;
     float* partial = (float*) g->dkv_partial->ptr;
     const size_t smem = (size_t) kRingWarps * (kTileFloats * sizeof(float) + kRingFineStages * kRingFineStageBytes + kRingFoldBytes) + 128;   // per warp: slot, ring, gradient rows
     LLSA_SMEM_LIMIT((attn_dkv_fine_ring_kernel), smem);

@@ -49,6 +49,15 @@ int raise_smem_limit(const void* kernel, size_t bytes);
 // Nominal entries per work range of the fine dK/dV kernel: the index transpose cuts the CSR entry list into ranges of this
 // many entries (transpose.cu), one warp of attn_dkv_fine_ring_kernel walks one range (attn_bwd_mma.cu).
 constexpr int kRangeEntries = 32;
+// Small problems (fewer ranges than about two rounds of the GPU's resident warps) are cut into ranges of half that size, so
+// that the dK/dV kernel still fills the SMs: the range size travels with the `ranges` tensor, whose length names it.
+constexpr int kRangeEntriesSmall = 16;
+// Range size S that a ranges tensor of R ranges over E entries was cut with (0: neither size fits)
+inline int range_entries_of(int64_t E, int64_t R) {
+  if ((E + kRangeEntries - 1) / kRangeEntries == R) return kRangeEntries;
+  if ((E + kRangeEntriesSmall - 1) / kRangeEntriesSmall == R) return kRangeEntriesSmall;
+  return 0;
+}
 
 inline size_t dtype_size(int dt) {
   switch (dt) {

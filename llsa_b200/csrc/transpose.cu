@@ -28,7 +28,8 @@ struct TransposeArgs {
   int off64;
   int32_t* flat;    // [BH, M*T]
   int32_t* pairs;   // [BH, M*T] or nullptr: entry position m*T + t in the order of `flat`
-  int2* ranges;     // [BH, ceil(M*T / kRangeEntries)] or nullptr: (first entry, its bucket) of the work ranges cut for the dK/dV kernel
+  int2* ranges;     // [BH, ceil(M*T / range_entries)] or nullptr: (first entry, its bucket) of the work ranges cut for the dK/dV kernel
+  int range_entries;
   int64_t E;        // entries per head
   int T;
   int64_t n_kv;
@@ -129,9 +130,9 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
   __syncthreads();
   // ranges that lie wholly behind the last entry (entries were dropped, or E is not a multiple of the range size) are empty
   if (a.ranges) {
-    const int64_t R = (E + kRangeEntries - 1) / kRangeEntries;
+    const int64_t R = (E + a.range_entries - 1) / a.range_entries;
     for (int64_t r = threadIdx.x; r < R; r += blockDim.x)
-      if (r * kRangeEntries >= carry) a.ranges[bh * R + r] = make_int2(carry, (int) n - 1);
+      if (r * a.range_entries >= carry) a.ranges[bh * R + r] = make_int2(carry, (int) n - 1);
   }
 
   // ---- 3: stable fill
@@ -151,13 +152,13 @@ __global__ void __launch_bounds__(1024) transpose_kernel(TransposeArgs a) {
       if (pos < E) {
         a.flat[bh * E + pos] = (int32_t) (e / a.T);
         if (a.pairs) a.pairs[bh * E + pos] = (int32_t) e;
-        // Work ranges of the dK/dV kernel: nominally kRangeEntries entries each, but a bucket of at most that many entries is
+        // Work ranges of the dK/dV kernel: nominally S = range_entries entries each, but a bucket of at most S entries is
         // never cut -- the range that would begin inside it begins at the bucket's first entry instead (ranges then hold
-        // 1 .. 2 kRangeEntries - 1 entries); only longer buckets are cut, at multiples of kRangeEntries.  The entry that lands
-        // on such a multiple knows its bucket and that bucket's extent.
-        if (a.ranges && pos % kRangeEntries == 0) {
-          const int b0 = base[key], b1 = key + 1 < n ? base[key + 1] : total_entries;
-          a.ranges[bh * ((E + kRangeEntries - 1) / kRangeEntries) + pos / kRangeEntries] = make_int2(b1 - b0 <= kRangeEntries ? b0 : pos, (int) key);
+        // 1 .. 2 S - 1 entries); only longer buckets are cut, at multiples of S.  The entry that lands on such a multiple knows
+        // its bucket and that bucket's extent.
+        if (a.ranges && pos % a.range_entries == 0) {
+          const int S = a.range_entries, b0 = base[key], b1 = key + 1 < n ? base[key + 1] : total_entries;
+          a.ranges[bh * ((E + S - 1) / S) + pos / S] = make_int2(b1 - b0 <= S ? b0 : pos, (int) key);
         }
       }
     }
@@ -189,7 +190,10 @@ static int plan_transpose(int64_t n_kv, int64_t E, size_t* smem, bool* global) {
 
 using namespace llsa;
 
-extern "C" int llsa_transpose_range_entries(void) { return kRangeEntries; }
+extern "C" int llsa_transpose_range_entries(int64_t B, int64_t H, int64_t M, int64_t T) {
+  const int64_t ranges = B * H * ((M * T + kRangeEntries - 1) / kRangeEntries);
+  return ranges < 2 * 148 * 8 * 2 ? kRangeEntriesSmall : kRangeEntries;      // fewer than two rounds of the dK/dV kernel's resident warps
+}
 
 extern "C" size_t llsa_transpose_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t T, int64_t n_kv) {
   size_t smem;
@@ -214,8 +218,15 @@ static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, cons
   if ((rc = check_contig(offsets, "offsets", offsets->dtype, 3, so))) return rc;
   if ((rc = check_contig(flat, "flat", LLSA_I32, 3, sf))) return rc;
   if (pairs && (rc = check_contig(pairs, "pairs", LLSA_I32, 3, sf))) return rc;
-  const int64_t sr[4] = {B, H, (E + kRangeEntries - 1) / kRangeEntries, 2};
-  if (ranges && (rc = check_contig(ranges, "ranges", LLSA_I32, 4, sr))) return rc;
+  int S = kRangeEntries;
+  if (ranges) {
+    LLSA_REQUIRE(ranges->ndim == 4, LLSA_ERR_SHAPE, "transpose_indices_pairs: ranges must be [B,H,R,2]");
+    S = range_entries_of(E, ranges->shape[2]);
+    LLSA_REQUIRE(S > 0, LLSA_ERR_SHAPE, "transpose_indices_pairs: ranges holds %lld ranges; expected ceil(%lld / %d) or ceil(%lld / %d)",
+                 (long long) ranges->shape[2], (long long) E, kRangeEntries, (long long) E, kRangeEntriesSmall);
+    const int64_t sr[4] = {B, H, (E + S - 1) / S, 2};
+    if ((rc = check_contig(ranges, "ranges", LLSA_I32, 4, sr))) return rc;
+  }
   // the per-key prefixes over the segments are 16-bit: with distinct keys inside a row a key occurs at most M times per head
   LLSA_REQUIRE(M <= 65535, LLSA_ERR_SHAPE, "transpose_indices: M=%lld query blocks per head exceed the supported 65535", (long long) M);
   if (B * H == 0) return LLSA_OK;
@@ -230,6 +241,7 @@ static int transpose_impl(const LlsaTensor* idx, const LlsaTensor* offsets, cons
   a.flat = (int32_t*) flat->ptr;
   a.pairs = pairs ? (int32_t*) pairs->ptr : nullptr;
   a.ranges = ranges ? (int2*) ranges->ptr : nullptr;
+  a.range_entries = S;
   a.E = E;
   a.T = (int) T;
   a.n_kv = n_kv;
@@ -338,6 +350,7 @@ extern "C" int llsa_transpose_indices_noalloc(const LlsaTensor* idx, const LlsaT
   a.flat = (int32_t*) flat->ptr;
   a.pairs = nullptr;
   a.ranges = nullptr;
+  a.range_entries = kRangeEntries;
   a.E = E;
   a.T = (int) T;
   a.n_kv = n_kv;

@@ -424,7 +424,7 @@ def _transpose(idx: torch.Tensor, k_ntx: int, offsets_dtype, want_pairs: bool):
     offsets = torch.empty((B, H, k_ntx + 1), device=idx.device, dtype=offsets_dtype)
     lists = torch.empty((2 if want_pairs else 1, B, H, M * T), device=idx.device, dtype=torch.int32)
     flat, pairs = lists[0], (lists[1] if want_pairs else None)
-    S = _lib.lib().llsa_transpose_range_entries()
+    S = _lib.lib().llsa_transpose_range_entries(B, H, M, T)
     ranges = torch.empty((B, H, (M * T + S - 1) // S, 2), device=idx.device, dtype=torch.int32) if want_pairs else None
     status = _new_status(idx.device)
     _mark("transpose_indices")

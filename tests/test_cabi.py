@@ -176,8 +176,8 @@ def test_reference_import_paths_resolve_to_this_package():
 
 def test_bwd_partial_scratch_size():
     L = _lib.lib()
-    S = L.llsa_transpose_range_entries()
-    assert L.llsa_attn_bwd_partial_elems(8, 6, 16384, 8) == 8 * 6 * (8192 // S // 4) * 4096      # a CTA of the dK/dV kernel owns four ranges
-    assert L.llsa_attn_bwd_partial_elems(1, 1, 256, 8) == 4096
+    assert L.llsa_transpose_range_entries(8, 6, 1024, 8) == 32 and L.llsa_transpose_range_entries(1, 6, 1024, 8) == 16
+    assert L.llsa_attn_bwd_partial_elems(8, 6, 16384, 8) == 8 * 6 * (8192 // 16 // 4) * 4096     # sized for 16-entry ranges, four per CTA
+    assert L.llsa_attn_bwd_partial_elems(1, 1, 256, 8) == 2 * 4096
     assert L.llsa_attn_bwd_pds_elems(1, 1, 256, 8) == 16 * 8 * 256                  # 1 KB per (query block, selected block) pair
     assert L.llsa_attn_bwd_partial_elems(0, 6, 16384, 8) == 0

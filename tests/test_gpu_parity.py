@@ -167,9 +167,9 @@ def test_transpose_pairs_and_work_ranges():
     """The two extra lists of llsa_transpose_indices_pairs: pairs names each entry's (query block, slot); ranges cuts the
     entry list at multiples of the range size S, moved back to a bucket's start where the bucket holds at most S entries."""
     from llsa_b200 import _lib, ops
-    S = _lib.lib().llsa_transpose_range_entries()
     gen = torch.Generator().manual_seed(7)
     M, T = 2048, 8
+    S = _lib.lib().llsa_transpose_range_entries(1, 3, M, T)
     hot = torch.randint(0, 24, (1, 3, M, T // 2), generator=gen)               # a few very long buckets
     cold = torch.randint(0, M, (1, 3, M, T - T // 2), generator=gen)
     idx = torch.cat([hot, cold], -1).to(torch.int32)
