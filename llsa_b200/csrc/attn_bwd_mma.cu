@@ -665,6 +665,15 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(
     const char* d_lane = reinterpret_cast<const char*>(a.d_o.row(b, h, lane >> 3) + (lane & 7) * 8);
     const int qblk = (int) (kBS * a.q.sn * sizeof(bf16)), dblk = (int) (kBS * a.d_o.sn * sizeof(bf16));
     const int qstep = (int) (4 * a.q.sn * sizeof(bf16)), dstep = (int) (4 * a.d_o.sn * sizeof(bf16));
+    // the P / dS registers of the whole range come from HBM (the hand-over does not fit the L2): every lane pulls its own
+    // entries' 1 KB towards L2 now, so that the loads three entries ahead find them there
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (lane + 32 * u < n) {
+        const char* pf = reinterpret_cast<const char*>(a.pds + (bh * (int64_t) E + my_pair[u]) * 64);
+#pragma unroll
+        for (int l = 0; l < 8; ++l) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf + 128 * l));
+      }
     const uint4* pds_lane = a.pds + bh * (int64_t) E * 64 + lane;
     uint4 pP[kRingFineStages], pD[kRingFineStages];       // P^T / dS^T registers of the entries in flight
     auto issue = [&](auto stage_tag, int i) {
@@ -720,19 +729,22 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(
       const uint4 P = pP[S], D = pD[S];
       if (i + kRingFineStages - 1 < n) issue(std::integral_constant<int, SF>{}, i + kRingFineStages - 1);
       cp_async_commit();
+      // all eight operand loads first, then the sixteen products: the statements are issued in this order, and a product
+      // issued right behind its own load would wait out the load's latency eight times per entry
+      uint32_t bd[4][4], bq[4][4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ldsm_x4_trans<SB + TB>(bd[c][0], bd[c][1], bd[c][2], bd[c][3], sa_m[c]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ldsm_x4_trans<SB>(bq[c][0], bq[c][1], bq[c][2], bq[c][3], sa_m[c]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r0, r1, r2, r3;
-        ldsm_x4_trans<SB + TB>(r0, r1, r2, r3, sa_m[c]);
-        mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, r0, r1);
-        mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, r2, r3);
+        mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, bd[c][0], bd[c][1]);
+        mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, bd[c][2], bd[c][3]);
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r0, r1, r2, r3;
-        ldsm_x4_trans<SB>(r0, r1, r2, r3, sa_m[c]);
-        mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, r0, r1);
-        mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, r2, r3);
+        mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, bq[c][0], bq[c][1]);
+        mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, bq[c][2], bq[c][3]);
       }
     };
     for (int i = 0; i < n; i += 4) {
