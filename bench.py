@@ -337,7 +337,7 @@ def main():
     for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
         if name != "end":
             per[name] = per.get(name, 0.0) + ev.elapsed_time(nxt)
-    per = {kname: max(tms, 0.0) / args.steps for kname, tms in per.items()}    # a stage moved to a side stream shows ~0 here
+    per = {kname: max(tms, 0.0) / args.steps for kname, tms in per.items()}
     if not seq_parallel:
         seq_ranks = 1
     units = n_slices * (N // seq_ranks) * D      # query rows x channels on this rank
@@ -386,7 +386,7 @@ def main():
                            step_launch="one CUDA graph replay per step (forward + backward captured once)" if use_graph else "eager launches",
                            timing="median of %d windows of %d steps (%.2f s timed); min %.4f / max %.4f ms per step" % (
                                len(windows), args.steps, sum(windows) * 1e-3, min(windows) / args.steps, max(windows) / args.steps),
-                           overlap="index transpose on a side stream next to the dQ / pooled backward stages (its kernel_ms entry is ~0)",
+                           overlap="index transpose on a side stream next to the dQ / pooled backward stages (kernel_ms times it alone, on the main stream)",
                            l2_policy="no flush: a step streams %.0f MB per GPU (q, k, v, do in, o, dq, dk, dv out: 8 x %.1f MB; P / dS scratch %.0f MB), "
                                      "%s the 126 MB L2" % (8 * units * 2 / 1e6 + nq1 * 8 * 1024 / 1e6, units * 2 / 1e6, nq1 * 8 * 1024 / 1e6,
                                                            "more than" if 8 * units * 2 + nq1 * 8 * 1024 > 126e6 else "LESS than (reads may hit L2)"),

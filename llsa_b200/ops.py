@@ -529,7 +529,7 @@ def _attn_bwd(do, q, k, v, pk, pv, pk2, pv2, o, lse, indices, p_indices, topk, t
     # The index transpose (one CTA per (b,h): a latency-bound kernel that leaves most SMs idle) is needed only by the fine
     # dK/dV stage, so it runs on a side stream next to the dQ and pooled stages.
     cur = torch.cuda.current_stream(q.device)
-    side = _side_stream(q.device) if _overlap_transpose else None
+    side = _side_stream(q.device) if _overlap_transpose and _stage_hook is None else None     # a stage hook times every stage on ONE stream
     n_kv = k.shape[2] // block_size                       # buckets = KEY blocks
     if side is not None:
         side.wait_stream(cur)
