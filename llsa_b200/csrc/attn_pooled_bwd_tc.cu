@@ -39,6 +39,8 @@
 // its loop, the host-visible status word is set and TMEM is freed.
 #include <string.h>
 
+#include <type_traits>
+
 #include "attn.cuh"
 #include "mma_frag.cuh"
 #include "tc05.cuh"
@@ -156,15 +158,20 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       // K-major operand: 32 bytes (2 units) per k-step of 16 channels inside the swizzled 128-byte row;
       // MN-major operand: 16 rows = 2048 bytes (128 units) per k-step.
       const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
-      auto lo = [](const void* p, uint32_t lbo_bytes) { return ((tc::smem_u32(p) >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16); };
-      constexpr uint32_t kStage = (uint32_t) (kTile * 2) >> 4;      // one 16 KB buffer further
+      // Every operand sits at a compile-time offset from the 1024-byte aligned base, and the address field counts 16-byte
+      // units below 2^14, so each low word is `sb` plus a constant: one live register instead of twenty.
+      const uint32_t sb = (tc::smem_u32(base) >> 4) & 0x3FFFu;
+      constexpr uint32_t kU = (uint32_t) (kTile * 2) >> 4;          // 16-byte units of one [128 x 64] tile
+      auto lo = [sb](uint32_t units, uint32_t lbo_bytes) { return sb + units + ((lbo_bytes >> 4) << 16); };
+      constexpr uint32_t kStage = kU;                                // one 16 KB buffer further
       constexpr uint32_t kT = kTile * 2;                             // bytes of a tile
-      const uint32_t lK2_k = lo(sK2, 16), lK2_m = lo(sK2, 1024), lV_k = lo(sV1, 16);                // [V1;V2] as N = 192 rows
-      const uint32_t lDS_k0 = lo(sP + 4 * kTile, 16), lDS_k1 = lo(sP + 5 * kTile, 16), lDS_k2 = lo(sP + 3 * kTile, 16);
-      const uint32_t lP1_m = lo(sP, kT), lDS1_m = lo(sP + 4 * kTile, kT), lP2_m = lo(sP + 2 * kTile, kT);   // M = 128 over two tiles
-      const uint32_t lQ_k0 = lo(sQ, 16), lDO_k0 = lo(sDO, 16), lQ_m0 = lo(sQ, 1024), lDO_m0 = lo(sDO, 1024);
-      const uint32_t lQDO_m0 = lo(sQ, 2 * kT);                       // N = 128: channels of Q, then of dO (32 KB further)
-      const uint32_t lK1_k0 = lo(sK1, 16), lK1_m0 = lo(sK1, 1024);
+      constexpr uint32_t uQ = 0, uDO = 2 * kU, uK1 = 4 * kU, uK2 = 6 * kU, uV1 = 6 * kU + kU / 2, uP = 8 * kU;
+      const uint32_t lK2_k = lo(uK2, 16), lK2_m = lo(uK2, 1024), lV_k = lo(uV1, 16);                // [V1;V2] as N = 192 rows
+      const uint32_t lDS_k0 = lo(uP + 4 * kU, 16), lDS_k1 = lo(uP + 5 * kU, 16), lDS_k2 = lo(uP + 3 * kU, 16);
+      const uint32_t lP1_m = lo(uP, kT), lDS1_m = lo(uP + 4 * kU, kT), lP2_m = lo(uP + 2 * kU, kT);   // M = 128 over two tiles
+      const uint32_t lQ_k0 = lo(uQ, 16), lDO_k0 = lo(uDO, 16), lQ_m0 = lo(uQ, 1024), lDO_m0 = lo(uDO, 1024);
+      const uint32_t lQDO_m0 = lo(uQ, 2 * kT);                       // N = 128: channels of Q, then of dO (32 KB further)
+      const uint32_t lK1_k0 = lo(uK1, 16), lK1_m0 = lo(uK1, 1024);
       auto issue_s = [&](int i) -> bool {          // S(i) = Q . [PK1 ; PK2]^T into columns [0,192)
         const int s = i & 1;
         if (!tc::bounded_wait(&bars.full[s], (i >> 1) & 1, abort_flag)) return false;
@@ -244,14 +251,13 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
     // ---------------------------------------------------------------- drain warpgroup
     const int qd = warp & 3, r = qd * 32 + lane;
     const uint32_t t_row = tmem + ((uint32_t) (qd * 32) << 16);
-    float va[32];
+    float va[16];
     auto red_cols = [&](float* dst, uint32_t col, float mul) {      // 64 columns of this lane -> dst[0..63]
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tc::tmem_ld32_async(t_row + col + 32 * half, va);
-        tc::tmem_ld_wait(va);
+      for (int c = 0; c < 4; ++c) {
+        tc::tmem_ld16(t_row + col + 16 * c, va);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) red_add_v4(dst + 32 * half + 4 * q, va[4 * q] * mul, va[4 * q + 1] * mul, va[4 * q + 2] * mul, va[4 * q + 3] * mul);
+        for (int q = 0; q < 4; ++q) red_add_v4(dst + 16 * c + 4 * q, va[4 * q] * mul, va[4 * q + 1] * mul, va[4 * q + 2] * mul, va[4 * q + 3] * mul);
       }
     };
     for (int i = 0; i < n_my; ++i) {
@@ -268,18 +274,17 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       tc::fence_after_sync();
       if (!ok) break;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tc::tmem_ld32_async(t_row + kColDQ + 32 * half, va);
-        tc::tmem_ld_wait(va);
+      for (int c = 0; c < 4; ++c) {
+        tc::tmem_ld16(t_row + kColDQ + 16 * c, va);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint4 f = old[4 * half + q];
+        for (int q = 0; q < 2; ++q) {
+          const uint4 f = old[2 * c + q];
           uint4 w;
           w.x = pack_bf16(bf16_lo(f.x) + va[8 * q], bf16_hi(f.x) + va[8 * q + 1]);
           w.y = pack_bf16(bf16_lo(f.y) + va[8 * q + 2], bf16_hi(f.y) + va[8 * q + 3]);
           w.z = pack_bf16(bf16_lo(f.z) + va[8 * q + 4], bf16_hi(f.z) + va[8 * q + 5]);
           w.w = pack_bf16(bf16_lo(f.w) + va[8 * q + 6], bf16_hi(f.w) + va[8 * q + 7]);
-          *reinterpret_cast<uint4*>(dqrow + 32 * half + 8 * q) = w;
+          *reinterpret_cast<uint4*>(dqrow + 16 * c + 8 * q) = w;
         }
       }
       tc::fence_before_sync();
@@ -304,9 +309,9 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
     const float sl2 = a.scale * kLog2eF;
     const float lw = log2f(wg < 2 ? a.w1 : a.w2);
     const uint32_t t_row = tmem + ((uint32_t) (qd * 32) << 16);
-    bf16* myP = sP + wg * kTile;
-    bf16* myDS = sP + (wg == 2 ? 3 : 4 + wg) * kTile;
-    float va[32];
+    // this thread's row in its P tile and its dS tile: start of the row with the swizzle of chunk 0 applied
+    const uint32_t myP = tc::smem_u32(sP + wg * kTile + tc::swz(r, 0));
+    const uint32_t myDS = tc::smem_u32(sP + (wg == 2 ? 3 : 4 + wg) * kTile + tc::swz(r, 0));
     float lse_n = 0.f, delta_n = 0.f;
     if (n_my > 0) {
       const int bh = t_begin / tiles_per_head, row = (t_begin % tiles_per_head) * kRows + r;
@@ -322,12 +327,12 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
       tc::fence_after_sync();
       if (!ok) break;
       uint32_t pk[32];          // this row's 64 probabilities, bf16 pairs, kept for dS
+      float vh[16];             // 16 columns at a time: the row's registers stay below the point where loop invariants spill
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tc::tmem_ld32_async(t_row + wg * 64 + 32 * half, va);
-        tc::tmem_ld_wait(va);
+      for (int c = 0; c < 4; ++c) {
+        tc::tmem_ld16(t_row + wg * 64 + 16 * c, vh);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) pk[16 * half + j] = pack_bf16(fast_exp2(fmaf(va[2 * j], sl2, off)), fast_exp2(fmaf(va[2 * j + 1], sl2, off)));
+        for (int j = 0; j < 8; ++j) pk[8 * c + j] = pack_bf16(fast_exp2(fmaf(vh[2 * j], sl2, off)), fast_exp2(fmaf(vh[2 * j + 1], sl2, off)));
       }
       tc::fence_before_sync();
       __syncwarp();
@@ -338,9 +343,14 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         tc::fence_after_sync();
         if (!ok) break;
       }
-#pragma unroll
-      for (int q = 0; q < 8; ++q)
-        *reinterpret_cast<uint4*>(myP + tc::swz(r, q)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      tc::sts128_xor<0>(myP, pk[0], pk[1], pk[2], pk[3]);
+      tc::sts128_xor<16>(myP, pk[4], pk[5], pk[6], pk[7]);
+      tc::sts128_xor<32>(myP, pk[8], pk[9], pk[10], pk[11]);
+      tc::sts128_xor<48>(myP, pk[12], pk[13], pk[14], pk[15]);
+      tc::sts128_xor<64>(myP, pk[16], pk[17], pk[18], pk[19]);
+      tc::sts128_xor<80>(myP, pk[20], pk[21], pk[22], pk[23]);
+      tc::sts128_xor<96>(myP, pk[24], pk[25], pk[26], pk[27]);
+      tc::sts128_xor<112>(myP, pk[28], pk[29], pk[30], pk[31]);
       ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.dp_ready, i & 1, abort_flag));
       tc::fence_after_sync();
       if (!ok) break;
@@ -349,22 +359,25 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         lse_n = a.lse[(int64_t) bhn * a.Nq + rown];
         delta_n = a.delta[(int64_t) bhn * a.Nq + rown];
       }
+      auto ds_chunk = [&](auto tag, int c) {          // dS of columns [16c, 16c+16): two 16-byte chunks of the row
+        constexpr int C = decltype(tag)::value;
+        uint32_t w[8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tc::tmem_ld32_async(t_row + wg * 64 + 32 * half, va);
-        tc::tmem_ld_wait(va);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 w;
-          uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t p2 = pk[half * 16 + 4 * q + e];
-            wp[e] = pack_bf16(bf16_lo(p2) * fmaf(va[8 * q + 2 * e], a.scale, -dls), bf16_hi(p2) * fmaf(va[8 * q + 2 * e + 1], a.scale, -dls));
-          }
-          *reinterpret_cast<uint4*>(myDS + tc::swz(r, half * 4 + q)) = w;
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t p2 = pk[8 * C + e];
+          w[e] = pack_bf16(bf16_lo(p2) * fmaf(vh[2 * e], a.scale, -dls), bf16_hi(p2) * fmaf(vh[2 * e + 1], a.scale, -dls));
         }
-      }
+        tc::sts128_xor<32 * C>(myDS, w[0], w[1], w[2], w[3]);
+        tc::sts128_xor<32 * C + 16>(myDS, w[4], w[5], w[6], w[7]);
+      };
+      tc::tmem_ld16(t_row + wg * 64, vh);
+      ds_chunk(std::integral_constant<int, 0>{}, 0);
+      tc::tmem_ld16(t_row + wg * 64 + 16, vh);
+      ds_chunk(std::integral_constant<int, 1>{}, 1);
+      tc::tmem_ld16(t_row + wg * 64 + 32, vh);
+      ds_chunk(std::integral_constant<int, 2>{}, 2);
+      tc::tmem_ld16(t_row + wg * 64 + 48, vh);
+      ds_chunk(std::integral_constant<int, 3>{}, 3);
       tc::fence_async_smem();          // P, dS must be visible to the tensor core's (async proxy) reads
       tc::fence_before_sync();
       __syncwarp();

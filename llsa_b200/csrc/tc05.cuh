@@ -192,6 +192,18 @@ __device__ __forceinline__ void tmem_ld_wait(float (&v)[32]) {
                :
                : "memory");
 }
+// 16 consecutive columns: half the registers of tmem_ld32 in flight
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 // registers -> TMEM: lane (32 * (warp % 4) + lane id) writes 16 consecutive 32-bit columns
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
@@ -202,6 +214,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 128-bit store to shared memory at (addr ^ XOR_BYTES): with addr = the swizzled start of a 128-byte row, XOR_BYTES = 16 * chunk
+// walks the row's chunks in swizzled order from ONE register (the address arithmetic stays inside the statement, so the
+// compiler cannot hoist eight precomputed addresses out of a loop and spill them).
+template <int XOR_BYTES>
+__device__ __forceinline__ void sts128_xor(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("{\n\t.reg .b32 t;\n\txor.b32 t, %0, %1;\n\tst.shared.v4.b32 [t], {%2, %3, %4, %5};\n\t}"
+               :
+               : "r"(addr), "n"(XOR_BYTES), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
 
 // ---- swizzled tile addressing (elements) ----
 __device__ __forceinline__ int swz(int r, int chunk) { return r * 64 + ((chunk ^ (r & 7)) << 3); }
