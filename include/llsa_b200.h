@@ -241,6 +241,14 @@ typedef struct LlsaAttnArgs {
                                   normally with LLSA_DEV_WAIT_EXPIRED in *status) */
   int32_t* status;             /* device int32 or NULL: kernels OR LlsaDeviceStatus bits into it; the
                                   caller zeroes it, and reads it back after synchronising */
+  const LlsaTensor* fwd_redo;  /* forward, optional: I32 scratch of at least B*H*N/4 elements (one byte per
+                                  query row; not read before it is written).  With it, a pooled stage
+                                  that walks a long pooled key list (more than 192 pooled keys per row)
+                                  makes ONE pass over the keys with the fine part's log-sum-exp as the
+                                  reference of its exponentials, marks here the rows whose pooled keys
+                                  outweigh the fine ones by more than 1e30, and a second launch redoes
+                                  exactly those rows with the exact two-pass form.  NULL: two passes for
+                                  every row.  Same results either way up to rounding */
 } LlsaAttnArgs;
 
 /* Forward: o, lse.  One level (pk2 == NULL) replaces sparse_indices_attn_res_fwd

@@ -36,6 +36,7 @@ class LlsaAttnArgs(C.Structure):
         ("fold_pool_bwd", C.c_int32), ("kv_weight", C.c_float), ("kv_weight_2", C.c_float),
         ("force_generic", C.c_int32), ("stage_mask", C.c_int32), ("dkv_partial", _P),
         ("fine_pds", _P), ("flat_pairs", _P), ("flat_ranges", _P), ("no_tcgen05", C.c_int32), ("wait_limit", C.c_int32), ("status", C.c_void_p),
+        ("fwd_redo", _P),
     ]
 
 

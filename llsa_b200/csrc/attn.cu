@@ -46,6 +46,13 @@ static int check_attn_args(const LlsaAttnArgs* g, bool bwd) {
   } else {
     LLSA_REQUIRE(n1 < 64 || n1 % 32 == 0, LLSA_ERR_SHAPE, "attn: N/16=%lld must be a multiple of 32", (long long) n1);
   }
+  if (!bwd && g->fwd_redo) {
+    int64_t have = 1;
+    for (int i = 0; i < g->fwd_redo->ndim; ++i) have *= g->fwd_redo->shape[i];
+    LLSA_REQUIRE(g->fwd_redo->ptr && g->fwd_redo->dtype == LLSA_I32 && is_contiguous(g->fwd_redo) && have * 4 >= B * H * Nq &&
+                     ((uintptr_t) g->fwd_redo->ptr % 4) == 0,
+                 LLSA_ERR_WORKSPACE, "attn_fwd: fwd_redo must be a contiguous I32 tensor of at least B*H*N/4 = %lld elements", (long long) ((B * H * Nq + 3) / 4));
+  }
   if (bwd) {
     LLSA_REQUIRE(g->d_o && g->dq && g->dk && g->dv && g->offsets && g->flat && g->delta && g->dpk_acc && g->dpv_acc, LLSA_ERR_NULL,
                  "attn_bwd: a required tensor is null");

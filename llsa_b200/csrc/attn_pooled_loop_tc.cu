@@ -9,6 +9,12 @@
 //   pass 1: S = Q.K_c^T per chunk, row maxima only;
 //   pass 2: S again, P = exp2(S*scale*log2e + log2 w - max) written back into TMEM over S (packed bf16) and used as
 //           the A operand of O += P.V_c; row sums on the side.
+// With a `redo` byte per query row from the caller the first pass is dropped: the pooled part only ever meets the fine
+// part through their log-sum-exp, so the fine part's log-sum-exp (already known per row) serves as the reference of the
+// exponentials, P = exp2(S' - lse_fine).  Anything below 2^-126 of the fine part's weight is irrelevant, and bf16 / fp32
+// hold anything up to 2^127 times it; a row whose pooled keys outweigh its fine keys by more than that (its row sum
+// passes 1e30, or is NaN) is left untouched and marked in `redo`, and a second launch of the two-pass form redoes
+// exactly the marked rows (it scans its tiles' marks first and returns at once when there are none).
 // Roles (one persistent CTA per SM, 10 warps):
 //   warp 8, one lane : TMA producer: Q per tile (2 stages), K chunks (ring of 3; every chunk is loaded in both
 //                      passes), V chunks (ring of 2, pass 2 only)
@@ -55,7 +61,7 @@ struct LoopBars {
 // contiguous pooled tensor.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps maps, int n_chunks, int gathered, int64_t n_c, int n_tiles,
-                               int tiles_per_head) {
+                               int tiles_per_head, int n_pass, unsigned char* redo) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ LoopBars bars;
   __shared__ uint32_t s_tmem;
@@ -67,6 +73,14 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
   bf16* sV = sK + kKStages * kTile;         // [kVStages][128][64]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   volatile tc::WaitCtl* abort_flag = &s_ctl;
+  const int n_my = (n_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x;
+  if (n_pass == 2 && redo) {
+    // the second launch: anything to redo in this CTA's tiles?  (a tile's 128 marks are 32 words)
+    int any = 0;
+    if (warp == 0)
+      for (int i = 0; i < n_my; ++i) any |= (int) reinterpret_cast<const uint32_t*>(redo)[(int64_t) (blockIdx.x + i * gridDim.x) * (kRows / 4) + lane];
+    if (!__syncthreads_or(any)) return;
+  }
 
   if (tid == 0) {
     s_ctl.abort = 0;
@@ -89,8 +103,9 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = s_tmem;
-  const int n_my = (n_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x;
-  const int jobs = 2 * n_chunks;            // per tile; even, so a job's buffer is its parity in every tile
+  // jobs per tile; job j of tile i has the CTA-wide number i * jobs + j, whose parity picks the S buffer and the softmax
+  // group (with one pass and an odd chunk count the parity of a tile's first job alternates)
+  const int jobs = n_pass * n_chunks, first_p2 = jobs - n_chunks;
 
   if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
@@ -109,7 +124,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         }
         bool ok = true;
         for (int j = 0; ok && j < jobs; ++j) {
-          const int c = j % n_chunks, pass = j / n_chunks;
+          const int c = j % n_chunks, pass = j >= first_p2;
           const int crow = (int) ((int64_t) bh * n_c + (int64_t) (c - gathered) * kChunk);      // contiguous chunk
           const int ks = kjob % kKStages;
           if (!(ok = tc::bounded_wait(&bars.k_empty[ks], ((kjob / kKStages) & 1) ^ 1, abort_flag))) break;
@@ -152,40 +167,41 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         const int qs = i & 1;
         if (!(ok = tc::bounded_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
         tc::fence_after_sync();
-        auto issue_s = [&](int j) -> bool {             // S of job j into buffer j & 1
+        auto issue_s = [&](int j) -> bool {             // S of job j into the buffer of its CTA-wide parity
           const int ks = kjob % kKStages;
           if (!tc::bounded_wait(&bars.k_full[ks], (kjob / kKStages) & 1, abort_flag)) return false;
           tc::fence_after_sync();
-          const uint32_t q_ = lQ + qs * kStage, k_ = lK + ks * kStage, d = tmem + (j & 1) * kChunk;
+          const int buf = (int) ((J + j) & 1);
+          const uint32_t q_ = lQ + qs * kStage, k_ = lK + ks * kStage, d = tmem + buf * kChunk;
           tc::umma_ss_lh<0>(d, q_, hi, k_, hi, id_s);
 #pragma unroll
           for (int s4 = 1; s4 < 4; ++s4) tc::umma_ss_lh<1>(d, q_ + 2 * s4, hi, k_ + 2 * s4, hi, id_s);
-          tc::umma_commit(&bars.s_ready[j & 1]);
+          tc::umma_commit(&bars.s_ready[buf]);
           tc::umma_commit(&bars.k_empty[ks]);
           ++kjob;
           return true;
         };
         auto issue_pv = [&](int j) -> bool {            // O (+)= P(job j, TMEM) . V chunk
-          const int vs = vjob % kVStages, c = j - n_chunks;
+          const int vs = vjob % kVStages, c = j - first_p2, buf = (int) ((J + j) & 1);
           if (!tc::bounded_wait(&bars.v_full[vs], (vjob / kVStages) & 1, abort_flag)) return false;
           if (c == 0 && i > 0 && !tc::bounded_wait(&bars.o_free, (i - 1) & 1, abort_flag)) return false;      // previous tile's O has been read
           tc::fence_after_sync();
           const uint64_t vdesc = ((uint64_t) hi << 32) | (uint64_t) (lV + vs * kStage);
 #pragma unroll
           for (int s8 = 0; s8 < 8; ++s8)       // P: 16 keys = 8 packed columns per k-step; V: 16 key rows = 2048 bytes
-            tc::umma_ts(tmem + kColO, tmem + (j & 1) * kChunk + s8 * 8, vdesc + 128 * s8, id_o, (c > 0 || s8 > 0) ? 1u : 0u);
+            tc::umma_ts(tmem + kColO, tmem + buf * kChunk + s8 * 8, vdesc + 128 * s8, id_o, (c > 0 || s8 > 0) ? 1u : 0u);
           tc::umma_commit(&bars.v_empty[vs]);
           ++vjob;
           return true;
         };
         for (int j = 0; ok && j < jobs; ++j) {
           if (j >= 2) {
-            // buffer j & 1 was used by job j - 2: wait until its group is done with it; a pass-2 job then feeds P.V,
+            // the buffer was used by job j - 2: wait until its group is done with it; a pass-2 job then feeds P.V,
             // which precedes the new S in issue order
             const int64_t Jp = J + j - 2;
-            if (!(ok = tc::bounded_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+            if (!(ok = tc::bounded_wait(&bars.wg_done[Jp & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
             tc::fence_after_sync();
-            if (j - 2 >= n_chunks && !(ok = issue_pv(j - 2))) break;
+            if (j - 2 >= first_p2 && !(ok = issue_pv(j - 2))) break;
           } else if (J > 0) {
             // first two jobs of a tile: the buffers' last users were the last two (pass-2) jobs of the previous tile,
             // whose P.V was issued at the end of that tile
@@ -195,7 +211,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         if (!ok) break;
         for (int j = jobs - 2; ok && j < jobs; ++j) {   // the last two jobs' P.V
           const int64_t Jp = J + j;
-          if (!(ok = tc::bounded_wait(&bars.wg_done[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.wg_done[Jp & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
           tc::fence_after_sync();
           ok = issue_pv(j);
         }
@@ -235,12 +251,13 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) of[q4] = *reinterpret_cast<const uint4*>(orow + 8 * q4);
       const float lse_f = a.lse[(int64_t) bh * a.Nq + row];
-      float mx = -INFINITY, lsum = 0.f;
+      // one pass: the fine part's log-sum-exp is the reference of the exponentials
+      float mx = n_pass == 1 ? lse_f * kLog2eF : -INFINITY, lsum = 0.f;
       bool ok = true;
-      for (int j = wg; j < jobs; j += 2) {
-        const int c = j % n_chunks, pass = j / n_chunks;
+      for (int j = (int) ((wg - (int64_t) i * jobs) & 1); j < jobs; j += 2) {
+        const int c = j % n_chunks, pass = j >= first_p2;
         const float lw = (gathered ? (c == 0) : !a.two_level) ? lw1 : lw2;
-        if (pass == 1 && j - 2 < n_chunks) {
+        if (n_pass == 2 && pass == 1 && j - 2 < first_p2) {
           // first pass-2 job of this group: exchange the row maxima of the two groups
           float other;
           if (!(ok = exchange(mx, other))) break;
@@ -287,6 +304,17 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         ok = exchange(lsum, other);
         lsum = wg == 0 ? lsum + other : other + lsum;          // the same order in both groups: identical bits
       }
+      // does this launch own the row?  One pass: unless its sum left the safe range (then the mark hands it to the
+      // second launch).  Second launch: only the marked rows.
+      bool mine = true;
+      if (redo) {
+        if (n_pass == 1) {
+          mine = lsum < 1e30f;                                  // false for NaN too
+          if (wg == 0 && ok) redo[(int64_t) bh * a.Nq + row] = mine ? 0 : 1;
+        } else {
+          mine = redo[(int64_t) bh * a.Nq + row] != 0;
+        }
+      }
       if (ok) {
         ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.o_ready, (uint32_t) (i & 1), abort_flag));
         tc::fence_after_sync();
@@ -298,7 +326,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         const float Lm = fmaxf(Lf, Lp);
         const float ef = fast_exp2(Lf - Lm), ep = fast_exp2(Lp - Lm);
         const float inv = 1.f / (ef + ep);
-        const float wf = ef * inv, wp = ep * inv / lsum;
+        const float wf = ef * inv, wp = lsum > 0.f ? ep * inv / lsum : 0.f;      // every exponential may have underflowed
         lse_out = (Lm + log2f(ef + ep)) * 0.6931471805599453f;
         tc::tmem_ld_wait(va);
 #pragma unroll
@@ -309,14 +337,14 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
           w.y = pack_bf16(bf16_lo(f.y) * wf + va[8 * q4 + 2] * wp, bf16_hi(f.y) * wf + va[8 * q4 + 3] * wp);
           w.z = pack_bf16(bf16_lo(f.z) * wf + va[8 * q4 + 4] * wp, bf16_hi(f.z) * wf + va[8 * q4 + 5] * wp);
           w.w = pack_bf16(bf16_lo(f.w) * wf + va[8 * q4 + 6] * wp, bf16_hi(f.w) * wf + va[8 * q4 + 7] * wp);
-          *reinterpret_cast<uint4*>(orow + 8 * q4) = w;
+          if (mine) *reinterpret_cast<uint4*>(orow + 8 * q4) = w;
         }
         tc::fence_before_sync();
         __syncwarp();
         if (lane == 0) tma::mbar_arrive(&bars.o_free);
       }
       // both groups read the fine lse above; group 0 replaces it only after both have (second exchange barrier)
-      if (wg == 0) a.lse[(int64_t) bh * a.Nq + row] = lse_out;
+      if (wg == 0 && mine) a.lse[(int64_t) bh * a.Nq + row] = lse_out;
       if (!ok) break;
     }
   }
@@ -360,7 +388,12 @@ int launch_attn_fwd_pooled_loop_tc(const LlsaAttnArgs* g, const AttnP<bf16>& a, 
   const int grid = n_tiles < sms ? n_tiles : sms;
   const size_t smem = 1024 + (size_t) (2 + kKStages + kVStages) * kTile * sizeof(bf16);
   LLSA_SMEM_LIMIT((attn_fwd_pooled_loop_tc_kernel), smem);
-  attn_fwd_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, np / kChunk, gathered, n_c, n_tiles, tiles_per_head);
+  unsigned char* redo = g->fwd_redo ? reinterpret_cast<unsigned char*>(g->fwd_redo->ptr) : nullptr;
+  if (redo) {        // one pass with the fine part's log-sum-exp as reference, then the two-pass form for the rows it marked
+    attn_fwd_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, np / kChunk, gathered, n_c, n_tiles, tiles_per_head, 1, redo);
+    LLSA_LAUNCH_OK("attn_fwd_pooled_loop_tc_kernel");
+  }
+  attn_fwd_pooled_loop_tc_kernel<<<grid, kThreads, smem, st>>>(a, maps, np / kChunk, gathered, n_c, n_tiles, tiles_per_head, 2, redo);
   LLSA_LAUNCH_OK("attn_fwd_pooled_loop_tc_kernel");
   return LLSA_OK;
 }

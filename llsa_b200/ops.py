@@ -50,6 +50,9 @@ _overlap_transpose = os.environ.get("LLSA_B200_OVERLAP_TRANSPOSE", "1") != "0"
 _side_streams = {}
 # Cross-check switch: keep the pooled-key stages on the mma.sync kernels (the form other shapes use).
 _no_tcgen05 = False
+# Cross-check switch: False = long pooled key lists take two passes over the keys for every row (no `fwd_redo` scratch).
+_one_pass_pooled = True
+_last_fwd_redo = None        # the marks of the most recent forward (tests look at how many rows the second launch redid)
 # Test hook: polls after which a bounded wait inside the tcgen05 kernels gives up (0 = the kernels' default).
 _wait_limit = 0
 # Device-side checks.  The kernels OR bits into a status word when they meet an out-of-range block index or when a
@@ -484,11 +487,18 @@ def _attn_fwd(q, k, v, pk, pv, pk2, pv2, indices, p_indices, topk, topk_p, block
     a, keep = _attn_args(q, k, v, pk, pv, pk2, pv2, indices, p_indices, o, lse, topk, topk_p, block_size, w1, w2)
     status = _new_status(q.device)
     a.status = status.data_ptr() if status is not None else None
+    # one byte per query row for the one-pass form of the long pooled key lists (include/llsa_b200.h: fwd_redo)
+    one_pass = q.dtype == torch.bfloat16 and _one_pass_pooled
+    redo = torch.empty((q.shape[0] * q.shape[1] * q.shape[2] + 3) // 4, device=q.device, dtype=torch.int32) if one_pass else None
+    redo_d = desc(redo)
+    a.fwd_redo = ptr(redo_d)
     _mark("attn_fwd")
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().llsa_attn_fwd(C.byref(a), _stream(q)), "attn_fwd")
     _mark("end")
     _check_status(status, "attn_fwd")
+    global _last_fwd_redo
+    _last_fwd_redo = redo
     return o, lse
 
 

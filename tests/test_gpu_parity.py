@@ -421,6 +421,52 @@ def test_llsa_l1_long_pooled_list_vs_oracle():
     assert_bf16_close(vg.grad, dv + O.mean_pool1d_bwd(dpv, 16), "dv")
 
 
+def _pooled_fwd_both_forms(L, q, k, v, monkeypatch):
+    """o, lse of llsa_l2's forward with the one-pass pooled stage (default) and with two passes for every row."""
+    from llsa_b200 import ops
+    out = []
+    for one_pass in (True, False):
+        monkeypatch.setattr(ops, "_one_pass_pooled", one_pass)
+        dbg = L.llsa_l2_debug(q.to(DEV), k.to(DEV), v.to(DEV), 8, 8, 16)
+        out.append({n: dbg[n].detach().cpu() for n in ("o", "lse", "indices", "p_indices", "pk", "pv", "pk2", "pv2")})
+        if one_pass:      # one byte per query row: 1 = left to the second launch
+            out[-1]["redone"] = int(ops._last_fwd_redo.view(torch.uint8)[:q.shape[0] * q.shape[1] * q.shape[2]].sum())
+    return out
+
+
+def test_long_pooled_list_one_pass_matches_two_passes(monkeypatch):
+    """The key-loop forward makes one pass over the pooled keys with the fine part's log-sum-exp as reference; the
+    two-pass form (row maxima first) must give the same o and lse up to bf16 rounding of P."""
+    L = _ops()
+    q, k, v, _ = synth.correlated_qkv(50, 1, 2, 65536, 64, dtype=torch.bfloat16)
+    one, two = _pooled_fwd_both_forms(L, q, k, v, monkeypatch)
+    assert torch.equal(one["indices"], two["indices"])
+    assert one["redone"] == 0
+    assert_bf16_close(one["o"], two["o"].float(), "o")
+    assert max_abs(one["lse"], two["lse"]) < 1e-3
+
+
+def test_long_pooled_list_rows_beyond_the_one_pass_range_are_redone(monkeypatch):
+    """Logits in the hundreds: in many rows a pooled key outweighs all fine keys by more than 1e30, the one-pass form
+    marks those rows and the second launch redoes them exactly.  Both forms against the oracle's fp32 evaluation."""
+    L = _ops()
+    q, k, v, _ = synth.correlated_qkv(51, 1, 1, 65536, 64, dtype=torch.bfloat16)
+    q, k = (q.float() * 12).to(torch.bfloat16), (k.float() * 12).to(torch.bfloat16)
+    one, two = _pooled_fwd_both_forms(L, q, k, v, monkeypatch)
+    assert 0 < one["redone"] < 65536, one["redone"]
+    o_ref, lse_ref = O.attn_fwd_l2(q, k, v, one["pk"], one["pv"], one["pk2"], one["pv2"], one["indices"], one["p_indices"].long(), 8, 8,
+                                   faithful=False)
+    # how many rows are out of range for the one-pass form: pooled log-sum-exp minus fine log-sum-exp above ln(1e30)
+    for got in (one, two):
+        assert torch.isfinite(got["o"].float()).all() and torch.isfinite(got["lse"]).all()
+        # the softmax is close to one-hot here: o is a value row rounded to bf16 (half an ulp = 0.016 at |v| = 4)
+        assert rel_l2(got["o"].float(), o_ref.float()) <= 1e-2
+        assert max_abs(got["o"].float(), o_ref.float()) <= 5e-2
+        assert max_abs(got["lse"], lse_ref) < 0.5                   # lse itself is in the hundreds here
+    assert max_abs(one["lse"], two["lse"]) < 0.25
+    assert max_abs(one["o"].float(), two["o"].float()) <= 5e-2
+
+
 def test_llsa_l2_cfg5_shape_vs_oracle():
     """BASELINE config 5's sequence length (N=262144: 1024 level-2 keys per row), one (b,h) slice.  Pooling and both
     selections are compared in full; o, lse and dq on two ranges of 1024 query rows (the oracle's fp32 evaluation of all
