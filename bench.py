@@ -264,7 +264,7 @@ def main():
         table = synth.rope_table_2d(int(round(math.sqrt(N))), dtype=cfg["dtype"]).to(dev)
         call = lambda q, k, v: llsa_b200.llsa_l1_rope(q, k, v, table, 8, 16)
 
-    seq_parallel = B * H < world or args.seq_parallel          # too few (b,h) slices to go round: shard the sequence
+    seq_parallel = (B * H) % world != 0 or args.seq_parallel   # the (b,h) slices do not go round evenly: shard the sequence too
     full = synth.correlated_qkv(cfg["seed"], B, H, N, D, dtype=cfg["dtype"])          # the ONE workload, the same on every rank
     if seq_parallel:
         # rank r owns tokens [r*N/W, (r+1)*N/W) of q, k, v (llsa_b200/seqpar.py)
@@ -392,7 +392,7 @@ def main():
                                                            "more than" if 8 * units * 2 + nq1 * 8 * 1024 > 126e6 else "LESS than (reads may hit L2)"),
                            parallelism=("%d rank(s): %d group(s) of (b,h) slices x %d rank(s) sharding the sequence (all-gather of k, v and pooled "
                                         "levels, reduce-scatter of dk, dv inside a group)" % (world, world // seq_ranks, seq_ranks))
-                           if seq_parallel else "%d rank(s), the 48 (batch, head) slices split contiguously, no collective" % world),
+                           if seq_parallel else "%d rank(s), the %d (batch, head) slices split contiguously, no collective" % (world, B * H)),
                windows=len(windows), eager_ms_per_step=eager_ms_step,
                effective_tflops=total_flops / (ms_step * 1e-3) / 1e12,
                effective_tflops_frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (peak * world),
