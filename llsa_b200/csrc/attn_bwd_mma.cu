@@ -416,42 +416,45 @@ __global__ void __launch_bounds__(NW * 32, 1) attn_dkv_pooled_kernel(AttnP<bf16>
 // fall inside a bucket of at most kRangeEntries entries to that bucket's start.  Most buckets are therefore finished
 // by one warp; longer ones are cut at multiples of kRangeEntries and their pieces meet in shared memory (same CTA) or
 // in the `partial` scratch (summed in window order by the finish kernel).  No atomics: bit-reproducible.
-constexpr int kTileFloats = 64 * 32;            // a parked dK + dV tile pair: 64 accumulators x 32 lanes
+constexpr int kTileFloats = 64 * 32;            // a parked dK + dV tile pair: 64 accumulators x 32 lanes (8 KB)
 
 __device__ __forceinline__ int64_t csr_off(const AttnP<bf16>& a, int64_t bh, int64_t j) {
   const int64_t o = bh * (a.n1 + 1) + j;
   return a.off64 ? reinterpret_cast<const int64_t*>(a.offsets)[o] : (int64_t) reinterpret_cast<const int32_t*>(a.offsets)[o];
 }
 
-// A parked dK + dV tile pair is [64 accumulators][32 lanes] fp32: every access of a warp is one contiguous 128-byte row.
+// A parked dK + dV tile pair is [16 accumulator quads][32 lanes] float4: every access of a warp is one 128-bit
+// instruction over 512 contiguous bytes.  (A warp gets about eight loads per memory round trip, however many it has issued:
+// the same tile as 64 32-bit loads cost the finish kernel eight round trips per piece in a clock trace.)
 __device__ __forceinline__ void tile_to_mem(float* s, const float (&dk)[8][4], const float (&dv)[8][4], int lane) {
+  float4* s4 = reinterpret_cast<float4*>(s) + lane;
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      s[(u * 4 + c) * 32 + lane] = dk[u][c];
-      s[(32 + u * 4 + c) * 32 + lane] = dv[u][c];
-    }
+  for (int u = 0; u < 8; ++u) {
+    s4[u * 32] = make_float4(dk[u][0], dk[u][1], dk[u][2], dk[u][3]);
+    s4[(8 + u) * 32] = make_float4(dv[u][0], dv[u][1], dv[u][2], dv[u][3]);
+  }
 }
 __device__ __forceinline__ void tile_add_mem(const float* s, float (&dk)[8][4], float (&dv)[8][4], int lane) {
+  const float4* s4 = reinterpret_cast<const float4*>(s) + lane;
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      dk[u][c] += s[(u * 4 + c) * 32 + lane];
-      dv[u][c] += s[(32 + u * 4 + c) * 32 + lane];
-    }
+  for (int u = 0; u < 8; ++u) {
+    const float4 x = s4[u * 32], y = s4[(8 + u) * 32];
+    dk[u][0] += x.x; dk[u][1] += x.y; dk[u][2] += x.z; dk[u][3] += x.w;
+    dv[u][0] += y.x; dv[u][1] += y.y; dv[u][2] += y.z; dv[u][3] += y.w;
+  }
 }
-// The same from global memory with all 64 loads in flight before the first add (64 more registers): for the finish kernels, whose
-// warps do little else than wait for these loads.
+// The same from global memory with all 16 loads in flight before the first add: for the finish kernel, whose warps do
+// little else than wait for these loads.
 __device__ __forceinline__ void tile_add_mem_batched(const float* s, float (&dk)[8][4], float (&dv)[8][4], int lane) {
-  float x[32], y[32];
+  const float4* s4 = reinterpret_cast<const float4*>(s) + lane;
+  float4 x[8], y[8];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) { x[i] = __ldcg(s + i * 32 + lane); y[i] = __ldcg(s + (32 + i) * 32 + lane); }
+  for (int u = 0; u < 8; ++u) { x[u] = __ldcg(s4 + u * 32); y[u] = __ldcg(s4 + (8 + u) * 32); }
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) { dk[u][c] += x[u * 4 + c]; dv[u][c] += y[u * 4 + c]; }
+  for (int u = 0; u < 8; ++u) {
+    dk[u][0] += x[u].x; dk[u][1] += x[u].y; dk[u][2] += x[u].z; dk[u][3] += x[u].w;
+    dv[u][0] += y[u].x; dv[u][1] += y[u].y; dv[u][2] += y[u].z; dv[u][3] += y[u].w;
+  }
 }
 __device__ __forceinline__ void tile_zero(float (&dk)[8][4], float (&dv)[8][4]) {
 #pragma unroll
@@ -482,19 +485,34 @@ constexpr int kRingFineStageBytes = 2 * kRingTileElems * (int) sizeof(bf16);    
 constexpr int kRingFoldBytes = 4 * 64 * (int) sizeof(float);                           // per warp: dpk, dpv, dpk2, dpv2 rows of the bucket
 
 // Pooling-backward fold and scale for the ldmatrix accumulator layout: afterwards dk / dv hold the final fp32 values.
-__device__ __forceinline__ void dkv_fine_fold_ld(const AttnP<bf16>& a, int64_t bh, int64_t j, float (&dk)[8][4], float (&dv)[8][4], int t) {
+// The four gradient rows of KV block j (64 fp32 each) arrive with two 128-bit loads per lane -- lanes 0..15 the 16 quads
+// of the key rows, lanes 16..31 of the value rows, level 1 and level 2 -- so that a warp can have the next block's rows
+// under way (8 registers) while it finishes this one.
+struct FoldRows { float4 e, f; };
+__device__ __forceinline__ FoldRows dkv_fold_rows_load(const AttnP<bf16>& a, int64_t bh, int64_t j, int lane) {
+  FoldRows r;
+  r.e = r.f = make_float4(0.f, 0.f, 0.f, 0.f);
   if (a.fold) {
-    const float* g1k = a.dpk + (bh * a.n1 + j) * kD + 2 * t;
-    const float* g1v = a.dpv + (bh * a.n1 + j) * kD + 2 * t;
-    const float* g2k = a.two_level ? a.dpk2 + (bh * a.n2 + j / kBS) * kD + 2 * t : nullptr;
-    const float* g2v = a.two_level ? a.dpv2 + (bh * a.n2 + j / kBS) * kD + 2 * t : nullptr;
+    const int half = lane >> 4, q = lane & 15;
+    r.e = __ldcg(reinterpret_cast<const float4*>((half ? a.dpv : a.dpk) + (bh * a.n1 + j) * kD + 4 * q));
+    if (a.two_level) r.f = __ldcg(reinterpret_cast<const float4*>((half ? a.dpv2 : a.dpk2) + (bh * a.n2 + j / kBS) * kD + 4 * q));
+  }
+  return r;
+}
+__device__ __forceinline__ void dkv_fine_fold_apply(const AttnP<bf16>& a, const FoldRows& r, float (&dk)[8][4], float (&dv)[8][4], int lane) {
+  if (a.fold) {
+    const int t = lane & 3;
+    float4 e = r.e;
+    if (a.two_level) { e.x += r.f.x * (1.f / kBS); e.y += r.f.y * (1.f / kBS); e.z += r.f.z * (1.f / kBS); e.w += r.f.w * (1.f / kBS); }
+    const bool hi = (t & 1) != 0;                 // channels 8u + 2t, 8u + 2t + 1: quad 2u + t/2, its first or second pair
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      float2 ek = *reinterpret_cast<const float2*>(g1k + 8 * u), ev = *reinterpret_cast<const float2*>(g1v + 8 * u);
-      if (a.two_level) {
-        const float2 fk = *reinterpret_cast<const float2*>(g2k + 8 * u), fv = *reinterpret_cast<const float2*>(g2v + 8 * u);
-        ek.x += fk.x * (1.f / kBS); ek.y += fk.y * (1.f / kBS); ev.x += fv.x * (1.f / kBS); ev.y += fv.y * (1.f / kBS);
-      }
+      const int src = 2 * u + (t >> 1);
+      const float kx0 = __shfl_sync(0xffffffffu, e.x, src), ky0 = __shfl_sync(0xffffffffu, e.y, src);
+      const float kx1 = __shfl_sync(0xffffffffu, e.z, src), ky1 = __shfl_sync(0xffffffffu, e.w, src);
+      const float vx0 = __shfl_sync(0xffffffffu, e.x, 16 + src), vy0 = __shfl_sync(0xffffffffu, e.y, 16 + src);
+      const float vx1 = __shfl_sync(0xffffffffu, e.z, 16 + src), vy1 = __shfl_sync(0xffffffffu, e.w, 16 + src);
+      const float2 ek = make_float2(hi ? kx1 : kx0, hi ? ky1 : ky0), ev = make_float2(hi ? vx1 : vx0, hi ? vy1 : vy0);
       dk[u][0] = dk[u][0] * a.scale + ek.x * (1.f / kBS); dk[u][1] = dk[u][1] * a.scale + ek.y * (1.f / kBS);
       dk[u][2] = dk[u][2] * a.scale + ek.x * (1.f / kBS); dk[u][3] = dk[u][3] * a.scale + ek.y * (1.f / kBS);
       dv[u][0] += ev.x * (1.f / kBS); dv[u][1] += ev.y * (1.f / kBS); dv[u][2] += ev.x * (1.f / kBS); dv[u][3] += ev.y * (1.f / kBS);
@@ -810,9 +828,26 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
 #pragma unroll
     for (int c = 0; c < 4; ++c) sa_m[c] = base ^ (c << 5);
   }
+  // pieces of the split buckets: towards L2 now (two of a piece's 64 lines per lane), they are read a few microseconds later
+  for (unsigned m = todo; m; m &= m - 1) {
+    const int l = __ffs((int) m) - 1;
+    const int bo = __shfl_sync(0xffffffffu, my_bo, l), be = __shfl_sync(0xffffffffu, my_be, l);
+    if (be > bo) {
+      const int c_first = bo / window, c_last = min((be - 1) / window, n_windows - 1);
+      for (int c = c_first; c <= c_last; ++c) {
+        const char* pf = reinterpret_cast<const char*>(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pf + 128 * lane));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pf + 128 * (32 + lane)));
+      }
+    }
+  }
+  // the gradient rows of the next bucket are requested before this one is finished
+  FoldRows rows = dkv_fold_rows_load(a, bh, j0 + __ffs((int) todo) - 1, lane);
   while (todo) {
     const int l = __ffs((int) todo) - 1;
     todo &= todo - 1;
+    const FoldRows mine = rows;
+    if (todo) rows = dkv_fold_rows_load(a, bh, j0 + __ffs((int) todo) - 1, lane);
     const int bo = __shfl_sync(0xffffffffu, my_bo, l), be = __shfl_sync(0xffffffffu, my_be, l);
     const int64_t j = j0 + l;
     float dk[8][4], dv[8][4];
@@ -824,7 +859,7 @@ __global__ void __launch_bounds__(128) attn_dkv_finish_ld_kernel(AttnP<bf16> a, 
       for (int c = c_first; c <= c_last; ++c)
         tile_add_mem_batched(partial + ((bh * n_windows + c) * 2 + (c == c_first ? 1 : 0)) * (int64_t) kTileFloats, dk, dv, lane);
     }
-    dkv_fine_fold_ld(a, bh, j, dk, dv, t);
+    dkv_fine_fold_apply(a, mine, dk, dv, lane);
     dkv_tile_store_staged<0>(a, b, h, j, dk, dv, sa_m, sa_cp0, sa_cp1, lane);
   }
 }
