@@ -278,7 +278,7 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
           mx = fmaxf(mx, fmaf(m, sl2, lw));
         } else {
           const float off = lw - mx;
-#pragma unroll
+#pragma unroll 1          // unrolled, the four quarters' registers overlap and 18 of them spill (to L2: L1 is 28 KB here)
           for (int q4 = 0; q4 < 4; ++q4) {
             tc::tmem_ld32_async(t_s + 32 * q4, va);
             tc::tmem_ld_wait(va);
