@@ -52,6 +52,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--batch", type=int, default=0, help="override the batch (profiling a smaller case)")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count (profiling a smaller case)")
     ap.add_argument("--seq-parallel", action="store_true", help="shard the sequence over the ranks even if B*H >= ranks")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the K-step window until this much has been timed")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of replaying a CUDA graph of the step")
@@ -256,7 +257,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     cfg = synth.CONFIGS[args.config]
-    B, H, N, D = args.batch or cfg["B"], cfg["H"], cfg["N"], cfg["D"]
+    B, H, N, D = args.batch or cfg["B"], args.heads or cfg["H"], cfg["N"], cfg["D"]
     fn = llsa_b200.llsa_l2 if cfg["op"] == "llsa_l2" else llsa_b200.llsa_l1
     call = (lambda q, k, v: fn(q, k, v, 8, 8, 16)) if cfg["op"] == "llsa_l2" else (lambda q, k, v: fn(q, k, v, 8, 16))
     if cfg["rope"]:      # the model's 2-D RoPE on q and k, fused into the pooling pass (rope_dit_transformer_2d.py:232-241)
@@ -264,8 +265,12 @@ def main():
         table = synth.rope_table_2d(int(round(math.sqrt(N))), dtype=cfg["dtype"]).to(dev)
         call = lambda q, k, v: llsa_b200.llsa_l1_rope(q, k, v, table, 8, 16)
 
-    seq_parallel = (B * H) % world != 0 or args.seq_parallel   # the (b,h) slices do not go round evenly: shard the sequence too
+    # Default: (b,h) slices over the ranks, no collective -- also when they do not go round (6 slices on 4 ranks run 2-2-1-1, on 8
+    # ranks two ranks idle: measured faster than sharding the sequence, whose exchange costs more than the imbalance).
+    # --seq-parallel: groups of ranks share slices and shard the sequence inside a group (llsa_b200/seqpar.py).
+    seq_parallel = args.seq_parallel
     full = synth.correlated_qkv(cfg["seed"], B, H, N, D, dtype=cfg["dtype"])          # the ONE workload, the same on every rank
+    idle = False
     if seq_parallel:
         # rank r owns tokens [r*N/W, (r+1)*N/W) of q, k, v (llsa_b200/seqpar.py)
         # (b,h) slices are split over groups of ranks first; inside a group rank r owns tokens [r*N/R, (r+1)*N/R)
@@ -283,11 +288,14 @@ def main():
         # rank r owns a contiguous range of the flattened (batch, head) axis: [1, slices, N, D] (llsa_b200/shard.py)
         hq, hk, hv, hdo = [shard.take_slices(t, world, rank).contiguous().pin_memory() for t in full]
         n_slices = hq.shape[1]
+    idle = n_slices == 0                     # more ranks than slices: this rank only keeps the barriers company
     del full
     q, k, v, do = [t.to(dev) for t in (hq, hk, hv, hdo)]
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
 
     def eager_step():
+        if idle:
+            return None
         q.grad = k.grad = v.grad = None
         o = call(q, k, v)
         o.backward(do)
@@ -296,7 +304,7 @@ def main():
     for _ in range(max(args.warmup, 3)):
         eager_step()
     torch.cuda.synchronize()
-    use_graph = not args.eager and not seq_parallel            # collectives stay eager
+    use_graph = not args.eager and not seq_parallel and not idle            # collectives stay eager
     if use_graph:
         graph, _outs = llsa_b200.capture_fwd_bwd(call, q.detach(), k.detach(), v.detach(), do)
         step = graph.replay
@@ -314,6 +322,12 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     ms_step = median(windows) / args.steps
     value = B * N / (ms_step * 1e-3)                           # the ONE workload's tokens over the slowest rank's time
+    if idle:                                                   # the e2e leg's barrier and reduction, then out
+        if not args.no_e2e and not seq_parallel:
+            dist.barrier()
+            dist.all_reduce(torch.zeros(1, device=dev), op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+        return
 
     # ---- per-kernel CUDA events: K eager steps with an event in front of every kernel group (on the launching stream)
     marks = []
@@ -392,7 +406,8 @@ def main():
                                                            "more than" if 8 * units * 2 + nq1 * 8 * 1024 > 126e6 else "LESS than (reads may hit L2)"),
                            parallelism=("%d rank(s): %d group(s) of (b,h) slices x %d rank(s) sharding the sequence (all-gather of k, v and pooled "
                                         "levels, reduce-scatter of dk, dv inside a group)" % (world, world // seq_ranks, seq_ranks))
-                           if seq_parallel else "%d rank(s), the %d (batch, head) slices split contiguously, no collective" % (world, B * H)),
+                           if seq_parallel else "%d rank(s), the %d (batch, head) slices split contiguously%s, no collective"
+                           % (world, B * H, " (%d rank(s) without a slice)" % (world - B * H) if world > B * H else "")),
                windows=len(windows), eager_ms_per_step=eager_ms_step,
                effective_tflops=total_flops / (ms_step * 1e-3) / 1e12,
                effective_tflops_frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (peak * world),
@@ -401,7 +416,7 @@ def main():
                roofline=roof, gpu_launches=len(KERNELS_PER_STEP) * args.steps, clocks=clocks)
 
     # ---- weak-scaling form as an extra key: every rank the whole workload (what data-parallel training does)
-    if args.weak and world > 1 and not seq_parallel:
+    if args.weak and world > 1 and not seq_parallel and world <= B * H:
         wq, wk, wv, wdo = [t.to(dev) for t in synth.correlated_qkv(cfg["seed"] + 100 * rank, B, H, N, D, dtype=cfg["dtype"])]
         wgraph, _w = llsa_b200.capture_fwd_bwd(call, wq, wk, wv, wdo)
         for _ in range(3):
