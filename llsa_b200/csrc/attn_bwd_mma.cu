@@ -694,25 +694,40 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(
       }
     const uint4* pds_lane = a.pds + bh * (int64_t) E * 64 + lane;
     uint4 pP[kRingFineStages], pD[kRingFineStages];       // P^T / dS^T registers of the entries in flight
-    auto issue = [&](auto stage_tag, int i) {
-      constexpr int ST = decltype(stage_tag)::value;
+    // The request for entry i goes out in four parts (PART 0..3) so that the entry loop can put a part between two groups of
+    // products: address arithmetic and copies of the entry three ahead then run while the tensor pipe works on this one.
+    const char* qp_i = q_lane;
+    const char* dp_i = d_lane;
+    auto issue_part = [&](auto stage_tag, auto part_tag, int i) {
+      constexpr int ST = decltype(stage_tag)::value, PART = decltype(part_tag)::value;
       constexpr int SB = ST * kRingFineStageBytes, TB = kRingTileElems * (int) sizeof(bf16);
-      const int u = i >> 5;
-      const int qb = __shfl_sync(0xffffffffu, u == 0 ? my_qb[0] : (u == 1 ? my_qb[1] : (u == 2 ? my_qb[2] : my_qb[3])), i & 31);
-      const int pair = __shfl_sync(0xffffffffu, u == 0 ? my_pair[0] : (u == 1 ? my_pair[1] : (u == 2 ? my_pair[2] : my_pair[3])), i & 31);
-      const char* qp = q_lane + (int64_t) qb * qblk;
-      const char* dp = d_lane + (int64_t) qb * dblk;
-      cp_async16_sa<SB>(sa_cp0, qp);
-      cp_async16_sa<SB + 512>(sa_cp1, qp + qstep);
-      cp_async16_sa<SB + 1024>(sa_cp0, qp + 2 * qstep);
-      cp_async16_sa<SB + 1536>(sa_cp1, qp + 3 * qstep);
-      cp_async16_sa<SB + TB>(sa_cp0, dp);
-      cp_async16_sa<SB + TB + 512>(sa_cp1, dp + dstep);
-      cp_async16_sa<SB + TB + 1024>(sa_cp0, dp + 2 * dstep);
-      cp_async16_sa<SB + TB + 1536>(sa_cp1, dp + 3 * dstep);
-      const uint4* pp = pds_lane + (int64_t) pair * 64;
-      pP[ST] = __ldcg(pp);
-      pD[ST] = __ldcg(pp + 32);
+      if (PART == 0) {
+        const int u = i >> 5;
+        const int qb = __shfl_sync(0xffffffffu, u == 0 ? my_qb[0] : (u == 1 ? my_qb[1] : (u == 2 ? my_qb[2] : my_qb[3])), i & 31);
+        const int pair = __shfl_sync(0xffffffffu, u == 0 ? my_pair[0] : (u == 1 ? my_pair[1] : (u == 2 ? my_pair[2] : my_pair[3])), i & 31);
+        qp_i = q_lane + (int64_t) qb * qblk;
+        dp_i = d_lane + (int64_t) qb * dblk;
+        const uint4* pp = pds_lane + (int64_t) pair * 64;
+        pP[ST] = __ldcg(pp);
+        pD[ST] = __ldcg(pp + 32);
+      } else if (PART == 1) {
+        cp_async16_sa<SB>(sa_cp0, qp_i);
+        cp_async16_sa<SB + 512>(sa_cp1, qp_i + qstep);
+        cp_async16_sa<SB + 1024>(sa_cp0, qp_i + 2 * qstep);
+        cp_async16_sa<SB + 1536>(sa_cp1, qp_i + 3 * qstep);
+      } else if (PART == 2) {
+        cp_async16_sa<SB + TB>(sa_cp0, dp_i);
+        cp_async16_sa<SB + TB + 512>(sa_cp1, dp_i + dstep);
+      } else {
+        cp_async16_sa<SB + TB + 1024>(sa_cp0, dp_i + 2 * dstep);
+        cp_async16_sa<SB + TB + 1536>(sa_cp1, dp_i + 3 * dstep);
+      }
+    };
+    auto issue = [&](auto stage_tag, int i) {
+      issue_part(stage_tag, std::integral_constant<int, 0>{}, i);
+      issue_part(stage_tag, std::integral_constant<int, 1>{}, i);
+      issue_part(stage_tag, std::integral_constant<int, 2>{}, i);
+      issue_part(stage_tag, std::integral_constant<int, 3>{}, i);
     };
     static_assert(kRingFineStages == 4, "the entry loop below is unrolled over four stages");
     if (0 < n) issue(std::integral_constant<int, 0>{}, 0);
@@ -745,25 +760,40 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2) attn_dkv_fine_ring_kernel(
         tile_zero(dk, dv);
       }
       const uint4 P = pP[S], D = pD[S];
-      if (i + kRingFineStages - 1 < n) issue(std::integral_constant<int, SF>{}, i + kRingFineStages - 1);
-      cp_async_commit();
-      // all eight operand loads first, then the sixteen products: the statements are issued in this order, and a product
-      // issued right behind its own load would wait out the load's latency eight times per entry
+      const bool more = i + kRingFineStages - 1 < n;
+      constexpr auto sf_tag = std::integral_constant<int, SF>{};
+      // all eight operand loads first (a product issued right behind its own load would wait out the load's latency), then
+      // the sixteen products in four groups with a part of the next request between them
       uint32_t bd[4][4], bq[4][4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) ldsm_x4_trans<SB + TB>(bd[c][0], bd[c][1], bd[c][2], bd[c][3], sa_m[c]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) ldsm_x4_trans<SB>(bq[c][0], bq[c][1], bq[c][2], bq[c][3], sa_m[c]);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, bd[c][0], bd[c][1]);
         mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, bd[c][2], bd[c][3]);
       }
+      if (more) issue_part(sf_tag, std::integral_constant<int, 0>{}, i + kRingFineStages - 1);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2; c < 4; ++c) {
+        mma_bf16_16816(dv[2 * c], P.x, P.y, P.z, P.w, bd[c][0], bd[c][1]);
+        mma_bf16_16816(dv[2 * c + 1], P.x, P.y, P.z, P.w, bd[c][2], bd[c][3]);
+      }
+      if (more) issue_part(sf_tag, std::integral_constant<int, 1>{}, i + kRingFineStages - 1);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, bq[c][0], bq[c][1]);
         mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, bq[c][2], bq[c][3]);
       }
+      if (more) issue_part(sf_tag, std::integral_constant<int, 2>{}, i + kRingFineStages - 1);
+#pragma unroll
+      for (int c = 2; c < 4; ++c) {
+        mma_bf16_16816(dk[2 * c], D.x, D.y, D.z, D.w, bq[c][0], bq[c][1]);
+        mma_bf16_16816(dk[2 * c + 1], D.x, D.y, D.z, D.w, bq[c][2], bq[c][3]);
+      }
+      if (more) issue_part(sf_tag, std::integral_constant<int, 3>{}, i + kRingFineStages - 1);
+      cp_async_commit();
     };
     for (int i = 0; i < n; i += 4) {
       entry(std::integral_constant<int, 0>{}, i);
