@@ -139,6 +139,9 @@ def test_attention_argument_errors():
     a = args()
     a.topk = 7
     assert lib.llsa_attn_fwd(C.byref(a), None) == ERR_ARG
+    # the forward's optional one-byte-per-row scratch: one I32 element per four query rows at least
+    assert lib.llsa_attn_fwd(C.byref(args(fwd_redo=fake((B * H * N // 4 - 1,), torch.int32))), None) == ERR_WORKSPACE
+    assert lib.llsa_attn_fwd(C.byref(args(fwd_redo=fake((B * H * N // 4,), torch.float32))), None) == ERR_WORKSPACE
     # backward without its outputs
     assert lib.llsa_attn_bwd(C.byref(args()), None) == ERR_NULL
     # two-level form without p_indices

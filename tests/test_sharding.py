@@ -14,7 +14,7 @@ from llsa_b200 import shard, synth
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("n,world", [(48, 1), (48, 2), (48, 8), (6, 4), (5, 8), (7, 3)])
+@pytest.mark.parametrize("n,world", [(48, 1), (48, 2), (48, 8), (6, 4), (6, 8), (5, 8), (7, 3)])       # (6, 8): two ranks without a slice
 def test_slice_ranges_tile_the_axis(n, world):
     ranges = [shard.slice_range(n, world, r) for r in range(world)]
     assert ranges[0][0] == 0 and ranges[-1][1] == n
