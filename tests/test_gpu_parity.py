@@ -325,6 +325,35 @@ def test_llsa_l1_bf16_rope_vs_oracle(force_generic, monkeypatch):
     assert_bf16_close(vg.grad, dv + O.mean_pool1d_bwd(dpv, 16), "dv")
 
 
+def test_llsa_l1_cfg2_full_shape_vs_oracle():
+    """BASELINE config 2 at its full shape (llsa_l1, B=4, H=6, N=4096, q / k through the 2-D RoPE), default kernels, through
+    the fused operator the benchmark times (llsa_l1_rope: rotation inside the pooling pass) against the oracle's
+    rope -> llsa_l1 chain; indices with the tie-aware comparator, o and the three gradients to bf16 tolerance."""
+    L = _ops()
+    B, H, N = 4, 6, 4096
+    q, k, v, do = synth.correlated_qkv(2, B, H, N, 64, dtype=torch.bfloat16)
+    table = synth.rope_table_2d(int(math.isqrt(N)), dtype=torch.bfloat16)
+    qr, kr = O.rope_fwd(q, table), O.rope_fwd(k, table)
+    qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    o = L.llsa_l1_rope(qg, kg, vg, table.to(DEV), 8, 16)
+    o.backward(do.to(DEV))
+    # the same selection as the GPU made (stage isolation), checked against the oracle's with the tie margin
+    dbg = L.llsa_l1_debug(qr.to(DEV), kr.to(DEV), v.to(DEV), 8, 16)
+    sel = O.llsa_l1_fwd_bwd(qr, kr, v, None)
+    s1 = (sel["pq"].float() @ sel["pk"].float().transpose(-1, -2)).to(torch.bfloat16).float()
+    differ, bad = topk_mismatch_rows(dbg["indices"].cpu(), sel["indices"], s1, margin=2.0 ** -7)
+    assert bad == 0 and differ <= 8 * B * H
+    idx = dbg["indices"].cpu()
+    o_ref, lse_ref = O.attn_fwd_l1(qr, kr, v, sel["pk"], sel["pv"], idx, faithful=False)
+    assert_bf16_close(o.detach(), o_ref, "o")
+    dq, dk, dv, dpk, dpv = O.attn_bwd_l1(do, qr, kr, v, sel["pk"], sel["pv"], o_ref.float(), lse_ref, idx, faithful=False)
+    dk = dk + O.mean_pool1d_bwd(dpk, 16)
+    dv = dv + O.mean_pool1d_bwd(dpv, 16)
+    assert_bf16_close(qg.grad, O.rope_bwd(dq.to(torch.bfloat16), table), "dq")
+    assert_bf16_close(kg.grad, O.rope_bwd(dk.to(torch.bfloat16), table), "dk")
+    assert_bf16_close(vg.grad, dv, "dv")
+
+
 def _gpu_l2(L, q, k, v, do, topk1=8, topk2=8):
     """llsa_l2 forward + backward on the GPU (default kernels); everything the comparisons need, on the host."""
     qg, kg, vg = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
