@@ -30,7 +30,7 @@ def _ops():
 
 
 def assert_bf16_close(got, ref, name):
-    got, ref = got.float().cpu(), ref.float().cpu()
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
     r = rel_l2(got, ref)
     err = (got - ref).abs()
     assert r <= 1e-2, "%s: rel-L2 %.3e" % (name, r)
