@@ -783,6 +783,29 @@ def test_host_pipeline_matches_direct_call(chunk_heads, graphs):
 
 
 # ------------------------------------------------------------------ full-size properties (BASELINE config 3 shape)
+def test_batch_of_288_slices_matches_its_own_slices():
+    """288 (b,h) slices (B=48, H=6, N=16384: 8 GB on the device, the P / dS hand-over alone 2.4 GB -- byte offsets past 2^31):
+    every slice is independent, so the first and the last two batch elements computed alone must give the same o and dq bit
+    for bit and the same dk, dv up to the order of their fp32 sums (the work ranges depend on the size of the launch)."""
+    L = _ops()
+    B, H, N = 48, 6, 16384
+    q, k, v, do = [t.to(DEV) for t in synth.correlated_qkv(11, 2, H, N, 64, dtype=torch.bfloat16)]
+    sc = torch.linspace(0.5, 1.5, B // 2, device=DEV).repeat_interleave(2).view(B, 1, 1, 1).to(torch.bfloat16)
+    Q = (q.repeat(B // 2, 1, 1, 1) * sc).contiguous().requires_grad_(True)
+    K = (k.repeat(B // 2, 1, 1, 1) * sc).contiguous().requires_grad_(True)
+    V = v.repeat(B // 2, 1, 1, 1).contiguous().requires_grad_(True)
+    DO = do.repeat(B // 2, 1, 1, 1).contiguous()
+    o = L.llsa_l2(Q, K, V, 8, 8, 16)
+    o.backward(DO)
+    assert torch.isfinite(K.grad.float()).all() and torch.isfinite(V.grad.float()).all() and torch.isfinite(Q.grad.float()).all()
+    for sl in (slice(0, 2), slice(B - 2, B)):
+        qs, ks, vs = [t[sl].detach().clone().requires_grad_(True) for t in (Q, K, V)]
+        os_ = L.llsa_l2(qs, ks, vs, 8, 8, 16)
+        os_.backward(DO[sl])
+        assert torch.equal(o[sl], os_) and torch.equal(Q.grad[sl], qs.grad)
+        assert rel_l2(K.grad[sl], ks.grad) < 2e-3 and rel_l2(V.grad[sl], vs.grad) < 2e-3
+
+
 def test_cfg3_full_size_properties():
     L = _ops()
     q, k, v, do, _ = synth.make_config_inputs("cfg3")
