@@ -32,9 +32,10 @@
 //                       the end of a head the level-2 results.
 //   warp 16, one lane : TMA producer (Q, dO and the level-1 keys double-buffered; level-1 values
 //                       reloaded as soon as dP of the parent's last tile has read them)
-//   warp 17, one lane : tcgen05.mma issuer.  tcgen05.mma operations execute in issue order, so S of the
-//                       next tile is issued as soon as dP of this tile has been read, ahead of this
-//                       tile's three output products.
+//   warp 17, one lane : tcgen05.mma issuer for S, dP and dQ.  Its operations execute in issue order, so S of
+//                       the next tile is issued as soon as dP of this tile has been read, ahead of dQ.
+//   warp 18, one lane : tcgen05.mma issuer for the three transposed products (accumulators and operands no
+//                       instruction of warp 17 writes; ordered against it by the barriers only).
 // Every mbarrier wait is bounded; a wait that expires raises a CTA-wide abort flag, every role leaves
 // its loop, the host-visible status word is set and TMEM is freed.
 #include <string.h>
@@ -51,7 +52,7 @@ namespace llsa {
 namespace {
 
 constexpr int kRows = 128;
-constexpr int kThreads = 576;         // 12 softmax warps + 4 drain warps + producer warp + MMA warp
+constexpr int kThreads = 608;         // 12 softmax warps + 4 drain warps + producer warp + two MMA warps
 constexpr int kTile = kRows * 64;     // elements of a [128 x 64] bf16 tile (16 KB)
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr uint32_t kColDQ = 192, kColPV1 = 256, kColPK1 = 320, kColYX = 384, kColY = 384, kColX = 448;
@@ -90,12 +91,12 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
     s_ctl.limit = a.wait_limit > 0 ? a.wait_limit : tc::kWaitPolls;
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.full[i], 1);
-      tc::mbar_init(&bars.mma_done[i], 1);
+      tc::mbar_init(&bars.mma_done[i], 2);
       tc::mbar_init(&bars.v_free[i], 1);
     }
     tc::mbar_init(&bars.s_ready, 1);
     tc::mbar_init(&bars.dp_ready, 1);
-    tc::mbar_init(&bars.out_ready, 1);
+    tc::mbar_init(&bars.out_ready, 2);        // one commit per MMA-issuing thread
     tc::mbar_init(&bars.s_consumed, 12);     // one arrival per softmax warp
     tc::mbar_init(&bars.pds_ready, 12);
     tc::mbar_init(&bars.dq_free, 4);         // one arrival per drain warp
@@ -187,7 +188,6 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         tc::umma_commit(&bars.s_ready);
         return true;
       };
-      int parents_done = 0;
       bool ok = n_my > 0 && issue_s(0);
       for (int i = 0; ok && i < n_my; ++i) {
         const int s = i & 1, tile = t_begin + i;
@@ -222,6 +222,31 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) tc::umma_ss_lh<1>(tmem + kColDQ, lDS_k2 + 2 * ks, hi, lK2_m + 128 * ks, hi, id_dq);
         }
+        tc::umma_commit(&bars.out_ready);           // this thread's half: S, dP, dQ of the tile
+        tc::umma_commit(&bars.mma_done[s]);
+        if (!next_early && i + 1 < n_my && !issue_s(i + 1)) break;
+      }
+    }
+  } else if (warp == 18) {
+    // ---------------------------------------------------------------- second MMA issuer: the three transposed products
+    // One thread issues a tcgen05.mma of these shapes every 56-90 cycles here, the pipe takes one every 48-64: the tile's 48
+    // instructions are dealt to two threads in two warps.  This one's 24 write accumulators nobody else's instructions
+    // touch and read P / dS, Q and dO only, so nothing orders the two threads but the barriers: out_ready and mma_done
+    // count one commit of each.
+    if (lane == 0) {
+      const uint32_t id_kv = tc::instr_desc(128, 64, 1, 1), id_kv2 = tc::instr_desc(128, 128, 1, 1);
+      const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
+      const uint32_t sb = (tc::smem_u32(base) >> 4) & 0x3FFFu;
+      constexpr uint32_t kU = (uint32_t) (kTile * 2) >> 4, kStage = kU, kT = kTile * 2;
+      auto lo = [sb](uint32_t units, uint32_t lbo_bytes) { return sb + units + ((lbo_bytes >> 4) << 16); };
+      constexpr uint32_t uQ = 0, uDO = 2 * kU, uP = 8 * kU;
+      const uint32_t lP1_m = lo(uP, kT), lDS1_m = lo(uP + 4 * kU, kT), lP2_m = lo(uP + 2 * kU, kT);   // M = 128 over two tiles
+      const uint32_t lQ_m0 = lo(uQ, 1024), lDO_m0 = lo(uDO, 1024), lQDO_m0 = lo(uQ, 2 * kT);
+      int parents_done = 0;
+      for (int i = 0; i < n_my; ++i) {
+        const int s = i & 1, tile = t_begin + i;
+        if (!tc::bounded_wait(&bars.pds_ready, i & 1, abort_flag)) break;
+        tc::fence_after_sync();
         // transposed products, K = 128 query rows in 8 k-steps.  Level-1 results accumulate over the tiles of a
         // parent, level-2 results over the tiles of a head; a fresh start waits for the drain warps to have read
         // the previous parent's results.
@@ -244,7 +269,6 @@ attn_bwd_pooled_tc_kernel(AttnP<bf16> a, const __grid_constant__ BwdMaps maps, i
         tc::umma_commit(&bars.out_ready);
         tc::umma_commit(&bars.mma_done[s]);
         if ((tile & 1) || i == n_my - 1) ++parents_done;
-        if (!next_early && i + 1 < n_my && !issue_s(i + 1)) break;
       }
     }
   } else if (warp >= 12) {
