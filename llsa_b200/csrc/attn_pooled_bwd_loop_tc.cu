@@ -9,11 +9,15 @@
 //     dQ += dS . K_c    [128 x 64]  (K = 64 keys)             dS read from TENSOR MEMORY (packed bf16 over S), K_c MN-major
 // The final log-sum-exp is known in the backward, so one pass over the chunks suffices.  dQ accumulates in TMEM over
 // all chunks of the tile and is then added to the fine part already in dq.
-// TMEM columns: buffer b (b = job parity): S at 128 b, dP at 128 b + 64; dQ at [256, 320).
-// Roles (one persistent CTA per SM, 10 warps): warp 8 lane 0 = TMA producer (Q, dO per tile, 2 stages; K and V
-// chunks in rings of 4), warp 9 lane 0 = MMA issuer, warps 0-3 / 4-7 = two softmax warpgroups on alternating chunks;
-// in the epilogue group w handles dQ columns [32 w, 32 w + 32).  tcgen05.mma executes in issue order: S / dP of chunk
-// j + 2 are issued right behind dQ of chunk j into the same buffer.
+// TMEM columns: three buffers, chunk number n of the CTA (counted over all its tiles) uses buffer n mod 3: S at 128 b,
+// dP at 128 b + 64; dQ at [384, 448).
+// Roles (one persistent CTA per SM, 11 warps): warp 8 lane 0 = TMA producer (Q, dO per tile, 2 stages; K and V
+// chunks in rings of 4), warp 9 lane 0 issues S and dP, warp 10 lane 0 issues dQ, warps 0-3 / 4-7 = two softmax
+// warpgroups on alternating chunks; in the epilogue group w handles dQ columns [32 w, 32 w + 32).
+// Two issuing threads because one is the pace of the kernel: with the waits, commits and fences around twelve
+// instructions per chunk a single thread needed 1,400 cycles per chunk against 576 of tensor-pipe time.  The two run
+// independently (S / dP of the next tile start while dQ of this one is still being issued); a buffer goes back to the
+// S / dP thread through buf_free, committed behind the dQ instructions that read its dS.
 // Every mbarrier wait is bounded (abort flag; the kernel then ends early and frees its TMEM; dq is left partial).
 #include <string.h>
 
@@ -31,9 +35,10 @@ constexpr int kCk = 64;                      // keys per chunk
 constexpr int kTile = kRows * 64;            // elements of a [128 x 64] bf16 tile (16 KB)
 constexpr int kChunkElems = kCk * 64;        // elements of a key chunk (8 KB)
 constexpr int kStages = 4;
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;
 constexpr float kLog2eF = 1.4426950408889634f;
-constexpr uint32_t kColDQ = 256;
+constexpr int kBufs = 3;
+constexpr uint32_t kColDQ = 384;
 
 struct DqMaps {
   CUtensorMap q, d_o;         // [B,H,Nq,64] 4-D, box 128 rows
@@ -43,7 +48,7 @@ struct DqMaps {
 
 struct DqBars {
   uint64_t q_full[2], q_empty[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t sdp_ready[2], ds_ready[2], dq_ready, dq_free;
+  uint64_t sdp_ready[kBufs], ds_ready[kBufs], buf_free[kBufs], dq_ready, dq_free;
 };
 
 // jobs: 64-key chunks per tile (even); gathered: number of leading chunks that are gathered level-1 blocks (0 or 2);
@@ -69,8 +74,11 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.q_full[i], 1);
       tc::mbar_init(&bars.q_empty[i], 1);
+    }
+    for (int i = 0; i < kBufs; ++i) {
       tc::mbar_init(&bars.sdp_ready[i], 1);
       tc::mbar_init(&bars.ds_ready[i], 4);        // one arrival per warp of the group
+      tc::mbar_init(&bars.buf_free[i], 1);
     }
     for (int i = 0; i < kStages; ++i) {
       tc::mbar_init(&bars.k_full[i], 1); tc::mbar_init(&bars.k_empty[i], 1);
@@ -131,29 +139,28 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
       }
     }
   } else if (warp == 9) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ---------------------------------------------------------------- MMA issuer 1: S and dP
     if (lane == 0) {
-      const uint32_t id_s = tc::instr_desc(kRows, kCk, 0, 0), id_dq = tc::instr_desc(kRows, 64, 0, 1);
+      const uint32_t id_s = tc::instr_desc(kRows, kCk, 0, 0);
       const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
       auto lo = [](const void* p, uint32_t lbo_bytes) { return ((tc::smem_u32(p) >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16); };
       constexpr uint32_t kQStage = (uint32_t) (kTile * 2) >> 4, kCStage = (uint32_t) (kChunkElems * 2) >> 4;
-      const uint32_t lQ = lo(sQ, 16), lDO = lo(sDO, 16), lK = lo(sK, 16), lV = lo(sV, 16), lKm = lo(sK, 1024);
-      int cj = 0;                                   // chunks whose S / dP have been issued
-      int64_t J = 0;
+      const uint32_t lQ = lo(sQ, 16), lDO = lo(sDO, 16), lK = lo(sK, 16), lV = lo(sV, 16);
+      int cj = 0, st = 0, buf = 0;                  // chunks issued so far; ring stage and buffer of the next one
+      uint32_t par = 0, bph = 0;                    // phase parities of the ring stage and of the buffer
       bool ok = true;
       for (int i = 0; ok && i < n_my; ++i) {
         const int qs = i & 1;
         if (!(ok = tc::bounded_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
-        tc::fence_after_sync();
-        const int cj0 = cj;                          // ring position of this tile's chunk 0
-        auto issue_sdp = [&](int j) -> bool {        // S and dP of chunk j into buffer j & 1
-          const int st = cj % kStages;
-          const uint32_t par = (cj / kStages) & 1;
-          if (!tc::bounded_wait(&bars.k_full[st], par, abort_flag)) return false;
-          if (!tc::bounded_wait(&bars.v_full[st], par, abort_flag)) return false;
+        const uint32_t q_ = lQ + qs * kQStage, o_ = lDO + qs * kQStage;
+        for (int j = 0; j < jobs; ++j) {
+          // the buffer's previous chunk (three back): its dQ instructions have read dS
+          if (cj >= kBufs && !(ok = tc::bounded_wait(&bars.buf_free[buf], bph ^ 1, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.k_full[st], par, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.v_full[st], par, abort_flag))) break;
           tc::fence_after_sync();
-          const uint32_t d = tmem + (j & 1) * 128;
-          const uint32_t q_ = lQ + qs * kQStage, o_ = lDO + qs * kQStage, k_ = lK + st * kCStage, v_ = lV + st * kCStage;
+          const uint32_t d = tmem + buf * 128;
+          const uint32_t k_ = lK + st * kCStage, v_ = lV + st * kCStage;
           tc::umma_ss_lh<0>(d, q_, hi, k_, hi, id_s);
           tc::umma_ss_lh<0>(d + 64, o_, hi, v_, hi, id_s);
 #pragma unroll
@@ -161,42 +168,42 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
             tc::umma_ss_lh<1>(d, q_ + 2 * s4, hi, k_ + 2 * s4, hi, id_s);
             tc::umma_ss_lh<1>(d + 64, o_ + 2 * s4, hi, v_ + 2 * s4, hi, id_s);
           }
-          tc::umma_commit(&bars.sdp_ready[j & 1]);
+          tc::umma_commit(&bars.sdp_ready[buf]);
           tc::umma_commit(&bars.v_empty[st]);        // the values are not needed again
           ++cj;
-          return true;
-        };
-        auto issue_dq = [&](int j) -> bool {         // dQ (+)= dS(chunk j, TMEM) . K chunk (16 key rows = 2048 bytes per k-step)
-          const int st = (cj0 + j) % kStages;
-          if (j == 0 && i > 0 && !tc::bounded_wait(&bars.dq_free, (i - 1) & 1, abort_flag)) return false;     // previous tile's dQ has been read
-          tc::fence_after_sync();
-          const uint64_t kdesc = ((uint64_t) hi << 32) | (uint64_t) (lKm + st * kCStage);
-#pragma unroll
-          for (int s4 = 0; s4 < 4; ++s4)
-            tc::umma_ts(tmem + kColDQ, tmem + (j & 1) * 128 + s4 * 8, kdesc + 128 * s4, id_dq, (j > 0 || s4 > 0) ? 1u : 0u);
-          tc::umma_commit(&bars.k_empty[st]);
-          return true;
-        };
-        for (int j = 0; ok && j < jobs; ++j) {
-          if (j >= 2) {
-            const int64_t Jp = J + j - 2;            // buffer j & 1 was used by chunk j - 2: its dS feeds dQ, then the buffer is free
-            if (!(ok = tc::bounded_wait(&bars.ds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
-            tc::fence_after_sync();
-            if (!(ok = issue_dq(j - 2))) break;
-          }
-          ok = issue_sdp(j);
+          if (++st == kStages) { st = 0; par ^= 1; }
+          if (++buf == kBufs) { buf = 0; bph ^= 1; }
         }
         if (!ok) break;
-        for (int j = jobs - 2; ok && j < jobs; ++j) {
-          const int64_t Jp = J + j;
-          if (!(ok = tc::bounded_wait(&bars.ds_ready[j & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
+        tc::umma_commit(&bars.q_empty[qs]);
+      }
+    }
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- MMA issuer 2: dQ (+)= dS(chunk, TMEM) . K chunk
+    if (lane == 0) {
+      const uint32_t id_dq = tc::instr_desc(kRows, 64, 0, 1);
+      const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
+      constexpr uint32_t kCStage = (uint32_t) (kChunkElems * 2) >> 4;
+      const uint32_t lKm = ((tc::smem_u32(sK) >> 4) & 0x3FFFu) | ((1024u >> 4) << 16);
+      int st = 0, buf = 0;
+      uint32_t bph = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < n_my; ++i) {
+        for (int j = 0; j < jobs; ++j) {
+          if (!(ok = tc::bounded_wait(&bars.ds_ready[buf], bph, abort_flag))) break;
+          if (j == 0 && i > 0 && !(ok = tc::bounded_wait(&bars.dq_free, (i - 1) & 1, abort_flag))) break;     // previous tile's dQ has been read
           tc::fence_after_sync();
-          ok = issue_dq(j);
+          const uint64_t kdesc = ((uint64_t) hi << 32) | (uint64_t) (lKm + st * kCStage);       // 16 key rows = 2048 bytes per k-step
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4)
+            tc::umma_ts(tmem + kColDQ, tmem + buf * 128 + s4 * 8, kdesc + 128 * s4, id_dq, (j > 0 || s4 > 0) ? 1u : 0u);
+          tc::umma_commit(&bars.k_empty[st]);
+          tc::umma_commit(&bars.buf_free[buf]);
+          if (++st == kStages) st = 0;
+          if (++buf == kBufs) { buf = 0; bph ^= 1; }
         }
         if (!ok) break;
         tc::umma_commit(&bars.dq_ready);
-        tc::umma_commit(&bars.q_empty[qs]);
-        J += jobs;
       }
     }
   } else {
@@ -204,9 +211,10 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
     const int wg = warp >> 2, qd = warp & 3, r = qd * 32 + lane;
     const float sl2 = a.scale * kLog2eF;
     const float lw1 = log2f(a.w1), lw2 = log2f(a.w2);
-    const uint32_t t_b = tmem + wg * 128 + ((uint32_t) (qd * 32) << 16);
+    const uint32_t t_lane = tmem + ((uint32_t) (qd * 32) << 16);
+    int buf = wg;                          // this group takes every other chunk: buffer and phase parity of its next one
+    uint32_t bph = 0;
     const uint32_t t_dq = tmem + kColDQ + wg * 32 + ((uint32_t) (qd * 32) << 16);
-    int64_t Jw = 0;
     float vs[32], vd[32];
     for (int i = 0; i < n_my; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
@@ -220,9 +228,10 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
       bool ok = true;
       for (int j = wg; j < jobs; j += 2) {
         const float off = ((gathered ? (j < gathered) : !a.two_level) ? lw1 : lw2) - L;
-        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.sdp_ready[wg], (uint32_t) (Jw & 1), abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.sdp_ready[buf], bph, abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
+        const uint32_t t_b = t_lane + buf * 128;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           tc::tmem_ld32_async(t_b + 32 * half, vs);
@@ -240,8 +249,9 @@ attn_dq_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ DqMaps maps
         tc::tmem_st_wait();
         tc::fence_before_sync();
         __syncwarp();
-        if (lane == 0) tma::mbar_arrive(&bars.ds_ready[wg]);
-        ++Jw;
+        if (lane == 0) tma::mbar_arrive(&bars.ds_ready[buf]);
+        buf += 2;
+        if (buf >= kBufs) { buf -= kBufs; bph ^= 1; }
       }
       if (!ok) break;
       ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.dq_ready, (uint32_t) (i & 1), abort_flag));

@@ -56,6 +56,7 @@ struct WaitCtl {
 };
 constexpr int kWaitPolls = 400000;
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile WaitCtl* c) {
+  if (mbar_try_wait(bar, parity)) return true;        // already complete: the common case for the threads that issue MMAs and copies
   const int limit = c->limit;
   for (int i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
