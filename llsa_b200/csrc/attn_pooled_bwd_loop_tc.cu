@@ -12,7 +12,7 @@
 // TMEM columns: three buffers, chunk number n of the CTA (counted over all its tiles) uses buffer n mod 3: S at 128 b,
 // dP at 128 b + 64; dQ at [384, 448).
 // Roles (one persistent CTA per SM, 11 warps): warp 8 lane 0 = TMA producer (Q, dO per tile, 2 stages; K and V
-// chunks in rings of 4), warp 9 lane 0 issues S and dP, warp 10 lane 0 issues dQ, warps 0-3 / 4-7 = two softmax
+// chunks in rings of 8: a stage is refilled four chunks before it is needed), warp 9 lane 0 issues S and dP, warp 10 lane 0 issues dQ, warps 0-3 / 4-7 = two softmax
 // warpgroups on alternating chunks; in the epilogue group w handles dQ columns [32 w, 32 w + 32).
 // Two issuing threads because one is the pace of the kernel: with the waits, commits and fences around twelve
 // instructions per chunk a single thread needed 1,400 cycles per chunk against 576 of tensor-pipe time.  The two run
@@ -34,7 +34,7 @@ constexpr int kRows = 128;
 constexpr int kCk = 64;                      // keys per chunk
 constexpr int kTile = kRows * 64;            // elements of a [128 x 64] bf16 tile (16 KB)
 constexpr int kChunkElems = kCk * 64;        // elements of a key chunk (8 KB)
-constexpr int kStages = 4;
+constexpr int kStages = 8;
 constexpr int kThreads = 352;
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr int kBufs = 3;

@@ -18,7 +18,7 @@
 // TMEM columns: three buffers, job number n of the CTA uses buffer n mod 3: S^T at 128 b, dP^T at 128 b + 64; dV at
 // [384,448), dK at [448,512).
 // Roles (one persistent CTA per SM, 11 warps): warp 8 lane 0 = TMA producer (K_c, V_c per unit; Q_t, dO_t, lse, delta per
-// job in a ring of 4), warp 9 lane 0 issues S^T and dP^T, warp 10 lane 0 issues dV and dK (one issuing thread, with its
+// job in a ring of 8), warp 9 lane 0 issues S^T and dP^T, warp 10 lane 0 issues dV and dK (one issuing thread, with its
 // waits, commits and fences, is slower than the tensor pipe), warps 0-3 / 4-7 = two softmax warpgroups on alternating
 // jobs; at the end of a unit group 0 writes dV, group 1 writes dK.  Every mbarrier wait is bounded (abort flag, TMEM freed).
 #include <string.h>
@@ -36,7 +36,7 @@ constexpr int kKeys = 128;                   // keys per unit (MMA M)
 constexpr int kQ = 64;                       // query rows per job (MMA N)
 constexpr int kKeyTile = kKeys * 64;         // elements of the K / V chunk (16 KB)
 constexpr int kQTile = kQ * 64;              // elements of a Q / dO job tile (8 KB)
-constexpr int kStages = 4;
+constexpr int kStages = 8;
 constexpr int kThreads = 352;
 constexpr int kBufs = 3;
 constexpr float kLog2eF = 1.4426950408889634f;

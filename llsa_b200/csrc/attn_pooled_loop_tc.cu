@@ -15,13 +15,15 @@
 // hold anything up to 2^127 times it; a row whose pooled keys outweigh its fine keys by more than that (its row sum
 // passes 1e30, or is NaN) is left untouched and marked in `redo`, and a second launch of the two-pass form redoes
 // exactly the marked rows (it scans its tiles' marks first and returns at once when there are none).
-// Roles (one persistent CTA per SM, 10 warps):
-//   warp 8, one lane : TMA producer: Q per tile (2 stages), K chunks (ring of 3; every chunk is loaded in both
-//                      passes), V chunks (ring of 2, pass 2 only)
-//   warp 9, one lane : tcgen05.mma issuer.  "Jobs" j = 0 .. 2*chunks-1 per tile alternate between two S buffers
-//                      (TMEM columns [0,128) and [128,256)); O lives in [256,320).  tcgen05.mma executes in issue
-//                      order, so S of job j+2 is issued right behind P.V of job j into the same buffer.
-//   warps 0-3 / 4-7  : two softmax warpgroups, group w owns the jobs j = w (mod 2); thread r owns query row r
+// Roles (one persistent CTA per SM, 11 warps):
+//   warp 8, one lane : TMA producer: Q per tile (2 stages), K chunks (ring of 4; every chunk is loaded in both
+//                      passes), V chunks (ring of 4, pass 2 only)
+//   warp 9, one lane : issues S of every "job" (a chunk of a pass).  Job number n, counted over all tiles of the CTA,
+//                      uses S buffer n mod 3 (TMEM columns [128 b, 128 b + 128)); O lives in [384,448).
+//   warp 10, one lane: issues O += P.V of the pass-2 jobs and hands every job's buffer back to warp 9 (buf_free,
+//                      committed behind the instructions that read P).  Two issuing threads because one, with its waits,
+//                      commits and fences, was the pace of the kernel: 2,050 cycles per job against 780 of pipe time.
+//   warps 0-3 / 4-7  : two softmax warpgroups, group w owns the jobs n = w (mod 2); thread r owns query row r
 //                      (TMEM lane r).  Row maxima and row sums of the two groups meet in shared memory (an
 //                      mbarrier with one arrival per softmax warp, so that this wait is bounded too).  Epilogue: group w merges O columns [32w, 32w+32)
 //                      with the fine part (o, lse written by the fine kernel) and stores them.
@@ -41,10 +43,11 @@ namespace {
 constexpr int kRows = 128;
 constexpr int kChunk = 128;                 // keys per chunk
 constexpr int kTile = kRows * 64;           // elements of a [128 x 64] bf16 tile (16 KB)
-constexpr int kKStages = 3, kVStages = 2;
-constexpr int kThreads = 320;
+constexpr int kKStages = 4, kVStages = 4;
+constexpr int kThreads = 352;
+constexpr int kBufs = 3;
 constexpr float kLog2eF = 1.4426950408889634f;
-constexpr uint32_t kColO = 256;
+constexpr uint32_t kColO = 384;
 
 struct LoopMaps {
   CUtensorMap q;              // [B,H,Nq,64] 4-D, box 128 rows
@@ -54,7 +57,7 @@ struct LoopMaps {
 
 struct LoopBars {
   uint64_t q_full[2], q_empty[2], k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
-  uint64_t s_ready[2], wg_done[2], o_ready, o_free, xchg;
+  uint64_t s_ready[kBufs], wg_done[kBufs], buf_free[kBufs], o_ready, o_free, xchg;
 };
 
 // n_chunks: chunks per tile; gathered: chunk 0 is the gathered level-1 set (two levels); n_c: rows per head of the
@@ -88,8 +91,11 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&bars.q_full[i], 1);
       tc::mbar_init(&bars.q_empty[i], 1);
+    }
+    for (int i = 0; i < kBufs; ++i) {
       tc::mbar_init(&bars.s_ready[i], 1);
       tc::mbar_init(&bars.wg_done[i], 4);         // one arrival per warp of the group
+      tc::mbar_init(&bars.buf_free[i], 1);
     }
     for (int i = 0; i < kKStages; ++i) { tc::mbar_init(&bars.k_full[i], 1); tc::mbar_init(&bars.k_empty[i], 1); }
     for (int i = 0; i < kVStages; ++i) { tc::mbar_init(&bars.v_full[i], 1); tc::mbar_init(&bars.v_empty[i], 1); }
@@ -103,8 +109,8 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = s_tmem;
-  // jobs per tile; job j of tile i has the CTA-wide number i * jobs + j, whose parity picks the S buffer and the softmax
-  // group (with one pass and an odd chunk count the parity of a tile's first job alternates)
+  // jobs per tile; job j of tile i has the CTA-wide number i * jobs + j, which picks the S buffer (mod 3) and the softmax
+  // group (mod 2; with one pass and an odd chunk count the parity of a tile's first job alternates)
   const int jobs = n_pass * n_chunks, first_p2 = jobs - n_chunks;
 
   if (warp == 8) {
@@ -153,72 +159,68 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
       }
     }
   } else if (warp == 9) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ---------------------------------------------------------------- MMA issuer 1: S of every job
     if (lane == 0) {
-      const uint32_t id_s = tc::instr_desc(kRows, kChunk, 0, 0), id_o = tc::instr_desc(kRows, 64, 0, 1);
+      const uint32_t id_s = tc::instr_desc(kRows, kChunk, 0, 0);
       const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
       auto lo = [](const void* p, uint32_t lbo_bytes) { return ((tc::smem_u32(p) >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16); };
       constexpr uint32_t kStage = (uint32_t) (kTile * 2) >> 4;
-      const uint32_t lQ = lo(sQ, 16), lK = lo(sK, 16), lV = lo(sV, 1024);
-      int kjob = 0, vjob = 0;
-      int64_t J = 0;                                   // jobs issued so far by this CTA (buffer b has seen J/2 of them)
+      const uint32_t lQ = lo(sQ, 16), lK = lo(sK, 16);
+      int n = 0, ks = 0, buf = 0;                   // jobs issued so far; K ring stage and S buffer of the next one
+      uint32_t kph = 0, bph = 0;                    // their phase parities
       bool ok = true;
       for (int i = 0; ok && i < n_my; ++i) {
         const int qs = i & 1;
         if (!(ok = tc::bounded_wait(&bars.q_full[qs], (i >> 1) & 1, abort_flag))) break;
-        tc::fence_after_sync();
-        auto issue_s = [&](int j) -> bool {             // S of job j into the buffer of its CTA-wide parity
-          const int ks = kjob % kKStages;
-          if (!tc::bounded_wait(&bars.k_full[ks], (kjob / kKStages) & 1, abort_flag)) return false;
+        const uint32_t q_ = lQ + qs * kStage;
+        for (int j = 0; j < jobs; ++j, ++n) {
+          // the buffer's previous job (three back): its group has read S and, in pass 2, P.V has read P
+          if (n >= kBufs && !(ok = tc::bounded_wait(&bars.buf_free[buf], bph ^ 1, abort_flag))) break;
+          if (!(ok = tc::bounded_wait(&bars.k_full[ks], kph, abort_flag))) break;
           tc::fence_after_sync();
-          const int buf = (int) ((J + j) & 1);
-          const uint32_t q_ = lQ + qs * kStage, k_ = lK + ks * kStage, d = tmem + buf * kChunk;
+          const uint32_t k_ = lK + ks * kStage, d = tmem + buf * kChunk;
           tc::umma_ss_lh<0>(d, q_, hi, k_, hi, id_s);
 #pragma unroll
           for (int s4 = 1; s4 < 4; ++s4) tc::umma_ss_lh<1>(d, q_ + 2 * s4, hi, k_ + 2 * s4, hi, id_s);
           tc::umma_commit(&bars.s_ready[buf]);
           tc::umma_commit(&bars.k_empty[ks]);
-          ++kjob;
-          return true;
-        };
-        auto issue_pv = [&](int j) -> bool {            // O (+)= P(job j, TMEM) . V chunk
-          const int vs = vjob % kVStages, c = j - first_p2, buf = (int) ((J + j) & 1);
-          if (!tc::bounded_wait(&bars.v_full[vs], (vjob / kVStages) & 1, abort_flag)) return false;
-          if (c == 0 && i > 0 && !tc::bounded_wait(&bars.o_free, (i - 1) & 1, abort_flag)) return false;      // previous tile's O has been read
-          tc::fence_after_sync();
-          const uint64_t vdesc = ((uint64_t) hi << 32) | (uint64_t) (lV + vs * kStage);
-#pragma unroll
-          for (int s8 = 0; s8 < 8; ++s8)       // P: 16 keys = 8 packed columns per k-step; V: 16 key rows = 2048 bytes
-            tc::umma_ts(tmem + kColO, tmem + buf * kChunk + s8 * 8, vdesc + 128 * s8, id_o, (c > 0 || s8 > 0) ? 1u : 0u);
-          tc::umma_commit(&bars.v_empty[vs]);
-          ++vjob;
-          return true;
-        };
-        for (int j = 0; ok && j < jobs; ++j) {
-          if (j >= 2) {
-            // the buffer was used by job j - 2: wait until its group is done with it; a pass-2 job then feeds P.V,
-            // which precedes the new S in issue order
-            const int64_t Jp = J + j - 2;
-            if (!(ok = tc::bounded_wait(&bars.wg_done[Jp & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
-            tc::fence_after_sync();
-            if (j - 2 >= first_p2 && !(ok = issue_pv(j - 2))) break;
-          } else if (J > 0) {
-            // first two jobs of a tile: the buffers' last users were the last two (pass-2) jobs of the previous tile,
-            // whose P.V was issued at the end of that tile
-          }
-          ok = issue_s(j);
+          if (++ks == kKStages) { ks = 0; kph ^= 1; }
+          if (++buf == kBufs) { buf = 0; bph ^= 1; }
         }
         if (!ok) break;
-        for (int j = jobs - 2; ok && j < jobs; ++j) {   // the last two jobs' P.V
-          const int64_t Jp = J + j;
-          if (!(ok = tc::bounded_wait(&bars.wg_done[Jp & 1], (uint32_t) ((Jp >> 1) & 1), abort_flag))) break;
-          tc::fence_after_sync();
-          ok = issue_pv(j);
+        tc::umma_commit(&bars.q_empty[qs]);
+      }
+    }
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- MMA issuer 2: O (+)= P(job, TMEM) . V chunk
+    if (lane == 0) {
+      const uint32_t id_o = tc::instr_desc(kRows, 64, 0, 1);
+      const uint32_t hi = (uint32_t) (tc::smem_desc(0, 0, 1024) >> 32);
+      constexpr uint32_t kStage = (uint32_t) (kTile * 2) >> 4;
+      const uint32_t lV = ((tc::smem_u32(sV) >> 4) & 0x3FFFu) | ((1024u >> 4) << 16);
+      int vs = 0, buf = 0;
+      uint32_t vph = 0, bph = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < n_my; ++i) {
+        for (int j = 0; j < jobs; ++j) {
+          if (!(ok = tc::bounded_wait(&bars.wg_done[buf], bph, abort_flag))) break;
+          if (j >= first_p2) {
+            const int c = j - first_p2;
+            if (!(ok = tc::bounded_wait(&bars.v_full[vs], vph, abort_flag))) break;
+            if (c == 0 && i > 0 && !(ok = tc::bounded_wait(&bars.o_free, (i - 1) & 1, abort_flag))) break;      // previous tile's O has been read
+            tc::fence_after_sync();
+            const uint64_t vdesc = ((uint64_t) hi << 32) | (uint64_t) (lV + vs * kStage);
+#pragma unroll
+            for (int s8 = 0; s8 < 8; ++s8)       // P: 16 keys = 8 packed columns per k-step; V: 16 key rows = 2048 bytes
+              tc::umma_ts(tmem + kColO, tmem + buf * kChunk + s8 * 8, vdesc + 128 * s8, id_o, (c > 0 || s8 > 0) ? 1u : 0u);
+            tc::umma_commit(&bars.v_empty[vs]);
+            if (++vs == kVStages) { vs = 0; vph ^= 1; }
+          }
+          tc::umma_commit(&bars.buf_free[buf]);
+          if (++buf == kBufs) { buf = 0; bph ^= 1; }
         }
         if (!ok) break;
         tc::umma_commit(&bars.o_ready);
-        tc::umma_commit(&bars.q_empty[qs]);
-        J += jobs;
       }
     }
   } else {
@@ -226,9 +228,10 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
     const int wg = warp >> 2, qd = warp & 3, r = qd * 32 + lane;
     const float sl2 = a.scale * kLog2eF;
     const float lw1 = log2f(a.w1), lw2 = log2f(a.w2);
-    const uint32_t t_s = tmem + wg * kChunk + ((uint32_t) (qd * 32) << 16);
-    const uint32_t t_o = tmem + kColO + wg * 32 + ((uint32_t) (qd * 32) << 16);
-    int64_t Jw = 0;                        // jobs this group has handled (its buffer's phase counter)
+    const uint32_t t_lane = tmem + ((uint32_t) (qd * 32) << 16);
+    const uint32_t t_o = t_lane + kColO + wg * 32;
+    int buf = wg;                          // S buffer of this group's next job (it takes every other job of the CTA) and
+    uint32_t bph = 0;                      // the phase parity of that buffer's barriers
     uint32_t n_x = 0;                      // exchanges so far
     float va[32];
     // Both groups publish a per-row value and read the other group's.  The buffer alternates with the exchange count:
@@ -263,9 +266,10 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
           if (!(ok = exchange(mx, other))) break;
           mx = fmaxf(mx, other);
         }
-        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.s_ready[wg], (uint32_t) (Jw & 1), abort_flag));
+        ok = __all_sync(0xffffffffu, tc::bounded_wait(&bars.s_ready[buf], bph, abort_flag));
         tc::fence_after_sync();
         if (!ok) break;
+        const uint32_t t_s = t_lane + buf * kChunk;
         if (pass == 0) {
           float m = -INFINITY;
 #pragma unroll
@@ -295,8 +299,9 @@ attn_fwd_pooled_loop_tc_kernel(AttnP<bf16> a, const __grid_constant__ LoopMaps m
         }
         tc::fence_before_sync();
         __syncwarp();
-        if (lane == 0) tma::mbar_arrive(&bars.wg_done[wg]);
-        ++Jw;
+        if (lane == 0) tma::mbar_arrive(&bars.wg_done[buf]);
+        buf += 2;
+        if (buf >= kBufs) { buf -= kBufs; bph ^= 1; }
       }
       float lse_out = __int_as_float(0x7fc00000);               // NaN unless everything completed
       if (ok) {
