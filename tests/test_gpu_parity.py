@@ -806,6 +806,30 @@ def test_batch_of_288_slices_matches_its_own_slices():
         assert rel_l2(K.grad[sl], ks.grad) < 2e-3 and rel_l2(V.grad[sl], vs.grad) < 2e-3
 
 
+def test_llsa_l1_288_slices_whole_and_partial_key_units():
+    """llsa_l1, 288 (b,h) slices of 4096 tokens: the key-major pooled dK/dV kernel cuts its flat (head, chunk, job) list
+    into one piece per SM, and with 576 (head, chunk) pairs a piece holds whole units (plain stores) between two partial
+    ones (reductions); with 2 batch elements every piece is partial.  Slices are independent, so both launches must
+    agree: o and dq bit for bit, dk and dv up to the order of their fp32 sums."""
+    L = _ops()
+    B, H, N = 48, 6, 4096
+    q, k, v, do = [t.to(DEV) for t in synth.correlated_qkv(12, 2, H, N, 64, dtype=torch.bfloat16)]
+    sc = torch.linspace(0.5, 1.5, B // 2, device=DEV).repeat_interleave(2).view(B, 1, 1, 1).to(torch.bfloat16)
+    Q = (q.repeat(B // 2, 1, 1, 1) * sc).contiguous().requires_grad_(True)
+    K = (k.repeat(B // 2, 1, 1, 1) * sc).contiguous().requires_grad_(True)
+    V = v.repeat(B // 2, 1, 1, 1).contiguous().requires_grad_(True)
+    DO = do.repeat(B // 2, 1, 1, 1).contiguous()
+    o = L.llsa_l1(Q, K, V, 8, 16)
+    o.backward(DO)
+    assert torch.isfinite(K.grad.float()).all() and torch.isfinite(V.grad.float()).all() and torch.isfinite(Q.grad.float()).all()
+    for sl in (slice(0, 2), slice(B // 2, B // 2 + 2), slice(B - 2, B)):
+        qs, ks, vs = [t[sl].detach().clone().requires_grad_(True) for t in (Q, K, V)]
+        os_ = L.llsa_l1(qs, ks, vs, 8, 16)
+        os_.backward(DO[sl])
+        assert torch.equal(o[sl], os_) and torch.equal(Q.grad[sl], qs.grad)
+        assert rel_l2(K.grad[sl], ks.grad) < 2e-3 and rel_l2(V.grad[sl], vs.grad) < 2e-3
+
+
 def test_cfg3_full_size_properties():
     L = _ops()
     q, k, v, do, _ = synth.make_config_inputs("cfg3")
