@@ -1,0 +1,321 @@
+"""Discrete-event model of the mbarrier protocol of the key-loop tcgen05 kernels
+(llsa_b200/csrc/attn_pooled_dkv_loop_tc.cu, attn_pooled_bwd_loop_tc.cu).
+
+Test infrastructure: nothing in the package imports it.  Every role of a CTA
+(TMA producer, the threads that issue MMAs, the eight softmax warps) is a Python
+generator that waits on barriers, spends random time and arrives, exactly in the
+order the kernel's role does.  The model keeps the hardware's semantics where
+they matter for correctness:
+
+* a barrier has an arrival count and a phase; a wait names a PARITY and passes
+  when the barrier's current (incomplete) phase has the other parity.  A wait
+  for "completion number u" therefore also passes when completion u - 1 has
+  not happened yet -- the case a protocol must exclude by construction;
+* `tcgen05.commit` arrives when the MMAs the committing thread issued before
+  it have completed; MMAs of all threads share one in-order pipe;
+* a TMA load arrives on its barrier after a random latency.
+
+On top of that the model tracks who owns each tensor-memory buffer and each
+operand ring stage and asserts at every read and overwrite, so that a protocol
+error shows as a failed assertion or as a deadlock (roles left waiting with no
+event pending), not as a wrong number.
+"""
+import heapq
+import random
+
+
+class Barrier:
+    def __init__(self, name, count):
+        self.name, self.count, self.pending, self.phase = name, count, count, 0
+
+    def parity(self):                     # parity of the current, incomplete phase
+        return self.phase & 1
+
+    def arrive(self, sim):
+        self.pending -= 1
+        assert self.pending >= 0, self.name
+        if self.pending == 0:
+            self.phase += 1
+            self.pending = self.count
+            sim.wake(self)
+
+
+class Sim:
+    def __init__(self, seed):
+        self.t, self.queue, self.serial = 0, [], 0
+        self.rng = random.Random(seed)
+        self.waiting = []                 # (role, barrier, parity)
+        self.roles = {}
+        self.pipe_free = 0                # the tensor pipe executes in issue order
+        self.last_mma_done = {}           # per issuing thread
+
+    def at(self, t, fn):
+        self.serial += 1
+        heapq.heappush(self.queue, (t, self.serial, fn))
+
+    def spawn(self, name, gen):
+        self.roles[name] = gen
+        self.at(0, lambda: self.step(name))
+
+    def step(self, name):
+        gen = self.roles.get(name)
+        if gen is None:
+            return
+        try:
+            op = next(gen)
+        except StopIteration:
+            del self.roles[name]
+            return
+        if op[0] == "delay":
+            self.at(self.t + op[1], lambda: self.step(name))
+        else:                             # ("wait", barrier, parity)
+            _, bar, par = op
+            if bar.parity() != par:
+                self.at(self.t + self.rng.randint(20, 120), lambda: self.step(name))
+            else:
+                self.waiting.append((name, bar, par))
+
+    def wake(self, bar):
+        still = []
+        for name, b, par in self.waiting:
+            if b is bar and b.parity() != par:
+                self.at(self.t + self.rng.randint(20, 150), (lambda nm: (lambda: self.step(nm)))(name))
+            else:
+                still.append((name, b, par))
+        self.waiting = still
+
+    def run(self):
+        while self.queue:
+            self.t, _, fn = heapq.heappop(self.queue)
+            fn()
+        return "deadlock" if self.roles else "ok"
+
+    def mma(self, thread, cycles):        # -> (start, done) on the shared pipe
+        start = max(self.pipe_free, self.t)
+        self.pipe_free = start + cycles
+        self.last_mma_done[thread] = self.pipe_free
+        return start, self.pipe_free
+
+    def commit(self, thread, bar):
+        done = max(self.last_mma_done.get(thread, 0), self.t) + self.rng.randint(20, 100)
+        self.at(done, lambda: bar.arrive(self))
+
+    def tma(self, bar, fn=None):
+        def land():
+            if fn:
+                fn()
+            bar.arrive(self)
+        self.at(self.t + self.rng.randint(500, 1500), land)
+
+    def r(self, a, b):
+        return self.rng.randint(a, b)
+
+
+def key_major_kernel(seed, units, score_threads=1, score_barriers=3, stages=8, buffers=3):
+    """attn_dkv_pooled_loop_tc_kernel.  `units`: job counts of the (head, chunk) units of one CTA's piece.
+    score_threads: threads that issue S^T / dP^T (1 = the kernel; 2 = even and odd jobs on two threads).
+    score_barriers: sdp_ready / buf_free barriers (3 = one per buffer, the kernel; 6 = one per job number mod 6)."""
+    sim = Sim(seed)
+    nb = score_barriers
+    kv_full, kv_empty = Barrier("kv_full", 1), Barrier("kv_empty", score_threads)
+    q_full = [Barrier("q_full%d" % i, 1) for i in range(stages)]
+    q_empty = [Barrier("q_empty%d" % i, 1) for i in range(stages)]
+    sdp = [Barrier("sdp_ready%d" % i, 1) for i in range(nb)]
+    pds = [Barrier("pds_ready%d" % i, 4) for i in range(buffers)]
+    free = [Barrier("buf_free%d" % i, 1) for i in range(nb)]
+    acc_ready, acc_free = Barrier("acc_ready", 1), Barrier("acc_free", 8)
+    owner = [None] * buffers              # None: free; ("s", job): scores; ("p", job): probabilities
+
+    def producer():
+        job = 0
+        for i, n in enumerate(units):
+            yield ("wait", kv_empty, (i & 1) ^ 1)
+            sim.tma(kv_full)
+            for _ in range(n):
+                st = job % stages
+                yield ("wait", q_empty[st], ((job // stages) & 1) ^ 1)
+                yield ("delay", sim.r(20, 80))
+                sim.tma(q_full[st])
+                job += 1
+
+    def score_issuer(mine):
+        job, first = mine, 0
+        for i, n in enumerate(units):
+            yield ("wait", kv_full, i & 1)
+            while job < first + n:
+                st, buf = job % stages, job % buffers
+                if job >= buffers:
+                    prev = job - buffers
+                    yield ("wait", free[prev % nb], (prev // nb) & 1)
+                yield ("wait", q_full[st], (job // stages) & 1)
+                if sim.rng.random() < 0.15:
+                    yield ("delay", sim.r(500, 4000))          # one thread falls behind the other
+                assert owner[buf] is None, ("scores written over a live buffer", buf, owner[buf], job)
+                start, done = sim.mma(("score", mine), 384)
+                sim.at(done, (lambda b=buf, j=job: owner.__setitem__(b, ("s", j))))
+                yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+                sim.commit(("score", mine), sdp[job % nb])
+                yield ("delay", sim.r(30, 80))
+                job += score_threads
+            first += n
+            sim.commit(("score", mine), kv_empty)
+            yield ("delay", sim.r(30, 80))
+
+    def out_issuer():
+        job = 0
+        for i, n in enumerate(units):
+            for j in range(n):
+                st, buf = job % stages, job % buffers
+                yield ("wait", pds[buf], (job // buffers) & 1)
+                if j == 0 and i > 0:
+                    yield ("wait", acc_free, (i - 1) & 1)
+                assert owner[buf] == ("p", job), ("dV / dK read", buf, owner[buf], job)
+                start, done = sim.mma("out", 384)
+                sim.at(done, (lambda b=buf: owner.__setitem__(b, None)))
+                yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+                sim.commit("out", q_empty[st])
+                sim.commit("out", free[job % nb])
+                yield ("delay", sim.r(60, 160))
+                job += 1
+            sim.commit("out", acc_ready)
+            yield ("delay", sim.r(30, 80))
+
+    def softmax(group, warp):
+        job, first = group, 0
+        for i, n in enumerate(units):
+            while job < first + n:
+                buf = job % buffers
+                yield ("wait", sdp[job % nb], (job // nb) & 1)
+                assert owner[buf] is not None and owner[buf][1] == job, ("softmax read", buf, owner[buf], job)
+                yield ("delay", sim.r(500, 1200))
+                if warp == 0:
+                    owner[buf] = ("p", job)
+                pds[buf].arrive(sim)
+                job += 2
+            first += n
+            yield ("wait", acc_ready, i & 1)
+            yield ("delay", sim.r(200, 600))
+            acc_free.arrive(sim)
+
+    sim.spawn("producer", producer())
+    for t in range(score_threads):
+        sim.spawn("score%d" % t, score_issuer(t))
+    sim.spawn("out", out_issuer())
+    for g in range(2):
+        for w in range(4):
+            sim.spawn("softmax%d%d" % (g, w), softmax(g, w))
+    return sim.run()
+
+
+def query_major_kernel(seed, tiles, jobs, score_threads=1, score_barriers=3, stages=8, buffers=3):
+    """attn_dq_pooled_loop_tc_kernel: `tiles` query tiles of `jobs` key chunks (even); Q / dO in two stages, K and V
+    chunks in rings, S / dP into three buffers, dQ accumulated per tile."""
+    sim = Sim(seed)
+    nb = score_barriers
+    q_full = [Barrier("q_full%d" % i, 1) for i in range(2)]
+    q_empty = [Barrier("q_empty%d" % i, score_threads) for i in range(2)]
+    k_full = [Barrier("k_full%d" % i, 1) for i in range(stages)]
+    k_empty = [Barrier("k_empty%d" % i, 1) for i in range(stages)]
+    v_full = [Barrier("v_full%d" % i, 1) for i in range(stages)]
+    v_empty = [Barrier("v_empty%d" % i, 1) for i in range(stages)]
+    sdp = [Barrier("sdp_ready%d" % i, 1) for i in range(nb)]
+    ds = [Barrier("ds_ready%d" % i, 4) for i in range(buffers)]
+    free = [Barrier("buf_free%d" % i, 1) for i in range(nb)]
+    dq_ready, dq_free = Barrier("dq_ready", 1), Barrier("dq_free", 8)
+    owner = [None] * buffers
+    held = [None] * stages                # chunk number a K ring stage holds
+
+    def producer():
+        job = 0
+        for i in range(tiles):
+            yield ("wait", q_empty[i & 1], ((i >> 1) & 1) ^ 1)
+            sim.tma(q_full[i & 1])
+            for _ in range(jobs):
+                st, par = job % stages, ((job // stages) & 1) ^ 1
+                yield ("wait", k_empty[st], par)
+                assert held[st] is None, ("keys loaded over a live stage", st, held[st], job)
+                sim.tma(k_full[st], (lambda s=st, j=job: held.__setitem__(s, j)))
+                yield ("wait", v_empty[st], par)
+                sim.tma(v_full[st])
+                job += 1
+
+    def score_issuer(mine):
+        job = mine
+        for i in range(tiles):
+            yield ("wait", q_full[i & 1], (i >> 1) & 1)
+            for _ in range(mine, jobs, score_threads):
+                st, par, buf = job % stages, (job // stages) & 1, job % buffers
+                if job >= buffers:
+                    prev = job - buffers
+                    yield ("wait", free[prev % nb], (prev // nb) & 1)
+                yield ("wait", k_full[st], par)
+                yield ("wait", v_full[st], par)
+                if sim.rng.random() < 0.15:
+                    yield ("delay", sim.r(500, 4000))
+                assert owner[buf] is None, ("scores written over a live buffer", buf, owner[buf], job)
+                assert held[st] == job, ("S read the wrong keys", st, held[st], job)
+                start, done = sim.mma(("score", mine), 384)
+                sim.at(done, (lambda b=buf, j=job: owner.__setitem__(b, ("s", j))))
+                yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+                sim.commit(("score", mine), sdp[job % nb])
+                sim.commit(("score", mine), v_empty[st])
+                yield ("delay", sim.r(30, 80))
+                job += score_threads
+            sim.commit(("score", mine), q_empty[i & 1])
+            yield ("delay", sim.r(30, 80))
+
+    def dq_issuer():
+        job = 0
+        for i in range(tiles):
+            for j in range(jobs):
+                st, buf = job % stages, job % buffers
+                yield ("wait", ds[buf], (job // buffers) & 1)
+                if j == 0 and i > 0:
+                    yield ("wait", dq_free, (i - 1) & 1)
+                assert owner[buf] == ("p", job), ("dQ read", buf, owner[buf], job)
+                assert held[st] == job, ("dQ read the wrong keys", st, held[st], job)
+                start, done = sim.mma("dq", 192)
+
+                def release(b=buf, s=st):
+                    owner[b] = None
+                    held[s] = None
+                sim.at(done, release)
+                yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+                sim.commit("dq", k_empty[st])
+                sim.commit("dq", free[job % nb])
+                yield ("delay", sim.r(60, 160))
+                job += 1
+            sim.commit("dq", dq_ready)
+            yield ("delay", sim.r(30, 80))
+
+    def softmax(group, warp):
+        job = group
+        for i in range(tiles):
+            for _ in range(group, jobs, 2):
+                buf = job % buffers
+                yield ("wait", sdp[job % nb], (job // nb) & 1)
+                assert owner[buf] is not None and owner[buf][1] == job, ("softmax read", buf, owner[buf], job)
+                yield ("delay", sim.r(400, 1000))
+                if warp == 0:
+                    owner[buf] = ("p", job)
+                ds[buf].arrive(sim)
+                job += 2
+            yield ("wait", dq_ready, i & 1)
+            yield ("delay", sim.r(200, 600))
+            dq_free.arrive(sim)
+
+    sim.spawn("producer", producer())
+    for t in range(score_threads):
+        sim.spawn("score%d" % t, score_issuer(t))
+    sim.spawn("dq", dq_issuer())
+    for g in range(2):
+        for w in range(4):
+            sim.spawn("softmax%d%d" % (g, w), softmax(g, w))
+    return sim.run()
+
+
+def outcome(fn, *args, **kw):
+    try:
+        return fn(*args, **kw)
+    except AssertionError as e:
+        return "hazard: %s" % (e.args[0],)
