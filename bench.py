@@ -347,6 +347,15 @@ def main():
     ops.set_stage_hook(None)
     torch.cuda.synchronize()
     eager_ms_step = e0.elapsed_time(e1) / args.steps
+    # One more step with the device checks on (every operator then reads the kernels' status word back and raises if a
+    # bounded wait ran out or a block index was out of range): a kernel that gave up a wait ends early, and a step
+    # timed that way would be a wrong number that looks fast or slow, not an error.
+    ops.set_device_checks(True)
+    try:
+        eager_step()
+        torch.cuda.synchronize()
+    finally:
+        ops.set_device_checks(False)
     per = {}
     for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
         if name != "end":
@@ -413,7 +422,8 @@ def main():
                effective_tflops_frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (peak * world),
                kernel_ms={kname: round(tms, 4) for kname, tms in sorted(per.items())},
                memory_bound_stages=memory_bound, hbm_peak_gbs=peaks["hbm_gbs"],
-               roofline=roof, gpu_launches=len(KERNELS_PER_STEP) * args.steps, clocks=clocks)
+               roofline=roof, gpu_launches=len(KERNELS_PER_STEP) * args.steps, clocks=clocks,
+               device_checks="one eager step with the kernels' status word read back after every operator: clean")
 
     # ---- weak-scaling form as an extra key: every rank the whole workload (what data-parallel training does)
     if args.weak and world > 1 and not seq_parallel and world <= B * H:
