@@ -1,5 +1,5 @@
 """Discrete-event model of the mbarrier protocol of the key-loop tcgen05 kernels
-(llsa_b200/csrc/attn_pooled_dkv_loop_tc.cu, attn_pooled_bwd_loop_tc.cu).
+(llsa_b200/csrc/attn_pooled_loop_tc.cu, attn_pooled_bwd_loop_tc.cu, attn_pooled_dkv_loop_tc.cu).
 
 Test infrastructure: nothing in the package imports it.  Every role of a CTA
 (TMA producer, the threads that issue MMAs, the eight softmax warps) is a Python
@@ -308,6 +308,141 @@ def query_major_kernel(seed, tiles, jobs, score_threads=1, score_barriers=3, sta
     for t in range(score_threads):
         sim.spawn("score%d" % t, score_issuer(t))
     sim.spawn("dq", dq_issuer())
+    for g in range(2):
+        for w in range(4):
+            sim.spawn("softmax%d%d" % (g, w), softmax(g, w))
+    return sim.run()
+
+
+def forward_kernel(seed, tiles, chunks, passes, k_stages=4, v_stages=4, buffers=3):
+    """attn_fwd_pooled_loop_tc_kernel: `tiles` query tiles of `chunks` key chunks; one pass (jobs = chunks, every job
+    feeds P.V) or two (jobs = 2 * chunks: row maxima first, then the exponentials; the two groups exchange their maxima
+    before their first second-pass job).  One thread issues S, one issues P.V and hands every job's buffer back; the two
+    softmax groups take the jobs of one parity of the CTA-wide job number each (with an odd job count the parity of a
+    tile's first job alternates) and exchange their row sums at the end of a tile."""
+    sim = Sim(seed)
+    jobs, first_p2 = passes * chunks, (passes - 1) * chunks
+    q_full = [Barrier("q_full%d" % i, 1) for i in range(2)]
+    q_empty = [Barrier("q_empty%d" % i, 1) for i in range(2)]
+    k_full = [Barrier("k_full%d" % i, 1) for i in range(k_stages)]
+    k_empty = [Barrier("k_empty%d" % i, 1) for i in range(k_stages)]
+    v_full = [Barrier("v_full%d" % i, 1) for i in range(v_stages)]
+    v_empty = [Barrier("v_empty%d" % i, 1) for i in range(v_stages)]
+    s_ready = [Barrier("s_ready%d" % i, 1) for i in range(buffers)]
+    wg_done = [Barrier("wg_done%d" % i, 4) for i in range(buffers)]
+    free = [Barrier("buf_free%d" % i, 1) for i in range(buffers)]
+    o_ready, o_free, xchg = Barrier("o_ready", 1), Barrier("o_free", 8), Barrier("xchg", 8)
+    owner = [None] * buffers
+    v_held = [None] * v_stages
+    o_busy = [False]                      # the O accumulator holds a finished tile that has not been read yet
+
+    def producer():
+        kjob = vjob = 0
+        for i in range(tiles):
+            yield ("wait", q_empty[i & 1], ((i >> 1) & 1) ^ 1)
+            sim.tma(q_full[i & 1])
+            for j in range(jobs):
+                ks = kjob % k_stages
+                yield ("wait", k_empty[ks], ((kjob // k_stages) & 1) ^ 1)
+                sim.tma(k_full[ks])
+                kjob += 1
+                if j >= first_p2:
+                    vs = vjob % v_stages
+                    yield ("wait", v_empty[vs], ((vjob // v_stages) & 1) ^ 1)
+                    assert v_held[vs] is None, ("values loaded over a live stage", vs, v_held[vs], vjob)
+                    sim.tma(v_full[vs], (lambda s=vs, j=vjob: v_held.__setitem__(s, j)))
+                    vjob += 1
+
+    def s_issuer():
+        n = 0
+        for i in range(tiles):
+            yield ("wait", q_full[i & 1], (i >> 1) & 1)
+            for _ in range(jobs):
+                buf, ks = n % buffers, n % k_stages
+                if n >= buffers:
+                    yield ("wait", free[buf], ((n // buffers) & 1) ^ 1)
+                yield ("wait", k_full[ks], (n // k_stages) & 1)
+                assert owner[buf] is None, ("scores written over a live buffer", buf, owner[buf], n)
+                start, done = sim.mma("s", 256)
+                sim.at(done, (lambda b=buf, j=n: owner.__setitem__(b, ("s", j))))
+                yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+                sim.commit("s", s_ready[buf])
+                sim.commit("s", k_empty[ks])
+                yield ("delay", sim.r(30, 80))
+                n += 1
+            sim.commit("s", q_empty[i & 1])
+            yield ("delay", sim.r(30, 80))
+
+    def pv_issuer():
+        n = vjob = 0
+        for i in range(tiles):
+            for j in range(jobs):
+                buf = n % buffers
+                yield ("wait", wg_done[buf], (n // buffers) & 1)
+                if j >= first_p2:
+                    vs = vjob % v_stages
+                    yield ("wait", v_full[vs], (vjob // v_stages) & 1)
+                    if j == first_p2 and i > 0:
+                        yield ("wait", o_free, (i - 1) & 1)
+                    if j == first_p2:
+                        assert not o_busy[0], ("O overwritten before it was read", i)
+                    assert owner[buf] == ("p", n), ("P.V read", buf, owner[buf], n)
+                    assert v_held[vs] == vjob, ("P.V read the wrong values", vs, v_held[vs], vjob)
+                    start, done = sim.mma("pv", 384)
+
+                    def release(b=buf, s=vs):
+                        owner[b] = None
+                        v_held[s] = None
+                    sim.at(done, release)
+                    yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+                    sim.commit("pv", v_empty[vs])
+                    vjob += 1
+                else:
+                    assert owner[buf] == ("m", n), ("first-pass buffer handed back early", buf, owner[buf], n)
+                    owner[buf] = None
+                sim.commit("pv", free[buf])
+                yield ("delay", sim.r(30, 80))
+                n += 1
+            last = max(sim.last_mma_done.get("pv", 0), sim.t)
+            sim.at(last, (lambda: o_busy.__setitem__(0, True)))
+            sim.commit("pv", o_ready)
+            yield ("delay", sim.r(30, 80))
+
+    def softmax(group, warp):
+        n_x = 0
+        state = {"n": group}              # this group's next job, numbered over the CTA
+
+        def exchange():
+            nonlocal n_x
+            xchg.arrive(sim)
+            yield ("wait", xchg, n_x & 1)
+            n_x += 1
+
+        for i in range(tiles):
+            j = (group - i * jobs) & 1
+            assert i * jobs + j == state["n"], ("job numbering", i, j, state["n"])
+            while j < jobs:
+                n, buf = state["n"], state["n"] % buffers
+                if passes == 2 and j >= first_p2 and j - 2 < first_p2:
+                    yield from exchange()                  # row maxima of the two groups
+                yield ("wait", s_ready[buf], (n // buffers) & 1)
+                assert owner[buf] is not None and owner[buf][1] == n, ("softmax read", buf, owner[buf], n)
+                yield ("delay", sim.r(400, 1400))
+                if warp == 0:
+                    owner[buf] = ("p" if j >= first_p2 else "m", n)
+                wg_done[buf].arrive(sim)
+                state["n"] += 2
+                j += 2
+            yield from exchange()                          # row sums
+            yield ("wait", o_ready, i & 1)
+            yield ("delay", sim.r(200, 600))
+            if group == 0 and warp == 0:
+                o_busy[0] = False
+            o_free.arrive(sim)
+
+    sim.spawn("producer", producer())
+    sim.spawn("s", s_issuer())
+    sim.spawn("pv", pv_issuer())
     for g in range(2):
         for w in range(4):
             sim.spawn("softmax%d%d" % (g, w), softmax(g, w))

@@ -6,7 +6,7 @@ import random
 
 import pytest
 
-from protocol_model import key_major_kernel, outcome, query_major_kernel
+from protocol_model import forward_kernel, key_major_kernel, outcome, query_major_kernel
 
 RUNS = 250
 
@@ -27,6 +27,15 @@ def test_query_major_kernel_protocol_has_no_hazard_or_deadlock():
     for seed in range(RUNS):
         rng = random.Random(seed)
         assert outcome(query_major_kernel, seed, rng.randint(1, 7), rng.choice([4, 6, 18])) == "ok", seed
+
+
+@pytest.mark.parametrize("passes", [1, 2])
+def test_forward_kernel_protocol_has_no_hazard_or_deadlock(passes):
+    """attn_fwd_pooled_loop_tc_kernel as built, in its one-pass form (odd and even chunk counts: with 9 chunks the groups
+    swap the parity of their first job from tile to tile) and in the two-pass form that redoes marked rows."""
+    for seed in range(RUNS):
+        rng = random.Random(seed)
+        assert outcome(forward_kernel, seed, rng.randint(1, 6), rng.choice([2, 3, 8, 9]), passes) == "ok", seed
 
 
 def test_model_catches_the_parity_hazard_of_two_score_threads():
