@@ -1,5 +1,6 @@
 """Discrete-event model of the mbarrier protocol of the key-loop tcgen05 kernels
-(llsa_b200/csrc/attn_pooled_loop_tc.cu, attn_pooled_bwd_loop_tc.cu, attn_pooled_dkv_loop_tc.cu).
+(llsa_b200/csrc/attn_pooled_loop_tc.cu, attn_pooled_bwd_loop_tc.cu, attn_pooled_dkv_loop_tc.cu) and of the
+single-shot pooled backward with its two MMA-issuing threads (attn_pooled_bwd_tc.cu).
 
 Test infrastructure: nothing in the package imports it.  Every role of a CTA
 (TMA producer, the threads that issue MMAs, the eight softmax warps) is a Python
@@ -446,6 +447,187 @@ def forward_kernel(seed, tiles, chunks, passes, k_stages=4, v_stages=4, buffers=
     for g in range(2):
         for w in range(4):
             sim.spawn("softmax%d%d" % (g, w), softmax(g, w))
+    return sim.run()
+
+
+class Resource:
+    """A buffer with one content tag; reads must see the expected tag, and an overwrite must come after the last read
+    (an MMA reads until it completes) has ended."""
+    def __init__(self, name):
+        self.name, self.tag, self.busy_until = name, None, 0
+
+    def read(self, sim, tag, until=None):
+        assert self.tag == tag, ("%s read" % self.name, self.tag, tag)
+        self.busy_until = max(self.busy_until, sim.t if until is None else until)
+
+    def write(self, sim, tag, at=None):
+        assert sim.t >= self.busy_until, ("%s overwritten while it is read" % self.name, self.tag, tag, sim.t, self.busy_until)
+        if at is None:
+            self.tag = tag
+        else:
+            self.tag = ("in flight", tag)
+            sim.at(at, (lambda: setattr(self, "tag", tag)))
+
+
+def single_shot_backward_kernel(seed, t_begin, n_tiles, tiles_per_head, mma_done_count=2, softmax_waits_for_products=True):
+    """attn_bwd_pooled_tc_kernel: tiles [t_begin, t_begin + n_tiles) of one CTA; a parent is two tiles (even, odd), a head is
+    tiles_per_head tiles (even).  Two MMA-issuing threads: A = S, dP, dQ; B = the three transposed products.
+    The last two arguments break the protocol on purpose (tests of the model itself): mma_done counting only thread A's
+    commit, and softmax warps that overwrite P / dS without waiting for the previous tile's products."""
+    sim = Sim(seed)
+    full = [Barrier("full%d" % i, 1) for i in range(2)]
+    mma_done = [Barrier("mma_done%d" % i, mma_done_count) for i in range(2)]
+    v_free = [Barrier("v_free%d" % i, 1) for i in range(2)]
+    s_ready, dp_ready, out_ready = Barrier("s_ready", 1), Barrier("dp_ready", 1), Barrier("out_ready", 2)
+    s_consumed, pds_ready = Barrier("s_consumed", 12), Barrier("pds_ready", 12)
+    dq_free, acc_free = Barrier("dq_free", 4), Barrier("acc_free", 4)
+    stage = [Resource("Q/dO stage %d" % i) for i in range(2)]
+    k1 = [Resource("K1 buffer %d" % i) for i in range(2)]
+    v1, kv2 = Resource("V1"), Resource("K2/V2")
+    scores, pds, dq = Resource("S/dP columns"), Resource("P/dS tiles"), Resource("dQ columns")
+    acc1, acc2 = Resource("level-1 accumulators"), Resource("level-2 accumulators")
+    tile_of = lambda i: t_begin + i
+    parent_of = lambda i: tile_of(i) >> 1
+    head_of = lambda i: tile_of(i) // tiles_per_head
+
+    def producer():
+        for i in range(n_tiles):
+            s, tile = i & 1, tile_of(i)
+            new_parent = i == 0 or tile % 2 == 0
+            new_head = i == 0 or tile % tiles_per_head == 0
+            if i >= 2:
+                yield ("wait", mma_done[s], ((i - 2) >> 1) & 1)
+            if i >= 1 and new_head:
+                yield ("wait", mma_done[(i - 1) & 1], ((i - 1) >> 1) & 1)
+            land = sim.t + sim.r(500, 1500)
+            stage[s].write(sim, tile, at=land)
+            if new_head:
+                kv2.write(sim, head_of(i), at=land)
+            if new_parent:
+                k1[parent_of(i) & 1].write(sim, parent_of(i), at=land)
+                if i >= 1:
+                    yield ("wait", v_free[(i - 1) & 1], ((i - 1) >> 1) & 1)
+                land = max(land, sim.t + sim.r(500, 1500))
+                v1.write(sim, parent_of(i), at=land)
+            sim.at(land, (lambda b=full[s]: b.arrive(sim)))
+            yield ("delay", sim.r(20, 80))
+
+    def issuer_a():
+        def issue_s(i):
+            s = i & 1
+            yield ("wait", full[s], (i >> 1) & 1)
+            start, done = sim.mma("A", 384)
+            stage[s].read(sim, tile_of(i), done)
+            k1[parent_of(i) & 1].read(sim, parent_of(i), done)
+            kv2.read(sim, head_of(i), done)
+            scores.write(sim, ("S", i), at=done)
+            yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+            sim.commit("A", s_ready)
+
+        if n_tiles > 0:
+            yield from issue_s(0)
+        for i in range(n_tiles):
+            s, tile = i & 1, tile_of(i)
+            yield ("wait", s_consumed, i & 1)
+            start, done = sim.mma("A", 384)
+            stage[s].read(sim, tile, done)
+            v1.read(sim, parent_of(i), done)
+            kv2.read(sim, head_of(i), done)
+            scores.write(sim, ("dP", i), at=done)
+            yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+            sim.commit("A", dp_ready)
+            sim.commit("A", v_free[s])
+            yield ("wait", pds_ready, i & 1)
+            next_early = i + 1 < n_tiles and (tile + 1) % tiles_per_head != 0
+            if next_early:
+                yield from issue_s(i + 1)
+            if i > 0:
+                yield ("wait", dq_free, (i - 1) & 1)
+            start, done = sim.mma("A", 576)
+            pds.read(sim, i, done)
+            k1[parent_of(i) & 1].read(sim, parent_of(i), done)
+            kv2.read(sim, head_of(i), done)
+            dq.write(sim, i, at=done)
+            yield ("delay", max(0, start - sim.t) + sim.r(50, 200))
+            sim.commit("A", out_ready)
+            sim.commit("A", mma_done[s])
+            if not next_early and i + 1 < n_tiles:
+                yield from issue_s(i + 1)
+
+    def issuer_b():
+        parents_done = 0
+        for i in range(n_tiles):
+            s, tile = i & 1, tile_of(i)
+            yield ("wait", pds_ready, i & 1)
+            fresh1 = not (i > 0 and tile % 2 == 1)
+            fresh2 = not (i > 0 and tile % tiles_per_head != 0)
+            if fresh1 and parents_done > 0:
+                yield ("wait", acc_free, (parents_done - 1) & 1)
+            start, done = sim.mma("B", 1280)
+            pds.read(sim, i, done)
+            stage[s].read(sim, tile, done)
+            if fresh1:
+                acc1.write(sim, parent_of(i))
+            else:
+                acc1.read(sim, parent_of(i))
+            if fresh2:
+                acc2.write(sim, head_of(i))
+            else:
+                acc2.read(sim, head_of(i))
+            acc1.busy_until = max(acc1.busy_until, 0)
+            yield ("delay", max(0, start - sim.t) + sim.r(50, 300))
+            sim.commit("B", out_ready)
+            if mma_done_count == 2:
+                sim.commit("B", mma_done[s])
+            if tile % 2 == 1 or i == n_tiles - 1:
+                parents_done += 1
+
+    def drain(warp):
+        for i in range(n_tiles):
+            tile = tile_of(i)
+            parent_end = tile % 2 == 1 or i == n_tiles - 1
+            yield ("wait", out_ready, i & 1)
+            dq.read(sim, i)
+            yield ("delay", sim.r(150, 400))
+            dq.busy_until = max(dq.busy_until, sim.t)
+            dq_free.arrive(sim)
+            if not parent_end:
+                continue
+            acc1.read(sim, parent_of(i))
+            if i == n_tiles - 1 or (tile + 1) % tiles_per_head == 0:
+                acc2.read(sim, head_of(i))
+            yield ("delay", sim.r(300, 900))
+            acc1.busy_until = max(acc1.busy_until, sim.t)
+            acc2.busy_until = max(acc2.busy_until, sim.t)
+            acc_free.arrive(sim)
+
+    def softmax(warp):
+        for i in range(n_tiles):
+            yield ("wait", s_ready, i & 1)
+            scores.read(sim, ("S", i))
+            yield ("delay", sim.r(200, 500))
+            scores.busy_until = max(scores.busy_until, sim.t)
+            s_consumed.arrive(sim)
+            if i > 0 and softmax_waits_for_products:
+                yield ("wait", out_ready, (i - 1) & 1)
+            if warp == 0:
+                pds.write(sim, ("being written", i))
+            yield ("delay", sim.r(100, 300))
+            yield ("wait", dp_ready, i & 1)
+            scores.read(sim, ("dP", i))
+            yield ("delay", sim.r(300, 700))
+            scores.busy_until = max(scores.busy_until, sim.t)
+            if warp == 0:
+                pds.tag = i
+            pds_ready.arrive(sim)
+
+    sim.spawn("producer", producer())
+    sim.spawn("A", issuer_a())
+    sim.spawn("B", issuer_b())
+    for w in range(4):
+        sim.spawn("drain%d" % w, drain(w))
+    for w in range(12):
+        sim.spawn("softmax%d" % w, softmax(w))
     return sim.run()
 
 

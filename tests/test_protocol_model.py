@@ -6,7 +6,7 @@ import random
 
 import pytest
 
-from protocol_model import forward_kernel, key_major_kernel, outcome, query_major_kernel
+from protocol_model import forward_kernel, key_major_kernel, outcome, query_major_kernel, single_shot_backward_kernel
 
 RUNS = 250
 
@@ -60,3 +60,25 @@ def test_barriers_per_job_number_mod_6_make_two_score_threads_safe(kernel):
             rng = random.Random(seed)
             r = outcome(query_major_kernel, seed, rng.randint(1, 7), rng.choice([4, 6, 18]), score_threads=2, score_barriers=6)
         assert r == "ok", seed
+
+
+def _single_shot_case(seed):
+    rng = random.Random(seed)
+    return rng.randint(0, 9), rng.randint(1, 14), rng.choice([2, 4, 8, 128])       # first tile, tiles of the CTA, tiles per head
+
+
+def test_single_shot_backward_protocol_has_no_hazard_or_deadlock():
+    """attn_bwd_pooled_tc_kernel as built: TMA producer, two MMA-issuing threads (S / dP / dQ; the transposed products) that
+    both commit out_ready and mma_done, twelve softmax warps, four drain warps; CTA ranges that start on odd tiles, cross
+    parents and heads, and end in the middle of a parent."""
+    for seed in range(RUNS):
+        assert outcome(single_shot_backward_kernel, seed, *_single_shot_case(seed)) == "ok", seed
+
+
+def test_model_catches_a_stage_freed_by_one_issuer_only_and_an_unguarded_overwrite():
+    """Two mutations of that protocol the model must catch: mma_done counting only one thread's commit (the producer then
+    reloads Q / dO under the other thread's products) and softmax warps that do not wait for the previous tile's
+    products before they overwrite P / dS."""
+    one = sum(outcome(single_shot_backward_kernel, s, *_single_shot_case(s), mma_done_count=1) != "ok" for s in range(80))
+    two = sum(outcome(single_shot_backward_kernel, s, *_single_shot_case(s), softmax_waits_for_products=False) != "ok" for s in range(80))
+    assert one > 0 and two > 0
